@@ -1,0 +1,107 @@
+"""ctypes binding of libglorcq_b200.so (the C ABI declared in include/glorcq_b200.h).
+
+There is no fallback: if the library is missing, or a call returns a non-zero status, a
+RuntimeError is raised -- the same exception type the reference's native modules raise through
+TORCH_CHECK (inference/kernels/turbo_matmul.cu:250-283).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libglorcq_b200.so")
+
+FMT_Q2, FMT_Q4, FMT_T2, FMT_F16 = 0, 1, 2, 3
+EPI_LINEAR, EPI_SWIGLU = 0, 1
+
+vp = C.c_void_p
+
+
+class Weight(C.Structure):
+    """glq_weight_t"""
+    _fields_ = [("codes", vp), ("sz", vp), ("norms", vp), ("centroids", vp), ("sv", vp), ("bias", vp),
+                ("N", C.c_int32), ("K", C.c_int32), ("rank", C.c_int32), ("reserved", C.c_int32)]
+
+
+class MMArgs(C.Structure):
+    """glq_mm_args_t"""
+    _fields_ = [("fmt", C.c_int32), ("group_size", C.c_int32), ("epilogue", C.c_int32), ("n_problems", C.c_int32),
+                ("max_rows", C.c_int32), ("rows_stride", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+                ("rank", C.c_int32), ("reserved", C.c_int32),
+                ("w0", Weight), ("w1", Weight), ("w0_table", vp), ("w1_table", vp),
+                ("slot_index", vp), ("n_slots", vp), ("slot_count", vp), ("slot_offset", vp), ("entry_row", vp),
+                ("entry_scale", vp),
+                ("x", vp), ("ldx", C.c_int64), ("a0", vp), ("a1", vp), ("lda", C.c_int64),
+                ("y", vp), ("ldy", C.c_int64), ("workspace", vp), ("workspace_bytes", C.c_size_t)]
+
+
+class MoeDesc(C.Structure):
+    """glq_moe_desc_t"""
+    _fields_ = [("H", C.c_int32), ("I", C.c_int32), ("E", C.c_int32), ("top_k", C.c_int32),
+                ("I_shared", C.c_int32), ("rank", C.c_int32), ("fmt", C.c_int32), ("group_size", C.c_int32),
+                ("norm_topk_prob", C.c_int32), ("max_tokens", C.c_int32), ("ordered_by_expert_above", C.c_int32),
+                ("reserved", C.c_int32),
+                ("router", vp), ("gate_w", vp), ("up_w", vp), ("down_w", vp),
+                ("gate_ut", vp), ("up_ut", vp), ("down_ut", vp),
+                ("shared_gate_w", Weight), ("shared_up_w", Weight), ("shared_down_w", Weight),
+                ("shared_gate_ut", vp), ("shared_up_ut", vp), ("shared_down_ut", vp)]
+
+
+_SIGS = {
+    "glq_version": (C.c_int, []),
+    "glq_status_string": (C.c_char_p, [C.c_int]),
+    "glq_last_cuda_error": (C.c_int, []),
+    "glq_turbo_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+    "glq_turbo_dequant_grouped_gemv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+    "glq_gptq_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                          C.c_int, vp]),
+    "glq_tiled_codes_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "glq_tiled_sz_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "glq_pack_codes_i32": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp]),
+    "glq_pack_codes_u8": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
+    "glq_pack_sz": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, vp]),
+    "glq_pack_f16": (C.c_int, [vp, C.c_long, C.c_long, C.c_int, C.c_int, vp, vp]),
+    "glq_dequant_tiled": (C.c_int, [C.c_int, C.POINTER(Weight), C.c_int, vp, vp]),
+    "glq_mm_workspace_bytes": (C.c_size_t, [C.POINTER(MMArgs)]),
+    "glq_grouped_matmul": (C.c_int, [C.POINTER(MMArgs), vp]),
+    "glq_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.POINTER(Weight), C.c_int]),
+    "glq_linear_forward": (C.c_int, [C.c_int, C.c_int, C.POINTER(Weight), vp, vp, C.c_int64, vp, vp, C.c_int64,
+                                     C.c_int, vp, C.c_size_t, vp]),
+    "glq_moe_workspace_bytes": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
+    "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, C.c_size_t, vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises RuntimeError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m glorcq_b200._build` (nvcc, sm_100a). "
+                "glorcq_b200 has no CPU or PyTorch fallback.")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGS.items():
+            if not hasattr(L, name):
+                continue
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def exported_symbols():
+    return list(_SIGS.keys())
+
+
+def check(status: int, what: str = "glorcq_b200"):
+    if status != 0:
+        L = lib()
+        msg = L.glq_status_string(status).decode()
+        extra = f" (cudaError {L.glq_last_cuda_error()})" if status == -4 else ""
+        raise RuntimeError(f"{what}: {msg}{extra}")

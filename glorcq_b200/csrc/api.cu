@@ -1,0 +1,455 @@
+// extern "C" entry points of libglorcq_b200: argument checks, launch geometry, launches.
+// No torch types, no allocation: the caller owns every buffer.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+#include "aux_kernels.cuh"
+#include "skinny_mm.cuh"
+
+using namespace glq;
+
+static thread_local int g_last_cuda_error = 0;
+
+#define GLQ_CUDA(call)                                   \
+    do {                                                 \
+        cudaError_t e__ = (call);                        \
+        if (e__ != cudaSuccess) {                        \
+            g_last_cuda_error = (int)e__;                \
+            return GLQ_ERR_CUDA;                         \
+        }                                                \
+    } while (0)
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+static inline int pow2ceil(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+extern "C" int glq_version(void) { return 100; }
+
+extern "C" const char* glq_status_string(int status) {
+    switch (status) {
+        case GLQ_OK: return "ok";
+        case GLQ_ERR_ARG: return "invalid argument (null pointer or inconsistent size)";
+        case GLQ_ERR_ALIGN: return "pointer or leading dimension not aligned to 16 bytes";
+        case GLQ_ERR_UNSUPPORTED: return "shape, group size or rank not supported by the sm_100a kernels";
+        case GLQ_ERR_CUDA: return "CUDA call failed (see glq_last_cuda_error)";
+        case GLQ_ERR_WORKSPACE: return "workspace too small";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int glq_last_cuda_error(void) { return g_last_cuda_error; }
+
+// ---------------------------------------------------------------------------------------------
+// tiled layout sizes
+// ---------------------------------------------------------------------------------------------
+static inline int fmt_kb(int fmt) { return (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_T2) ? 128 : 64; }
+static inline int fmt_ld(int fmt) { return fmt == GLQ_FMT_F16 ? 4 : 1; }
+
+extern "C" size_t glq_tiled_codes_bytes(int fmt, int N, int K) {
+    if (fmt < 0 || fmt > 3 || N <= 0 || K <= 0) return 0;
+    return (size_t)cdiv(N, 16) * cdiv(K, fmt_kb(fmt)) * fmt_ld(fmt) * 512;
+}
+extern "C" size_t glq_tiled_sz_bytes(int N, int n_groups) {
+    if (N <= 0 || n_groups <= 0) return 0;
+    return (size_t)cdiv(N, 16) * n_groups * 64;
+}
+
+// ---------------------------------------------------------------------------------------------
+// launch geometry of the skinny kernel (shared by the workspace query and the launcher)
+// ---------------------------------------------------------------------------------------------
+struct Geometry {
+    int nw, ntt, ntc, nkb, group_blocks, tile_groups, sk, kb_per_split, kb_chunk, max_passes;
+    size_t smem, counters_bytes, scratch_bytes;
+};
+
+static int num_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) !=
+                                                      cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+static int plan_geometry(int fmt, int epilogue, int N, int K, int group_size, int n_problems, int max_rows,
+                         bool allow_split, Geometry* out) {
+    if (fmt < 0 || fmt > 3 || N <= 0 || K <= 0 || n_problems <= 0 || max_rows <= 0) return GLQ_ERR_ARG;
+    Geometry g{};
+    g.nw = (epilogue == GLQ_EPI_SWIGLU) ? 2 : 1;
+    if (g.nw == 2 && fmt == GLQ_FMT_F16) return GLQ_ERR_UNSUPPORTED;
+    const int kb = fmt_kb(fmt);
+    g.nkb = cdiv(K, kb);
+    g.group_blocks = 1;
+    if (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_Q4) {
+        if (group_size <= 0 || group_size % kb != 0) return GLQ_ERR_UNSUPPORTED;
+        g.group_blocks = group_size / kb;
+    }
+    if (max_rows <= 8) g.ntt = 1;
+    else if (max_rows <= 16 || g.nw == 2) g.ntt = 2;
+    else g.ntt = 4;
+    g.ntc = g.ntt == 1 ? std::max(2, pow2ceil(max_rows)) : 8 * g.ntt;
+    g.max_passes = cdiv(max_rows, 8 * g.ntt);
+    g.tile_groups = cdiv(cdiv(N, kRowTile), kRW);
+
+    // CTA-level k split: fill the machine about twice over while every warp keeps >= 1 k block
+    const long ctas = (long)n_problems * g.tile_groups;
+    const int units = cdiv(g.nkb, g.group_blocks);  // split granularity = one scale group
+    int sk = 1;
+    if (allow_split) {
+        const long want = 2L * num_sms();
+        if (ctas < want) sk = (int)std::min<long>((want + ctas - 1) / ctas, std::max(1, units / kKW));
+    }
+    g.kb_per_split = cdiv(units, sk) * g.group_blocks;
+    g.sk = cdiv(g.nkb, g.kb_per_split);
+    // shared memory holds kb_chunk blocks of staged activations at a time (two CTAs per SM)
+    const size_t per_kb = skinny_smem_bytes(fmt, 1, g.ntc, g.nw, g.ntt) - skinny_smem_bytes(fmt, 0, g.ntc, g.nw, g.ntt);
+    const size_t fixed = skinny_smem_bytes(fmt, 0, g.ntc, g.nw, g.ntt);
+    const size_t smem_cap = 100 * 1024;
+    g.kb_chunk = (int)std::max<size_t>(1, std::min<size_t>((size_t)std::min(g.kb_per_split, g.nkb),
+                                                             (smem_cap - fixed) / per_kb));
+    g.smem = skinny_smem_bytes(fmt, g.kb_chunk, g.ntc, g.nw, g.ntt);
+    const size_t tiles = (size_t)n_problems * g.tile_groups * g.max_passes;
+    g.counters_bytes = g.sk > 1 ? ((tiles * sizeof(int) + 255) / 256) * 256 : 0;
+    g.scratch_bytes = g.sk > 1 ? tiles * g.sk * (size_t)(kRW * g.nw * g.ntt * 32) * sizeof(float4) : 0;
+    *out = g;
+    return GLQ_OK;
+}
+
+template <int FMT, int NW, int NTT, bool RM>
+static int launch_one(const SkinnyParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kern = skinny_kernel<FMT, NW, NTT, RM>;
+    if (smem > 48 * 1024) {
+        static size_t configured[16] = {0};
+        int dev = 0;
+        GLQ_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 16 || configured[dev] < smem) {
+            GLQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (dev >= 0 && dev < 16) configured[dev] = smem;
+        }
+    }
+    kern<<<grid, kThreads, smem, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+template <int FMT, bool RM>
+static int launch_fmt(const SkinnyParams& p, const Geometry& g, int grid, cudaStream_t st) {
+    if (g.nw == 2) {
+        if constexpr (FMT == GLQ_FMT_F16 || RM) {
+            return GLQ_ERR_UNSUPPORTED;
+        } else {
+            if (g.ntt == 1) return launch_one<FMT, 2, 1, false>(p, grid, g.smem, st);
+            return launch_one<FMT, 2, 2, false>(p, grid, g.smem, st);
+        }
+    }
+    if (g.ntt == 1) return launch_one<FMT, 1, 1, RM>(p, grid, g.smem, st);
+    if (g.ntt == 2) return launch_one<FMT, 1, 2, RM>(p, grid, g.smem, st);
+    return launch_one<FMT, 1, 4, RM>(p, grid, g.smem, st);
+}
+
+static int launch_skinny(int fmt, bool rowmajor, const SkinnyParams& p, const Geometry& g, int n_problems,
+                         cudaStream_t st) {
+    const long grid = (long)n_problems * g.tile_groups * g.sk;
+    if (grid <= 0 || grid > 0x7fffffffL) return GLQ_ERR_UNSUPPORTED;
+    if (rowmajor) {
+        if (fmt != GLQ_FMT_T2) return GLQ_ERR_UNSUPPORTED;
+        return launch_fmt<GLQ_FMT_T2, true>(p, g, (int)grid, st);
+    }
+    switch (fmt) {
+        case GLQ_FMT_Q2: return launch_fmt<GLQ_FMT_Q2, false>(p, g, (int)grid, st);
+        case GLQ_FMT_Q4: return launch_fmt<GLQ_FMT_Q4, false>(p, g, (int)grid, st);
+        case GLQ_FMT_T2: return launch_fmt<GLQ_FMT_T2, false>(p, g, (int)grid, st);
+        case GLQ_FMT_F16: return launch_fmt<GLQ_FMT_F16, false>(p, g, (int)grid, st);
+    }
+    return GLQ_ERR_ARG;
+}
+
+static void fill_geometry(SkinnyParams& p, const Geometry& g) {
+    p.tile_groups = g.tile_groups;
+    p.sk = g.sk;
+    p.kb_per_split = g.kb_per_split;
+    p.kb_chunk = g.kb_chunk;
+    p.group_blocks = g.group_blocks;
+    p.nkb = g.nkb;
+    p.ntc = g.ntc;
+    p.max_passes = g.max_passes;
+}
+
+// ---------------------------------------------------------------------------------------------
+// glq_grouped_matmul
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t glq_mm_workspace_bytes(const glq_mm_args_t* a) {
+    if (!a) return 0;
+    Geometry g;
+    if (plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows, true, &g) != GLQ_OK)
+        return 0;
+    return g.counters_bytes + g.scratch_bytes;
+}
+
+extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
+    if (!a || !a->x || !a->y) return GLQ_ERR_ARG;
+    if (a->n_problems == 0 || a->max_rows == 0) return GLQ_OK;
+    if (a->epilogue != GLQ_EPI_LINEAR && a->epilogue != GLQ_EPI_SWIGLU) return GLQ_ERR_ARG;
+    if (a->rank < 0 || a->rank % 16 != 0) return GLQ_ERR_UNSUPPORTED;
+    if (a->rank > 0 && (a->a0 || a->a1) && (a->lda % 8 != 0 || !aligned16(a->a0) || !aligned16(a->a1)))
+        return GLQ_ERR_ALIGN;
+    Geometry g;
+    int rc = plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows, true, &g);
+    if (rc != GLQ_OK) return rc;
+    if (g.sk > 1) {
+        if (!a->workspace || a->workspace_bytes < g.counters_bytes + g.scratch_bytes) return GLQ_ERR_WORKSPACE;
+        if (!aligned16(a->workspace)) return GLQ_ERR_ALIGN;
+    }
+    if (!a->w0_table && !a->w0.codes) return GLQ_ERR_ARG;
+    if (g.nw == 2 && !a->w1_table && !a->w1.codes) return GLQ_ERR_ARG;
+
+    SkinnyParams p{};
+    p.w[0] = a->w0;
+    p.w[1] = a->w1;
+    p.table[0] = a->w0_table;
+    p.table[1] = a->w1_table;
+    p.slot_index = a->slot_index;
+    p.n_slots = a->n_slots;
+    p.slot_count = a->slot_count;
+    p.slot_offset = a->slot_offset;
+    p.entry_row = a->entry_row;
+    p.entry_scale = reinterpret_cast<const __half*>(a->entry_scale);
+    p.x = reinterpret_cast<const __half*>(a->x);
+    p.ldx = a->ldx;
+    p.a[0] = reinterpret_cast<const __half*>(a->a0);
+    p.a[1] = reinterpret_cast<const __half*>(a->a1);
+    p.lda = a->lda;
+    p.y = reinterpret_cast<__half*>(a->y);
+    p.ldy = a->ldy;
+    p.counters = reinterpret_cast<int*>(a->workspace);
+    p.scratch = reinterpret_cast<float4*>(reinterpret_cast<char*>(a->workspace) + g.counters_bytes);
+    p.max_rows = a->max_rows;
+    p.rows_stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
+    p.epilogue = a->epilogue;
+    p.x_vec = (aligned16(a->x) && a->ldx % 8 == 0) ? 1 : 0;
+    fill_geometry(p, g);
+    return launch_skinny(a->fmt, false, p, g, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// glq_linear_forward
+// ---------------------------------------------------------------------------------------------
+static void linear_args(int fmt, int group_size, const glq_weight_t* w, int B, glq_mm_args_t* m) {
+    std::memset(m, 0, sizeof(*m));
+    m->fmt = fmt;
+    m->group_size = group_size;
+    m->epilogue = GLQ_EPI_LINEAR;
+    m->n_problems = 1;
+    m->max_rows = B;
+    m->rows_stride = B;
+    m->N = w->N;
+    m->K = w->K;
+    m->rank = w->rank;
+    m->w0 = *w;
+}
+static void xu_args(const glq_weight_t* w, const void* ut, int B, glq_mm_args_t* m) {
+    std::memset(m, 0, sizeof(*m));
+    m->fmt = GLQ_FMT_F16;
+    m->epilogue = GLQ_EPI_LINEAR;
+    m->n_problems = 1;
+    m->max_rows = B;
+    m->rows_stride = B;
+    m->N = w->rank;
+    m->K = w->K;
+    m->w0.codes = ut;
+    m->w0.N = w->rank;
+    m->w0.K = w->K;
+}
+static inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+extern "C" size_t glq_linear_workspace_bytes(int fmt, int group_size, const glq_weight_t* w, int B) {
+    if (!w || B <= 0) return 0;
+    glq_mm_args_t m;
+    linear_args(fmt, group_size, w, B, &m);
+    size_t total = up256(glq_mm_workspace_bytes(&m));
+    if (w->rank > 0) {
+        glq_mm_args_t u;
+        xu_args(w, w->codes, B, &u);
+        total += up256((size_t)B * w->rank * sizeof(__half)) + up256(glq_mm_workspace_bytes(&u));
+    }
+    return total;
+}
+
+extern "C" int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w, const void* ut, const void* x,
+                                  int64_t ldx, const void* a, void* y, int64_t ldy, int B, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    if (!w || !x || !y || B < 0) return GLQ_ERR_ARG;
+    if (B == 0 || w->N == 0) return GLQ_OK;
+    glq_mm_args_t m;
+    linear_args(fmt, group_size, w, B, &m);
+    char* ws = reinterpret_cast<char*>(workspace);
+    size_t used = 0;
+    const size_t main_ws = up256(glq_mm_workspace_bytes(&m));
+    const void* a_use = a;
+    if (!a && ut && w->rank > 0 && w->sv) {
+        glq_mm_args_t u;
+        xu_args(w, ut, B, &u);
+        const size_t a_bytes = up256((size_t)B * w->rank * sizeof(__half));
+        const size_t u_ws = up256(glq_mm_workspace_bytes(&u));
+        if (!ws || workspace_bytes < main_ws + a_bytes + u_ws) return GLQ_ERR_WORKSPACE;
+        u.x = x;
+        u.ldx = ldx;
+        u.y = ws + main_ws;
+        u.ldy = w->rank;
+        u.workspace = ws + main_ws + a_bytes;
+        u.workspace_bytes = u_ws;
+        int rc = glq_grouped_matmul(&u, stream);
+        if (rc != GLQ_OK) return rc;
+        a_use = ws + main_ws;
+        used = a_bytes + u_ws;
+    }
+    (void)used;
+    if (main_ws > 0 && (!ws || workspace_bytes < main_ws)) return GLQ_ERR_WORKSPACE;
+    m.x = x;
+    m.ldx = ldx;
+    m.a0 = a_use;
+    m.lda = w->rank;
+    m.y = y;
+    m.ldy = ldy;
+    m.workspace = ws;
+    m.workspace_bytes = main_ws;
+    if (!a_use) m.w0.rank = 0, m.rank = 0;
+    return glq_grouped_matmul(&m, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Drop-ins for the reference's native modules
+// ---------------------------------------------------------------------------------------------
+static int turbo_rowmajor(const void* x, const uint8_t* packed, const float* norms, const float* centroids, void* y,
+                          int n_problems, int rows, int N, int K, int slot_rows, void* stream) {
+    if (!x || !packed || !norms || !centroids || !y) return GLQ_ERR_ARG;
+    if (K <= 0 || K % 4 != 0) return GLQ_ERR_UNSUPPORTED;
+    Geometry g;
+    int rc = plan_geometry(GLQ_FMT_T2, GLQ_EPI_LINEAR, N, K, 0, n_problems, rows, false, &g);
+    if (rc != GLQ_OK) return rc;
+    SkinnyParams p{};
+    p.w[0].codes = packed;
+    p.w[0].norms = norms;
+    p.w[0].centroids = centroids;
+    p.w[0].N = N;
+    p.w[0].K = K;
+    p.x = reinterpret_cast<const __half*>(x);
+    p.ldx = K;
+    p.y = reinterpret_cast<__half*>(y);
+    p.ldy = N;
+    p.max_rows = rows;
+    p.rows_stride = rows;
+    p.x_vec = (aligned16(x) && K % 8 == 0) ? 1 : 0;
+    p.slot_rows = slot_rows;
+    fill_geometry(p, g);
+    return launch_skinny(GLQ_FMT_T2, true, p, g, n_problems, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int glq_turbo_dequant_matmul(const void* x_rot, const uint8_t* packed, const float* norms,
+                                        const float* centroids, void* y, int B, int N, int K, void* stream) {
+    if (B < 0 || N < 0) return GLQ_ERR_ARG;
+    if (B == 0 || N == 0) return GLQ_OK;
+    return turbo_rowmajor(x_rot, packed, norms, centroids, y, 1, B, N, K, 0, stream);
+}
+
+extern "C" int glq_turbo_dequant_grouped_gemv(const void* x_grouped, const uint8_t* packed_cat, const float* norms_cat,
+                                              const float* centroids, void* y, int E, int N_out, int K,
+                                              void* stream) {
+    if (E < 0 || N_out < 0) return GLQ_ERR_ARG;
+    if (E == 0 || N_out == 0) return GLQ_OK;
+    return turbo_rowmajor(x_grouped, packed_cat, norms_cat, centroids, y, E, 1, N_out, K, N_out, stream);
+}
+
+extern "C" int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const void* scales, const void* zeros,
+                                       const float* lora_out, float* y, int B, int N, int K, int groupsize,
+                                       int n_groups, int sym, void* stream) {
+    if (B < 0 || N < 0 || K < 0) return GLQ_ERR_ARG;
+    if (B == 0 || N == 0) return GLQ_OK;
+    if (!x || !q || !scales || !y || (!sym && !zeros)) return GLQ_ERR_ARG;
+    if (groupsize <= 0 || n_groups <= 0 || (long)n_groups * groupsize < K) return GLQ_ERR_ARG;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const size_t smem = (size_t)K * sizeof(float);
+    for (int b0 = 0; b0 < B; b0 += 4) {
+        const int nb = std::min(4, B - b0);
+        const dim3 grid(cdiv(N, kWarpsPerCta));
+        if (smem * nb > 48 * 1024) {
+            GLQ_CUDA(cudaFuncSetAttribute(gptq_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)(smem * 4)));
+        }
+        gptq_i8_kernel<<<grid, kThreads, smem * nb, st>>>(
+            x + (size_t)b0 * K, q, reinterpret_cast<const __half*>(scales), reinterpret_cast<const __half*>(zeros),
+            lora_out ? lora_out + (size_t)b0 * N : nullptr, y + (size_t)b0 * N, nb, N, K, groupsize, n_groups, sym);
+        GLQ_CUDA(cudaGetLastError());
+    }
+    return GLQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Load-time re-tiling and the dequantised-tile check
+// ---------------------------------------------------------------------------------------------
+extern "C" int glq_pack_codes_i32(const int32_t* q, int bits, int N, int K, void* tiled, void* stream) {
+    if (!q || !tiled || N <= 0 || K <= 0) return GLQ_ERR_ARG;
+    if (bits != 2 && bits != 4) return GLQ_ERR_UNSUPPORTED;
+    const int fmt = bits == 2 ? GLQ_FMT_Q2 : GLQ_FMT_Q4;
+    const size_t words = glq_tiled_codes_bytes(fmt, N, K) / 4;
+    pack_codes_i32_kernel<<<(unsigned)((words + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        q, bits, N, K, reinterpret_cast<uint32_t*>(tiled), words);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+extern "C" int glq_pack_codes_u8(const uint8_t* packed, int N, int K, void* tiled, void* stream) {
+    if (!packed || !tiled || N <= 0 || K <= 0) return GLQ_ERR_ARG;
+    if (K % 4 != 0) return GLQ_ERR_UNSUPPORTED;
+    const size_t words = glq_tiled_codes_bytes(GLQ_FMT_T2, N, K) / 4;
+    pack_codes_u8_kernel<<<(unsigned)((words + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        packed, N, K, reinterpret_cast<uint32_t*>(tiled), words);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+extern "C" int glq_pack_sz(const void* scales, const void* zeros, int N, int n_groups, void* tiled, void* stream) {
+    if (!scales || !tiled || N <= 0 || n_groups <= 0) return GLQ_ERR_ARG;
+    const size_t elems = glq_tiled_sz_bytes(N, n_groups) / 2;
+    pack_sz_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half*>(scales), reinterpret_cast<const __half*>(zeros), N, n_groups,
+        reinterpret_cast<__half*>(tiled), elems);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+extern "C" int glq_pack_f16(const void* W, long stride_n, long stride_k, int N, int K, void* tiled, void* stream) {
+    if (!W || !tiled || N <= 0 || K <= 0) return GLQ_ERR_ARG;
+    const size_t elems = glq_tiled_codes_bytes(GLQ_FMT_F16, N, K) / 2;
+    pack_f16_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half*>(W), stride_n, stride_k, N, K, reinterpret_cast<__half*>(tiled), elems);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+extern "C" int glq_dequant_tiled(int fmt, const glq_weight_t* w, int group_size, void* out, void* stream) {
+    if (!w || !w->codes || !out || w->N <= 0 || w->K <= 0) return GLQ_ERR_ARG;
+    const size_t elems = (size_t)w->N * w->K;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_Q4) {
+        if (!w->sz || group_size <= 0 || group_size % fmt_kb(fmt) != 0) return GLQ_ERR_UNSUPPORTED;
+        dequant_tiled_q_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(
+            fmt, *w, group_size, reinterpret_cast<__half*>(out));
+    } else if (fmt == GLQ_FMT_T2) {
+        if (!w->norms || !w->centroids) return GLQ_ERR_ARG;
+        dequant_tiled_t2_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(*w, reinterpret_cast<float*>(out));
+    } else {
+        return GLQ_ERR_UNSUPPORTED;
+    }
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}

@@ -1,0 +1,201 @@
+"""Quantized linear layer and fused-experts adapter on the sm_100a kernels.
+
+Same class names, attributes, loaders and forward signature as the reference's
+``inference.quantized_linear`` (inference/quantized_linear.py:152-428):
+
+    y = dequant(W_q) x + (x U) SV^T + bias
+
+The loaders additionally re-tile the weights for the kernels (glorcq_b200.tiled); forward runs
+one fused launch for the quantized matmul with the low-rank epilogue (plus a small launch for
+a = x U when it is not handed in).  Nothing falls back to PyTorch arithmetic.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import tiled
+from .kernels import gptq_dequant_matmul_fused, is_cuda_available, is_gptq_cuda_available
+from .tiled import TiledWeight
+
+_HAS_FUSED_KERNEL = is_cuda_available()
+_HAS_GPTQ_FUSED_KERNEL = is_gptq_cuda_available()
+
+
+def _tileable(bits, groupsize):
+    kb = {2: 128, 4: 64}.get(bits)
+    return kb is not None and groupsize is not None and groupsize > 0 and groupsize % kb == 0
+
+
+class GLoRCQLinear(nn.Module):
+    """Drop-in for the reference layer (inference/quantized_linear.py:152-362)."""
+
+    def __init__(self, in_features, out_features, bias=False):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.quant_type = None       # "gptq" or "turbo"
+
+        # integer-code format
+        self.qweight_int = None      # (out_d, in_d) int32; dropped after tiling unless keep_raw
+        self.scales = None           # (out_d, n_groups) fp16
+        self.zeros = None            # (out_d, n_groups) fp16
+        self.gptq_bits = None
+        self.gptq_groupsize = None
+        self.gptq_sym = False
+
+        # codebook format
+        self.packed_indices = None   # (out_d, in_d/4) uint8
+        self.norms = None            # (out_d,) fp32
+        self.turbo_bits = None
+        self.turbo_dim = None
+        self.turbo_seed = 42
+        self._rotation_cache = None
+        self._rht_signs = None
+        self._turbo_dequant_W = None
+
+        # low-rank correction
+        self.U = None                # (in_d, rank) fp16, shared by a cluster
+        self.SV = None               # (out_d, rank) fp16
+        self.cluster_id = None
+
+        self.bias_param = None       # (out_d,) fp16
+
+        # device layout of the kernels
+        self._tiled = None           # TiledWeight
+        self._ut = None              # TiledWeight of U^T (shared through tiled.tiled_ut)
+
+    # ---- loaders (inference/quantized_linear.py:195-269) ---------------------------------
+    def load_gptq(self, packed_data, device="cuda", keep_raw=False):
+        """Integer codes + per-group scale/zero.  2- and 4-bit codes with a group size that is a
+        multiple of 128 (64 for 4-bit) are re-tiled for the fused kernel; anything else keeps the
+        (N,K) codes and runs through the int8 drop-in kernel."""
+        self.quant_type = "gptq"
+        q = packed_data["qweight_int"].to(device)
+        self.scales = packed_data["scales"].to(device).to(torch.float16)
+        self.zeros = packed_data["zeros"].to(device).to(torch.float16)
+        self.gptq_bits = packed_data["bits"]
+        self.gptq_groupsize = packed_data["groupsize"]
+        self.gptq_sym = packed_data.get("sym", False)
+        in_range = True
+        if _tileable(self.gptq_bits, self.gptq_groupsize):
+            in_range = bool(((q >= 0) & (q < 2 ** self.gptq_bits)).all())   # load time only
+        if _tileable(self.gptq_bits, self.gptq_groupsize) and in_range:
+            self._tiled = TiledWeight.from_gptq(q, self.scales, self.zeros, self.gptq_bits,
+                                                self.gptq_groupsize, self.gptq_sym)
+            self.qweight_int = q if keep_raw else None
+        else:
+            self._tiled = None
+            self.qweight_int = q
+        self._sync_tiled()
+
+    def load_turbo(self, compressed_data, rotation_cache, device="cuda"):
+        """2-bit codebook indices for runtime dequant; the codes stay packed on the device."""
+        self.quant_type = "turbo"
+        self.turbo_bits = compressed_data["bits"]
+        self.turbo_dim = compressed_data["dim"]
+        self.turbo_seed = compressed_data.get("seed", 42)
+        if self.turbo_bits != 2:
+            raise RuntimeError(f"codebook kernels cover bits == 2, got {self.turbo_bits}")
+        self.packed_indices = compressed_data["packed_indices"].to(device)
+        self.norms = compressed_data["norms"].float().to(device)
+        self._rotation_cache = rotation_cache
+        rotation_cache.register(self.turbo_dim, self.turbo_bits, self.turbo_seed)
+        centroids = rotation_cache.get_centroids(self.turbo_dim, self.turbo_bits, self.turbo_seed)
+        self._tiled = TiledWeight.from_turbo(self.packed_indices, self.norms, centroids.to(device))
+        self._sync_tiled()
+
+    def load_lora(self, U, S, V, device="cuda"):
+        """Old format: pre-fuse S into V (inference/quantized_linear.py:249-259)."""
+        if U is not None:
+            self.U = U.half().to(device)
+            self.SV = (V * S.unsqueeze(0)).half().to(device)
+            self._sync_tiled()
+
+    def load_sv(self, U, SV, device="cuda"):
+        """New format: SV already fused.  Pass the cluster's shared U tensor itself (not a copy) so
+        that every layer of the cluster uses one tiled U^T."""
+        if U is not None:
+            dev = torch.device(device)
+            same = U.dtype == torch.float16 and U.is_cuda and (dev.type == "cuda") and \
+                (dev.index is None or dev.index == U.device.index)
+            self.U = U if same else U.half().to(device)
+            self.SV = SV.half().to(device).contiguous()
+            self._sync_tiled()
+
+    def set_bias(self, bias):
+        self.bias_param = None if bias is None else bias.half()
+        self._sync_tiled()
+
+    def _sync_tiled(self):
+        if self._tiled is None:
+            return
+        self._tiled.set_sv(self.SV)
+        self._tiled.set_bias(self.bias_param)
+        self._ut = tiled.tiled_ut(self.U) if (self.U is not None and self.SV is not None) else None
+
+    # ---- checks -------------------------------------------------------------------------------
+    def _dequant_gptq(self):
+        """fp16 weight tile fp16((q - z) * s) read back from the tiled codes
+        (inference/quantized_linear.py:271-284)."""
+        if self._tiled is None:
+            raise RuntimeError("weights are not in the tiled layout")
+        return self._tiled.dequantize()
+
+    # ---- forward (inference/quantized_linear.py:286-355) ------------------------------------
+    def _rotate(self, x):
+        if self._rht_signs is not None:
+            from .rotation import rht_forward
+            return rht_forward(x, self._rht_signs)
+        Pi = self._rotation_cache.get_pi(self.turbo_dim, self.turbo_bits, self.turbo_seed)
+        return (x.float() @ Pi.float().T).half()
+
+    def forward(self, x, precomputed_xU=None, precomputed_x_rot=None):
+        orig_shape = x.shape
+        if x.dim() != 2:
+            x = x.reshape(-1, self.in_features)
+        if x.dtype != torch.float16:
+            x = x.half()
+        x = x.contiguous()
+        a = None
+        if precomputed_xU is not None and self.SV is not None:
+            a = precomputed_xU.reshape(-1, self.SV.shape[1]).to(torch.float16)
+
+        if self.quant_type == "gptq":
+            if self._tiled is not None:
+                y = tiled.linear_forward(self._tiled, x, ut=self._ut, a=a)
+            else:
+                y = gptq_dequant_matmul_fused(x, self.qweight_int, self.scales, self.zeros,
+                                              self.gptq_groupsize, self.gptq_sym, lora_USV=None)
+                if self.SV is not None:
+                    if a is None:
+                        a = tiled.dense_matmul(tiled.tiled_ut(self.U), x)
+                    y = y + a @ self.SV.T
+                if self.bias_param is not None:
+                    y = y + self.bias_param
+        elif self.quant_type == "turbo":
+            if self._tiled is None:
+                raise RuntimeError("TurboQuant weights not loaded")
+            if precomputed_x_rot is not None:
+                x_rot = precomputed_x_rot.reshape(-1, self.in_features)
+                if x_rot.dtype != torch.float16:
+                    x_rot = x_rot.half()
+                x_rot = x_rot.contiguous()
+            else:
+                x_rot = self._rotate(x)
+            if self.SV is not None and a is None:
+                a = tiled.dense_matmul(self._ut, x)          # the low-rank term sees the unrotated x
+            y = tiled.linear_forward(self._tiled, x_rot, ut=None, a=a)
+        else:
+            raise RuntimeError(f"Unknown quant_type: {self.quant_type}")
+
+        if len(orig_shape) != 2:
+            y = y.reshape(*orig_shape[:-1], self.out_features)
+        return y
+
+    def extra_repr(self):
+        s = f"in_features={self.in_features}, out_features={self.out_features}, quant_type={self.quant_type}"
+        if self.U is not None:
+            s += f", lora_rank={self.U.shape[1]}"
+        return s

@@ -126,3 +126,51 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.double().reshape(-1)
     b = b.double().reshape(-1)
     return float((a - b).norm() / (b.norm() + 1e-30))
+
+
+# --------------------------------------------------------------------------------------
+# Conversions to the CUDA package's modules (need a GPU)
+# --------------------------------------------------------------------------------------
+class FixedRotationCache:
+    """Hands a given rotation and codebook to GLoRCQLinear.load_turbo (the reference builds them
+    with a third-party package that is not part of this repository)."""
+
+    def __init__(self, Pi, centroids):
+        self._pi, self._c = Pi, centroids
+
+    def register(self, dim, bits, seed=42):
+        pass
+
+    def get_pi(self, dim, bits, seed=42):
+        return self._pi
+
+    def get_centroids(self, dim, bits, seed=42):
+        return self._c
+
+
+def to_b200_linear(d, device="cuda", shared_u=None):
+    """Build glorcq_b200's GLoRCQLinear from a case dict.  shared_u: dict id(U cpu tensor) -> device
+    tensor, so that layers of one cluster share one device U."""
+    from glorcq_b200.quantized_linear import GLoRCQLinear
+    lin = GLoRCQLinear(d["K"], d["N"])
+    if d["fmt"] == "gptq":
+        lin.load_gptq({"qweight_int": d["qweight_int"], "scales": d["scales"], "zeros": d["zeros"],
+                       "bits": d["bits"], "groupsize": d["groupsize"], "sym": d["sym"]}, device=device)
+    else:
+        Pi = d.get("Pi")
+        if Pi is None:
+            Pi = torch.eye(d["K"], dtype=torch.float16)
+        lin.load_turbo({"packed_indices": d["packed_indices"], "norms": d["norms"], "bits": 2,
+                        "dim": d["K"], "seed": 42},
+                       FixedRotationCache(Pi.to(device), d["centroids"].to(device)), device=device)
+    if "SV" in d:
+        U = d["U"]
+        if shared_u is not None:
+            if id(U) not in shared_u:
+                shared_u[id(U)] = U.to(device)
+            U = shared_u[id(U)]
+        else:
+            U = U.to(device)
+        lin.load_sv(U, d["SV"], device=device)
+        lin.cluster_id = d.get("cluster_id")
+    return lin

@@ -1,0 +1,72 @@
+"""CPU checks of the C ABI: the library builds, loads, and exports every symbol the header declares."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def libpath():
+    from glorcq_b200 import _build
+    return _build.build()
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "glorcq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(glq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(libpath):
+    L = ctypes.CDLL(libpath)
+    syms = header_symbols()
+    assert len(syms) >= 15
+    missing = [s for s in syms if not hasattr(L, s)]
+    assert not missing, f"declared in include/glorcq_b200.h but not exported: {missing}"
+
+
+def test_binding_covers_header(libpath):
+    from glorcq_b200 import _lib
+    assert set(header_symbols()) <= set(_lib.exported_symbols())
+
+
+def test_status_strings_and_sizes(libpath):
+    from glorcq_b200 import _lib
+    L = _lib.lib()
+    assert L.glq_version() >= 100
+    for st in (0, -1, -2, -3, -4, -5):
+        assert len(L.glq_status_string(st)) > 0
+    # C1 expert projection: 1408 x 2048, 2-bit -> 88 row tiles x 16 blocks x 512 B
+    assert L.glq_tiled_codes_bytes(_lib.FMT_Q2, 1408, 2048) == 88 * 16 * 512 == 1408 * 2048 // 4
+    assert L.glq_tiled_codes_bytes(_lib.FMT_Q4, 2048, 2048) == 2048 * 2048 // 2
+    assert L.glq_tiled_codes_bytes(_lib.FMT_F16, 64, 2048) == 64 * 2048 * 2
+    assert L.glq_tiled_sz_bytes(1408, 16) == 1408 * 16 * 4
+    # ragged shapes are padded to whole tiles
+    assert L.glq_tiled_codes_bytes(_lib.FMT_T2, 17, 130) == 2 * 2 * 512
+
+
+def test_host_side_argument_checks(libpath):
+    """Errors decided on the host, before any launch: no GPU needed."""
+    from glorcq_b200 import _lib
+    L = _lib.lib()
+    assert L.glq_turbo_dequant_matmul(None, None, None, None, None, 1, 8, 64, None) == -1
+    assert L.glq_turbo_dequant_matmul(None, None, None, None, None, 0, 8, 64, None) == 0      # B == 0: no-op
+    assert L.glq_turbo_dequant_matmul(None, None, None, None, None, -1, 8, 64, None) == -1
+    assert L.glq_gptq_dequant_matmul(None, None, None, None, None, None, 0, 8, 64, 128, 1, 0, None) == 0
+    assert L.glq_pack_codes_i32(None, 2, 16, 128, None, None) == -1
+    assert L.glq_grouped_matmul(None, None) == -1
+
+
+def test_no_fallback_without_gpu():
+    """Without a CUDA device the product path must fail loudly, not compute on the CPU."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    from tests import cases
+    d = cases.make_linear(1, 32, 128, rank=16)
+    with pytest.raises((RuntimeError, AssertionError)):
+        cases.to_b200_linear(d, device="cpu")

@@ -1,0 +1,188 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI (ctypes) and the Python
+classes that mirror the reference.  Bars: dequantised tiles bit-exact; layer outputs
+rel-L2 <= 1e-3 (fp16 storage, fp32 accumulation); the reference's own kernel-test bound
+max|err| < 0.01 (inference/kernels/test_kernels.py:105) on its data distributions."""
+
+import pytest
+import torch
+
+from oracle import glorcq_oracle as O
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+REL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from glorcq_b200 import _build
+    _build.build()
+    return torch.device("cuda:0")
+
+
+# ---- tiles ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,K,bits,gs,int_zeros", [
+    (1408, 2048, 2, 128, True), (2048, 1408, 2, 128, True), (40, 200, 2, 128, True), (17, 128, 2, 128, False),
+    (64, 256, 4, 128, True), (2048, 2048, 4, 128, True), (33, 192, 4, 64, False), (48, 512, 2, 256, True)])
+def test_gptq_tiles_bit_exact(dev, N, K, bits, gs, int_zeros):
+    from glorcq_b200.tiled import TiledWeight
+    d = cases.make_linear(101 + N + K, N, K, fmt="gptq", bits=bits, groupsize=gs, int_zeros=int_zeros, with_lora=False)
+    tw = TiledWeight.from_gptq(d["qweight_int"].to(dev), d["scales"].to(dev), d["zeros"].to(dev), bits, gs)
+    W = tw.dequantize().cpu()
+    ref = O.gptq_tile_fp16(d["qweight_int"], d["scales"], d["zeros"], gs)
+    assert torch.equal(W, ref)
+
+
+@pytest.mark.parametrize("N,K", [(1408, 2048), (72, 256), (19, 132), (64, 64)])
+def test_turbo_tiles_bit_exact(dev, N, K):
+    from glorcq_b200.tiled import TiledWeight
+    d = cases.make_linear(202 + N, N, K, fmt="turbo", with_lora=False)
+    tw = TiledWeight.from_turbo(d["packed_indices"].to(dev), d["norms"].to(dev), d["centroids"].to(dev))
+    W = tw.dequantize().cpu()
+    assert torch.equal(W, O.turbo_tile(d["packed_indices"], d["norms"], d["centroids"], K))
+
+
+# ---- GLoRCQLinear.forward ------------------------------------------------------------------
+LIN = [
+    # N, K, rank, fmt, bits, groupsize, sym
+    (1408, 2048, 64, "gptq", 2, 128, False),     # expert gate/up projection
+    (2048, 1408, 64, "gptq", 2, 128, False),     # expert down projection, 11 groups
+    (5632, 2048, 64, "gptq", 2, 128, False),     # shared expert
+    (2048, 5632, 64, "gptq", 2, 128, True),
+    (2048, 2048, 128, "gptq", 4, 128, False),    # attention projection, 4-bit
+    (100, 392, 16, "gptq", 2, 128, False),       # ragged rows, K not a multiple of 128
+    (24, 128, 0, "gptq", 2, 128, False),
+    (1408, 2048, 64, "turbo", 2, 0, False),
+    (2048, 1408, 64, "turbo", 2, 0, False),
+    (52, 192, 16, "turbo", 2, 0, False),
+]
+
+
+@pytest.mark.parametrize("B", [1, 2, 5, 8, 13, 16, 33, 70])
+@pytest.mark.parametrize("N,K,rank,fmt,bits,gs,sym", LIN)
+def test_linear_forward(dev, N, K, rank, fmt, bits, gs, sym, B):
+    if B > 16 and N * K > 3_000_000:
+        pytest.skip("large batch only on the smaller shapes")
+    d = cases.make_linear(7 * N + K + B, N, K, rank=max(rank, 16), fmt=fmt, bits=bits, groupsize=gs or 128, sym=sym,
+                          with_lora=rank > 0)
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(N + K + 31 * B, B, K)
+    y = lin(x.to(dev)).cpu()
+    ref = O.linear_forward(cases.to_oracle_linear(d), x, x_rot_half=True)
+    assert y.dtype == torch.float16 and y.shape == ref.shape
+    assert cases.rel_l2(y, ref) <= REL
+    if rank > 0:
+        a = (x @ d["U"])
+        y2 = lin(x.to(dev), precomputed_xU=a.to(dev)).cpu()
+        assert cases.rel_l2(y2, ref) <= REL
+
+
+def test_linear_batch_dims_and_empty(dev):
+    d = cases.make_linear(5, 96, 256, rank=16)
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(6, 6, 256).reshape(2, 3, 256)
+    y = lin(x.to(dev))
+    assert y.shape == (2, 3, 96)
+    ref = O.linear_forward(cases.to_oracle_linear(d), x)
+    assert cases.rel_l2(y.cpu(), ref) <= REL
+    y0 = lin(torch.empty(0, 256, dtype=torch.float16, device=dev))
+    assert y0.shape == (0, 96)
+    torch.cuda.synchronize()
+
+
+def test_linear_turbo_with_rotation(dev):
+    d = cases.make_linear(21, 72, 256, rank=16, fmt="turbo")
+    g = torch.Generator().manual_seed(5021)
+    q, _ = torch.linalg.qr(torch.randn(256, 256, generator=g))
+    d["Pi"] = q.to(torch.float16)
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(1021, 4, 256)
+    ref = O.linear_forward(cases.to_oracle_linear(d), x, x_rot_half=True)
+    assert cases.rel_l2(lin(x.to(dev)).cpu(), ref) <= REL
+    xr = (x.float() @ d["Pi"].float().T).half()
+    assert cases.rel_l2(lin(x.to(dev), precomputed_x_rot=xr.to(dev)).cpu(), ref) <= REL
+
+
+def test_shared_u_is_tiled_once(dev):
+    from glorcq_b200 import tiled
+    blk = cases.make_moe(77, 256, 128, 4, 2, rank=16, experts_per_cluster=2)
+    shared = {}
+    lins = [cases.to_b200_linear(ex["gate_proj"], dev, shared) for ex in blk["experts"]]
+    assert lins[0]._ut is lins[1]._ut and lins[2]._ut is lins[3]._ut and lins[0]._ut is not lins[2]._ut
+    assert lins[0].U.data_ptr() == lins[1].U.data_ptr()
+
+
+def test_against_golden(dev, golden):
+    from tests.golden.make_golden import LINEAR_CASES
+    for name, kw, B in LINEAR_CASES:
+        d = cases.make_linear(**kw)
+        if d["fmt"] == "turbo":
+            gen = torch.Generator().manual_seed(kw["seed"] + 5000)
+            q, _ = torch.linalg.qr(torch.randn(kw["K"], kw["K"], generator=gen))
+            d["Pi"] = q.to(torch.float16)
+        lin = cases.to_b200_linear(d, dev)
+        x = cases.make_x(kw["seed"] + 1000, B, kw["K"])
+        y = lin(x.to(dev)).cpu()
+        assert cases.rel_l2(y, golden["linear"][name]["y"]) <= REL, name
+
+
+# ---- drop-ins for the reference's native modules ---------------------------------------------
+@pytest.mark.parametrize("B,N,K", [(1, 1408, 2048), (4, 2048, 1408), (5, 1408, 2048), (16, 4096, 4096),
+                                   (32, 512, 14336), (1, 64, 64), (3, 30, 36), (1, 2048, 5632), (8, 5632, 2048)])
+def test_turbo_dropin(dev, B, N, K):
+    import glorcq_b200.kernels as GK
+    g = torch.Generator().manual_seed(B * 1000 + N + K)
+    packed = torch.randint(0, 256, (N, K // 4), generator=g, dtype=torch.int32).to(torch.uint8)
+    norms = torch.randn(N, generator=g).abs() + 0.1
+    centroids = torch.randn(4, generator=g)
+    x = torch.randn(B, K, generator=g).half()
+    y = GK.turbo_dequant_matmul_fused(None, packed.to(dev), norms.to(dev), None, centroids.to(dev), 2, K,
+                                      precomputed_x_rot=x.to(dev))
+    ref = O.turbo_matmul(x, packed, norms, centroids)
+    assert y.dtype == torch.float16 and tuple(y.shape) == (B, N)
+    assert cases.rel_l2(y.cpu(), ref) <= REL
+
+
+def test_turbo_dropin_empty_batch(dev):
+    import glorcq_b200.kernels as GK
+    packed = torch.zeros(8, 16, dtype=torch.uint8, device=dev)
+    y = GK.turbo_dequant_matmul(torch.empty(0, 64, dtype=torch.float16, device=dev), packed,
+                                torch.ones(8, device=dev), torch.ones(4, device=dev))
+    assert tuple(y.shape) == (0, 8)
+    torch.cuda.synchronize()      # the context stays healthy
+    with pytest.raises(RuntimeError):
+        GK.turbo_dequant_matmul(torch.empty(1, 64, dtype=torch.float32, device=dev), packed,
+                                torch.ones(8, device=dev), torch.ones(4, device=dev))
+
+
+@pytest.mark.parametrize("E,n_out,K", [(3, 16, 128), (60, 2048, 1408), (5, 100, 256)])
+def test_turbo_grouped_dropin(dev, E, n_out, K):
+    import glorcq_b200.kernels as GK
+    d = cases.make_linear(43 + E, E * n_out, K, fmt="turbo", with_lora=False)
+    x = cases.make_x(44 + E, E, K)
+    y = GK.turbo_dequant_grouped_gemv_fused(x.to(dev), d["packed_indices"].to(dev), d["norms"].to(dev),
+                                            d["centroids"].to(dev), n_out)
+    ref = O.turbo_grouped_gemv(x, d["packed_indices"], d["norms"], d["centroids"], n_out)
+    assert tuple(y.shape) == (E * n_out,)
+    assert cases.rel_l2(y.cpu(), ref) <= REL
+
+
+@pytest.mark.parametrize("B,N,K,sym,lora", [(1, 1408, 2048, False, False), (4, 2048, 1408, False, True),
+                                            (5, 100, 392, True, False), (9, 64, 256, False, True),
+                                            (0, 16, 128, False, False)])
+def test_gptq_i8_dropin(dev, B, N, K, sym, lora):
+    import glorcq_b200.kernels as GK
+    d = cases.make_linear(900 + N, N, K, fmt="gptq", with_lora=False, int_zeros=False, sym=sym, signed_codes=True)
+    x = cases.make_x(901, B, K, torch.float32)
+    lo = cases.make_x(902, B, N, torch.float32) * 0.1 if lora else torch.empty(0)
+    q8 = d["qweight_int"].to(torch.int8)
+    y = GK.gptq_dequant_matmul(x.to(dev), q8.to(dev), d["scales"].to(dev), d["zeros"].to(dev), 128, sym, lo.to(dev))
+    assert y.dtype == torch.float32 and tuple(y.shape) == (B, N)
+    if B:
+        ref = O.gptq_matmul(x, d["qweight_int"], d["scales"], d["zeros"], 128, sym, lo if lora else None)
+        assert cases.rel_l2(y.cpu(), ref) <= 1e-5
+        assert float((y.cpu() - ref).abs().max()) < 0.01
+        yh = GK.gptq_dequant_matmul_fused(x.half().to(dev), d["qweight_int"].to(dev), d["scales"].to(dev),
+                                          d["zeros"].to(dev), 128, sym)
+        assert yh.dtype == torch.float16
