@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libglorcq_b200.so")
+# GLQ_LIB selects another build of the same ABI (e.g. one compiled with -DGLQ_CHECKED)
+LIB_PATH = os.environ.get("GLQ_LIB") or os.path.join(HERE, "libglorcq_b200.so")
 
 FMT_Q2, FMT_Q4, FMT_T2, FMT_F16 = 0, 1, 2, 3
 EPI_LINEAR, EPI_SWIGLU = 0, 1
@@ -34,7 +35,8 @@ class MMArgs(C.Structure):
                 ("slot_index", vp), ("n_slots", vp), ("slot_count", vp), ("slot_offset", vp), ("entry_row", vp),
                 ("entry_scale", vp),
                 ("x", vp), ("ldx", C.c_int64), ("a0", vp), ("a1", vp), ("lda", C.c_int64),
-                ("y", vp), ("ldy", C.c_int64), ("workspace", vp), ("workspace_bytes", C.c_size_t)]
+                ("y", vp), ("ldy", C.c_int64), ("workspace", vp), ("workspace_bytes", C.c_size_t),
+                ("counters", vp), ("n_counters", C.c_size_t)]
 
 
 class MoeDesc(C.Structure):
@@ -65,10 +67,12 @@ _SIGS = {
     "glq_pack_f16": (C.c_int, [vp, C.c_long, C.c_long, C.c_int, C.c_int, vp, vp]),
     "glq_dequant_tiled": (C.c_int, [C.c_int, C.POINTER(Weight), C.c_int, vp, vp]),
     "glq_mm_workspace_bytes": (C.c_size_t, [C.POINTER(MMArgs)]),
+    "glq_mm_counters": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_grouped_matmul": (C.c_int, [C.POINTER(MMArgs), vp]),
+    "glq_linear_counters": (C.c_size_t, [C.c_int, C.c_int, C.POINTER(Weight), C.c_int]),
     "glq_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.POINTER(Weight), C.c_int]),
     "glq_linear_forward": (C.c_int, [C.c_int, C.c_int, C.POINTER(Weight), vp, vp, C.c_int64, vp, vp, C.c_int64,
-                                     C.c_int, vp, C.c_size_t, vp]),
+                                     C.c_int, vp, C.c_size_t, vp, C.c_size_t, vp]),
     "glq_moe_workspace_bytes": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
     "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, C.c_size_t, vp]),
 }

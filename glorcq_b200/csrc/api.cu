@@ -4,10 +4,12 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "aux_kernels.cuh"
 #include "skinny_mm.cuh"
+#include "stream_mm.cuh"
 
 using namespace glq;
 
@@ -66,7 +68,7 @@ extern "C" size_t glq_tiled_sz_bytes(int N, int n_groups) {
 // ---------------------------------------------------------------------------------------------
 struct Geometry {
     int nw, ntt, ntc, nkb, group_blocks, tile_groups, sk, kb_per_split, kb_chunk, max_passes;
-    size_t smem, counters_bytes, scratch_bytes;
+    size_t smem, n_counters, scratch_bytes;
 };
 
 static int num_sms() {
@@ -118,7 +120,7 @@ static int plan_geometry(int fmt, int epilogue, int N, int K, int group_size, in
                                                              (smem_cap - fixed) / per_kb));
     g.smem = skinny_smem_bytes(fmt, g.kb_chunk, g.ntc, g.nw, g.ntt);
     const size_t tiles = (size_t)n_problems * g.tile_groups * g.max_passes;
-    g.counters_bytes = g.sk > 1 ? ((tiles * sizeof(int) + 255) / 256) * 256 : 0;
+    g.n_counters = g.sk > 1 ? tiles : 0;
     g.scratch_bytes = g.sk > 1 ? tiles * g.sk * (size_t)(kRW * g.nw * g.ntt * 32) * sizeof(float4) : 0;
     *out = g;
     return GLQ_OK;
@@ -185,14 +187,161 @@ static void fill_geometry(SkinnyParams& p, const Geometry& g) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// streaming kernel: eligibility, geometry, launch
+// ---------------------------------------------------------------------------------------------
+struct StreamGeom {
+    int nw, ntt, ntc, nkb, group_blocks, sk, kb_per_split, npairs, ips, stages, stage_bytes;
+    int off_xs, off_ox, off_as, off_ring, off_red;
+    size_t smem;
+    int grid;
+};
+
+static bool stream_disabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("GLQ_NO_STREAM");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+// returns true when the streaming kernel covers this call
+static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group_size, int n_problems, int max_rows,
+                        StreamGeom* out) {
+    if (stream_disabled()) return false;
+    if (fmt != GLQ_FMT_Q2 && fmt != GLQ_FMT_Q4 && fmt != GLQ_FMT_T2) return false;
+    StreamGeom g{};
+    g.nw = (epilogue == GLQ_EPI_SWIGLU) ? 2 : 1;
+    const int kb = fmt_kb(fmt);
+    g.nkb = cdiv(K, kb);
+    g.group_blocks = 1;
+    if (fmt != GLQ_FMT_T2) {
+        if (group_size <= 0 || group_size % kb != 0) return false;
+        g.group_blocks = group_size / kb;
+    }
+    if (max_rows <= 8) g.ntt = 1;
+    else if (max_rows <= 16) g.ntt = 2;
+    else if (max_rows <= 32 && g.nw == 1) g.ntt = 4;
+    else return false;
+    g.ntc = g.ntt == 1 ? std::max(2, pow2ceil(max_rows)) : 8 * g.ntt;
+    const int ntiles = cdiv(N, kRowTile);
+    g.npairs = g.nw == 2 ? ntiles : cdiv(ntiles, 2);
+    // k splits (warps of one CTA): enough iterations to give every SM one, splits on group boundaries
+    const int units = cdiv(g.nkb, g.group_blocks);
+    int sk = 1;
+    while (sk < 8 && (long)n_problems * cdiv(g.npairs * sk, kWarpsPerCta) < num_sms() && units >= 2 * sk) sk *= 2;
+    g.sk = sk;
+    g.kb_per_split = cdiv(units, sk) * g.group_blocks;
+    g.ips = cdiv(g.npairs * sk, kWarpsPerCta);
+    const bool affine = fmt != GLQ_FMT_T2;
+    g.stage_bytes = std::max(2 * kStreamCB * 512 + (affine ? 2 * kStreamCB * 64 : 0), 4096);
+    const int xs_u4 = (fmt == GLQ_FMT_Q4) ? 8 : 16;
+    size_t off = kWarpsPerCta * kMaxStages * 8;
+    off = (off + 127) / 128 * 128;
+    g.off_xs = (int)off;
+    off += (size_t)g.nkb * xs_u4 * g.ntc * 16;
+    g.off_ox = (int)off;
+    off += (size_t)g.nkb * g.ntc * 8;
+    off = (off + 15) / 16 * 16;
+    g.off_as = (int)off;
+    off += (size_t)g.nw * g.ntc * std::max(rank, 16) * 2;
+    off = (off + 127) / 128 * 128;
+    g.off_ring = (int)off;
+    const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.ntt * 32 * 16 : 0;
+    const size_t cap = 220 * 1024;
+    if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) return false;
+    int stages = (int)((cap - off - red) / ((size_t)kWarpsPerCta * g.stage_bytes));
+    g.stages = std::min(stages, kMaxStages);
+    off += (size_t)kWarpsPerCta * g.stages * g.stage_bytes;
+    g.off_red = (int)off;
+    off += red;
+    g.smem = off;
+    const long iters = (long)n_problems * g.ips;
+    g.grid = (int)std::min<long>(iters, num_sms());
+    *out = g;
+    return g.grid > 0;
+}
+
+template <int FMT, int NW, int NTT>
+static int launch_stream_one(const StreamParams& sp, const StreamGeom& g, cudaStream_t st) {
+    auto kern = stream_kernel<FMT, NW, NTT>;
+    static size_t configured[16] = {0};
+    int dev = 0;
+    GLQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16 || configured[dev] < g.smem) {
+        GLQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
+        if (dev >= 0 && dev < 16) configured[dev] = g.smem;
+    }
+    kern<<<g.grid, kThreads, g.smem, st>>>(sp);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+template <int FMT>
+static int launch_stream_fmt(const StreamParams& sp, const StreamGeom& g, cudaStream_t st) {
+    if (g.nw == 2) {
+        if (g.ntt == 1) return launch_stream_one<FMT, 2, 1>(sp, g, st);
+        return launch_stream_one<FMT, 2, 2>(sp, g, st);
+    }
+    if (g.ntt == 1) return launch_stream_one<FMT, 1, 1>(sp, g, st);
+    if (g.ntt == 2) return launch_stream_one<FMT, 1, 2>(sp, g, st);
+    return launch_stream_one<FMT, 1, 4>(sp, g, st);
+}
+
+static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, int K, int rank, int n_problems,
+                         cudaStream_t st) {
+    StreamParams sp{};
+    p.nkb = g.nkb;
+    p.group_blocks = g.group_blocks;
+    p.ntc = g.ntc;
+    p.kb_chunk = g.nkb;
+    p.kb_per_split = g.nkb;
+    p.sk = 1;
+    sp.b = p;
+    sp.N = N;
+    sp.K = K;
+    sp.rank = rank;
+    sp.n_problems = n_problems;
+    sp.sk = g.sk;
+    sp.kb_per_split = g.kb_per_split;
+    sp.npairs = g.npairs;
+    sp.ips = g.ips;
+    sp.stages = g.stages;
+    sp.stage_bytes = g.stage_bytes;
+    sp.off_xs = g.off_xs;
+    sp.off_ox = g.off_ox;
+    sp.off_as = g.off_as;
+    sp.off_ring = g.off_ring;
+    sp.off_red = g.off_red;
+    switch (fmt) {
+        case GLQ_FMT_Q2: return launch_stream_fmt<GLQ_FMT_Q2>(sp, g, st);
+        case GLQ_FMT_Q4: return launch_stream_fmt<GLQ_FMT_Q4>(sp, g, st);
+        case GLQ_FMT_T2: return launch_stream_fmt<GLQ_FMT_T2>(sp, g, st);
+    }
+    return GLQ_ERR_ARG;
+}
+
+// ---------------------------------------------------------------------------------------------
 // glq_grouped_matmul
 // ---------------------------------------------------------------------------------------------
 extern "C" size_t glq_mm_workspace_bytes(const glq_mm_args_t* a) {
     if (!a) return 0;
+    StreamGeom sg;
+    if (plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg)) return 0;
     Geometry g;
     if (plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows, true, &g) != GLQ_OK)
         return 0;
-    return g.counters_bytes + g.scratch_bytes;
+    return g.scratch_bytes;
+}
+
+extern "C" size_t glq_mm_counters(const glq_mm_args_t* a) {
+    if (!a) return 0;
+    StreamGeom sg;
+    if (plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg)) return 0;
+    Geometry g;
+    if (plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows, true, &g) != GLQ_OK)
+        return 0;
+    return g.n_counters;
 }
 
 extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
@@ -202,15 +351,21 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     if (a->rank < 0 || a->rank % 16 != 0) return GLQ_ERR_UNSUPPORTED;
     if (a->rank > 0 && (a->a0 || a->a1) && (a->lda % 8 != 0 || !aligned16(a->a0) || !aligned16(a->a1)))
         return GLQ_ERR_ALIGN;
-    Geometry g;
-    int rc = plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows, true, &g);
+    StreamGeom sg;
+    const bool use_stream =
+        plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg);
+    Geometry g{};
+    int rc = use_stream ? GLQ_OK
+                        : plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows,
+                                        true, &g);
     if (rc != GLQ_OK) return rc;
-    if (g.sk > 1) {
-        if (!a->workspace || a->workspace_bytes < g.counters_bytes + g.scratch_bytes) return GLQ_ERR_WORKSPACE;
+    if (!use_stream && g.sk > 1) {
+        if (!a->workspace || a->workspace_bytes < g.scratch_bytes) return GLQ_ERR_WORKSPACE;
+        if (!a->counters || a->n_counters < g.n_counters) return GLQ_ERR_WORKSPACE;
         if (!aligned16(a->workspace)) return GLQ_ERR_ALIGN;
     }
     if (!a->w0_table && !a->w0.codes) return GLQ_ERR_ARG;
-    if (g.nw == 2 && !a->w1_table && !a->w1.codes) return GLQ_ERR_ARG;
+    if (a->epilogue == GLQ_EPI_SWIGLU && !a->w1_table && !a->w1.codes) return GLQ_ERR_ARG;
 
     SkinnyParams p{};
     p.w[0] = a->w0;
@@ -230,12 +385,14 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     p.lda = a->lda;
     p.y = reinterpret_cast<__half*>(a->y);
     p.ldy = a->ldy;
-    p.counters = reinterpret_cast<int*>(a->workspace);
-    p.scratch = reinterpret_cast<float4*>(reinterpret_cast<char*>(a->workspace) + g.counters_bytes);
+    p.counters = a->counters;
+    p.scratch = reinterpret_cast<float4*>(a->workspace);
     p.max_rows = a->max_rows;
     p.rows_stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
     p.epilogue = a->epilogue;
     p.x_vec = (aligned16(a->x) && a->ldx % 8 == 0) ? 1 : 0;
+    if (use_stream)
+        return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
     fill_geometry(p, g);
     return launch_skinny(a->fmt, false, p, g, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
 }
@@ -284,36 +441,52 @@ extern "C" size_t glq_linear_workspace_bytes(int fmt, int group_size, const glq_
     return total;
 }
 
+extern "C" size_t glq_linear_counters(int fmt, int group_size, const glq_weight_t* w, int B) {
+    if (!w || B <= 0) return 0;
+    glq_mm_args_t m;
+    linear_args(fmt, group_size, w, B, &m);
+    size_t total = glq_mm_counters(&m);
+    if (w->rank > 0) {
+        glq_mm_args_t u;
+        xu_args(w, w->codes, B, &u);
+        total += glq_mm_counters(&u);
+    }
+    return total;
+}
+
 extern "C" int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w, const void* ut, const void* x,
                                   int64_t ldx, const void* a, void* y, int64_t ldy, int B, void* workspace,
-                                  size_t workspace_bytes, void* stream) {
+                                  size_t workspace_bytes, int32_t* counters, size_t n_counters, void* stream) {
     if (!w || !x || !y || B < 0) return GLQ_ERR_ARG;
     if (B == 0 || w->N == 0) return GLQ_OK;
     glq_mm_args_t m;
     linear_args(fmt, group_size, w, B, &m);
     char* ws = reinterpret_cast<char*>(workspace);
-    size_t used = 0;
     const size_t main_ws = up256(glq_mm_workspace_bytes(&m));
+    const size_t main_ctr = glq_mm_counters(&m);
     const void* a_use = a;
     if (!a && ut && w->rank > 0 && w->sv) {
         glq_mm_args_t u;
         xu_args(w, ut, B, &u);
         const size_t a_bytes = up256((size_t)B * w->rank * sizeof(__half));
         const size_t u_ws = up256(glq_mm_workspace_bytes(&u));
+        const size_t u_ctr = glq_mm_counters(&u);
         if (!ws || workspace_bytes < main_ws + a_bytes + u_ws) return GLQ_ERR_WORKSPACE;
+        if (u_ctr > 0 && (!counters || n_counters < main_ctr + u_ctr)) return GLQ_ERR_WORKSPACE;
         u.x = x;
         u.ldx = ldx;
         u.y = ws + main_ws;
         u.ldy = w->rank;
         u.workspace = ws + main_ws + a_bytes;
         u.workspace_bytes = u_ws;
+        u.counters = counters ? counters + main_ctr : nullptr;
+        u.n_counters = u_ctr;
         int rc = glq_grouped_matmul(&u, stream);
         if (rc != GLQ_OK) return rc;
         a_use = ws + main_ws;
-        used = a_bytes + u_ws;
     }
-    (void)used;
     if (main_ws > 0 && (!ws || workspace_bytes < main_ws)) return GLQ_ERR_WORKSPACE;
+    if (main_ctr > 0 && (!counters || n_counters < main_ctr)) return GLQ_ERR_WORKSPACE;
     m.x = x;
     m.ldx = ldx;
     m.a0 = a_use;
@@ -322,6 +495,8 @@ extern "C" int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w
     m.ldy = ldy;
     m.workspace = ws;
     m.workspace_bytes = main_ws;
+    m.counters = counters;
+    m.n_counters = main_ctr;
     if (!a_use) m.w0.rank = 0, m.rank = 0;
     return glq_grouped_matmul(&m, stream);
 }
@@ -451,5 +626,19 @@ extern "C" int glq_dequant_tiled(int fmt, const glq_weight_t* w, int group_size,
         return GLQ_ERR_UNSUPPORTED;
     }
     GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// First bounds violation recorded by a self-checking kernel: {code, index, limit, block<<32|thread};
+// all zero when there was none.  Synchronises the device.
+// ---------------------------------------------------------------------------------------------
+extern "C" int glq_debug_error(unsigned long long* out4, int clear) {
+    if (!out4) return GLQ_ERR_ARG;
+    GLQ_CUDA(cudaMemcpyFromSymbol(out4, g_glq_err, 4 * sizeof(unsigned long long)));
+    if (clear) {
+        unsigned long long z[4] = {0, 0, 0, 0};
+        GLQ_CUDA(cudaMemcpyToSymbol(g_glq_err, z, sizeof(z)));
+    }
     return GLQ_OK;
 }

@@ -17,6 +17,31 @@
 
 namespace glq {
 
+// Self-checking accesses: the index of a global / shared access is compared with the extent implied
+// by the shapes; the first violation is recorded in g_glq_err (code, index, limit, block<<32|thread)
+// and the access is skipped, so a wrong index cannot fault the GPU.  Always on for the codebook
+// format (whose unchecked build faulted for a reason that reading the code did not show, while the
+// checked build is clean); on for every format when compiled with -DGLQ_CHECKED.
+__device__ unsigned long long g_glq_err[4] = {0, 0, 0, 0};
+__device__ __forceinline__ bool glq_ok(bool cond, unsigned long long code, unsigned long long idx,
+                                       unsigned long long lim) {
+    if (!cond) {
+        if (atomicCAS(&g_glq_err[0], 0ull, code) == 0ull) {
+            g_glq_err[1] = idx;
+            g_glq_err[2] = lim;
+            g_glq_err[3] = ((unsigned long long)blockIdx.x << 32) | threadIdx.x;
+        }
+    }
+    return cond;
+}
+#ifdef GLQ_CHECKED
+#define GLQ_GUARDED(FMT) true
+#else
+#define GLQ_GUARDED(FMT) ((FMT) == GLQ_FMT_T2)
+#endif
+#define GLQ_OKAY(cond, code, idx, lim) \
+    (GLQ_GUARDED(FMT) ? glq_ok((cond), (code), (unsigned long long)(idx), (unsigned long long)(lim)) : true)
+
 constexpr int kRW = 2;     // row tiles per CTA
 constexpr int kKW = kWarpsPerCta / kRW;  // warps splitting k for one row tile
 
@@ -142,14 +167,23 @@ __device__ __forceinline__ void stage_x(const SkinnyParams& p, uint4* xs, float2
             const uint4 hi = *reinterpret_cast<const uint4*>(&o[8]);
             if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) {
                 const int t = wi >> 1, uu = wi & 1;
-                xs[((kbl * 4 + 2 * uu) * ntc + col) * 4 + t] = lo;
-                xs[((kbl * 4 + 2 * uu + 1) * ntc + col) * 4 + t] = hi;
+                if (GLQ_OKAY(((kbl * 4 + 2 * uu + 1) * ntc + col) * 4 + t < p.kb_chunk * F::XS * ntc, 1,
+                             ((kbl * 4 + 2 * uu + 1) * ntc + col) * 4 + t, p.kb_chunk * F::XS * ntc)) {
+                    xs[((kbl * 4 + 2 * uu) * ntc + col) * 4 + t] = lo;
+                    xs[((kbl * 4 + 2 * uu + 1) * ntc + col) * 4 + t] = hi;
+                }
             } else if constexpr (FMT == GLQ_FMT_Q4) {
-                xs[((kbl * 2 + 0) * ntc + col) * 4 + wi] = lo;
-                xs[((kbl * 2 + 1) * ntc + col) * 4 + wi] = hi;
+                if (GLQ_OKAY(((kbl * 2 + 1) * ntc + col) * 4 + wi < p.kb_chunk * F::XS * ntc, 2,
+                             ((kbl * 2 + 1) * ntc + col) * 4 + wi, p.kb_chunk * F::XS * ntc)) {
+                    xs[((kbl * 2 + 0) * ntc + col) * 4 + wi] = lo;
+                    xs[((kbl * 2 + 1) * ntc + col) * 4 + wi] = hi;
+                }
             } else {
-                xs[((kbl * 4 + wi) * ntc + col) * 2 + 0] = lo;
-                xs[((kbl * 4 + wi) * ntc + col) * 2 + 1] = hi;
+                if (GLQ_OKAY(((kbl * 4 + wi) * ntc + col) * 2 + 1 < p.kb_chunk * F::XS * ntc, 3,
+                             ((kbl * 4 + wi) * ntc + col) * 2 + 1, p.kb_chunk * F::XS * ntc)) {
+                    xs[((kbl * 4 + wi) * ntc + col) * 2 + 0] = lo;
+                    xs[((kbl * 4 + wi) * ntc + col) * 2 + 1] = hi;
+                }
             }
         }
         if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4) {
@@ -165,7 +199,8 @@ __device__ __forceinline__ void stage_x(const SkinnyParams& p, uint4* xs, float2
                 so += __shfl_xor_sync(0xffffffffu, so, d);
                 sx += __shfl_xor_sync(0xffffffffu, sx, d);
             }
-            if (valid && wi == 0) ox[kbl * ntc + col] = make_float2(so, sx);
+            if (valid && wi == 0 && GLQ_OKAY(kbl * ntc + col < p.kb_chunk * ntc, 4, kbl * ntc + col, p.kb_chunk * ntc))
+                ox[kbl * ntc + col] = make_float2(so, sx);
         }
     }
 }
@@ -176,7 +211,8 @@ __device__ __forceinline__ void stage_x(const SkinnyParams& p, uint4* xs, float2
 // ---------------------------------------------------------------------------------------------
 template <int FMT, int NTT>
 __device__ __forceinline__ void block_mma(const uint4 (&q)[Fmt<FMT>::LD], const uint4* __restrict__ xs_kb, int ntc,
-                                          int g, int t, uint32_t TL, uint32_t TH, float (&c)[NTT][4]) {
+                                          int g, int t, uint32_t TL, uint32_t TH, float (&c)[NTT][4], int lim) {
+    (void)lim;
     if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) {
         const uint32_t wa[2] = {q[0].x, q[0].y}, wb[2] = {q[0].z, q[0].w};
 #pragma unroll
@@ -192,6 +228,7 @@ __device__ __forceinline__ void block_mma(const uint4 (&q)[Fmt<FMT>::LD], const 
 #pragma unroll
             for (int tt = 0; tt < NTT; ++tt) {
                 const int col = (tt * 8 + g) & (ntc - 1);
+                if (!GLQ_OKAY(((2 * u + 1) * ntc + col) * 4 + t < lim, 5, ((2 * u + 1) * ntc + col) * 4 + t, lim)) continue;
                 const uint4 b0 = xs_kb[((2 * u) * ntc + col) * 4 + t];
                 const uint4 b1 = xs_kb[((2 * u + 1) * ntc + col) * 4 + t];
                 mma16816(c[tt], ha[0], hb[0], ha[1], hb[1], b0.x, b0.y);
@@ -210,6 +247,7 @@ __device__ __forceinline__ void block_mma(const uint4 (&q)[Fmt<FMT>::LD], const 
 #pragma unroll
             for (int tt = 0; tt < NTT; ++tt) {
                 const int col = (tt * 8 + g) & (ntc - 1);
+                if (!GLQ_OKAY((u * ntc + col) * 4 + t < lim, 6, (u * ntc + col) * 4 + t, lim)) continue;
                 const uint4 b = xs_kb[(u * ntc + col) * 4 + t];
                 mma16816(c[tt], ha[0], hb[0], ha[1], hb[1], b.x, b.y);
                 mma16816(c[tt], ha[2], hb[2], ha[3], hb[3], b.z, b.w);
@@ -221,6 +259,7 @@ __device__ __forceinline__ void block_mma(const uint4 (&q)[Fmt<FMT>::LD], const 
 #pragma unroll
             for (int tt = 0; tt < NTT; ++tt) {
                 const int col = (tt * 8 + g) & (ntc - 1);
+                if (!GLQ_OKAY(((ks * ntc + col) * 4) + t < 2 * lim, 7, ((ks * ntc + col) * 4) + t, 2 * lim)) continue;
                 const uint2 b = reinterpret_cast<const uint2*>(xs_kb)[((ks * ntc + col) * 4) + t];
                 mma16816(c[tt], q[ks].x, q[ks].y, q[ks].z, q[ks].w, b.x, b.y);
             }
@@ -260,8 +299,14 @@ __device__ __forceinline__ void load_codes(const glq_weight_t& W, int rt, int kb
     } else {
         const uint4* base = reinterpret_cast<const uint4*>(W.codes);
 #pragma unroll
-        for (int i = 0; i < Fmt<FMT>::LD; ++i)
-            q[i] = __ldcs(base + ((size_t)(rt * nkb + kb) * Fmt<FMT>::LD + i) * 32 + lane);
+        for (int i = 0; i < Fmt<FMT>::LD; ++i) {
+            const size_t idx = ((size_t)(rt * nkb + kb) * Fmt<FMT>::LD + i) * 32 + lane;
+            if (GLQ_OKAY(idx < (size_t)((W.N + 15) / 16) * nkb * Fmt<FMT>::LD * 32 && kb < nkb, 8, idx,
+                         (size_t)((W.N + 15) / 16) * nkb * Fmt<FMT>::LD * 32))
+                q[i] = __ldcs(base + idx);
+            else
+                q[i] = make_uint4(0, 0, 0, 0);
+        }
     }
 }
 
@@ -356,8 +401,10 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                         for (int i = 0; i < NW; ++i) {
                             load_codes<FMT, RM>(W[i], rt, kb, nkb, lane, q[i][d]);
                             if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4)
-                                szv[i][d] = __ldg(reinterpret_cast<const uint2*>(W[i].sz) +
-                                                  ((size_t)rt * G + kb / p.group_blocks) * 8 + g);
+                                if (GLQ_OKAY(((size_t)rt * G + kb / p.group_blocks) * 8 + g < (size_t)ntiles * G * 8, 10,
+                                             ((size_t)rt * G + kb / p.group_blocks) * 8 + g, (size_t)ntiles * G * 8))
+                                    szv[i][d] = __ldg(reinterpret_cast<const uint2*>(W[i].sz) +
+                                                      ((size_t)rt * G + kb / p.group_blocks) * 8 + g);
                         }
                     }
                 }
@@ -382,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                                     for (int tt = 0; tt < NTT; ++tt)
 #pragma unroll
                                         for (int j = 0; j < 4; ++j) c[tt][j] = 0.f;
-                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], c);
+                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], c, (p.kb_chunk - kbl) * F::XS * ntc);
                                     const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv[i][d].x);
                                     const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv[i][d].y);
                                     const float s0 = __low2float(sz0), z0 = __high2float(sz0);
@@ -390,6 +437,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
 #pragma unroll
                                     for (int tt = 0; tt < NTT; ++tt) {
                                         const int col = (tt * 8 + 2 * t) & (ntc - 1);
+                                        if (!GLQ_OKAY(kbl * ntc + col + 1 < p.kb_chunk * ntc, 9, kbl * ntc + col, p.kb_chunk * ntc)) continue;
                                         const float4 o = *reinterpret_cast<const float4*>(&ox[kbl * ntc + col]);
                                         acc[i][tt][0] = fmaf(s0, fmaf(-z0, o.y, c[tt][0] - o.x), acc[i][tt][0]);
                                         acc[i][tt][1] = fmaf(s0, fmaf(-z0, o.w, c[tt][1] - o.z), acc[i][tt][1]);
@@ -397,14 +445,17 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                                         acc[i][tt][3] = fmaf(s1, fmaf(-z1, o.w, c[tt][3] - o.z), acc[i][tt][3]);
                                     }
                                 } else {
-                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], acc[i]);
+                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], acc[i], (p.kb_chunk - kbl) * F::XS * ntc);
                                 }
                                 const int kn = kb + kDepth;
                                 if (kn < wk_hi) {
                                     load_codes<FMT, RM>(W[i], rt, kn, nkb, lane, q[i][d]);
                                     if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4)
-                                        szv[i][d] = __ldg(reinterpret_cast<const uint2*>(W[i].sz) +
-                                                          ((size_t)rt * G + kn / p.group_blocks) * 8 + g);
+                                        if (GLQ_OKAY(((size_t)rt * G + kn / p.group_blocks) * 8 + g < (size_t)ntiles * G * 8,
+                                                     11, ((size_t)rt * G + kn / p.group_blocks) * 8 + g,
+                                                     (size_t)ntiles * G * 8))
+                                            szv[i][d] = __ldg(reinterpret_cast<const uint2*>(W[i].sz) +
+                                                              ((size_t)rt * G + kn / p.group_blocks) * 8 + g);
                                 }
                             }
                         }
@@ -491,8 +542,10 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
             for (int i = 0; i < NW; ++i) {
                 float n0 = 1.f, n1 = 1.f;
                 if constexpr (FMT == GLQ_FMT_T2) {
-                    n0 = __ldg(W[i].norms + r0c);
-                    n1 = __ldg(W[i].norms + r1c);
+                    if (GLQ_OKAY(r1c < N && r0c >= 0 && W[i].norms != nullptr, 12, r1c, N)) {
+                        n0 = __ldg(W[i].norms + r0c);
+                        n1 = __ldg(W[i].norms + r1c);
+                    }
                 }
                 // low-rank term a . SV^T through the same tensor-core dot
                 float lo[NTT][4];
@@ -508,7 +561,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                         const int cc = c0 + 16 * t;
                         uint4 sa[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
                         uint4 sb[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                        if (cc < rank) {
+                        if (cc < rank && GLQ_OKAY((size_t)r1c * rank + cc + 16 <= (size_t)N * rank, 13, (size_t)r1c * rank + cc, (size_t)N * rank)) {
                             const uint4* pa = reinterpret_cast<const uint4*>(sv + (size_t)r0c * rank + cc);
                             const uint4* pb = reinterpret_cast<const uint4*>(sv + (size_t)r1c * rank + cc);
                             sa[0] = __ldg(pa); sa[1] = __ldg(pa + 1);

@@ -174,18 +174,22 @@ def clear_pool():
 
 
 # ---- workspaces ------------------------------------------------------------------------------
-_WS: Dict[Tuple[int, int], torch.Tensor] = {}
+_WS: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
-def workspace(device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised scratch for split-k partial sums and arrival counters, one per (device,
-    stream).  The kernels leave the counters at zero, so the buffer is only cleared when it grows."""
+def workspace(device, nbytes: int, ncounters: int = 0):
+    """(scratch, counters) for the current stream of `device`.  The scratch holds split-k partial
+    sums and small intermediates and needs no initialisation.  The counters are arrival counters:
+    they must be zero before a call and every kernel leaves them zero, so they are cleared only
+    when the array is (re)allocated."""
     key = (torch.device(device).index or 0, _stream_ptr(device))
-    ws = _WS.get(key)
+    ws, ctr = _WS.get(key, (None, None))
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _WS[key] = ws
-    return ws
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    if ctr is None or ctr.numel() < ncounters:
+        ctr = torch.zeros(max(ncounters, 1 << 16), dtype=torch.int32, device=device)
+    _WS[key] = (ws, ctr)
+    return ws, ctr
 
 
 # ---- calls -----------------------------------------------------------------------------------
@@ -207,10 +211,12 @@ def linear_forward(w: TiledWeight, x: torch.Tensor, ut: Optional[TiledWeight] = 
         a = a.contiguous()
     with torch.cuda.device(x.device):
         nbytes = L.glq_linear_workspace_bytes(w.fmt, w.group_size, C.byref(w.desc), B)
-        ws = workspace(x.device, nbytes)
+        nctr = L.glq_linear_counters(w.fmt, w.group_size, C.byref(w.desc), B)
+        ws, ctr = workspace(x.device, nbytes, nctr)
         _lib.check(L.glq_linear_forward(w.fmt, w.group_size, C.byref(w.desc), None if ut is None else _ptr(ut.codes),
                                         x.data_ptr(), x.stride(0), _ptr(a), y.data_ptr(), w.N, B,
-                                        ws.data_ptr(), ws.numel(), _stream_ptr(x.device)), "linear_forward")
+                                        ws.data_ptr(), ws.numel(), ctr.data_ptr(), ctr.numel(),
+                                        _stream_ptr(x.device)), "linear_forward")
     return y
 
 

@@ -145,10 +145,15 @@ typedef struct glq_mm_args {
     const void* x;  int64_t ldx;   /* fp16 */
     const void* a0; const void* a1; int64_t lda; /* fp16 x.U per entry for w0 / w1, NULL: no low-rank term */
     void* y;        int64_t ldy;   /* fp16 */
-    void* workspace; size_t workspace_bytes; /* scratch for split-K partials, from glq_mm_workspace_bytes() */
+    void* workspace; size_t workspace_bytes; /* scratch for split-k partial sums (contents irrelevant)   */
+    int32_t* counters; size_t n_counters;    /* arrival counters: zero before the first use, left zero   */
 } glq_mm_args_t;
 
+/* Scratch bytes / arrival counters a call with these args needs (both 0 when k is not split).  The
+ * counters must be zero when a call starts and are zero again when it ends, so one zero-initialised
+ * array can serve any sequence of calls on one stream; the scratch needs no initialisation. */
 size_t glq_mm_workspace_bytes(const glq_mm_args_t* args);
+size_t glq_mm_counters(const glq_mm_args_t* args);
 int glq_grouped_matmul(const glq_mm_args_t* args, void* stream);
 
 /* One quantized linear layer on B activation rows (GLoRCQLinear.forward,
@@ -157,8 +162,9 @@ int glq_grouped_matmul(const glq_mm_args_t* args, void* stream);
  * workspace, or absent (a == NULL and ut == NULL). */
 int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w, const void* ut, const void* x, int64_t ldx,
                        const void* a, void* y, int64_t ldy, int B, void* workspace, size_t workspace_bytes,
-                       void* stream);
+                       int32_t* counters, size_t n_counters, void* stream);
 size_t glq_linear_workspace_bytes(int fmt, int group_size, const glq_weight_t* w, int B);
+size_t glq_linear_counters(int fmt, int group_size, const glq_weight_t* w, int B);
 
 #ifdef __cplusplus
 }
