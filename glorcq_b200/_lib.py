@@ -22,7 +22,7 @@ vp = C.c_void_p
 
 class Weight(C.Structure):
     """glq_weight_t"""
-    _fields_ = [("codes", vp), ("sz", vp), ("norms", vp), ("centroids", vp), ("sv", vp), ("bias", vp),
+    _fields_ = [("codes", vp), ("reserved0", vp), ("norms", vp), ("centroids", vp), ("sv", vp), ("bias", vp),
                 ("N", C.c_int32), ("K", C.c_int32), ("rank", C.c_int32), ("reserved", C.c_int32)]
 
 
@@ -31,7 +31,7 @@ class MMArgs(C.Structure):
     _fields_ = [("fmt", C.c_int32), ("group_size", C.c_int32), ("epilogue", C.c_int32), ("n_problems", C.c_int32),
                 ("max_rows", C.c_int32), ("rows_stride", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
                 ("rank", C.c_int32), ("reserved", C.c_int32),
-                ("w0", Weight), ("w1", Weight), ("w0_table", vp), ("w1_table", vp),
+                ("w", Weight), ("w_table", vp),
                 ("slot_index", vp), ("n_slots", vp), ("slot_count", vp), ("slot_offset", vp), ("entry_row", vp),
                 ("entry_scale", vp),
                 ("x", vp), ("ldx", C.c_int64), ("a0", vp), ("a1", vp), ("lda", C.c_int64),
@@ -59,13 +59,17 @@ _SIGS = {
     "glq_turbo_dequant_grouped_gemv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
     "glq_gptq_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_int, vp]),
-    "glq_tiled_codes_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
-    "glq_tiled_sz_bytes": (C.c_size_t, [C.c_int, C.c_int]),
-    "glq_pack_codes_i32": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp]),
-    "glq_pack_codes_u8": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
-    "glq_pack_sz": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, vp]),
+    "glq_tiled_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "glq_sv_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "glq_rows_f32_count": (C.c_size_t, [C.c_int, C.c_int]),
+    "glq_tiled_f16_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "glq_pack_gptq": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, C.c_int, C.c_int, vp]),
+    "glq_pack_turbo": (C.c_int, [vp, C.c_int, C.c_int, vp, C.c_int, C.c_int, vp]),
+    "glq_pack_rows_f32": (C.c_int, [vp, C.c_int, vp, C.c_int, C.c_int, vp]),
+    "glq_pack_sv": (C.c_int, [vp, C.c_int, C.c_int, vp, C.c_int, C.c_int, vp]),
     "glq_pack_f16": (C.c_int, [vp, C.c_long, C.c_long, C.c_int, C.c_int, vp, vp]),
-    "glq_dequant_tiled": (C.c_int, [C.c_int, C.POINTER(Weight), C.c_int, vp, vp]),
+    "glq_dequant_tiled": (C.c_int, [C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
+    "glq_debug_error": (C.c_int, [vp, C.c_int]),
     "glq_mm_workspace_bytes": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_mm_counters": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_grouped_matmul": (C.c_int, [C.POINTER(MMArgs), vp]),

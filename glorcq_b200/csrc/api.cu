@@ -52,15 +52,23 @@ extern "C" int glq_last_cuda_error(void) { return g_last_cuda_error; }
 // tiled layout sizes
 // ---------------------------------------------------------------------------------------------
 static inline int fmt_kb(int fmt) { return (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_T2) ? 128 : 64; }
-static inline int fmt_ld(int fmt) { return fmt == GLQ_FMT_F16 ? 4 : 1; }
+static inline int dest_pairs(int n_rows, int count) { return (cdiv(n_rows, 16) * count + 1) / 2; }
 
-extern "C" size_t glq_tiled_codes_bytes(int fmt, int N, int K) {
-    if (fmt < 0 || fmt > 3 || N <= 0 || K <= 0) return 0;
-    return (size_t)cdiv(N, 16) * cdiv(K, fmt_kb(fmt)) * fmt_ld(fmt) * 512;
+extern "C" size_t glq_tiled_bytes(int fmt, int n_rows, int K, int count) {
+    if (fmt < 0 || fmt > 2 || n_rows <= 0 || K <= 0 || count < 1 || count > 2) return 0;
+    return (size_t)dest_pairs(n_rows, count) * cdiv(K, fmt_kb(fmt)) * 2 * block_bytes_of(fmt);
 }
-extern "C" size_t glq_tiled_sz_bytes(int N, int n_groups) {
-    if (N <= 0 || n_groups <= 0) return 0;
-    return (size_t)cdiv(N, 16) * n_groups * 64;
+extern "C" size_t glq_sv_bytes(int n_rows, int rank, int count) {
+    if (n_rows <= 0 || rank <= 0 || count < 1 || count > 2) return 0;
+    return (size_t)dest_pairs(n_rows, count) * cdiv(rank, 64) * 4096;
+}
+extern "C" size_t glq_rows_f32_count(int n_rows, int count) {
+    if (n_rows <= 0 || count < 1 || count > 2) return 0;
+    return (size_t)dest_pairs(n_rows, count) * 32;
+}
+extern "C" size_t glq_tiled_f16_bytes(int N, int K) {
+    if (N <= 0 || K <= 0) return 0;
+    return (size_t)cdiv(N, 16) * cdiv(K, 64) * 4 * 512;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -190,7 +198,7 @@ static void fill_geometry(SkinnyParams& p, const Geometry& g) {
 // streaming kernel: eligibility, geometry, launch
 // ---------------------------------------------------------------------------------------------
 struct StreamGeom {
-    int nw, ntt, ntc, nkb, group_blocks, sk, kb_per_split, npairs, ips, stages, stage_bytes;
+    int i8, nt, ntc, nkb, sk, kb_per_split, npairs, ips, stages, stage_bytes, swiglu;
     int off_xs, off_ox, off_as, off_ring, off_red;
     size_t smem;
     int grid;
@@ -204,50 +212,76 @@ static bool stream_disabled() {
     }
     return v == 1;
 }
+static bool i8_disabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("GLQ_NO_I8");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
 
 // returns true when the streaming kernel covers this call
 static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group_size, int n_problems, int max_rows,
                         StreamGeom* out) {
     if (stream_disabled()) return false;
     if (fmt != GLQ_FMT_Q2 && fmt != GLQ_FMT_Q4 && fmt != GLQ_FMT_T2) return false;
+    if (N <= 0 || K <= 0 || n_problems <= 0 || max_rows <= 0 || rank < 0 || rank % 16 != 0) return false;
     StreamGeom g{};
-    g.nw = (epilogue == GLQ_EPI_SWIGLU) ? 2 : 1;
+    g.swiglu = (epilogue == GLQ_EPI_SWIGLU) ? 1 : 0;
     const int kb = fmt_kb(fmt);
     g.nkb = cdiv(K, kb);
-    g.group_blocks = 1;
+    int group_blocks = 1;
     if (fmt != GLQ_FMT_T2) {
         if (group_size <= 0 || group_size % kb != 0) return false;
-        g.group_blocks = group_size / kb;
+        group_blocks = group_size / kb;
     }
-    if (max_rows <= 8) g.ntt = 1;
-    else if (max_rows <= 16) g.ntt = 2;
-    else if (max_rows <= 32 && g.nw == 1) g.ntt = 4;
-    else return false;
-    g.ntc = g.ntt == 1 ? std::max(2, pow2ceil(max_rows)) : 8 * g.ntt;
+    const bool affine = fmt != GLQ_FMT_T2;
+    int rows;
+    if (affine && max_rows <= 8 && !i8_disabled()) {
+        g.i8 = 1;
+        g.nt = max_rows <= 4 ? 1 : 2;
+        rows = 4 * g.nt;
+        g.ntc = 8 * g.nt;
+    } else {
+        g.i8 = 0;
+        if (max_rows <= 8) g.nt = 1;
+        else if (max_rows <= 16) g.nt = 2;
+        else if (max_rows <= 32) g.nt = 4;
+        else return false;
+        rows = 8 * g.nt;
+        g.ntc = g.nt == 1 ? std::max(2, pow2ceil(max_rows)) : 8 * g.nt;
+    }
     const int ntiles = cdiv(N, kRowTile);
-    g.npairs = g.nw == 2 ? ntiles : cdiv(ntiles, 2);
-    // k splits (warps of one CTA): enough iterations to give every SM one, splits on group boundaries
-    const int units = cdiv(g.nkb, g.group_blocks);
+    g.npairs = g.swiglu ? ntiles : cdiv(ntiles, 2);
+    // k splits (warps of one CTA): enough iterations to give every SM one; splits on group boundaries
+    const int units = cdiv(g.nkb, group_blocks);
     int sk = 1;
     while (sk < 8 && (long)n_problems * cdiv(g.npairs * sk, kWarpsPerCta) < num_sms() && units >= 2 * sk) sk *= 2;
     g.sk = sk;
-    g.kb_per_split = cdiv(units, sk) * g.group_blocks;
+    g.kb_per_split = cdiv(units, sk) * group_blocks;
     g.ips = cdiv(g.npairs * sk, kWarpsPerCta);
-    const bool affine = fmt != GLQ_FMT_T2;
-    g.stage_bytes = std::max(2 * kStreamCB * 512 + (affine ? 2 * kStreamCB * 64 : 0), 4096);
-    const int xs_u4 = (fmt == GLQ_FMT_Q4) ? 8 : 16;
+    g.stage_bytes = std::max(kStreamCB * 2 * block_bytes_of(fmt), 4096);
     size_t off = kWarpsPerCta * kMaxStages * 8;
     off = (off + 127) / 128 * 128;
     g.off_xs = (int)off;
-    off += (size_t)g.nkb * xs_u4 * g.ntc * 16;
-    g.off_ox = (int)off;
-    off += (size_t)g.nkb * g.ntc * 8;
+    if (g.i8) {
+        const int p8 = fmt == GLQ_FMT_Q2 ? 2 : 1;
+        off += (size_t)g.nkb * p8 * (2 * rows) * 4 * 16;
+        g.off_ox = (int)off;
+        off += (size_t)g.nkb * rows * 8;
+    } else {
+        const int xs_u4 = (fmt == GLQ_FMT_Q4) ? 8 : 16;
+        off += (size_t)g.nkb * xs_u4 * g.ntc * 16;
+        g.off_ox = (int)off;
+        off += (size_t)g.nkb * g.ntc * 8;
+    }
     off = (off + 15) / 16 * 16;
     g.off_as = (int)off;
-    off += (size_t)g.nw * g.ntc * std::max(rank, 16) * 2;
+    off += (size_t)(g.swiglu ? 2 : 1) * rows * std::max(rank, 16) * 2;
     off = (off + 127) / 128 * 128;
     g.off_ring = (int)off;
-    const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.ntt * 32 * 16 : 0;
+    const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.nt * 32 * 16 : 0;
     const size_t cap = 220 * 1024;
     if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) return false;
     int stages = (int)((cap - off - red) / ((size_t)kWarpsPerCta * g.stage_bytes));
@@ -262,9 +296,9 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     return g.grid > 0;
 }
 
-template <int FMT, int NW, int NTT>
+template <int FMT, bool I8, int NT>
 static int launch_stream_one(const StreamParams& sp, const StreamGeom& g, cudaStream_t st) {
-    auto kern = stream_kernel<FMT, NW, NTT>;
+    auto kern = stream_kernel<FMT, I8, NT>;
     static size_t configured[16] = {0};
     int dev = 0;
     GLQ_CUDA(cudaGetDevice(&dev));
@@ -279,20 +313,21 @@ static int launch_stream_one(const StreamParams& sp, const StreamGeom& g, cudaSt
 
 template <int FMT>
 static int launch_stream_fmt(const StreamParams& sp, const StreamGeom& g, cudaStream_t st) {
-    if (g.nw == 2) {
-        if (g.ntt == 1) return launch_stream_one<FMT, 2, 1>(sp, g, st);
-        return launch_stream_one<FMT, 2, 2>(sp, g, st);
+    if constexpr (FMT != GLQ_FMT_T2) {
+        if (g.i8) {
+            if (g.nt == 1) return launch_stream_one<FMT, true, 1>(sp, g, st);
+            return launch_stream_one<FMT, true, 2>(sp, g, st);
+        }
     }
-    if (g.ntt == 1) return launch_stream_one<FMT, 1, 1>(sp, g, st);
-    if (g.ntt == 2) return launch_stream_one<FMT, 1, 2>(sp, g, st);
-    return launch_stream_one<FMT, 1, 4>(sp, g, st);
+    if (g.nt == 1) return launch_stream_one<FMT, false, 1>(sp, g, st);
+    if (g.nt == 2) return launch_stream_one<FMT, false, 2>(sp, g, st);
+    return launch_stream_one<FMT, false, 4>(sp, g, st);
 }
 
 static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, int K, int rank, int n_problems,
                          cudaStream_t st) {
     StreamParams sp{};
     p.nkb = g.nkb;
-    p.group_blocks = g.group_blocks;
     p.ntc = g.ntc;
     p.kb_chunk = g.nkb;
     p.kb_per_split = g.nkb;
@@ -302,6 +337,7 @@ static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, i
     sp.K = K;
     sp.rank = rank;
     sp.n_problems = n_problems;
+    sp.swiglu = g.swiglu;
     sp.sk = g.sk;
     sp.kb_per_split = g.kb_per_split;
     sp.npairs = g.npairs;
@@ -364,14 +400,12 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
         if (!a->counters || a->n_counters < g.n_counters) return GLQ_ERR_WORKSPACE;
         if (!aligned16(a->workspace)) return GLQ_ERR_ALIGN;
     }
-    if (!a->w0_table && !a->w0.codes) return GLQ_ERR_ARG;
-    if (a->epilogue == GLQ_EPI_SWIGLU && !a->w1_table && !a->w1.codes) return GLQ_ERR_ARG;
+    if (!a->w_table && !a->w.codes) return GLQ_ERR_ARG;
 
     SkinnyParams p{};
-    p.w[0] = a->w0;
-    p.w[1] = a->w1;
-    p.table[0] = a->w0_table;
-    p.table[1] = a->w1_table;
+    p.w = a->w;
+    p.table = a->w_table;
+    p.sv_slices = cdiv(std::max(a->rank, 1), 64);
     p.slot_index = a->slot_index;
     p.n_slots = a->n_slots;
     p.slot_count = a->slot_count;
@@ -411,7 +445,7 @@ static void linear_args(int fmt, int group_size, const glq_weight_t* w, int B, g
     m->N = w->N;
     m->K = w->K;
     m->rank = w->rank;
-    m->w0 = *w;
+    m->w = *w;
 }
 static void xu_args(const glq_weight_t* w, const void* ut, int B, glq_mm_args_t* m) {
     std::memset(m, 0, sizeof(*m));
@@ -422,9 +456,9 @@ static void xu_args(const glq_weight_t* w, const void* ut, int B, glq_mm_args_t*
     m->rows_stride = B;
     m->N = w->rank;
     m->K = w->K;
-    m->w0.codes = ut;
-    m->w0.N = w->rank;
-    m->w0.K = w->K;
+    m->w.codes = ut;
+    m->w.N = w->rank;
+    m->w.K = w->K;
 }
 static inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
@@ -497,7 +531,7 @@ extern "C" int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w
     m.workspace_bytes = main_ws;
     m.counters = counters;
     m.n_counters = main_ctr;
-    if (!a_use) m.w0.rank = 0, m.rank = 0;
+    if (!a_use) m.w.rank = 0, m.rank = 0;
     return glq_grouped_matmul(&m, stream);
 }
 
@@ -512,11 +546,12 @@ static int turbo_rowmajor(const void* x, const uint8_t* packed, const float* nor
     int rc = plan_geometry(GLQ_FMT_T2, GLQ_EPI_LINEAR, N, K, 0, n_problems, rows, false, &g);
     if (rc != GLQ_OK) return rc;
     SkinnyParams p{};
-    p.w[0].codes = packed;
-    p.w[0].norms = norms;
-    p.w[0].centroids = centroids;
-    p.w[0].N = N;
-    p.w[0].K = K;
+    p.w.codes = packed;
+    p.w.norms = norms;
+    p.w.centroids = centroids;
+    p.w.N = N;
+    p.w.K = K;
+    p.sv_slices = 1;
     p.x = reinterpret_cast<const __half*>(x);
     p.ldx = K;
     p.y = reinterpret_cast<__half*>(y);
@@ -525,6 +560,8 @@ static int turbo_rowmajor(const void* x, const uint8_t* packed, const float* nor
     p.rows_stride = rows;
     p.x_vec = (aligned16(x) && K % 8 == 0) ? 1 : 0;
     p.slot_rows = slot_rows;
+    p.x_extent = (long long)n_problems * rows * K;
+    p.y_extent = (long long)n_problems * rows * N;
     fill_geometry(p, g);
     return launch_skinny(GLQ_FMT_T2, true, p, g, n_problems, reinterpret_cast<cudaStream_t>(stream));
 }
@@ -571,57 +608,72 @@ extern "C" int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const vo
 // ---------------------------------------------------------------------------------------------
 // Load-time re-tiling and the dequantised-tile check
 // ---------------------------------------------------------------------------------------------
-extern "C" int glq_pack_codes_i32(const int32_t* q, int bits, int N, int K, void* tiled, void* stream) {
-    if (!q || !tiled || N <= 0 || K <= 0) return GLQ_ERR_ARG;
+static inline bool slot_ok(int slot, int count) { return count >= 1 && count <= 2 && slot >= 0 && slot < count; }
+
+extern "C" int glq_pack_gptq(const int32_t* q, const void* scales, const void* zeros, int bits, int N, int K,
+                             int group_size, void* tiled, int slot, int count, void* stream) {
+    if (!q || !scales || !tiled || N <= 0 || K <= 0 || !slot_ok(slot, count)) return GLQ_ERR_ARG;
     if (bits != 2 && bits != 4) return GLQ_ERR_UNSUPPORTED;
-    const int fmt = bits == 2 ? GLQ_FMT_Q2 : GLQ_FMT_Q4;
-    const size_t words = glq_tiled_codes_bytes(fmt, N, K) / 4;
-    pack_codes_i32_kernel<<<(unsigned)((words + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        q, bits, N, K, reinterpret_cast<uint32_t*>(tiled), words);
+    const int kb = bits == 2 ? 128 : 64;
+    if (group_size <= 0 || group_size % kb != 0) return GLQ_ERR_UNSUPPORTED;
+    const size_t words = (size_t)cdiv(N, 16) * cdiv(K, kb) * 144;
+    pack_gptq_kernel<<<(unsigned)((words + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        q, reinterpret_cast<const __half*>(scales), reinterpret_cast<const __half*>(zeros), bits, N, K, group_size,
+        reinterpret_cast<unsigned char*>(tiled), slot, count);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
 }
 
-extern "C" int glq_pack_codes_u8(const uint8_t* packed, int N, int K, void* tiled, void* stream) {
-    if (!packed || !tiled || N <= 0 || K <= 0) return GLQ_ERR_ARG;
+extern "C" int glq_pack_turbo(const uint8_t* packed, int N, int K, void* tiled, int slot, int count, void* stream) {
+    if (!packed || !tiled || N <= 0 || K <= 0 || !slot_ok(slot, count)) return GLQ_ERR_ARG;
     if (K % 4 != 0) return GLQ_ERR_UNSUPPORTED;
-    const size_t words = glq_tiled_codes_bytes(GLQ_FMT_T2, N, K) / 4;
-    pack_codes_u8_kernel<<<(unsigned)((words + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        packed, N, K, reinterpret_cast<uint32_t*>(tiled), words);
+    const size_t words = (size_t)cdiv(N, 16) * cdiv(K, 128) * 128;
+    pack_turbo_kernel<<<(unsigned)((words + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        packed, N, K, reinterpret_cast<unsigned char*>(tiled), slot, count);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
 }
 
-extern "C" int glq_pack_sz(const void* scales, const void* zeros, int N, int n_groups, void* tiled, void* stream) {
-    if (!scales || !tiled || N <= 0 || n_groups <= 0) return GLQ_ERR_ARG;
-    const size_t elems = glq_tiled_sz_bytes(N, n_groups) / 2;
-    pack_sz_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __half*>(scales), reinterpret_cast<const __half*>(zeros), N, n_groups,
-        reinterpret_cast<__half*>(tiled), elems);
+extern "C" int glq_pack_rows_f32(const float* v, int N, float* out, int slot, int count, void* stream) {
+    if (!v || !out || N <= 0 || !slot_ok(slot, count)) return GLQ_ERR_ARG;
+    const int n = cdiv(N, 16) * 16;
+    pack_rows_f32_kernel<<<(n + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(v, N, out, slot, count);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+extern "C" int glq_pack_sv(const void* sv, int N, int rank, void* out, int slot, int count, void* stream) {
+    if (!sv || !out || N <= 0 || rank <= 0 || !slot_ok(slot, count)) return GLQ_ERR_ARG;
+    if (rank % 16 != 0) return GLQ_ERR_UNSUPPORTED;
+    const size_t total = (size_t)cdiv(N, 16) * cdiv(rank, 64) * 1024;
+    pack_sv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half*>(sv), N, rank, reinterpret_cast<__half*>(out), slot, count);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
 }
 
 extern "C" int glq_pack_f16(const void* W, long stride_n, long stride_k, int N, int K, void* tiled, void* stream) {
     if (!W || !tiled || N <= 0 || K <= 0) return GLQ_ERR_ARG;
-    const size_t elems = glq_tiled_codes_bytes(GLQ_FMT_F16, N, K) / 2;
+    const size_t elems = glq_tiled_f16_bytes(N, K) / 2;
     pack_f16_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const __half*>(W), stride_n, stride_k, N, K, reinterpret_cast<__half*>(tiled), elems);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
 }
 
-extern "C" int glq_dequant_tiled(int fmt, const glq_weight_t* w, int group_size, void* out, void* stream) {
-    if (!w || !w->codes || !out || w->N <= 0 || w->K <= 0) return GLQ_ERR_ARG;
-    const size_t elems = (size_t)w->N * w->K;
+extern "C" int glq_dequant_tiled(int fmt, const void* tiled, const float* norms_tiled, const float* centroids, int N,
+                                 int K, int slot, int count, void* out, void* stream) {
+    if (!tiled || !out || N <= 0 || K <= 0 || !slot_ok(slot, count)) return GLQ_ERR_ARG;
+    const size_t elems = (size_t)N * K;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_Q4) {
-        if (!w->sz || group_size <= 0 || group_size % fmt_kb(fmt) != 0) return GLQ_ERR_UNSUPPORTED;
         dequant_tiled_q_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(
-            fmt, *w, group_size, reinterpret_cast<__half*>(out));
+            fmt, reinterpret_cast<const unsigned char*>(tiled), N, K, slot, count, reinterpret_cast<__half*>(out));
     } else if (fmt == GLQ_FMT_T2) {
-        if (!w->norms || !w->centroids) return GLQ_ERR_ARG;
-        dequant_tiled_t2_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(*w, reinterpret_cast<float*>(out));
+        if (!norms_tiled || !centroids) return GLQ_ERR_ARG;
+        dequant_tiled_t2_kernel<<<(unsigned)((elems + 255) / 256), 256, 0, st>>>(
+            reinterpret_cast<const unsigned char*>(tiled), norms_tiled, centroids, N, K, slot, count,
+            reinterpret_cast<float*>(out));
     } else {
         return GLQ_ERR_UNSUPPORTED;
     }

@@ -7,69 +7,109 @@
 namespace glq {
 
 // ---------------------------------------------------------------------------------------------
-// (N,K) int32 codes -> tiled Q2 / Q4.  One thread per output word.
-// word index = ((rt*nkb + kb)*32 + lane)*4 + wsel ; lane = 4g+t ; wsel>>1 selects row g / g+8,
-// wsel&1 the first / second word of the lane's codes.
+// Pair-interleaved tiled layout of the quantized formats.  Source row tile i of a matrix goes to
+// destination tile d = i*count + slot (count = 2 interleaves two matrices, e.g. gate and up);
+// destination pair = d/2, j = d%2.  Block (pair, kb, j) starts at ((pair*nkb + kb)*2 + j)*BB bytes,
+// BB = 576 (affine) or 512 (codebook): 32 lanes x 16 B of codes, lane = 4g+t holding codes
+// k = KB*kb + (KB/4)*t + 0..KB/4-1 of row 16i+g (words 0,1) and of row 16i+g+8 (words 2,3); then,
+// affine formats only, 8 x (scale g, zero g, scale g+8, zero g+8) fp16 of the group of block kb.
 // ---------------------------------------------------------------------------------------------
-__global__ void pack_codes_i32_kernel(const int32_t* __restrict__ q, int bits, int N, int K,
-                                      uint32_t* __restrict__ out, size_t nwords) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= nwords) return;
-    const int cpw = 32 / bits, kbk = 8 * cpw;  // codes per word, k per block (128 or 64)
-    const int nkb = (K + kbk - 1) / kbk;
-    const int wsel = idx & 3, lane = (idx >> 2) & 31;
-    const size_t blk = idx >> 7;
-    const int kb = (int)(blk % nkb), rt = (int)(blk / nkb);
-    const int g = lane >> 2, t = lane & 3;
-    const int row = rt * 16 + g + 8 * (wsel >> 1);
-    const int k0 = kb * kbk + t * 2 * cpw + (wsel & 1) * cpw;
-    uint32_t w = 0;
-    if (row < N) {
-        const uint32_t mask = (1u << bits) - 1u;
-        for (int j = 0; j < cpw; ++j)
-            if (k0 + j < K) w |= ((uint32_t)q[(size_t)row * K + k0 + j] & mask) << (bits * j);
-    }
-    out[idx] = w;
+__device__ __forceinline__ size_t tiled_block_offset(int src_tile, int slot, int count, int kb, int nkb, int bb) {
+    const int d = src_tile * count + slot;
+    return (((size_t)(d >> 1) * nkb + kb) * 2 + (d & 1)) * bb;
 }
 
-// (N,K/4) uint8 packed 2-bit codes -> tiled T2 / Q2
-__global__ void pack_codes_u8_kernel(const uint8_t* __restrict__ packed, int N, int K, uint32_t* __restrict__ out,
-                                     size_t nwords) {
+// one thread per 32-bit word of the destination blocks of one source matrix
+__global__ void pack_gptq_kernel(const int32_t* __restrict__ q, const __half* __restrict__ scales,
+                                 const __half* __restrict__ zeros, int bits, int N, int K, int group_size,
+                                 unsigned char* __restrict__ out, int slot, int count) {
+    const int cpw = 32 / bits, kbk = 8 * cpw;
+    const int nkb = (K + kbk - 1) / kbk, ntiles = (N + 15) / 16;
+    const int G = (K + group_size - 1) / group_size;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= nwords) return;
-    const int nkb = (K + 127) / 128;
-    const int wsel = idx & 3, lane = (idx >> 2) & 31;
+    const size_t total = (size_t)ntiles * nkb * 144;  // 144 words per block
+    if (idx >= total) return;
+    const int wsel = (int)(idx % 144);
+    const size_t blk = idx / 144;
+    const int kb = (int)(blk % nkb), tile = (int)(blk / nkb);
+    uint32_t word = 0;
+    if (wsel < 128) {
+        const int lane = wsel >> 2, ws = wsel & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const int row = tile * 16 + g + 8 * (ws >> 1);
+        const int k0 = kb * kbk + t * 2 * cpw + (ws & 1) * cpw;
+        if (row < N) {
+            const uint32_t mask = (1u << bits) - 1u;
+            for (int j = 0; j < cpw; ++j)
+                if (k0 + j < K) word |= ((uint32_t)q[(size_t)row * K + k0 + j] & mask) << (bits * j);
+        }
+    } else {
+        const int e = wsel - 128;           // 16 words: 8 x (s_g, z_g) (s_g8, z_g8)
+        const int g = e >> 1, row = tile * 16 + g + 8 * (e & 1);
+        const int grp = min((kb * kbk) / group_size, G - 1);
+        if (row < N) {
+            const unsigned short sv = __half_as_ushort(scales[(size_t)row * G + grp]);
+            const unsigned short zv = zeros ? __half_as_ushort(zeros[(size_t)row * G + grp]) : (unsigned short)0;
+            word = (uint32_t)sv | ((uint32_t)zv << 16);
+        }
+    }
+    reinterpret_cast<uint32_t*>(out + tiled_block_offset(tile, slot, count, kb, nkb, 576))[wsel] = word;
+}
+
+// (N,K/4) uint8 packed 2-bit codes -> tiled codebook format
+__global__ void pack_turbo_kernel(const uint8_t* __restrict__ packed, int N, int K, unsigned char* __restrict__ out,
+                                  int slot, int count) {
+    const int nkb = (K + 127) / 128, ntiles = (N + 15) / 16;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)ntiles * nkb * 128;
+    if (idx >= total) return;
+    const int wsel = (int)(idx & 127);
     const size_t blk = idx >> 7;
-    const int kb = (int)(blk % nkb), rt = (int)(blk / nkb);
+    const int kb = (int)(blk % nkb), tile = (int)(blk / nkb);
+    const int lane = wsel >> 2, ws = wsel & 3;
     const int g = lane >> 2, t = lane & 3;
-    const int row = rt * 16 + g + 8 * (wsel >> 1);
-    const int k0 = kb * 128 + t * 32 + (wsel & 1) * 16;
-    uint32_t w = 0;
+    const int row = tile * 16 + g + 8 * (ws >> 1);
+    const int k0 = kb * 128 + t * 32 + (ws & 1) * 16;
+    uint32_t word = 0;
     if (row < N) {
         const int rowbytes = K >> 2;
         for (int b = 0; b < 4; ++b) {
             const int byte = (k0 >> 2) + b;
-            if (byte < rowbytes) w |= (uint32_t)packed[(size_t)row * rowbytes + byte] << (8 * b);
+            if (byte < rowbytes) word |= (uint32_t)packed[(size_t)row * rowbytes + byte] << (8 * b);
         }
     }
-    out[idx] = w;
+    reinterpret_cast<uint32_t*>(out + tiled_block_offset(tile, slot, count, kb, nkb, 512))[wsel] = word;
 }
 
-// (N,G) fp16 scales, zeros -> [rt][grp][g][s_g, z_g, s_g+8, z_g+8]
-__global__ void pack_sz_kernel(const __half* __restrict__ scales, const __half* __restrict__ zeros, int N, int G,
-                               __half* __restrict__ out, size_t nelem) {
+// clear the padding tile of an odd tile count (destination tile d_total, if d_total is odd)
+__global__ void clear_bytes_kernel(unsigned char* __restrict__ p, size_t n) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= nelem) return;
-    const int c = idx & 3, g = (idx >> 2) & 7;
-    const size_t blk = idx >> 5;
-    const int grp = (int)(blk % G), rt = (int)(blk / G);
-    const int row = rt * 16 + g + 8 * (c >> 1);
-    __half v = __float2half(0.f);
-    if (row < N) {
-        if ((c & 1) == 0) v = scales[(size_t)row * G + grp];
-        else if (zeros) v = zeros[(size_t)row * G + grp];
-    }
-    out[idx] = v;
+    if (idx < n) p[idx] = 0;
+}
+
+// per-row fp32 values (norms) -> tile order: out[(i*count + slot)*16 + r] = v[16i + r]
+__global__ void pack_rows_f32_kernel(const float* __restrict__ v, int N, float* __restrict__ out, int slot, int count) {
+    const int ntiles = (N + 15) / 16;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= ntiles * 16) return;
+    const int tile = idx >> 4, r = idx & 15, row = tile * 16 + r;
+    out[(size_t)(tile * count + slot) * 16 + r] = row < N ? v[row] : 0.f;
+}
+
+// SV (N, rank) fp16 -> [pair][64-column slice][32 rows of the pair][64 columns]
+__global__ void pack_sv_kernel(const __half* __restrict__ sv, int N, int rank, __half* __restrict__ out, int slot,
+                               int count) {
+    const int ntiles = (N + 15) / 16, ns = (rank + 63) / 64;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)ntiles * ns * 16 * 64;
+    if (idx >= total) return;
+    const int c = (int)(idx & 63), r = (int)((idx >> 6) & 15);
+    const size_t rest = idx >> 10;
+    const int sl = (int)(rest % ns), tile = (int)(rest / ns);
+    const int row = tile * 16 + r, col = sl * 64 + c;
+    const int d = tile * count + slot;
+    const __half v = (row < N && col < rank) ? sv[(size_t)row * rank + col] : __float2half(0.f);
+    out[((((size_t)(d >> 1) * ns + sl) * 32) + (d & 1) * 16 + r) * 64 + c] = v;
 }
 
 // fp16 matrix (element (n,k) at W[n*stride_n + k*stride_k]) -> tiled m16n8k16 A fragments
@@ -90,36 +130,38 @@ __global__ void pack_f16_kernel(const __half* __restrict__ W, long stride_n, lon
 // ---------------------------------------------------------------------------------------------
 // Dequantised weights from the tiled layout (checks only).
 // ---------------------------------------------------------------------------------------------
-__global__ void dequant_tiled_q_kernel(int fmt, const glq_weight_t w, int group_size, __half* __restrict__ out) {
+__global__ void dequant_tiled_q_kernel(int fmt, const unsigned char* __restrict__ tiled, int N, int K, int slot,
+                                       int count, __half* __restrict__ out) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)w.N * w.K) return;
-    const int n = (int)(idx / w.K), k = (int)(idx % w.K);
+    if (idx >= (size_t)N * K) return;
+    const int n = (int)(idx / K), k = (int)(idx % K);
     const int bits = fmt == GLQ_FMT_Q2 ? 2 : 4;
     const int cpw = 32 / bits, kbk = 8 * cpw;
-    const int nkb = (w.K + kbk - 1) / kbk;
-    const int G = (w.K + group_size - 1) / group_size;
-    const int rt = n >> 4, rr = n & 15, g = rr & 7, hi = rr >> 3;
+    const int nkb = (K + kbk - 1) / kbk;
+    const int tile = n >> 4, rr = n & 15, g = rr & 7, hi = rr >> 3;
     const int kb = k / kbk, kin = k % kbk;
     const int t = kin / (2 * cpw), u = (kin % (2 * cpw)) / cpw, j = kin % cpw;
-    const uint32_t word =
-        reinterpret_cast<const uint32_t*>(w.codes)[(((size_t)rt * nkb + kb) * 32 + g * 4 + t) * 4 + hi * 2 + u];
+    const unsigned char* blk = tiled + tiled_block_offset(tile, slot, count, kb, nkb, 576);
+    const uint32_t word = reinterpret_cast<const uint32_t*>(blk)[(g * 4 + t) * 4 + hi * 2 + u];
     const uint32_t code = (word >> (bits * j)) & ((1u << bits) - 1u);
-    const __half* sz = reinterpret_cast<const __half*>(w.sz) + (((size_t)rt * G + k / group_size) * 8 + g) * 4 + hi * 2;
+    const __half* sz = reinterpret_cast<const __half*>(blk + 512) + g * 4 + hi * 2;
     // fp16 arithmetic step by step, as an fp16 tensor expression evaluates it
     out[idx] = __hmul(__hsub(__ushort2half_rn((unsigned short)code), sz[1]), sz[0]);
 }
 
-__global__ void dequant_tiled_t2_kernel(const glq_weight_t w, float* __restrict__ out) {
+__global__ void dequant_tiled_t2_kernel(const unsigned char* __restrict__ tiled, const float* __restrict__ norms_t,
+                                        const float* __restrict__ centroids, int N, int K, int slot, int count,
+                                        float* __restrict__ out) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)w.N * w.K) return;
-    const int n = (int)(idx / w.K), k = (int)(idx % w.K);
-    const int nkb = (w.K + 127) / 128;
-    const int rt = n >> 4, rr = n & 15, g = rr & 7, hi = rr >> 3;
+    if (idx >= (size_t)N * K) return;
+    const int n = (int)(idx / K), k = (int)(idx % K);
+    const int nkb = (K + 127) / 128;
+    const int tile = n >> 4, rr = n & 15, g = rr & 7, hi = rr >> 3;
     const int kb = k >> 7, kin = k & 127;
     const int t = kin >> 5, u = (kin & 31) >> 4, j = kin & 15;
-    const uint32_t word =
-        reinterpret_cast<const uint32_t*>(w.codes)[(((size_t)rt * nkb + kb) * 32 + g * 4 + t) * 4 + hi * 2 + u];
-    out[idx] = __fmul_rn(w.centroids[(word >> (2 * j)) & 3u], w.norms[n]);
+    const unsigned char* blk = tiled + tiled_block_offset(tile, slot, count, kb, nkb, 512);
+    const uint32_t word = reinterpret_cast<const uint32_t*>(blk)[(g * 4 + t) * 4 + hi * 2 + u];
+    out[idx] = __fmul_rn(centroids[(word >> (2 * j)) & 3u], norms_t[(size_t)(tile * count + slot) * 16 + rr]);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -46,8 +46,9 @@ constexpr int kRW = 2;     // row tiles per CTA
 constexpr int kKW = kWarpsPerCta / kRW;  // warps splitting k for one row tile
 
 struct SkinnyParams {
-    glq_weight_t w[2];
-    const glq_weight_t* table[2];
+    glq_weight_t w;              // inline descriptor (used when table == nullptr)
+    const glq_weight_t* table;   // per-problem descriptors
+    int sv_slices;               // ceil(rank / 64) of the packed SV layout
     const int* slot_index;
     const int* n_slots;
     const int* slot_count;
@@ -74,6 +75,8 @@ struct SkinnyParams {
     int max_passes;
     int epilogue;
     int x_vec;         // 1: x rows can be read with 16-byte loads
+    long long x_extent;  // elements of x / y that may be touched (0: unknown), self-check only
+    long long y_extent;
     int slot_rows;     // row-major operands only: slot s uses weight rows [s*slot_rows, (s+1)*slot_rows)
 };
 
@@ -84,6 +87,13 @@ template <> struct Fmt<GLQ_FMT_Q2> { static constexpr int KB = 128, XS = 16, UPK
 template <> struct Fmt<GLQ_FMT_T2> { static constexpr int KB = 128, XS = 16, UPK = 8, LD = 1, DEPTH = 4; };
 template <> struct Fmt<GLQ_FMT_Q4> { static constexpr int KB = 64, XS = 8, UPK = 4, LD = 1, DEPTH = 4; };
 template <> struct Fmt<GLQ_FMT_F16> { static constexpr int KB = 64, XS = 8, UPK = 4, LD = 4, DEPTH = 2; };
+
+// Pair-interleaved tiled layout of the quantized formats: [pair][k block][tile in pair][block bytes],
+// block bytes = 512 B of codes (+ 64 B of (scale, zero) pairs for the affine formats).
+template <int FMT> __host__ __device__ constexpr int block_bytes() {
+    return (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4) ? 576 : 512;
+}
+__host__ __device__ inline int block_bytes_of(int fmt) { return (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_Q4) ? 576 : 512; }
 
 __host__ __device__ inline size_t skinny_smem_bytes(int fmt, int kb_cta, int ntc, int nw, int ntt) {
     const int xs = (fmt == GLQ_FMT_Q2 || fmt == GLQ_FMT_T2) ? 16 : 8;
@@ -116,7 +126,11 @@ __device__ __forceinline__ void stage_x(const SkinnyParams& p, uint4* xs, float2
             const int entry = e0 + pass0 + col;
             const long long row = p.entry_row ? p.entry_row[entry] : entry;
             const __half* src = p.x + row * p.ldx + k0;
-            if (p.x_vec && k0 + 16 <= K) {
+            if (!GLQ_OKAY(p.x_extent == 0 || (row >= 0 && row * p.ldx + k0 + min(16, K - k0) <= p.x_extent), 21,
+                          row * p.ldx + k0, p.x_extent)) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __float2half(0.f);
+            } else if (p.x_vec && k0 + 16 <= K) {
                 *reinterpret_cast<uint4*>(&v[0]) = __ldg(reinterpret_cast<const uint4*>(src));
                 *reinterpret_cast<uint4*>(&v[8]) = __ldg(reinterpret_cast<const uint4*>(src) + 1);
             } else {
@@ -267,10 +281,11 @@ __device__ __forceinline__ void block_mma(const uint4 (&q)[Fmt<FMT>::LD], const 
     }
 }
 
-// load the lane's codes of k block kb of row tile rt
+// load the lane's codes (and scale/zero pairs) of k block kb of tile (pair, j); F16 and the row-major
+// operand address by row tile rt
 template <int FMT, bool RM>
-__device__ __forceinline__ void load_codes(const glq_weight_t& W, int rt, int kb, int nkb, int lane,
-                                           uint4 (&q)[Fmt<FMT>::LD]) {
+__device__ __forceinline__ void load_codes(const glq_weight_t& W, int rt, int pair, int j, int kb, int nkb, int lane,
+                                           uint4 (&q)[Fmt<FMT>::LD], uint2& szv) {
     if constexpr (RM) {
         // row-major (N, K/4) uint8 operand of the reference's native module
         const int g = lane >> 2, t = lane & 3;
@@ -283,7 +298,9 @@ __device__ __forceinline__ void load_codes(const glq_weight_t& W, int rt, int kb
             int row = rt * kRowTile + g + 8 * h;
             row = row < W.N ? row : W.N - 1;
             const uint8_t* ptr = base + (size_t)row * rowbytes + boff;
-            if ((rowbytes & 7) == 0 && boff + 8 <= rowbytes) {
+            if (!GLQ_OKAY(row >= 0 && kb >= 0 && kb < nkb, 20, (size_t)row * rowbytes + boff, (size_t)W.N * rowbytes)) {
+                r[h] = make_uint2(0, 0);
+            } else if ((rowbytes & 7) == 0 && boff + 8 <= rowbytes) {
                 r[h] = __ldg(reinterpret_cast<const uint2*>(ptr));
             } else {
                 uint32_t lo = 0, hi = 0;
@@ -296,17 +313,16 @@ __device__ __forceinline__ void load_codes(const glq_weight_t& W, int rt, int kb
             }
         }
         q[0] = make_uint4(r[0].x, r[0].y, r[1].x, r[1].y);
-    } else {
+    } else if constexpr (FMT == GLQ_FMT_F16) {
         const uint4* base = reinterpret_cast<const uint4*>(W.codes);
 #pragma unroll
-        for (int i = 0; i < Fmt<FMT>::LD; ++i) {
-            const size_t idx = ((size_t)(rt * nkb + kb) * Fmt<FMT>::LD + i) * 32 + lane;
-            if (GLQ_OKAY(idx < (size_t)((W.N + 15) / 16) * nkb * Fmt<FMT>::LD * 32 && kb < nkb, 8, idx,
-                         (size_t)((W.N + 15) / 16) * nkb * Fmt<FMT>::LD * 32))
-                q[i] = __ldcs(base + idx);
-            else
-                q[i] = make_uint4(0, 0, 0, 0);
-        }
+        for (int i = 0; i < Fmt<FMT>::LD; ++i) q[i] = __ldcs(base + ((size_t)(rt * nkb + kb) * Fmt<FMT>::LD + i) * 32 + lane);
+    } else {
+        const unsigned char* blk =
+            reinterpret_cast<const unsigned char*>(W.codes) + (((size_t)pair * nkb + kb) * 2 + j) * block_bytes<FMT>();
+        q[0] = __ldcs(reinterpret_cast<const uint4*>(blk) + lane);
+        if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4)
+            szv = __ldg(reinterpret_cast<const uint2*>(blk + 512) + (lane >> 2));
     }
 }
 
@@ -331,16 +347,15 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
     const int e0 = p.slot_offset ? __ldg(p.slot_offset + slot) : slot * p.rows_stride;
     const int widx = p.slot_index ? __ldg(p.slot_index + slot) : slot;
 
-    glq_weight_t W[NW];
-#pragma unroll
-    for (int i = 0; i < NW; ++i) W[i] = p.table[i] ? p.table[i][widx] : p.w[i];
+    // one weight per problem; NW == 2 means a fused gate|up weight whose pair p is (gate tile p, up tile p)
+    glq_weight_t W = p.table ? p.table[widx] : p.w;
     if constexpr (RM) {
         if (p.slot_rows > 0) {
-            W[0].codes = reinterpret_cast<const uint8_t*>(W[0].codes) + (size_t)slot * p.slot_rows * (W[0].K >> 2);
-            W[0].norms += (size_t)slot * p.slot_rows;
+            W.codes = reinterpret_cast<const uint8_t*>(W.codes) + (size_t)slot * p.slot_rows * (W.K >> 2);
+            W.norms += (size_t)slot * p.slot_rows;
         }
     }
-    const int N = W[0].N, K = W[0].K;
+    const int N = W.N, K = W.K;
     const int ntiles = (N + kRowTile - 1) / kRowTile;
     const int nkb = p.nkb;
 
@@ -359,14 +374,12 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
     float2* ox = reinterpret_cast<float2*>(xs + (size_t)p.kb_chunk * F::XS * ntc);
     float4* red = reinterpret_cast<float4*>(ox + (size_t)p.kb_chunk * ntc);
 
-    uint32_t TL[NW], TH[NW];
-#pragma unroll
-    for (int i = 0; i < NW; ++i) {
-        TL[i] = TH[i] = 0;
-        if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(W[i].centroids, TL[i], TH[i]);
-    }
+    uint32_t TL = 0, TH = 0;
+    if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(W.centroids, TL, TH);
+    // tile i of this warp in the pair-interleaved layout
+    const int pr = NW == 2 ? rt : (rt >> 1);
+    const int pj0 = NW == 2 ? 0 : (rt & 1);
 
-    const int G = (nkb + p.group_blocks - 1) / p.group_blocks;
     const int rows_per_pass = 8 * NTT;
     const int npass = (cnt + rows_per_pass - 1) / rows_per_pass;
     int iter = 0;
@@ -398,14 +411,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                     const int kb = wk_lo + d;
                     if (kb < wk_hi) {
 #pragma unroll
-                        for (int i = 0; i < NW; ++i) {
-                            load_codes<FMT, RM>(W[i], rt, kb, nkb, lane, q[i][d]);
-                            if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4)
-                                if (GLQ_OKAY(((size_t)rt * G + kb / p.group_blocks) * 8 + g < (size_t)ntiles * G * 8, 10,
-                                             ((size_t)rt * G + kb / p.group_blocks) * 8 + g, (size_t)ntiles * G * 8))
-                                    szv[i][d] = __ldg(reinterpret_cast<const uint2*>(W[i].sz) +
-                                                      ((size_t)rt * G + kb / p.group_blocks) * 8 + g);
-                        }
+                        for (int i = 0; i < NW; ++i) load_codes<FMT, RM>(W, rt, pr, pj0 + i, kb, nkb, lane, q[i][d], szv[i][d]);
                     }
                 }
             }
@@ -429,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                                     for (int tt = 0; tt < NTT; ++tt)
 #pragma unroll
                                         for (int j = 0; j < 4; ++j) c[tt][j] = 0.f;
-                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], c, (p.kb_chunk - kbl) * F::XS * ntc);
+                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL, TH, c, (p.kb_chunk - kbl) * F::XS * ntc);
                                     const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv[i][d].x);
                                     const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv[i][d].y);
                                     const float s0 = __low2float(sz0), z0 = __high2float(sz0);
@@ -445,18 +451,10 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                                         acc[i][tt][3] = fmaf(s1, fmaf(-z1, o.w, c[tt][3] - o.z), acc[i][tt][3]);
                                     }
                                 } else {
-                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], acc[i], (p.kb_chunk - kbl) * F::XS * ntc);
+                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL, TH, acc[i], (p.kb_chunk - kbl) * F::XS * ntc);
                                 }
                                 const int kn = kb + kDepth;
-                                if (kn < wk_hi) {
-                                    load_codes<FMT, RM>(W[i], rt, kn, nkb, lane, q[i][d]);
-                                    if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4)
-                                        if (GLQ_OKAY(((size_t)rt * G + kn / p.group_blocks) * 8 + g < (size_t)ntiles * G * 8,
-                                                     11, ((size_t)rt * G + kn / p.group_blocks) * 8 + g,
-                                                     (size_t)ntiles * G * 8))
-                                            szv[i][d] = __ldg(reinterpret_cast<const uint2*>(W[i].sz) +
-                                                              ((size_t)rt * G + kn / p.group_blocks) * 8 + g);
-                                }
+                                if (kn < wk_hi) load_codes<FMT, RM>(W, rt, pr, pj0 + i, kn, nkb, lane, q[i][d], szv[i][d]);
                             }
                         }
                     }
@@ -542,9 +540,12 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
             for (int i = 0; i < NW; ++i) {
                 float n0 = 1.f, n1 = 1.f;
                 if constexpr (FMT == GLQ_FMT_T2) {
-                    if (GLQ_OKAY(r1c < N && r0c >= 0 && W[i].norms != nullptr, 12, r1c, N)) {
-                        n0 = __ldg(W[i].norms + r0c);
-                        n1 = __ldg(W[i].norms + r1c);
+                    // row-major operand: norms by row; tiled: norms in tile order
+                    const size_t i0 = RM ? (size_t)r0c : ((size_t)(pr * 2 + pj0 + i) * 16 + g);
+                    const size_t i1 = RM ? (size_t)r1c : i0 + 8;
+                    if (GLQ_OKAY(W.norms != nullptr, 12, i1, N)) {
+                        n0 = __ldg(W.norms + i0);
+                        n1 = __ldg(W.norms + i1);
                     }
                 }
                 // low-rank term a . SV^T through the same tensor-core dot
@@ -553,17 +554,19 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                 for (int tt = 0; tt < NTT; ++tt)
 #pragma unroll
                     for (int j = 0; j < 4; ++j) lo[tt][j] = 0.f;
-                const int rank = W[i].rank;
-                const bool has_lr = rank > 0 && W[i].sv != nullptr && p.a[i] != nullptr;
+                const int rank = W.rank;
+                const bool has_lr = !RM && FMT != GLQ_FMT_F16 && rank > 0 && W.sv != nullptr && p.a[i] != nullptr;
                 if (has_lr) {
-                    const __half* sv = reinterpret_cast<const __half*>(W[i].sv);
+                    // packed SV: [pair][64-column slice][32 rows of the pair][64 columns]
+                    const __half* sv = reinterpret_cast<const __half*>(W.sv);
                     for (int c0 = 0; c0 < rank; c0 += 64) {
                         const int cc = c0 + 16 * t;
                         uint4 sa[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
                         uint4 sb[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                        if (cc < rank && GLQ_OKAY((size_t)r1c * rank + cc + 16 <= (size_t)N * rank, 13, (size_t)r1c * rank + cc, (size_t)N * rank)) {
-                            const uint4* pa = reinterpret_cast<const uint4*>(sv + (size_t)r0c * rank + cc);
-                            const uint4* pb = reinterpret_cast<const uint4*>(sv + (size_t)r1c * rank + cc);
+                        if (cc < rank) {
+                            const size_t row0 = ((size_t)pr * p.sv_slices + (c0 >> 6)) * 32 + (pj0 + i) * 16 + g;
+                            const uint4* pa = reinterpret_cast<const uint4*>(sv + row0 * 64 + 16 * t);
+                            const uint4* pb = reinterpret_cast<const uint4*>(sv + (row0 + 8) * 64 + 16 * t);
                             sa[0] = __ldg(pa); sa[1] = __ldg(pa + 1);
                             sb[0] = __ldg(pb); sb[1] = __ldg(pb + 1);
                         }
@@ -584,7 +587,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                         }
                     }
                 }
-                const __half* bias = reinterpret_cast<const __half*>(W[i].bias);
+                const __half* bias = reinterpret_cast<const __half*>(W.bias);
                 const float b0 = bias ? __half2float(__ldg(bias + r0c)) : 0.f;
                 const float b1 = bias ? __half2float(__ldg(bias + r1c)) : 0.f;
 #pragma unroll
@@ -611,7 +614,9 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                             v = res[0][tt][j];
                             if (p.entry_scale) v = round16(__half2float(__ldg(p.entry_scale + e0 + row)) * v);
                         }
-                        p.y[(size_t)(e0 + row) * p.ldy + n] = __float2half_rn(v);
+                        if (GLQ_OKAY(p.y_extent == 0 || (long long)(e0 + row) * p.ldy + n < p.y_extent, 22,
+                                     (long long)(e0 + row) * p.ldy + n, p.y_extent))
+                            p.y[(size_t)(e0 + row) * p.ldy + n] = __float2half_rn(v);
                     }
                 }
         }

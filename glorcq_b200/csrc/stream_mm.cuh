@@ -1,46 +1,62 @@
-// Persistent streaming variant of the grouped skinny matmul (same maths and the same operands as
-// skinny_mm.cuh; this is the fast path, that one the general fallback).
+// Persistent streaming kernel of the grouped skinny matmul: the decode GEMV / batched-decode fast
+// path (skinny_mm.cuh has the same maths for every shape and is the fallback).
 //
-// The decode GEMV is bound by the HBM stream of packed codes, so this kernel is built as a copy
-// pipeline with compute attached:
-//   * one CTA per SM, each CTA walks a contiguous range of work items (problem, row-tile pair,
-//     k split), so the activations of a problem are staged once per CTA and not once per tile;
-//   * every warp owns a ring of shared-memory stages that is filled by bulk asynchronous copies
-//     (cp.async.bulk global -> shared, completion on an mbarrier), issued by the warp itself several
-//     stages ahead of where it computes, across item boundaries: the bytes in flight per SM stay
-//     constant (about 100 KB) instead of collapsing at every tile boundary.  In the tiled layout a
-//     row tile's codes for consecutive k blocks are contiguous, so a stage is one 2 KB copy per tile
-//     plus one small copy of its scales; the 16 rows of the output-side factor SV ride the same ring;
-//   * a warp item is TWO row tiles that share the activation fragments (gate and up of one expert,
-//     or two consecutive tiles of one matrix), halving the shared-memory traffic per weight;
-//   * k splits of a tile are the warps of one CTA, reduced through shared memory in a fixed order
-//     (named barrier per tile group): no global scratch, no atomics, deterministic.
-// Every mbarrier wait is bounded; a wait that runs out records an error word and carries on, so
-// the kernel always terminates.  No cluster launch, no multicast.
+// The op is bound by the HBM stream of packed codes, so the kernel is a copy pipeline with compute
+// attached:
+//   * one CTA per SM walks a contiguous range of work items (problem, tile pair, k split); the
+//     activations of a problem are staged once per CTA, not once per tile;
+//   * every warp owns a ring of shared-memory stages filled by bulk asynchronous copies
+//     (cp.async.bulk global -> shared, completion counted on an mbarrier) that the warp issues itself,
+//     several stages ahead of where it computes and across item boundaries, so the bytes in flight
+//     per SM stay constant.  In the pair-interleaved layout the codes and scales of a tile pair for
+//     consecutive k blocks are one contiguous run: one copy per stage (4.5 KB); the 32 rows of the
+//     packed output-side factor SV are one more 4 KB copy on the same ring;
+//   * a warp item is a PAIR of row tiles that share the activation fragments (gate and up tile of an
+//     expert, or two consecutive tiles of one matrix);
+//   * up to 8 activation rows take the integer path: the activations are turned into 16-bit block
+//     fixed point (two int8 digits per value, one power-of-two scale per row and k block) when they
+//     are staged, the 2/4-bit codes become int8 with two bit-ops per four weights, and the s8 x s8
+//     -> s32 tensor-core op (m16n8k32) does the dot products exactly; scale, zero point and the digit
+//     weights are applied in fp32 per k block.  More rows (and the codebook format) use the fp16 op;
+//   * k splits of a pair are warps of one CTA, reduced through shared memory in a fixed order
+//     (named barrier per pair): no global scratch, no atomics, deterministic.
+// Every mbarrier wait is bounded in time; a wait that runs out records an error word and the warp
+// stops waiting, so the kernel always terminates.  No cluster launch, no multicast.
 #pragma once
 
 #include "skinny_mm.cuh"
 
 namespace glq {
 
-constexpr int kMaxStages = 4;
-constexpr int kStreamCB = 4;  // k blocks per ring stage and tile
+constexpr int kMaxStages = 6;
+constexpr int kStreamCB = 4;  // k blocks per ring stage
 
 struct StreamParams {
-    SkinnyParams b;    // operands (geometry fields of the fallback kernel unused except ntc, nkb, group_blocks)
+    SkinnyParams b;    // operands (of its geometry fields only ntc, nkb are used)
     int N, K, rank;
     int n_problems;
+    int swiglu;        // 1: the weight is a fused gate|up matrix, the output is silu(gate) * up
     int sk;            // k splits (warps of one CTA): 1, 2, 4 or 8
     int kb_per_split;
-    int npairs;        // warp items per problem and split: tile pairs
+    int npairs;        // tile pairs per problem
     int ips;           // iterations (8 warp items) per problem
     int stages;        // ring depth
     int stage_bytes;
     int off_xs, off_ox, off_as, off_ring, off_red;  // shared memory carve-up (bytes)
 };
 
-// ---- mbarrier / bulk copy primitives -----------------------------------------------------------
+// ---- shared memory, mbarrier and bulk copy primitives ------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -94,7 +110,109 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// ---- one k block of one tile against preloaded activation fragments ---------------------------
+// D(16x8, s32) = A(16x32, s8, row) * B(32x8, s8, col) + C.  Lane = 4g+t owns
+//   a0 = (row g, k 4t..4t+3)  a1 = (row g+8, same k)  a2 = (row g, k 16+4t..)  a3 = (row g+8, k 16+4t..)
+//   b0 = (k 4t..4t+3 ; col g) b1 = (k 16+4t.. ; col g);  d0,d1 = (row g ; col 2t,2t+1)  d2,d3 = (row g+8)
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+
+// ---- integer path: staging of the activations ----------------------------------------------------
+// x rows -> int8 digit fragments.  Per row and k block: sh = 14 - exponent(max |x|), v = rint(x * 2^sh)
+// (|v| < 2^15, exact for every x within 2^-13 of the block maximum), v = 256*d1 + d0 with d0, d1 in
+// [-128, 127].  Fragment order: for the lane-t chunk of a block, word u, op m: b0 = digits of codes
+// {2m, 2m+4, 2m+8, 2m+12}, b1 = codes {2m+1, ...} (2-bit); word u: b0 = even codes, b1 = odd codes
+// (4-bit).  Layout: xs[kb][piece][col = 2*row + digit][t] of uint4, piece = u (2-bit) / 0 (4-bit);
+// ox[kb][row] = (2^-sh, sum of x).
+template <int FMT>
+__device__ __forceinline__ void stage_x_i8(const SkinnyParams& p, uint4* xs, float2* ox, int nkb, int ncol, int e0,
+                                           int cnt, int K) {
+    using F = Fmt<FMT>;
+    constexpr int P8 = F::UPK / 4;  // pieces per block: 2 (2-bit), 1 (4-bit)
+    const int nrow = ncol >> 1;
+    const int total = nrow * nkb * F::UPK;
+    for (int base = 0; base < total; base += kThreads) {
+        const int u = base + (int)threadIdx.x;
+        const bool valid = u < total;
+        const int row = valid ? u / (nkb * F::UPK) : 0;
+        const int rem = valid ? u % (nkb * F::UPK) : 0;
+        const int kb = rem / F::UPK, wi = rem % F::UPK;
+        const int k0 = kb * F::KB + wi * 16;
+        __align__(16) __half v[16];
+        const bool live = valid && row < cnt && k0 < K;
+        if (live) {
+            const int entry = e0 + row;
+            const long long xr = p.entry_row ? p.entry_row[entry] : entry;
+            const __half* src = p.x + xr * p.ldx + k0;
+            if (p.x_vec && k0 + 16 <= K) {
+                *reinterpret_cast<uint4*>(&v[0]) = __ldg(reinterpret_cast<const uint4*>(src));
+                *reinterpret_cast<uint4*>(&v[8]) = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = (k0 + j < K) ? src[j] : __float2half(0.f);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __float2half(0.f);
+        }
+        float f[16], mx = 0.f, sx = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            f[j] = __half2float(v[j]);
+            mx = fmaxf(mx, fabsf(f[j]));
+            sx += f[j];
+        }
+#pragma unroll
+        for (int d = 1; d < F::UPK; d <<= 1) {
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+            sx += __shfl_xor_sync(0xffffffffu, sx, d);
+        }
+        int ex = 0;
+        if (mx > 0.f) (void)frexpf(mx, &ex);  // mx = m * 2^ex, m in [0.5, 1)
+        const int sh = 14 - ex;
+        const float scale = ldexpf(1.f, sh);
+        int d0[16], d1[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int q = __float2int_rn(f[j] * scale);
+            d1[j] = (q + 128) >> 8;
+            d0[j] = q - (d1[j] << 8);
+        }
+        // byte order of a word's fragment pair (b0, b1)
+        auto pack4 = [](const int* d, int c0, int c1, int c2, int c3) -> uint32_t {
+            return (uint32_t)(d[c0] & 0xff) | ((uint32_t)(d[c1] & 0xff) << 8) | ((uint32_t)(d[c2] & 0xff) << 16) |
+                   ((uint32_t)(d[c3] & 0xff) << 24);
+        };
+        if (valid) {
+            uint4 lo, hi;  // digit 0, digit 1
+            int t, piece;
+            if constexpr (FMT == GLQ_FMT_Q2) {
+                t = wi >> 1;
+                piece = wi & 1;
+                lo = make_uint4(pack4(d0, 0, 4, 8, 12), pack4(d0, 1, 5, 9, 13), pack4(d0, 2, 6, 10, 14),
+                                pack4(d0, 3, 7, 11, 15));
+                hi = make_uint4(pack4(d1, 0, 4, 8, 12), pack4(d1, 1, 5, 9, 13), pack4(d1, 2, 6, 10, 14),
+                                pack4(d1, 3, 7, 11, 15));
+            } else {
+                t = wi;
+                piece = 0;
+                lo = make_uint4(pack4(d0, 0, 2, 4, 6), pack4(d0, 1, 3, 5, 7), pack4(d0, 8, 10, 12, 14),
+                                pack4(d0, 9, 11, 13, 15));
+                hi = make_uint4(pack4(d1, 0, 2, 4, 6), pack4(d1, 1, 3, 5, 7), pack4(d1, 8, 10, 12, 14),
+                                pack4(d1, 9, 11, 13, 15));
+            }
+            xs[((size_t)(kb * P8 + piece) * ncol + 2 * row) * 4 + t] = lo;
+            xs[((size_t)(kb * P8 + piece) * ncol + 2 * row + 1) * 4 + t] = hi;
+            if (wi == 0) ox[kb * nrow + row] = make_float2(ldexpf(1.f, -sh), sx);
+        }
+    }
+}
+
+// ---- fp16 path: one k block of one tile against preloaded activation fragments --------------------
 template <int FMT, int NTT>
 __device__ __forceinline__ void tile_block(const uint4 q, const uint4 (&bx)[NTT][4], uint32_t TL, uint32_t TH,
                                            float (&c)[NTT][4]) {
@@ -135,25 +253,62 @@ __device__ __forceinline__ void tile_block(const uint4 q, const uint4 (&bx)[NTT]
     }
 }
 
+// ---- integer path: one k block of one tile; bx[nt][piece] are the digit fragments ------------------
+template <int FMT, int NT>
+__device__ __forceinline__ void tile_block_i8(const uint4 q, const uint4 (&bx)[NT][2], int (&c)[NT][4]) {
+    if constexpr (FMT == GLQ_FMT_Q2) {
+        const uint32_t m = 0x03030303u;
+        const uint32_t wa[2] = {q.x, q.y}, wb[2] = {q.z, q.w};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const uint32_t a0 = wa[u] & m, a1 = (wa[u] >> 2) & m, a2 = (wa[u] >> 4) & m, a3 = (wa[u] >> 6) & m;
+            const uint32_t b0 = wb[u] & m, b1 = (wb[u] >> 2) & m, b2 = (wb[u] >> 4) & m, b3 = (wb[u] >> 6) & m;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 x = bx[nt][u];
+                if (u == 0)
+                    imma16832(c[nt], a0, b0, a1, b1, x.x, x.y, 0, 0, 0, 0);
+                else
+                    imma16832(c[nt], a0, b0, a1, b1, x.x, x.y, c[nt][0], c[nt][1], c[nt][2], c[nt][3]);
+                imma16832(c[nt], a2, b2, a3, b3, x.z, x.w, c[nt][0], c[nt][1], c[nt][2], c[nt][3]);
+            }
+        }
+    } else {  // Q4: a word holds 8 codes = the A operand of one op
+        const uint32_t m = 0x0F0F0F0Fu;
+        const uint32_t a0 = q.x & m, a1 = (q.x >> 4) & m, a2 = q.y & m, a3 = (q.y >> 4) & m;
+        const uint32_t b0 = q.z & m, b1 = (q.z >> 4) & m, b2 = q.w & m, b3 = (q.w >> 4) & m;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint4 x = bx[nt][0];
+            imma16832(c[nt], a0, b0, a1, b1, x.x, x.y, 0, 0, 0, 0);
+            imma16832(c[nt], a2, b2, a3, b3, x.z, x.w, c[nt][0], c[nt][1], c[nt][2], c[nt][3]);
+        }
+    }
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------
-template <int FMT, int NW, int NTT>
+// I8 = true : NT tiles of 4 activation rows (integer path, affine formats only)
+// I8 = false: NT tiles of 8 activation rows (fp16 path)
+template <int FMT, bool I8, int NT>
 __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams sp) {
     using F = Fmt<FMT>;
     static_assert(FMT != GLQ_FMT_F16, "dense weights use the fallback kernel");
+    static_assert(!I8 || FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4, "integer path needs integer codes");
     constexpr bool kAffine = (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4);
-    constexpr int kPieces = F::XS / 4;                      // uint4 fragments per k block, lane and column
-    constexpr int kCodeBytes = kStreamCB * 512;              // per tile and stage
-    constexpr int kSzBytes = kAffine ? kStreamCB * 64 : 0;   // per tile and stage
+    constexpr int BB = block_bytes<FMT>();
+    constexpr int kPieces = I8 ? F::UPK / 4 : F::XS / 4;  // uint4 fragments per k block, lane and column
+    constexpr int kRowsPerTile = I8 ? 4 : 8;
+    constexpr int kRows = kRowsPerTile * NT;
     const SkinnyParams& p = sp.b;
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int N = sp.N, K = sp.K, rank = sp.rank;
-    const int ntiles = (N + kRowTile - 1) / kRowTile;
-    const int nkb = p.nkb, gb = p.group_blocks, ntc = p.ntc;
-    const int G = (nkb + gb - 1) / gb;
+    const int nkb = p.nkb, ntc = p.ntc;
     const int S = sp.stages, sk = sp.sk;
+    const bool swiglu = sp.swiglu != 0;
+    const int ns = (rank + 63) / 64;
 
     const int n_live = p.n_slots ? min(__ldg(p.n_slots), sp.n_problems) : sp.n_problems;
     const long total = (long)n_live * sp.ips;
@@ -165,106 +320,67 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
     uint4* xs = reinterpret_cast<uint4*>(smem + sp.off_xs);
     float2* ox = reinterpret_cast<float2*>(smem + sp.off_ox);
     __half* as = reinterpret_cast<__half*>(smem + sp.off_as);
-    unsigned char* ring = smem + sp.off_ring + (size_t)w * S * sp.stage_bytes;
     float4* red = reinterpret_cast<float4*>(smem + sp.off_red);
+    const uint32_t xs_a = smem_u32(xs), ox_a = smem_u32(ox);
+    const uint32_t ring_a = smem_u32(smem + sp.off_ring) + (uint32_t)(w * S * sp.stage_bytes);
+    const uint32_t bar_a = smem_u32(bars) + (uint32_t)(w * kMaxStages * 8);
 
     if (lane == 0) {
-        for (int s = 0; s < S; ++s) mbar_init(smem_u32(&bars[w * kMaxStages + s]), 1);
+        for (int s = 0; s < S; ++s) mbar_init(bar_a + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
-    // ---- item description, shared by the fetch cursor and the compute cursor ----
+    // ---- per-slot data and item description: one copy for the fetch cursor, one for the compute loop
+    struct Slot {
+        int slot = -1, cnt = 0, e0 = 0;
+        const unsigned char* codes = nullptr;
+        const unsigned char* sv = nullptr;
+        const float* norms = nullptr;
+        const float* centroids = nullptr;
+        const __half* bias = nullptr;
+    };
+    auto load_slot = [&](Slot& sc, int slot) {
+        if (slot == sc.slot) return;
+        sc.slot = slot;
+        sc.cnt = min(p.slot_count ? __ldg(p.slot_count + slot) : p.max_rows, p.max_rows);
+        sc.e0 = p.slot_offset ? __ldg(p.slot_offset + slot) : slot * p.rows_stride;
+        const int widx = p.slot_index ? __ldg(p.slot_index + slot) : slot;
+        const glq_weight_t* W = p.table ? p.table + widx : &p.w;
+        sc.codes = reinterpret_cast<const unsigned char*>(W->codes);
+        sc.sv = (rank > 0 && p.a[0] != nullptr) ? reinterpret_cast<const unsigned char*>(W->sv) : nullptr;
+        sc.norms = W->norms;
+        sc.centroids = W->centroids;
+        sc.bias = reinterpret_cast<const __half*>(W->bias);
+    };
+    // item of warp w in iteration it: (slot, pair, split) -> k range and chunk counts
     struct Item {
-        int it, slot, pair, s, kb_lo, kb_hi, ncode, nch, rt[2];
-        bool valid, tile_ok[2];
-        const unsigned char* codes[2];
-        const unsigned char* sz[2];
-        const unsigned char* sv[2];
+        int slot, pair, s, kb_lo, kb_hi, ncode, nch;
+        bool valid;
     };
-    struct SlotCache {
-        int slot = -1, cnt = 0;
-        glq_weight_t W[NW];
-    };
-    auto resolve = [&](Item& im, SlotCache& sc, int it) {
-        im.it = it;
-        im.slot = it / sp.ips;
+    auto make_item = [&](Item& im, const Slot& sc, int it) {
         const int local = (it % sp.ips) * kWarpsPerCta + w;
+        im.slot = it / sp.ips;
         im.pair = local / sk;
         im.s = local % sk;
-        if (im.slot != sc.slot) {
-            sc.slot = im.slot;
-            sc.cnt = min(p.slot_count ? __ldg(p.slot_count + im.slot) : p.max_rows, p.max_rows);
-            const int widx = p.slot_index ? __ldg(p.slot_index + im.slot) : im.slot;
-#pragma unroll
-            for (int i = 0; i < NW; ++i) sc.W[i] = p.table[i] ? p.table[i][widx] : p.w[i];
-        }
         im.valid = im.pair < sp.npairs && sc.cnt > 0;
         im.kb_lo = im.s * sp.kb_per_split;
         im.kb_hi = min(nkb, im.kb_lo + sp.kb_per_split);
         im.ncode = im.kb_hi > im.kb_lo ? (im.kb_hi - im.kb_lo + kStreamCB - 1) / kStreamCB : 0;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int wi = NW == 2 ? j : 0;
-            im.rt[j] = NW == 2 ? im.pair : 2 * im.pair + j;
-            im.tile_ok[j] = im.rt[j] < ntiles;
-            im.codes[j] = reinterpret_cast<const unsigned char*>(sc.W[wi].codes);
-            im.sz[j] = reinterpret_cast<const unsigned char*>(sc.W[wi].sz);
-            im.sv[j] = reinterpret_cast<const unsigned char*>(sc.W[wi].sv);
-        }
-        const bool has_lr = rank > 0 && im.sv[0] != nullptr && p.a[0] != nullptr;
-        im.nch = im.ncode + ((im.s == 0 && has_lr) ? (rank + 63) / 64 : 0);
+        im.nch = im.ncode + ((im.s == 0 && sc.sv != nullptr) ? ns : 0);
     };
 
-    // ---- fetch side: issue the copies of chunk c of item im into ring stage (seq % S) ----
-    auto issue = [&](const Item& im, int c, int seq) {
-        const int stage = seq % S;
-        const uint32_t bar = smem_u32(&bars[w * kMaxStages + stage]);
-        const uint32_t dst = smem_u32(ring + (size_t)stage * sp.stage_bytes);
-        if (c < im.ncode) {
-            const int kb0 = im.kb_lo + c * kStreamCB;
-            const int nblk = min(kStreamCB, im.kb_hi - kb0);
-            const int g0 = kb0 / gb, g1 = (kb0 + nblk - 1) / gb;
-            if (lane == 0) {
-                uint32_t bytes = 0;
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
-                    if (im.tile_ok[j]) bytes += nblk * 512 + (kAffine ? (g1 - g0 + 1) * 64 : 0);
-                mbar_expect_tx(bar, bytes);
-#pragma unroll
-                for (int j = 0; j < 2; ++j)
-                    if (im.tile_ok[j]) {
-                        bulk_g2s(dst + j * kCodeBytes, im.codes[j] + ((size_t)im.rt[j] * nkb + kb0) * 512, nblk * 512,
-                                 bar);
-                        if constexpr (kAffine)
-                            bulk_g2s(dst + 2 * kCodeBytes + j * kSzBytes, im.sz[j] + ((size_t)im.rt[j] * G + g0) * 64,
-                                     (g1 - g0 + 1) * 64, bar);
-                    }
-            }
-        } else {
-            // 16 rows x (up to) 64 columns of SV per tile: one 128-byte copy per row and lane
-            const int r0 = (c - im.ncode) * 64;
-            const int j = lane >> 4, row = im.rt[j] * kRowTile + (lane & 15);
-            const uint32_t nb = (im.tile_ok[j] && row < N) ? (uint32_t)min(64, rank - r0) * 2u : 0u;
-            uint32_t tot = nb;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-            if (lane == 0) mbar_expect_tx(bar, tot);
-            __syncwarp();
-            if (nb) bulk_g2s(dst + j * 2048 + (lane & 15) * 128, im.sv[j] + ((size_t)row * rank + r0) * 2, nb, bar);
-        }
-    };
-
-    // The fetch cursor runs over the same (item, chunk) sequence as the compute loop, S stages ahead.
+    // ---- fetch cursor: runs over the same (item, chunk) sequence as the compute loop, S stages ahead
+    Slot fs, cs;
     Item fi;
-    SlotCache fcache, ccache;
     int f_it = it_lo, f_c = 0, fseq = 0, cseq = 0;
     bool f_live = false;
-    auto fetch_seek = [&]() {  // position the fetch cursor on the next item that has chunks
+    auto fetch_seek = [&]() {
         f_live = false;
         while (f_it < it_hi) {
-            resolve(fi, fcache, f_it);
+            load_slot(fs, f_it / sp.ips);
+            make_item(fi, fs, f_it);
             if (fi.valid && fi.nch > 0) {
                 f_live = true;
                 return;
@@ -273,7 +389,23 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
         }
     };
     auto fetch_one = [&]() {
-        issue(fi, f_c, fseq);
+        if (lane == 0) {
+            const int stage = fseq % S;
+            const uint32_t bar = bar_a + 8 * stage;
+            const uint32_t dst = ring_a + (uint32_t)(stage * sp.stage_bytes);
+            const void* src;
+            uint32_t bytes;
+            if (f_c < fi.ncode) {
+                const int kb0 = fi.kb_lo + f_c * kStreamCB;
+                bytes = (uint32_t)(min(kStreamCB, fi.kb_hi - kb0) * 2 * BB);
+                src = fs.codes + ((size_t)fi.pair * nkb + kb0) * (2 * BB);
+            } else {
+                bytes = 4096;
+                src = fs.sv + ((size_t)fi.pair * ns + (f_c - fi.ncode)) * 4096;
+            }
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(dst, src, bytes, bar);
+        }
         ++fseq;
         if (++f_c >= fi.nch) {
             f_c = 0;
@@ -284,114 +416,136 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
     fetch_seek();
     while (f_live && fseq < S) fetch_one();
 
-    uint32_t TL[NW], TH[NW];
-    int staged_slot = -1;
-    int red_par = 0;
+    uint32_t TL = 0, TH = 0;
+    int staged_slot = -1, red_par = 0;
     bool dead = false;
+    constexpr int ncol_i8 = 2 * kRows;  // digit columns staged on the integer path
 
     for (int it = it_lo; it < it_hi; ++it) {
+        load_slot(cs, it / sp.ips);
         Item im;
-        resolve(im, ccache, it);
-        const int cnt = ccache.cnt;
-        const glq_weight_t(&W)[NW] = ccache.W;
+        make_item(im, cs, it);
+        const int cnt = cs.cnt, e0 = cs.e0;
 
-        // ---- activations of a new problem: stage x (all of K) and a = x.U once per CTA ----
+        // ---- activations of a new problem: staged once per CTA ----
         if (im.slot != staged_slot) {
             __syncthreads();
-            const int e0s = p.slot_offset ? __ldg(p.slot_offset + im.slot) : im.slot * p.rows_stride;
             if (cnt > 0) {
-                stage_x<FMT>(p, xs, ox, 0, nkb, e0s, 0, cnt, K);
-                if (rank > 0 && p.a[0] != nullptr) {
-                    for (int idx = tid; idx < NW * ntc * (rank / 8); idx += kThreads) {
-                        const int i = idx / (ntc * (rank / 8)), rem = idx % (ntc * (rank / 8));
-                        const int col = rem / (rank / 8), ch = rem % (rank / 8);
+                if constexpr (I8)
+                    stage_x_i8<FMT>(p, xs, ox, nkb, ncol_i8, e0, cnt, K);
+                else
+                    stage_x<FMT>(p, xs, ox, 0, nkb, e0, 0, cnt, K);
+                if (cs.sv != nullptr) {
+                    const int na = swiglu ? 2 : 1, r8 = rank / 8;
+                    for (int idx = tid; idx < na * kRows * r8; idx += kThreads) {
+                        const int i = idx / (kRows * r8), rem = idx % (kRows * r8);
+                        const int row = rem / r8, ch = rem % r8;
                         uint4 v = make_uint4(0, 0, 0, 0);
-                        if (col < cnt && p.a[i] != nullptr)
-                            v = __ldg(reinterpret_cast<const uint4*>(p.a[i] + (size_t)(e0s + col) * p.lda) + ch);
+                        if (row < cnt && p.a[i] != nullptr)
+                            v = __ldg(reinterpret_cast<const uint4*>(p.a[i] + (size_t)(e0 + row) * p.lda) + ch);
                         reinterpret_cast<uint4*>(as)[idx] = v;
                     }
                 }
             }
             __syncthreads();
             staged_slot = im.slot;
-#pragma unroll
-            for (int i = 0; i < NW; ++i) {
-                TL[i] = TH[i] = 0;
-                if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(W[i].centroids, TL[i], TH[i]);
-            }
+            if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(cs.centroids, TL, TH);
         }
         if (!im.valid) continue;
-        const int e0 = p.slot_offset ? __ldg(p.slot_offset + im.slot) : im.slot * p.rows_stride;
 
-        float acc[2][NTT][4];
+        // accumulators [tile in pair][activation tile]: {row g: 2 values, row g+8: 2 values}.
+        // fp16 path: the two values are activation rows 2t, 2t+1 of the tile; integer path: only
+        // [0] and [2] are used (activation row t of the tile)
+        float acc[2][NT][4];
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int tt = 0; tt < NTT; ++tt)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) acc[j][tt][q] = 0.f;
-
-        // values the epilogue needs, requested early
-        float nrm[2][2] = {{1.f, 1.f}, {1.f, 1.f}};
-        if constexpr (FMT == GLQ_FMT_T2) {
-            if (im.s == 0) {
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int r0 = min(im.rt[j] * kRowTile + g, N - 1), r1 = min(im.rt[j] * kRowTile + g + 8, N - 1);
-                    nrm[j][0] = __ldg(W[NW == 2 ? j : 0].norms + r0);
-                    nrm[j][1] = __ldg(W[NW == 2 ? j : 0].norms + r1);
-                }
-            }
-        }
+                for (int q = 0; q < 4; ++q) acc[j][nt][q] = 0.f;
 
         // ---- code chunks ----
         for (int c = 0; c < im.ncode; ++c) {
             const int stage = cseq % S;
-            mbar_wait(smem_u32(&bars[w * kMaxStages + stage]), (cseq / S) & 1, dead);
-            const unsigned char* st = ring + (size_t)stage * sp.stage_bytes;
+            mbar_wait(bar_a + 8 * stage, (cseq / S) & 1, dead);
+            const uint32_t st = ring_a + (uint32_t)(stage * sp.stage_bytes);
             const int kb0 = im.kb_lo + c * kStreamCB;
             const int nblk = min(kStreamCB, im.kb_hi - kb0);
-            const int g0 = kb0 / gb;
-#pragma unroll 1
+#pragma unroll 2
             for (int b = 0; b < nblk; ++b) {
                 const int kb = kb0 + b;
-                uint4 bx[NTT][4];
+                if constexpr (I8) {
+                    uint4 bx[NT][2];
+                    float2 o[NT];
 #pragma unroll
-                for (int tt = 0; tt < NTT; ++tt) {
-                    const int col = (tt * 8 + g) & (ntc - 1);
+                    for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-                    for (int i = 0; i < kPieces; ++i)
-                        bx[tt][i] = (NTT > 1 || g < ntc) ? xs[(((size_t)kb * kPieces + i) * ntc + col) * 4 + t]
-                                                        : make_uint4(0, 0, 0, 0);
-                }
+                        for (int i = 0; i < kPieces; ++i)
+                            bx[nt][i] = lds128(
+                                xs_a + (uint32_t)((((kb * kPieces + i) * ncol_i8) + nt * 8 + g) * 4 + t) * 16u);
+                        const uint2 ov = lds64(ox_a + (uint32_t)(kb * kRows + nt * 4 + t) * 8u);
+                        o[nt] = make_float2(__uint_as_float(ov.x), __uint_as_float(ov.y));
+                    }
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    if (!im.tile_ok[j]) continue;
-                    const uint4 q = reinterpret_cast<const uint4*>(st + j * kCodeBytes)[b * 32 + lane];
-                    if constexpr (kAffine) {
-                        float cc[NTT][4];
-#pragma unroll
-                        for (int tt = 0; tt < NTT; ++tt)
-#pragma unroll
-                            for (int q4 = 0; q4 < 4; ++q4) cc[tt][q4] = 0.f;
-                        tile_block<FMT, NTT>(q, bx, 0, 0, cc);
-                        const uint2 szv =
-                            reinterpret_cast<const uint2*>(st + 2 * kCodeBytes + j * kSzBytes)[(kb / gb - g0) * 8 + g];
+                    for (int j = 0; j < 2; ++j) {
+                        const uint32_t blk = st + (uint32_t)((b * 2 + j) * BB);
+                        const uint4 q = lds128(blk + lane * 16);
+                        const uint2 szv = lds64(blk + 512 + g * 8);
+                        int ci[NT][4];
+                        tile_block_i8<FMT, NT>(q, bx, ci);
                         const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv.x);
                         const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv.y);
                         const float s0 = __low2float(sz0), z0 = __high2float(sz0);
                         const float s1 = __low2float(sz1), z1 = __high2float(sz1);
 #pragma unroll
-                        for (int tt = 0; tt < NTT; ++tt) {
-                            const int col = (tt * 8 + 2 * t) & (ntc - 1);
-                            const float4 o = *reinterpret_cast<const float4*>(&ox[kb * ntc + col]);
-                            acc[j][tt][0] = fmaf(s0, fmaf(-z0, o.y, cc[tt][0] - o.x), acc[j][tt][0]);
-                            acc[j][tt][1] = fmaf(s0, fmaf(-z0, o.w, cc[tt][1] - o.z), acc[j][tt][1]);
-                            acc[j][tt][2] = fmaf(s1, fmaf(-z1, o.y, cc[tt][2] - o.x), acc[j][tt][2]);
-                            acc[j][tt][3] = fmaf(s1, fmaf(-z1, o.w, cc[tt][3] - o.z), acc[j][tt][3]);
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const float f0 = (float)(ci[nt][0] + (ci[nt][1] << 8)) * o[nt].x;
+                            const float f1 = (float)(ci[nt][2] + (ci[nt][3] << 8)) * o[nt].x;
+                            acc[j][nt][0] = fmaf(s0, fmaf(-z0, o[nt].y, f0), acc[j][nt][0]);
+                            acc[j][nt][2] = fmaf(s1, fmaf(-z1, o[nt].y, f1), acc[j][nt][2]);
                         }
-                    } else {
-                        tile_block<FMT, NTT>(q, bx, TL[NW == 2 ? j : 0], TH[NW == 2 ? j : 0], acc[j]);
+                    }
+                } else {
+                    uint4 bx[NT][4];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int col = (nt * 8 + g) & (ntc - 1);
+#pragma unroll
+                        for (int i = 0; i < kPieces; ++i)
+                            bx[nt][i] = (NT > 1 || g < ntc)
+                                            ? lds128(xs_a + (uint32_t)(((kb * kPieces + i) * ntc + col) * 4 + t) * 16u)
+                                            : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const uint32_t blk = st + (uint32_t)((b * 2 + j) * BB);
+                        const uint4 q = lds128(blk + lane * 16);
+                        if constexpr (kAffine) {
+                            const uint2 szv = lds64(blk + 512 + g * 8);
+                            float cc[NT][4];
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                                for (int q4 = 0; q4 < 4; ++q4) cc[nt][q4] = 0.f;
+                            tile_block<FMT, NT>(q, bx, 0, 0, cc);
+                            const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv.x);
+                            const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv.y);
+                            const float s0 = __low2float(sz0), z0 = __high2float(sz0);
+                            const float s1 = __low2float(sz1), z1 = __high2float(sz1);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const int col = (nt * 8 + 2 * t) & (ntc - 1);
+                                const uint4 ov = lds128(ox_a + (uint32_t)(kb * ntc + col) * 8u);
+                                const float ox0 = __uint_as_float(ov.x), xx0 = __uint_as_float(ov.y);
+                                const float ox1 = __uint_as_float(ov.z), xx1 = __uint_as_float(ov.w);
+                                acc[j][nt][0] = fmaf(s0, fmaf(-z0, xx0, cc[nt][0] - ox0), acc[j][nt][0]);
+                                acc[j][nt][1] = fmaf(s0, fmaf(-z0, xx1, cc[nt][1] - ox1), acc[j][nt][1]);
+                                acc[j][nt][2] = fmaf(s1, fmaf(-z1, xx0, cc[nt][2] - ox0), acc[j][nt][2]);
+                                acc[j][nt][3] = fmaf(s1, fmaf(-z1, xx1, cc[nt][3] - ox1), acc[j][nt][3]);
+                            }
+                        } else {
+                            tile_block<FMT, NT>(q, bx, TL, TH, acc[j]);
+                        }
                     }
                 }
             }
@@ -400,16 +554,16 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
             if (f_live) fetch_one();
         }
 
-        // ---- k splits of this tile pair: fixed-order reduction through shared memory ----
+        // ---- k splits of this pair: fixed-order reduction through shared memory ----
         if (sk > 1) {
-            float4* rbuf = red + (size_t)red_par * (kWarpsPerCta * 2 * NTT * 32);
+            float4* rbuf = red + (size_t)red_par * (kWarpsPerCta * 2 * NT * 32);
             if (im.s != 0) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
-                    for (int tt = 0; tt < NTT; ++tt)
-                        rbuf[((w * 2 + j) * NTT + tt) * 32 + lane] =
-                            make_float4(acc[j][tt][0], acc[j][tt][1], acc[j][tt][2], acc[j][tt][3]);
+                    for (int nt = 0; nt < NT; ++nt)
+                        rbuf[((w * 2 + j) * NT + nt) * 32 + lane] =
+                            make_float4(acc[j][nt][0], acc[j][nt][1], acc[j][nt][2], acc[j][nt][3]);
             }
             named_bar_sync(1 + w / sk, sk * 32);
             if (im.s == 0) {
@@ -417,52 +571,53 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int tt = 0; tt < NTT; ++tt) {
-                            const float4 v = rbuf[(((w + s2) * 2 + j) * NTT + tt) * 32 + lane];
-                            acc[j][tt][0] += v.x;
-                            acc[j][tt][1] += v.y;
-                            acc[j][tt][2] += v.z;
-                            acc[j][tt][3] += v.w;
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const float4 v = rbuf[(((w + s2) * 2 + j) * NT + nt) * 32 + lane];
+                            acc[j][nt][0] += v.x;
+                            acc[j][nt][1] += v.y;
+                            acc[j][nt][2] += v.z;
+                            acc[j][nt][3] += v.w;
                         }
             }
             red_par ^= 1;
         }
         if (im.s != 0) continue;
 
-        // ---- low-rank term: SV chunks from the ring, a from shared memory ----
-        float lo[2][NTT][4];
+        // ---- low-rank term on the fp16 op: SV chunks from the ring, a from shared memory.
+        // lo[j][m] covers activation rows 8m + 2t, 8m + 2t + 1 (the columns of the op)
+        constexpr int NM = (kRows + 7) / 8;
+        float lo[2][NM][4];
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int tt = 0; tt < NTT; ++tt)
+            for (int m = 0; m < NM; ++m)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) lo[j][tt][q] = 0.f;
+                for (int q = 0; q < 4; ++q) lo[j][m][q] = 0.f;
         const int nsv = im.nch - im.ncode;
         for (int c = 0; c < nsv; ++c) {
             const int stage = cseq % S;
-            mbar_wait(smem_u32(&bars[w * kMaxStages + stage]), (cseq / S) & 1, dead);
-            const unsigned char* st = ring + (size_t)stage * sp.stage_bytes;
-            // every lane runs the tensor-core op (it is warp-wide); lanes beyond the rank feed zeros
+            mbar_wait(bar_a + 8 * stage, (cseq / S) & 1, dead);
+            const uint32_t st = ring_a + (uint32_t)(stage * sp.stage_bytes);
+            // every lane runs the (warp-wide) op; lanes beyond the rank feed zeros
             const int cc0 = c * 64 + 16 * t;
             const bool in_rank = cc0 < rank;
             const uint4 z4 = make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                if (!im.tile_ok[j]) continue;
-                const uint4* pa = reinterpret_cast<const uint4*>(st + j * 2048 + g * 128 + t * 32);
-                const uint4* pb = reinterpret_cast<const uint4*>(st + j * 2048 + (g + 8) * 128 + t * 32);
-                const uint4 sa0 = in_rank ? pa[0] : z4, sa1 = in_rank ? pa[1] : z4;
-                const uint4 sb0 = in_rank ? pb[0] : z4, sb1 = in_rank ? pb[1] : z4;
+                const uint32_t pa = st + (uint32_t)((j * 16 + g) * 128 + t * 32);
+                const uint4 sa0 = in_rank ? lds128(pa) : z4, sa1 = in_rank ? lds128(pa + 16) : z4;
+                const uint4 sb0 = in_rank ? lds128(pa + 8 * 128) : z4, sb1 = in_rank ? lds128(pa + 8 * 128 + 16) : z4;
 #pragma unroll
-                for (int tt = 0; tt < NTT; ++tt) {
-                    const int col = (tt * 8 + g) & (ntc - 1);
-                    const uint4* pav =
-                        reinterpret_cast<const uint4*>(as + ((size_t)(NW == 2 ? j : 0) * ntc + col) * rank + cc0);
-                    const uint4 av0 = in_rank ? pav[0] : z4, av1 = in_rank ? pav[1] : z4;
-                    mma16816(lo[j][tt], sa0.x, sb0.x, sa0.y, sb0.y, av0.x, av0.y);
-                    mma16816(lo[j][tt], sa0.z, sb0.z, sa0.w, sb0.w, av0.z, av0.w);
-                    mma16816(lo[j][tt], sa1.x, sb1.x, sa1.y, sb1.y, av1.x, av1.y);
-                    mma16816(lo[j][tt], sa1.z, sb1.z, sa1.w, sb1.w, av1.z, av1.w);
+                for (int m = 0; m < NM; ++m) {
+                    const int row = m * 8 + g;
+                    const bool ok = in_rank && row < kRows;
+                    const uint4* pav = reinterpret_cast<const uint4*>(
+                        as + ((size_t)(swiglu ? j : 0) * kRows + (ok ? row : 0)) * rank + (ok ? cc0 : 0));
+                    const uint4 av0 = ok ? pav[0] : z4, av1 = ok ? pav[1] : z4;
+                    mma16816(lo[j][m], sa0.x, sb0.x, sa0.y, sb0.y, av0.x, av0.y);
+                    mma16816(lo[j][m], sa0.z, sb0.z, sa0.w, sb0.w, av0.z, av0.w);
+                    mma16816(lo[j][m], sa1.x, sb1.x, sa1.y, sb1.y, av1.x, av1.y);
+                    mma16816(lo[j][m], sa1.z, sb1.z, sa1.w, sb1.w, av1.z, av1.w);
                 }
             }
             __syncwarp();
@@ -470,48 +625,69 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
             if (f_live) fetch_one();
         }
 
-        // ---- epilogue ----
-        float res[2][NTT][4];
+        // ---- epilogue: this lane's activation rows, weight rows g and g+8 of both tiles ----
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int wi = NW == 2 ? j : 0;
-            const __half* bias = reinterpret_cast<const __half*>(W[wi].bias);
-            const int r0c = min(im.rt[j] * kRowTile + g, N - 1), r1c = min(im.rt[j] * kRowTile + g + 8, N - 1);
-            const float b0 = bias ? __half2float(__ldg(bias + r0c)) : 0.f;
-            const float b1 = bias ? __half2float(__ldg(bias + r1c)) : 0.f;
+        for (int nt = 0; nt < NT; ++nt) {
+            constexpr int kVals = I8 ? 1 : 2;  // activation rows this lane owns per tile
 #pragma unroll
-            for (int tt = 0; tt < NTT; ++tt)
+            for (int e = 0; e < kVals; ++e) {
+                const int row = I8 ? (nt * 4 + t) : (nt * 8 + 2 * t + e);
+                float val[2][2];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float v = round16(acc[j][tt][q] * nrm[j][q >> 1]);
-                    if (nsv > 0) v = round16(v + round16(lo[j][tt][q]));
-                    if (bias) v = round16(v + (q < 2 ? b0 : b1));
-                    res[j][tt][q] = v;
+                for (int j = 0; j < 2; ++j) {
+                    float n0 = 1.f, n1 = 1.f;
+                    if constexpr (FMT == GLQ_FMT_T2) {
+                        n0 = __ldg(cs.norms + ((size_t)im.pair * 2 + j) * 16 + g);
+                        n1 = __ldg(cs.norms + ((size_t)im.pair * 2 + j) * 16 + g + 8);
+                    }
+                    float v0 = round16(acc[j][nt][I8 ? 0 : e] * n0);
+                    float v1 = round16(acc[j][nt][I8 ? 2 : 2 + e] * n1);
+                    if (nsv > 0) {
+                        float l0, l1;
+                        if constexpr (I8) {
+                            // the low-rank op holds rows 2t', 2t'+1 in lane t': fetch this lane's row
+                            const int src = (g << 2) | ((row & 7) >> 1);
+                            const float a0 = __shfl_sync(0xffffffffu, lo[j][0][0], src);
+                            const float a1 = __shfl_sync(0xffffffffu, lo[j][0][1], src);
+                            const float b0 = __shfl_sync(0xffffffffu, lo[j][0][2], src);
+                            const float b1 = __shfl_sync(0xffffffffu, lo[j][0][3], src);
+                            l0 = (row & 1) ? a1 : a0;
+                            l1 = (row & 1) ? b1 : b0;
+                        } else {
+                            l0 = lo[j][nt][e];
+                            l1 = lo[j][nt][2 + e];
+                        }
+                        v0 = round16(v0 + round16(l0));
+                        v1 = round16(v1 + round16(l1));
+                    }
+                    val[j][0] = v0;
+                    val[j][1] = v1;
                 }
-        }
-#pragma unroll
-        for (int tt = 0; tt < NTT; ++tt)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int row = tt * 8 + 2 * t + (q & 1);
                 if (row >= cnt) continue;
-                if constexpr (NW == 2) {
-                    const int n = im.rt[0] * kRowTile + g + (q < 2 ? 0 : 8);
-                    if (n < N)
-                        p.y[(size_t)(e0 + row) * p.ldy + n] =
-                            __float2half_rn(round16(silu16(res[0][tt][q]) * res[1][tt][q]));
+                if (swiglu) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int n = im.pair * kRowTile + g + 8 * h;
+                        if (n < N)
+                            p.y[(size_t)(e0 + row) * p.ldy + n] =
+                                __float2half_rn(round16(silu16(val[0][h]) * val[1][h]));
+                    }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int n = im.rt[j] * kRowTile + g + (q < 2 ? 0 : 8);
-                        if (im.tile_ok[j] && n < N) {
-                            float v = res[j][tt][q];
-                            if (p.entry_scale) v = round16(__half2float(__ldg(p.entry_scale + e0 + row)) * v);
-                            p.y[(size_t)(e0 + row) * p.ldy + n] = __float2half_rn(v);
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int n = (im.pair * 2 + j) * kRowTile + g + 8 * h;
+                            if (n < N) {
+                                float v = val[j][h];
+                                if (cs.bias) v = round16(v + __half2float(__ldg(cs.bias + n)));
+                                if (p.entry_scale) v = round16(__half2float(__ldg(p.entry_scale + e0 + row)) * v);
+                                p.y[(size_t)(e0 + row) * p.ldy + n] = __float2half_rn(v);
+                            }
                         }
-                    }
                 }
             }
+        }
     }
 }
 

@@ -131,7 +131,10 @@ class GLoRCQLinear(nn.Module):
     def _sync_tiled(self):
         if self._tiled is None:
             return
-        self._tiled.set_sv(self.SV)
+        if self.SV is not None:
+            self._tiled.put_sv(0, self.SV)
+        else:
+            self._tiled.clear_sv()
         self._tiled.set_bias(self.bias_param)
         self._ut = tiled.tiled_ut(self.U) if (self.U is not None and self.SV is not None) else None
 

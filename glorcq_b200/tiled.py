@@ -1,10 +1,10 @@
 """Weights in the tiled device layout of the sm_100a kernels, and the calls that consume them.
 
-`TiledWeight` owns the re-tiled tensors of one matrix (built once at load time by the
-glq_pack_* entry points) and hands out the glq_weight_t descriptor the C ABI takes.  The shared
-input-side factor U of a cluster is tiled once (as U^T, dense fp16) and cached by storage, so
-every layer of the cluster points at the same device memory -- the "global U pool" the reference's
-loader builds (inference/model_builder.py:143-173) but its compute path never reads.
+`TiledWeight` owns the re-tiled tensors of one matrix -- or of a fused gate|up pair -- built once at
+load time by the glq_pack_* entry points, and hands out the glq_weight_t descriptor the C ABI takes.
+The shared input-side factor U of a cluster is tiled once (as U^T, dense fp16) and cached by
+storage, so every layer of the cluster points at the same device memory: the "global U pool" the
+reference's loader builds (inference/model_builder.py:143-173) but its compute path never reads.
 """
 
 from __future__ import annotations
@@ -34,59 +34,113 @@ def _need_cuda(t: torch.Tensor, name: str):
 
 
 class TiledWeight:
-    """One weight matrix (N, K) in the tiled layout."""
+    """One weight matrix (N, K) -- or two of the same shape fused tile by tile (count == 2: slot 0
+    is the gate projection, slot 1 the up projection) -- in the tiled layout."""
 
-    def __init__(self, fmt: int, N: int, K: int, group_size: int = 0):
-        self.fmt, self.N, self.K, self.group_size = fmt, N, K, group_size
-        self.codes = self.sz = self.norms = self.centroids = self.sv = self.bias = None
+    def __init__(self, fmt: int, N: int, K: int, group_size: int = 0, count: int = 1, device=None):
+        self.fmt, self.N, self.K, self.group_size, self.count = fmt, N, K, group_size, count
+        self.codes = self.norms = self.centroids = self.sv = self.bias = None
         self.rank = 0
+        self._desc = None
+        self._device = device
+        L = _lib.lib()
+        if fmt == FMT_F16:
+            nbytes = L.glq_tiled_f16_bytes(N, K)
+        else:
+            nbytes = L.glq_tiled_bytes(fmt, N, K, count)
+        # zero-filled: padding tiles and padding columns are never written by the pack kernels
+        self.codes = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        if fmt == FMT_T2:
+            self.norms = torch.zeros(L.glq_rows_f32_count(N, count), dtype=torch.float32, device=device)
+
+    # ---- filling one slot -----------------------------------------------------------------
+    def put_gptq(self, slot, qweight_int, scales, zeros, bits, sym=False):
+        _need_cuda(qweight_int, "qweight_int")
+        _need_cuda(scales, "scales")
+        N, K = qweight_int.shape
+        if (N, K) != (self.N, self.K):
+            raise RuntimeError("shape mismatch between fused matrices")
+        G = scales.shape[1]
+        if G != (K + self.group_size - 1) // self.group_size:
+            raise RuntimeError("scales shape does not match K / groupsize")
+        q32 = qweight_int if qweight_int.dtype == torch.int32 else qweight_int.to(torch.int32)
+        s = scales.to(torch.float16).contiguous()
+        z = None if (sym or zeros is None) else zeros.to(torch.float16).contiguous()
+        with torch.cuda.device(self.codes.device):
+            _lib.check(_lib.lib().glq_pack_gptq(q32.data_ptr(), s.data_ptr(), _ptr(z), bits, N, K, self.group_size,
+                                                self.codes.data_ptr(), slot, self.count,
+                                                _stream_ptr(self.codes.device)), "pack_gptq")
+
+    def put_turbo(self, slot, packed_indices, norms, centroids):
+        _need_cuda(packed_indices, "packed_indices")
+        N, K4 = packed_indices.shape
+        if (N, K4 * 4) != (self.N, self.K):
+            raise RuntimeError("shape mismatch between fused matrices")
+        dev = self.codes.device
+        nrm = norms.to(device=dev, dtype=torch.float32).contiguous()
+        cen = centroids.to(device=dev, dtype=torch.float32).contiguous()
+        if self.centroids is not None and not torch.equal(self.centroids, cen):
+            raise RuntimeError("fused codebook weights must share one codebook")
+        self.centroids = cen
+        L = _lib.lib()
+        with torch.cuda.device(dev):
+            _lib.check(L.glq_pack_turbo(packed_indices.data_ptr(), N, self.K, self.codes.data_ptr(), slot, self.count,
+                                        _stream_ptr(dev)), "pack_turbo")
+            _lib.check(L.glq_pack_rows_f32(nrm.data_ptr(), N, self.norms.data_ptr(), slot, self.count,
+                                           _stream_ptr(dev)), "pack_rows_f32")
+
+    def put_sv(self, slot, SV: Optional[torch.Tensor]):
+        """Attach the (N, rank) output-side factor of the matrix in `slot` (packed layout)."""
+        self._desc = None
+        if SV is None:
+            return
+        if SV.shape[0] != self.N or SV.shape[1] % 16 != 0:
+            raise RuntimeError("SV must be (N, rank) with rank a multiple of 16")
+        rank = SV.shape[1]
+        L = _lib.lib()
+        dev = self.codes.device
+        if self.sv is None or self.rank != rank:
+            self.sv = torch.zeros(L.glq_sv_bytes(self.N, rank, self.count), dtype=torch.uint8, device=dev)
+            self.rank = rank
+        src = SV.to(device=dev, dtype=torch.float16).contiguous()
+        with torch.cuda.device(dev):
+            _lib.check(L.glq_pack_sv(src.data_ptr(), self.N, rank, self.sv.data_ptr(), slot, self.count,
+                                     _stream_ptr(dev)), "pack_sv")
+
+    def clear_sv(self):
+        self.sv, self.rank, self._desc = None, 0, None
+
+    def set_bias(self, bias: Optional[torch.Tensor]):
+        if bias is not None and self.count != 1:
+            raise RuntimeError("bias is only supported on plain (un-fused) weights")
+        self.bias = None if bias is None else bias.to(device=self.codes.device, dtype=torch.float16).contiguous()
         self._desc = None
 
     # ---- constructors -------------------------------------------------------------------
-    @classmethod
-    def from_gptq(cls, qweight_int, scales, zeros, bits, groupsize, sym=False):
-        """(N,K) int32 codes in [0, 2^bits) + (N,G) fp16 scales/zeros -> Q2 / Q4 tiles."""
-        _need_cuda(qweight_int, "qweight_int")
-        _need_cuda(scales, "scales")
+    @staticmethod
+    def _gptq_fmt(bits, groupsize):
         if bits not in (2, 4):
             raise RuntimeError(f"tiled layout covers 2- and 4-bit codes, got bits={bits}")
-        N, K = qweight_int.shape
         kb = 128 if bits == 2 else 64
         if groupsize <= 0 or groupsize % kb != 0:
             raise RuntimeError(f"group size {groupsize} must be a positive multiple of {kb} for {bits}-bit codes")
-        G = scales.shape[1]
-        if G != (K + groupsize - 1) // groupsize:
-            raise RuntimeError("scales shape does not match K / groupsize")
-        L = _lib.lib()
-        fmt = FMT_Q2 if bits == 2 else FMT_Q4
-        self = cls(fmt, N, K, groupsize)
-        dev = qweight_int.device
-        q32 = qweight_int if qweight_int.dtype == torch.int32 else qweight_int.to(torch.int32)
-        self.codes = torch.empty(L.glq_tiled_codes_bytes(fmt, N, K), dtype=torch.uint8, device=dev)
-        self.sz = torch.empty(L.glq_tiled_sz_bytes(N, G), dtype=torch.uint8, device=dev)
-        st = _stream_ptr(dev)
-        with torch.cuda.device(dev):
-            _lib.check(L.glq_pack_codes_i32(q32.data_ptr(), bits, N, K, self.codes.data_ptr(), st), "pack_codes_i32")
-            z = None if (sym or zeros is None) else zeros.to(torch.float16).contiguous()
-            s = scales.to(torch.float16).contiguous()
-            _lib.check(L.glq_pack_sz(s.data_ptr(), _ptr(z), N, G, self.sz.data_ptr(), st), "pack_sz")
+        return FMT_Q2 if bits == 2 else FMT_Q4
+
+    @classmethod
+    def from_gptq(cls, qweight_int, scales, zeros, bits, groupsize, sym=False):
+        """(N,K) int32 codes in [0, 2^bits) + (N,G) fp16 scales/zeros -> Q2 / Q4 tiles."""
+        fmt = cls._gptq_fmt(bits, groupsize)
+        N, K = qweight_int.shape
+        self = cls(fmt, N, K, groupsize, 1, qweight_int.device)
+        self.put_gptq(0, qweight_int, scales, zeros, bits, sym)
         return self
 
     @classmethod
     def from_turbo(cls, packed_indices, norms, centroids):
         """(N,K/4) uint8 2-bit indices + (N,) norms + (4,) codebook -> T2 tiles."""
-        _need_cuda(packed_indices, "packed_indices")
         N, K4 = packed_indices.shape
-        K = K4 * 4
-        L = _lib.lib()
-        self = cls(FMT_T2, N, K)
-        dev = packed_indices.device
-        self.codes = torch.empty(L.glq_tiled_codes_bytes(FMT_T2, N, K), dtype=torch.uint8, device=dev)
-        with torch.cuda.device(dev):
-            _lib.check(L.glq_pack_codes_u8(packed_indices.data_ptr(), N, K, self.codes.data_ptr(), _stream_ptr(dev)),
-                       "pack_codes_u8")
-        self.norms = norms.to(device=dev, dtype=torch.float32).contiguous()
-        self.centroids = centroids.to(device=dev, dtype=torch.float32).contiguous()
+        self = cls(FMT_T2, N, K4 * 4, 0, 1, packed_indices.device)
+        self.put_turbo(0, packed_indices, norms, centroids)
         return self
 
     @classmethod
@@ -101,34 +155,17 @@ class TiledWeight:
         else:
             N, K = W.shape
             sn, sk = W.stride(0), W.stride(1)
-        L = _lib.lib()
-        self = cls(FMT_F16, N, K)
-        self.codes = torch.empty(L.glq_tiled_codes_bytes(FMT_F16, N, K), dtype=torch.uint8, device=W.device)
+        self = cls(FMT_F16, N, K, 0, 1, W.device)
         with torch.cuda.device(W.device):
-            _lib.check(L.glq_pack_f16(W.data_ptr(), sn, sk, N, K, self.codes.data_ptr(), _stream_ptr(W.device)),
-                       "pack_f16")
-        self._keep = W
+            _lib.check(_lib.lib().glq_pack_f16(W.data_ptr(), sn, sk, N, K, self.codes.data_ptr(),
+                                               _stream_ptr(W.device)), "pack_f16")
         return self
 
-    # ---- low-rank / bias attachments ------------------------------------------------------
-    def set_sv(self, SV: Optional[torch.Tensor]):
-        if SV is None:
-            self.sv, self.rank = None, 0
-        else:
-            if SV.shape[0] != self.N or SV.shape[1] % 16 != 0:
-                raise RuntimeError("SV must be (N, rank) with rank a multiple of 16")
-            self.sv = SV.to(torch.float16).contiguous()
-            self.rank = SV.shape[1]
-        self._desc = None
-
-    def set_bias(self, bias: Optional[torch.Tensor]):
-        self.bias = None if bias is None else bias.to(torch.float16).contiguous()
-        self._desc = None
-
+    # ---- descriptor ---------------------------------------------------------------------------
     @property
     def desc(self) -> Weight:
         if self._desc is None:
-            self._desc = Weight(_ptr(self.codes), _ptr(self.sz), _ptr(self.norms), _ptr(self.centroids),
+            self._desc = Weight(_ptr(self.codes), None, _ptr(self.norms), _ptr(self.centroids),
                                 _ptr(self.sv), _ptr(self.bias), self.N, self.K, self.rank, 0)
         return self._desc
 
@@ -140,17 +177,18 @@ class TiledWeight:
         return self.codes.device
 
     def nbytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.codes, self.sz, self.norms, self.sv, self.bias)
+        return sum(t.numel() * t.element_size() for t in (self.codes, self.norms, self.sv, self.bias)
                    if t is not None)
 
     # ---- checks ------------------------------------------------------------------------------
-    def dequantize(self) -> torch.Tensor:
-        """Dequantised (N,K) weights from the tiles: fp16 for Q2/Q4, fp32 for T2."""
+    def dequantize(self, slot: int = 0) -> torch.Tensor:
+        """Dequantised (N,K) weights of the matrix in `slot`: fp16 for Q2/Q4, fp32 for T2."""
         L = _lib.lib()
         dt = torch.float32 if self.fmt == FMT_T2 else torch.float16
         out = torch.empty(self.N, self.K, dtype=dt, device=self.device)
         with torch.cuda.device(self.device):
-            _lib.check(L.glq_dequant_tiled(self.fmt, C.byref(self.desc), self.group_size, out.data_ptr(),
+            _lib.check(L.glq_dequant_tiled(self.fmt, self.codes.data_ptr(), _ptr(self.norms), _ptr(self.centroids),
+                                           self.N, self.K, slot, self.count, out.data_ptr(),
                                            _stream_ptr(self.device)), "dequant_tiled")
         return out
 
@@ -165,6 +203,7 @@ def tiled_ut(U: torch.Tensor) -> TiledWeight:
     tw = _UT_POOL.get(key)
     if tw is None:
         tw = TiledWeight.from_dense(U, transposed=True)
+        tw._keep = U           # the key is the storage address: keep it alive
         _UT_POOL[key] = tw
     return tw
 
@@ -190,6 +229,14 @@ def workspace(device, nbytes: int, ncounters: int = 0):
         ctr = torch.zeros(max(ncounters, 1 << 16), dtype=torch.int32, device=device)
     _WS[key] = (ws, ctr)
     return ws, ctr
+
+
+def debug_error(clear: bool = True):
+    """First bounds violation / timed-out wait recorded by a kernel, or None."""
+    out = (C.c_ulonglong * 4)()
+    _lib.check(_lib.lib().glq_debug_error(out, int(clear)), "debug_error")
+    vals = [int(v) for v in out]
+    return None if vals[0] == 0 else vals
 
 
 # ---- calls -----------------------------------------------------------------------------------

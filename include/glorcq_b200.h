@@ -38,16 +38,16 @@ extern "C" {
 
 /* epilogues of glq_grouped_matmul */
 #define GLQ_EPI_LINEAR 0 /* y = fp16(fp16(q-part) + fp16(low-rank part)) [* entry scale] [+ bias] */
-#define GLQ_EPI_SWIGLU 1 /* two weights w0 (gate), w1 (up): y = silu(lin0(x)) * lin1(x)           */
+#define GLQ_EPI_SWIGLU 1 /* fused gate|up weight: y = silu(gate(x)) * up(x)                            */
 
 /* One weight matrix in the tiled layout (all device pointers; unused ones NULL). */
 typedef struct glq_weight {
-    const void* codes;      /* tiled codes (Q2/Q4/T2) or tiled fp16 values (F16)                 */
-    const void* sz;         /* Q2/Q4: tiled (scale, zero) fp16 pairs                             */
-    const float* norms;     /* T2: (N,) fp32                                                     */
+    const void* codes;      /* tiled codes with their scales (Q2/Q4/T2) or tiled fp16 values (F16) */
+    const void* reserved0;
+    const float* norms;     /* T2: per-row norms in tile order                                   */
     const float* centroids; /* T2: (4,) fp32                                                     */
-    const void* sv;         /* (N, rank) fp16 row-major output-side low-rank factor, or NULL     */
-    const void* bias;       /* (N,) fp16 or NULL                                                 */
+    const void* sv;         /* packed output-side low-rank factor, or NULL                       */
+    const void* bias;       /* (N,) fp16 or NULL (GLQ_EPI_LINEAR only)                           */
     int32_t N;              /* output features                                                   */
     int32_t K;              /* input features                                                    */
     int32_t rank;           /* low-rank width (multiple of 16), 0 = none                         */
@@ -86,31 +86,43 @@ int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const void* scales,
                             int sym, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
- * Load-time re-tiling (device to device).  Tiled layouts, rows in tiles of 16:
- *   Q2/T2: [row tile][k block of 128][lane 0..31][4 x u32]; lane = 4*g + t holds codes
- *          k = 128*kb + 32*t + 0..31 of row 16*rt+g (words 0,1) and of row 16*rt+g+8 (words 2,3)
- *   Q4   : same with k blocks of 64, 16 codes per lane and row
- *   F16  : [row tile][k block of 64][k step 0..3][lane][4 x half2] = the m16n8k16 A fragment
- *   sz   : [row tile][group][g 0..7][scale g, zero g, scale g+8, zero g+8] fp16
- * replacing the (N,K) int32 / (N,K/4) uint8 / (N,G) fp16 tensors stored by the reference's
+ * Load-time re-tiling (device to device).  Rows are grouped in tiles of 16, tiles in pairs.
+ *   Q2  : [pair][k block of 128][tile in pair][576 B]; a block is 32 lanes x 16 B of codes -- lane
+ *         4g+t holds codes k = 128*kb + 32*t + 0..31 of row 16*i+g (words 0,1) and of row 16*i+g+8
+ *         (words 2,3) -- followed by 8 x (scale g, zero g, scale g+8, zero g+8) fp16 of the block's group
+ *   Q4  : the same with k blocks of 64 (16 codes per lane and row)
+ *   T2  : [pair][k block of 128][tile in pair][512 B] of codebook indices; norms in tile order
+ *   F16 : [row tile][k block of 64][k step 0..3][lane][4 x half2] = the m16n8k16 A fragment
+ *   SV  : [pair][64-column slice][32 rows of the pair][64 columns] fp16
+ * Source tile i of a matrix lands in destination tile i*count + slot: count = 1 is a plain matrix,
+ * count = 2 interleaves two matrices of one shape tile by tile (slot 0 = gate, slot 1 = up), so that
+ * a pair is (gate tile p, up tile p) and one launch computes silu(gate x) * (up x).  The
+ * destination buffers must be zero-filled before packing (padding tiles are not written).
+ * These replace the (N,K) int32 / (N,K/4) uint8 / (N,G) fp16 tensors stored by the reference's
  * quantizer (joint_optim.py:319-327; turbo_weight_quantizer.py:149-156).
  * ------------------------------------------------------------------------------------------ */
-size_t glq_tiled_codes_bytes(int fmt, int N, int K);
-size_t glq_tiled_sz_bytes(int N, int n_groups);
+size_t glq_tiled_bytes(int fmt, int n_rows, int K, int count);       /* codes (+ scales) buffer */
+size_t glq_sv_bytes(int n_rows, int rank, int count);                /* packed SV buffer         */
+size_t glq_rows_f32_count(int n_rows, int count);                    /* floats of a tile-ordered row vector */
 
-/* codes (N,K) int32 with values in [0, 2^bits) -> tiled Q2 (bits 2) or Q4 (bits 4) */
-int glq_pack_codes_i32(const int32_t* q, int bits, int N, int K, void* tiled, void* stream);
-/* packed (N,K/4) uint8 2-bit codes -> tiled T2 (or Q2) */
-int glq_pack_codes_u8(const uint8_t* packed, int N, int K, void* tiled, void* stream);
-/* scales, zeros (N,G) fp16 (zeros may be NULL: symmetric) -> tiled sz */
-int glq_pack_sz(const void* scales, const void* zeros, int N, int n_groups, void* tiled, void* stream);
+/* codes (N,K) int32 in [0, 2^bits), scales/zeros (N,G) fp16 (zeros NULL: symmetric) -> Q2 / Q4 */
+int glq_pack_gptq(const int32_t* q, const void* scales, const void* zeros, int bits, int N, int K, int group_size,
+                  void* tiled, int slot, int count, void* stream);
+/* packed (N,K/4) uint8 2-bit indices -> T2 */
+int glq_pack_turbo(const uint8_t* packed, int N, int K, void* tiled, int slot, int count, void* stream);
+/* (N,) fp32 row values (norms) -> tile order */
+int glq_pack_rows_f32(const float* v, int N, float* out, int slot, int count, void* stream);
+/* SV (N, rank) fp16 row-major -> packed SV */
+int glq_pack_sv(const void* sv, int N, int rank, void* out, int slot, int count, void* stream);
 /* W fp16 -> tiled F16.  element (n,k) is read from W[n*stride_n + k*stride_k] */
+size_t glq_tiled_f16_bytes(int N, int K);
 int glq_pack_f16(const void* W, long stride_n, long stride_k, int N, int K, void* tiled, void* stream);
 
-/* Dequantised weights from the tiled layout, for bit-exact checks against the reference's tiles:
- * Q2/Q4 -> out (N,K) fp16 = fp16((q - z) * s)  (inference/quantized_linear.py:271-284);
- * T2    -> out (N,K) fp32 = centroids[idx] * norm (inference/kernels/__init__.py:142-143). */
-int glq_dequant_tiled(int fmt, const glq_weight_t* w, int group_size, void* out, void* stream);
+/* Dequantised weights of the matrix in (slot, count) of a tiled buffer, for bit-exact checks against
+ * the reference's tiles: Q2/Q4 -> out (N,K) fp16 = fp16((q - z) * s) (inference/quantized_linear.py:271-284);
+ * T2 -> out (N,K) fp32 = centroids[idx] * norm (inference/kernels/__init__.py:142-143). */
+int glq_dequant_tiled(int fmt, const void* tiled, const float* norms_tiled, const float* centroids, int N, int K,
+                      int slot, int count, void* out, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Grouped skinny matmul: the decode GEMV / batched-decode kernel.
@@ -121,8 +133,10 @@ int glq_dequant_tiled(int fmt, const glq_weight_t* w, int group_size, void* out,
  *     x row of entry e   = x + entry_row[e] * ldx      (entry_row NULL: e)
  *     y row of entry e   = y + e * ldy
  *     a row of entry e   = a + e * lda                 (precomputed x.U, fp16, width rank)
- * and y = epilogue(x . dequant(W)^T, a . SV^T).  All slots share format, shape class and group
- * size.  With table == NULL the inline descriptor is used for every slot.
+ * and y = epilogue(x . dequant(W)^T, a . SV^T).  All slots share format, shape and group size.
+ * With table == NULL the inline descriptor is used for every slot.  GLQ_EPI_SWIGLU takes a fused
+ * gate|up weight (count = 2 above), N is then the width of each of the two, a0 / a1 are x.U of the
+ * gate / up cluster.
  * ------------------------------------------------------------------------------------------ */
 typedef struct glq_mm_args {
     int32_t fmt;         /* GLQ_FMT_* */
@@ -133,9 +147,8 @@ typedef struct glq_mm_args {
     int32_t rows_stride; /* entries reserved per slot when slot_offset is NULL */
     int32_t N, K, rank;  /* shape shared by all slots */
     int32_t reserved;
-    glq_weight_t w0, w1;           /* inline descriptors (w1 only for GLQ_EPI_SWIGLU) */
-    const glq_weight_t* w0_table;  /* device arrays indexed by slot_index[], or NULL */
-    const glq_weight_t* w1_table;
+    glq_weight_t w;              /* inline descriptor */
+    const glq_weight_t* w_table; /* device array indexed by slot_index[], or NULL */
     const int32_t* slot_index;  /* device, NULL: identity */
     const int32_t* n_slots;     /* device scalar, NULL: n_problems */
     const int32_t* slot_count;  /* device, NULL: max_rows for every slot */
@@ -143,18 +156,23 @@ typedef struct glq_mm_args {
     const int32_t* entry_row;   /* device, NULL: identity */
     const void* entry_scale;    /* device fp16 per entry, NULL: none (GLQ_EPI_LINEAR only) */
     const void* x;  int64_t ldx;   /* fp16 */
-    const void* a0; const void* a1; int64_t lda; /* fp16 x.U per entry for w0 / w1, NULL: no low-rank term */
+    const void* a0; const void* a1; int64_t lda; /* fp16 x.U per entry, NULL: no low-rank term */
     void* y;        int64_t ldy;   /* fp16 */
     void* workspace; size_t workspace_bytes; /* scratch for split-k partial sums (contents irrelevant)   */
     int32_t* counters; size_t n_counters;    /* arrival counters: zero before the first use, left zero   */
 } glq_mm_args_t;
 
-/* Scratch bytes / arrival counters a call with these args needs (both 0 when k is not split).  The
- * counters must be zero when a call starts and are zero again when it ends, so one zero-initialised
- * array can serve any sequence of calls on one stream; the scratch needs no initialisation. */
+/* Scratch bytes / arrival counters a call with these args needs (both 0 when no CTA-level k split is
+ * used).  The counters must be zero when a call starts and are zero again when it ends, so one
+ * zero-initialised array can serve any sequence of calls on one stream; the scratch needs no
+ * initialisation. */
 size_t glq_mm_workspace_bytes(const glq_mm_args_t* args);
 size_t glq_mm_counters(const glq_mm_args_t* args);
 int glq_grouped_matmul(const glq_mm_args_t* args, void* stream);
+
+/* First bounds violation or timed-out wait recorded by a kernel: {code, index, limit,
+ * block<<32|thread}, all zero when there was none.  Synchronises the device; clear != 0 resets it. */
+int glq_debug_error(unsigned long long* out4, int clear);
 
 /* One quantized linear layer on B activation rows (GLoRCQLinear.forward,
  * inference/quantized_linear.py:286-355): y = Q(x) + a . SV^T + bias with a = x . U given by the

@@ -40,13 +40,17 @@ def test_status_strings_and_sizes(libpath):
     assert L.glq_version() >= 100
     for st in (0, -1, -2, -3, -4, -5):
         assert len(L.glq_status_string(st)) > 0
-    # C1 expert projection: 1408 x 2048, 2-bit -> 88 row tiles x 16 blocks x 512 B
-    assert L.glq_tiled_codes_bytes(_lib.FMT_Q2, 1408, 2048) == 88 * 16 * 512 == 1408 * 2048 // 4
-    assert L.glq_tiled_codes_bytes(_lib.FMT_Q4, 2048, 2048) == 2048 * 2048 // 2
-    assert L.glq_tiled_codes_bytes(_lib.FMT_F16, 64, 2048) == 64 * 2048 * 2
-    assert L.glq_tiled_sz_bytes(1408, 16) == 1408 * 16 * 4
-    # ragged shapes are padded to whole tiles
-    assert L.glq_tiled_codes_bytes(_lib.FMT_T2, 17, 130) == 2 * 2 * 512
+    # C1 expert projection 1408 x 2048, 2-bit: 44 tile pairs x 16 blocks x 2 tiles x (512 B codes + 64 B scales)
+    assert L.glq_tiled_bytes(_lib.FMT_Q2, 1408, 2048, 1) == 44 * 16 * 2 * 576
+    # the same fused with a second matrix of that shape (gate | up): twice the pairs
+    assert L.glq_tiled_bytes(_lib.FMT_Q2, 1408, 2048, 2) == 88 * 16 * 2 * 576
+    assert L.glq_tiled_bytes(_lib.FMT_Q4, 2048, 2048, 1) == 64 * 32 * 2 * 576
+    assert L.glq_tiled_bytes(_lib.FMT_T2, 1408, 2048, 1) == 1408 * 2048 // 4
+    assert L.glq_tiled_f16_bytes(64, 2048) == 64 * 2048 * 2
+    assert L.glq_sv_bytes(1408, 64, 1) == 44 * 4096 == 1408 * 64 * 2
+    # ragged shapes are padded to whole tile pairs and k blocks
+    assert L.glq_tiled_bytes(_lib.FMT_T2, 17, 130, 1) == 1 * 2 * 2 * 512
+    assert L.glq_rows_f32_count(17, 1) == 32
 
 
 def test_host_side_argument_checks(libpath):
@@ -57,7 +61,7 @@ def test_host_side_argument_checks(libpath):
     assert L.glq_turbo_dequant_matmul(None, None, None, None, None, 0, 8, 64, None) == 0      # B == 0: no-op
     assert L.glq_turbo_dequant_matmul(None, None, None, None, None, -1, 8, 64, None) == -1
     assert L.glq_gptq_dequant_matmul(None, None, None, None, None, None, 0, 8, 64, 128, 1, 0, None) == 0
-    assert L.glq_pack_codes_i32(None, 2, 16, 128, None, None) == -1
+    assert L.glq_pack_gptq(None, None, None, 2, 16, 128, 128, None, 0, 1, None) == -1
     assert L.glq_grouped_matmul(None, None) == -1
 
 
