@@ -257,7 +257,8 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     // k splits (warps of one CTA): enough iterations to give every SM one; splits on group boundaries
     const int units = cdiv(g.nkb, group_blocks);
     int sk = 1;
-    while (sk < 8 && (long)n_problems * cdiv(g.npairs * sk, kWarpsPerCta) < num_sms() && units >= 2 * sk) sk *= 2;
+    const long want_iters = (long)kStreamCtasPerSm * num_sms();
+    while (sk < 8 && (long)n_problems * cdiv(g.npairs * sk, kWarpsPerCta) < want_iters && units >= 2 * sk) sk *= 2;
     g.sk = sk;
     g.kb_per_split = cdiv(units, sk) * group_blocks;
     g.ips = cdiv(g.npairs * sk, kWarpsPerCta);
@@ -282,7 +283,7 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     off = (off + 127) / 128 * 128;
     g.off_ring = (int)off;
     const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.nt * 32 * 16 : 0;
-    const size_t cap = 220 * 1024;
+    const size_t cap = (size_t)(kStreamCtasPerSm == 1 ? 220 : 110) * 1024;
     if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) return false;
     int stages = (int)((cap - off - red) / ((size_t)kWarpsPerCta * g.stage_bytes));
     g.stages = std::min(stages, kMaxStages);
@@ -291,7 +292,7 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     off += red;
     g.smem = off;
     const long iters = (long)n_problems * g.ips;
-    g.grid = (int)std::min<long>(iters, num_sms());
+    g.grid = (int)std::min<long>(iters, (long)kStreamCtasPerSm * num_sms());
     *out = g;
     return g.grid > 0;
 }

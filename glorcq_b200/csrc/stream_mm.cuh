@@ -29,7 +29,14 @@
 namespace glq {
 
 constexpr int kMaxStages = 6;
-constexpr int kStreamCB = 4;  // k blocks per ring stage
+#ifndef GLQ_STREAM_CB
+#define GLQ_STREAM_CB 4
+#endif
+constexpr int kStreamCB = GLQ_STREAM_CB;  // k blocks per ring stage
+#ifndef GLQ_STREAM_CTAS
+#define GLQ_STREAM_CTAS 2
+#endif
+constexpr int kStreamCtasPerSm = GLQ_STREAM_CTAS;
 
 struct StreamParams {
     SkinnyParams b;    // operands (of its geometry fields only ntc, nkb are used)
@@ -290,7 +297,7 @@ __device__ __forceinline__ void tile_block_i8(const uint4 q, const uint4 (&bx)[N
 // I8 = true : NT tiles of 4 activation rows (integer path, affine formats only)
 // I8 = false: NT tiles of 8 activation rows (fp16 path)
 template <int FMT, bool I8, int NT>
-__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams sp) {
+__global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(const StreamParams sp) {
     using F = Fmt<FMT>;
     static_assert(FMT != GLQ_FMT_F16, "dense weights use the fallback kernel");
     static_assert(!I8 || FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4, "integer path needs integer codes");
@@ -471,8 +478,9 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const StreamParams 
             const uint32_t st = ring_a + (uint32_t)(stage * sp.stage_bytes);
             const int kb0 = im.kb_lo + c * kStreamCB;
             const int nblk = min(kStreamCB, im.kb_hi - kb0);
-#pragma unroll 2
-            for (int b = 0; b < nblk; ++b) {
+#pragma unroll
+            for (int b = 0; b < kStreamCB; ++b) {
+                if (b >= nblk) break;
                 const int kb = kb0 + b;
                 if constexpr (I8) {
                     uint4 bx[NT][2];
