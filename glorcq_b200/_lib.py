@@ -43,12 +43,12 @@ class MoeDesc(C.Structure):
     """glq_moe_desc_t"""
     _fields_ = [("H", C.c_int32), ("I", C.c_int32), ("E", C.c_int32), ("top_k", C.c_int32),
                 ("I_shared", C.c_int32), ("rank", C.c_int32), ("fmt", C.c_int32), ("group_size", C.c_int32),
-                ("norm_topk_prob", C.c_int32), ("max_tokens", C.c_int32), ("ordered_by_expert_above", C.c_int32),
+                ("norm_topk_prob", C.c_int32), ("router_rows", C.c_int32), ("slot_order_max_tokens", C.c_int32),
                 ("reserved", C.c_int32),
-                ("router", vp), ("gate_w", vp), ("up_w", vp), ("down_w", vp),
-                ("gate_ut", vp), ("up_ut", vp), ("down_ut", vp),
-                ("shared_gate_w", Weight), ("shared_up_w", Weight), ("shared_down_w", Weight),
-                ("shared_gate_ut", vp), ("shared_up_ut", vp), ("shared_down_ut", vp)]
+                ("router_t", vp), ("gate_up", vp), ("down", vp), ("ut_gate", vp), ("ut_up", vp), ("ut_down", vp),
+                ("sh_gate_up", Weight), ("sh_down", Weight),
+                ("sh_ut_gate", vp), ("sh_ut_up", vp), ("sh_ut_down", vp),
+                ("rot_in", vp), ("rot_mid", vp), ("sh_rot_mid", vp)]
 
 
 _SIGS = {
@@ -78,7 +78,8 @@ _SIGS = {
     "glq_linear_forward": (C.c_int, [C.c_int, C.c_int, C.POINTER(Weight), vp, vp, C.c_int64, vp, vp, C.c_int64,
                                      C.c_int, vp, C.c_size_t, vp, C.c_size_t, vp]),
     "glq_moe_workspace_bytes": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
-    "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, C.c_size_t, vp]),
+    "glq_moe_counters": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
+    "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, vp, vp, C.c_size_t, vp, C.c_size_t, vp]),
 }
 
 _lib = None

@@ -1,0 +1,455 @@
+// MoE block forward on the device: routing plan, expert matmuls through glq_grouped_matmul, combine.
+// Everything is enqueued on one stream with launch shapes that depend only on (desc, n_tokens), so
+// the call is capturable into a CUDA graph; nothing is read back to the host.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "glq_common.cuh"
+
+using namespace glq;
+
+namespace {
+
+inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+// ---- workspace carve-up ---------------------------------------------------------------------------
+struct MoeLayout {
+    size_t logits, sel, wts, active, n_active, slot_count, slot_offset, entry_row, entry_scale, tok_entries;
+    size_t a_gate, a_up, h, b, yd, a_sg, a_su, hs, bs, ysh, xr, hr, hsr, mm;
+    size_t total, mm_bytes, mm_counters;
+};
+
+void set_mm(glq_mm_args_t* m, int fmt, int group_size, int epi, int P, int rows, int N, int K, int rank) {
+    std::memset(m, 0, sizeof(*m));
+    m->fmt = fmt;
+    m->group_size = group_size;
+    m->epilogue = epi;
+    m->n_problems = P;
+    m->max_rows = rows;
+    m->rows_stride = rows;
+    m->N = N;
+    m->K = K;
+    m->rank = rank;
+}
+
+MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
+    MoeLayout L{};
+    const size_t nk = (size_t)n * d->top_k, R = (size_t)std::max(d->rank, 16);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += up256(bytes);
+        return o;
+    };
+    L.logits = take((size_t)n * d->router_rows * 2);
+    L.sel = take(nk * 4);
+    L.wts = take(nk * 2);
+    L.active = take((size_t)d->E * 4);
+    L.n_active = take(4);
+    L.slot_count = take((size_t)d->E * 4);
+    L.slot_offset = take((size_t)d->E * 4);
+    L.entry_row = take(nk * 4);
+    L.entry_scale = take(nk * 2);
+    L.tok_entries = take(nk * 4);
+    L.a_gate = take(nk * R * 2);
+    L.a_up = take(nk * R * 2);
+    L.h = take(nk * d->I * 2);
+    L.b = take(nk * R * 2);
+    L.yd = take(nk * d->H * 2);
+    if (d->I_shared > 0) {
+        L.a_sg = take((size_t)n * R * 2);
+        L.a_su = take((size_t)n * R * 2);
+        L.hs = take((size_t)n * d->I_shared * 2);
+        L.bs = take((size_t)n * R * 2);
+        L.ysh = take((size_t)n * d->H * 2);
+    }
+    if (d->rot_in) L.xr = take((size_t)n * d->H * 2);
+    if (d->rot_mid) L.hr = take(nk * d->I * 2);
+    if (d->sh_rot_mid && d->I_shared > 0) L.hsr = take((size_t)n * d->I_shared * 2);
+    // scratch / counters of the matmul calls: they run one after the other, so they share
+    const int P = (int)std::min<size_t>(nk, (size_t)d->E);
+    glq_mm_args_t m;
+    size_t wb = 0, wc = 0;
+    auto acc = [&]() {
+        wb = std::max(wb, glq_mm_workspace_bytes(&m));
+        wc = std::max(wc, glq_mm_counters(&m));
+    };
+    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->router_rows, d->H, 0); acc();
+    if (d->rot_in) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->H, d->H, 0); acc(); }
+    if (d->rot_mid) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, (int)nk, d->I, d->I, 0); acc(); }
+    if (d->sh_rot_mid && d->I_shared > 0) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->I_shared, d->I_shared, 0); acc(); }
+    if (d->rank > 0) {
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->H, 0); acc();
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->I, 0); acc();
+    }
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, d->rank); acc();
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, d->rank); acc();
+    if (d->I_shared > 0) {
+        if (d->rank > 0) {
+            set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->rank, d->H, 0); acc();
+            set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->rank, d->I_shared, 0); acc();
+        }
+        set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, 1, n, d->I_shared, d->H, d->rank); acc();
+        set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, 1, n, d->H, d->I_shared, d->rank); acc();
+    }
+    L.mm_bytes = up256(wb);
+    L.mm_counters = wc;
+    L.mm = take(L.mm_bytes);
+    L.total = off;
+    return L;
+}
+
+// ---- routing plan -----------------------------------------------------------------------------------
+// One CTA.  Phase A, thread per token: softmax over the fp16 router logits in fp32, top-k (ties to
+// the lower expert index), optional renormalisation, weights rounded to fp16.  Phase B, thread per
+// expert: the expert's entry list in token order (deterministic), then the list of live experts.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict__ logits, int ldl, int n, int E, int k,
+                                                        int renorm, int* __restrict__ sel, __half* __restrict__ wts,
+                                                        int* __restrict__ active, int* __restrict__ n_active,
+                                                        int* __restrict__ slot_count, int* __restrict__ slot_offset,
+                                                        int* __restrict__ entry_row, __half* __restrict__ entry_scale,
+                                                        int* __restrict__ tok_entries, __half* __restrict__ logits_out,
+                                                        int* __restrict__ sel_out, __half* __restrict__ wts_out) {
+    extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
+    int* sm_off = sm_cnt + E;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) {
+        const __half* row = logits + (size_t)t * ldl;
+        float mx = -INFINITY;
+        for (int e = 0; e < E; ++e) mx = fmaxf(mx, __half2float(row[e]));
+        float sum = 0.f;
+        for (int e = 0; e < E; ++e) sum += expf(__half2float(row[e]) - mx);
+        float wk[16];
+        int ek[16];
+        float wsum = 0.f;
+        for (int s = 0; s < k; ++s) {
+            float best = -1.f;
+            int be = 0;
+            for (int e = 0; e < E; ++e) {
+                bool taken = false;
+                for (int s2 = 0; s2 < s; ++s2) taken |= (ek[s2] == e);
+                const float pe = expf(__half2float(row[e]) - mx) / sum;
+                if (!taken && pe > best) {
+                    best = pe;
+                    be = e;
+                }
+            }
+            wk[s] = best;
+            ek[s] = be;
+            wsum += best;
+        }
+        for (int s = 0; s < k; ++s) {
+            const float wv = renorm ? wk[s] / wsum : wk[s];
+            const __half wh = __float2half_rn(wv);
+            sel[t * k + s] = ek[s];
+            wts[t * k + s] = wh;
+            if (sel_out) sel_out[t * k + s] = ek[s];
+            if (wts_out) wts_out[t * k + s] = wh;
+        }
+        if (logits_out)
+            for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = row[e];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < n * k; ++i) c += (sel[i] == e);
+        sm_cnt[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, j = 0;
+        for (int e = 0; e < E; ++e) {
+            sm_off[e] = off;
+            if (sm_cnt[e] > 0) {
+                active[j] = e;
+                slot_count[j] = sm_cnt[e];
+                slot_offset[j] = off;
+                ++j;
+            }
+            off += sm_cnt[e];
+        }
+        *n_active = j;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int pos = sm_off[e];
+        if (sm_cnt[e] == 0) continue;
+        for (int i = 0; i < n * k; ++i)
+            if (sel[i] == e) {
+                entry_row[pos] = i / k;
+                entry_scale[pos] = wts[i];
+                tok_entries[i] = pos;
+                ++pos;
+            }
+    }
+}
+
+// ---- combine ------------------------------------------------------------------------------------------
+// out[t] = sum over the token's experts of (already weighted, fp16) down outputs, accumulated in fp16
+// in slot order or in expert order, + sigmoid(shared gate) * shared expert output.  8 columns/thread.
+__global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __restrict__ tok_entries,
+                                   const int* __restrict__ sel, int k, int H, int by_expert,
+                                   const __half* __restrict__ ysh, const __half* __restrict__ logits, int ldl,
+                                   int gate_col, __half* __restrict__ out) {
+    const int t = blockIdx.y;
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c0 >= H) return;
+    int order[16];
+    for (int s = 0; s < k; ++s) order[s] = s;
+    if (by_expert) {
+        for (int i = 1; i < k; ++i) {
+            const int v = order[i];
+            const int ev = sel[t * k + v];
+            int j = i - 1;
+            while (j >= 0 && sel[t * k + order[j]] > ev) {
+                order[j + 1] = order[j];
+                --j;
+            }
+            order[j + 1] = v;
+        }
+    }
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int s = 0; s < k; ++s) {
+        const int entry = tok_entries[t * k + order[s]];
+        __align__(16) __half v[8];
+        *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(yd + (size_t)entry * H + c0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = round16(acc[i] + __half2float(v[i]));
+    }
+    if (ysh) {
+        const float gate = gate_col >= 0 ? sigmoid16(__half2float(logits[(size_t)t * ldl + gate_col])) : 1.f;
+        __align__(16) __half v[8];
+        *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(ysh + (size_t)t * H + c0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = round16(acc[i] + round16(gate * __half2float(v[i])));
+    }
+    __align__(16) __half o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __float2half_rn(acc[i]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * H + c0) = *reinterpret_cast<const uint4*>(o);
+}
+
+}  // namespace
+
+extern "C" size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens) {
+    if (!d || n_tokens <= 0) return 0;
+    return moe_layout(d, n_tokens).total;
+}
+extern "C" size_t glq_moe_counters(const glq_moe_desc_t* d, int n_tokens) {
+    if (!d || n_tokens <= 0) return 0;
+    return moe_layout(d, n_tokens).mm_counters;
+}
+
+extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, void* out, void* router_logits,
+                               int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes,
+                               int32_t* counters, size_t n_counters, void* stream) {
+    if (!d || !x || !out || n < 0) return GLQ_ERR_ARG;
+    if (n == 0) return GLQ_OK;
+    if (d->top_k < 1 || d->top_k > 16 || d->E < d->top_k || d->H % 8 != 0 || d->I % 8 != 0) return GLQ_ERR_UNSUPPORTED;
+    if (!d->router_t || !d->gate_up || !d->down) return GLQ_ERR_ARG;
+    if (d->rank > 0 && (!d->ut_gate || !d->ut_up || !d->ut_down)) return GLQ_ERR_ARG;
+    const MoeLayout L = moe_layout(d, n);
+    if (!workspace || workspace_bytes < L.total) return GLQ_ERR_WORKSPACE;
+    if (L.mm_counters > 0 && (!counters || n_counters < L.mm_counters)) return GLQ_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return GLQ_ERR_ALIGN;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    char* ws = reinterpret_cast<char*>(workspace);
+    const int k = d->top_k, nk = n * k, R = d->rank;
+    const int P = std::min(nk, d->E);
+
+    auto p_logits = reinterpret_cast<__half*>(ws + L.logits);
+    auto p_sel = reinterpret_cast<int*>(ws + L.sel);
+    auto p_wts = reinterpret_cast<__half*>(ws + L.wts);
+    auto p_active = reinterpret_cast<int*>(ws + L.active);
+    auto p_nact = reinterpret_cast<int*>(ws + L.n_active);
+    auto p_cnt = reinterpret_cast<int*>(ws + L.slot_count);
+    auto p_off = reinterpret_cast<int*>(ws + L.slot_offset);
+    auto p_erow = reinterpret_cast<int*>(ws + L.entry_row);
+    auto p_escale = reinterpret_cast<__half*>(ws + L.entry_scale);
+    auto p_tok = reinterpret_cast<int*>(ws + L.tok_entries);
+
+    glq_mm_args_t m;
+    auto finish = [&](glq_mm_args_t& mm) {
+        mm.workspace = ws + L.mm;
+        mm.workspace_bytes = L.mm_bytes;
+        mm.counters = counters;
+        mm.n_counters = n_counters;
+        return glq_grouped_matmul(&mm, stream);
+    };
+    int rc;
+    // y = x . Pi^T for a tiled dense Pi (rows x dim -> rows x dim)
+    auto rotate = [&](const void* pi_t, const void* src, int rows, int dim, void* dst) {
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, rows, dim, dim, 0);
+        m.w.codes = pi_t;
+        m.w.N = dim;
+        m.w.K = dim;
+        m.x = src;
+        m.ldx = dim;
+        m.y = dst;
+        m.ldy = dim;
+        return finish(m);
+    };
+    const void* xq = x;  // input of the quantized gate/up products
+    if (d->rot_in) {
+        if ((rc = rotate(d->rot_in, x, n, d->H, ws + L.xr)) != GLQ_OK) return rc;
+        xq = ws + L.xr;
+    }
+
+    // 1. router logits (and the shared expert's gate logit): dense fp16 matmul
+    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->router_rows, d->H, 0);
+    m.w.codes = d->router_t;
+    m.w.N = d->router_rows;
+    m.w.K = d->H;
+    m.x = x;
+    m.ldx = d->H;
+    m.y = p_logits;
+    m.ldy = d->router_rows;
+    if ((rc = finish(m)) != GLQ_OK) return rc;
+
+    // 2. routing plan
+    moe_plan_kernel<<<1, 1024, 2 * d->E * sizeof(int), st>>>(
+        p_logits, d->router_rows, n, d->E, k, d->norm_topk_prob, p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow,
+        p_escale, p_tok, reinterpret_cast<__half*>(router_logits), sel_out, reinterpret_cast<__half*>(weight_out));
+    if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
+
+    auto routed = [&](glq_mm_args_t& mm) {
+        mm.slot_index = p_active;
+        mm.n_slots = p_nact;
+        mm.slot_count = p_cnt;
+        mm.slot_offset = p_off;
+    };
+
+    // 3. x.U of the routed experts' gate and up clusters
+    if (R > 0) {
+        for (int which = 0; which < 2; ++which) {
+            set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, R, d->H, 0);
+            m.w_table = which == 0 ? d->ut_gate : d->ut_up;
+            routed(m);
+            m.entry_row = p_erow;
+            m.x = x;
+            m.ldx = d->H;
+            m.y = ws + (which == 0 ? L.a_gate : L.a_up);
+            m.ldy = R;
+            if ((rc = finish(m)) != GLQ_OK) return rc;
+        }
+    }
+    // 4. h = silu(gate x) * (up x), one row per (token, expert) entry
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, R);
+    m.w_table = d->gate_up;
+    routed(m);
+    m.entry_row = p_erow;
+    m.x = xq;
+    m.ldx = d->H;
+    if (R > 0) {
+        m.a0 = ws + L.a_gate;
+        m.a1 = ws + L.a_up;
+        m.lda = R;
+    }
+    m.y = ws + L.h;
+    m.ldy = d->I;
+    if ((rc = finish(m)) != GLQ_OK) return rc;
+    // 5. h.U of the down clusters
+    if (R > 0) {
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, R, d->I, 0);
+        m.w_table = d->ut_down;
+        routed(m);
+        m.x = ws + L.h;
+        m.ldx = d->I;
+        m.y = ws + L.b;
+        m.ldy = R;
+        if ((rc = finish(m)) != GLQ_OK) return rc;
+    }
+    // 6. down projection, scaled by the routing weight
+    const void* hq = ws + L.h;
+    if (d->rot_mid) {
+        // rotates every entry row (rows beyond the live entries hold stale but finite data)
+        if ((rc = rotate(d->rot_mid, ws + L.h, nk, d->I, ws + L.hr)) != GLQ_OK) return rc;
+        hq = ws + L.hr;
+    }
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, R);
+    m.w_table = d->down;
+    routed(m);
+    m.entry_scale = p_escale;
+    m.x = hq;
+    m.ldx = d->I;
+    if (R > 0) {
+        m.a0 = ws + L.b;
+        m.lda = R;
+    }
+    m.y = ws + L.yd;
+    m.ldy = d->H;
+    if ((rc = finish(m)) != GLQ_OK) return rc;
+
+    // 7. shared expert
+    const bool shared = d->I_shared > 0 && d->sh_gate_up.codes != nullptr;
+    if (shared) {
+        const bool lr = R > 0 && d->sh_ut_gate && d->sh_ut_up && d->sh_ut_down;
+        if (lr) {
+            for (int which = 0; which < 2; ++which) {
+                set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, R, d->H, 0);
+                m.w.codes = which == 0 ? d->sh_ut_gate : d->sh_ut_up;
+                m.w.N = R;
+                m.w.K = d->H;
+                m.x = x;
+                m.ldx = d->H;
+                m.y = ws + (which == 0 ? L.a_sg : L.a_su);
+                m.ldy = R;
+                if ((rc = finish(m)) != GLQ_OK) return rc;
+            }
+        }
+        set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, 1, n, d->I_shared, d->H, lr ? R : 0);
+        m.w = d->sh_gate_up;
+        if (!lr) m.w.rank = 0;
+        m.x = xq;
+        m.ldx = d->H;
+        if (lr) {
+            m.a0 = ws + L.a_sg;
+            m.a1 = ws + L.a_su;
+            m.lda = R;
+        }
+        m.y = ws + L.hs;
+        m.ldy = d->I_shared;
+        if ((rc = finish(m)) != GLQ_OK) return rc;
+        if (lr) {
+            set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, R, d->I_shared, 0);
+            m.w.codes = d->sh_ut_down;
+            m.w.N = R;
+            m.w.K = d->I_shared;
+            m.x = ws + L.hs;
+            m.ldx = d->I_shared;
+            m.y = ws + L.bs;
+            m.ldy = R;
+            if ((rc = finish(m)) != GLQ_OK) return rc;
+        }
+        const void* hsq = ws + L.hs;
+        if (d->sh_rot_mid) {
+            if ((rc = rotate(d->sh_rot_mid, ws + L.hs, n, d->I_shared, ws + L.hsr)) != GLQ_OK) return rc;
+            hsq = ws + L.hsr;
+        }
+        set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, 1, n, d->H, d->I_shared, lr ? R : 0);
+        m.w = d->sh_down;
+        if (!lr) m.w.rank = 0;
+        m.x = hsq;
+        m.ldx = d->I_shared;
+        if (lr) {
+            m.a0 = ws + L.bs;
+            m.lda = R;
+        }
+        m.y = ws + L.ysh;
+        m.ldy = d->H;
+        if ((rc = finish(m)) != GLQ_OK) return rc;
+    }
+
+    // 8. combine
+    const dim3 grid((d->H / 8 + 255) / 256, n);
+    moe_combine_kernel<<<grid, 256, 0, st>>>(
+        reinterpret_cast<const __half*>(ws + L.yd), p_tok, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
+        shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, d->router_rows,
+        d->router_rows > d->E ? d->E : -1, reinterpret_cast<__half*>(out));
+    if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
+    return GLQ_OK;
+}

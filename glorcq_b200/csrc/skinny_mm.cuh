@@ -374,8 +374,12 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
     float2* ox = reinterpret_cast<float2*>(xs + (size_t)p.kb_chunk * F::XS * ntc);
     float4* red = reinterpret_cast<float4*>(ox + (size_t)p.kb_chunk * ntc);
 
-    uint32_t TL = 0, TH = 0;
-    if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(W.centroids, TL, TH);
+    uint32_t TL[NW], TH[NW];  // a fused gate|up weight carries two codebooks (4 floats each)
+#pragma unroll
+    for (int i = 0; i < NW; ++i) {
+        TL[i] = TH[i] = 0;
+        if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(W.centroids + 4 * i, TL[i], TH[i]);
+    }
     // tile i of this warp in the pair-interleaved layout
     const int pr = NW == 2 ? rt : (rt >> 1);
     const int pj0 = NW == 2 ? 0 : (rt & 1);
@@ -435,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                                     for (int tt = 0; tt < NTT; ++tt)
 #pragma unroll
                                         for (int j = 0; j < 4; ++j) c[tt][j] = 0.f;
-                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL, TH, c, (p.kb_chunk - kbl) * F::XS * ntc);
+                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], c, (p.kb_chunk - kbl) * F::XS * ntc);
                                     const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv[i][d].x);
                                     const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv[i][d].y);
                                     const float s0 = __low2float(sz0), z0 = __high2float(sz0);
@@ -451,7 +455,7 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
                                         acc[i][tt][3] = fmaf(s1, fmaf(-z1, o.w, c[tt][3] - o.z), acc[i][tt][3]);
                                     }
                                 } else {
-                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL, TH, acc[i], (p.kb_chunk - kbl) * F::XS * ntc);
+                                    block_mma<FMT, NTT>(q[i][d], xs_kb, ntc, g, t, TL[i], TH[i], acc[i], (p.kb_chunk - kbl) * F::XS * ntc);
                                 }
                                 const int kn = kb + kDepth;
                                 if (kn < wk_hi) load_codes<FMT, RM>(W, rt, pr, pj0 + i, kn, nkb, lane, q[i][d], szv[i][d]);

@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
     fetch_seek();
     while (f_live && fseq < S) fetch_one();
 
-    uint32_t TL = 0, TH = 0;
+    uint32_t TL[2] = {0, 0}, TH[2] = {0, 0};  // codebook tables of the two tiles of a pair
     int staged_slot = -1, red_par = 0;
     bool dead = false;
     constexpr int ncol_i8 = 2 * kRows;  // digit columns staged on the integer path
@@ -456,7 +456,11 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
             }
             __syncthreads();
             staged_slot = im.slot;
-            if constexpr (FMT == GLQ_FMT_T2) make_t2_tables(cs.centroids, TL, TH);
+            if constexpr (FMT == GLQ_FMT_T2) {
+                // a fused gate|up weight carries two codebooks (4 floats each)
+                make_t2_tables(cs.centroids, TL[0], TH[0]);
+                make_t2_tables(cs.centroids + (swiglu ? 4 : 0), TL[1], TH[1]);
+            }
         }
         if (!im.valid) continue;
 
@@ -552,7 +556,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                                 acc[j][nt][3] = fmaf(s1, fmaf(-z1, xx1, cc[nt][3] - ox1), acc[j][nt][3]);
                             }
                         } else {
-                            tile_block<FMT, NT>(q, bx, TL, TH, acc[j]);
+                            tile_block<FMT, NT>(q, bx, TL[j], TH[j], acc[j]);
                         }
                     }
                 }

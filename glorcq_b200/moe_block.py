@@ -1,0 +1,210 @@
+"""MoE block on the sm_100a kernels.
+
+Drop-in for the reference's ``inference.moe_block.GraphCompatibleMoeBlock``
+(inference/moe_block.py:42-436): it is built from the sub-modules of a Qwen2-MoE style sparse block
+(``num_experts, top_k, norm_topk_prob, gate, experts[i].{gate_proj, up_proj, down_proj},
+shared_expert, shared_expert_gate``) and returns ``(hidden_states, router_logits)``.
+
+Where the reference has three Python dispatch paths (a per-token decode loop with a host
+synchronisation, a sparse loop over all experts for prefill, and a dense all-experts path for CUDA
+graphs), this block makes ONE call into the C ABI (``glq_moe_forward``): routing, per-expert token
+lists, the cluster-shared x.U, fused gate|up + SwiGLU, down, shared expert and the weighted combine
+all run on the device with launch shapes fixed by the token count, so the same code serves eager
+prefill, eager decode and graph capture, and only the routed experts' weights are read.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib, tiled
+from ._lib import FMT_T2, MoeDesc, Weight
+from .tiled import TiledWeight
+
+
+def _fuse_tiles(a: TiledWeight, b: TiledWeight) -> TiledWeight:
+    """gate|up fused weight from two plain tiled weights of one shape: pair p = (tile p of a, tile p of b).
+    Pure re-indexing of the already tiled buffers (load time)."""
+    if (a.fmt, a.N, a.K, a.group_size, a.rank) != (b.fmt, b.N, b.K, b.group_size, b.rank):
+        raise RuntimeError("gate_proj and up_proj must share format, shape, group size and rank")
+    L = _lib.lib()
+    f = TiledWeight(a.fmt, a.N, a.K, a.group_size, 2, a.device)
+    ntiles = (a.N + 15) // 16
+    bb = 512 if a.fmt == FMT_T2 else 576
+    nkb = a.codes.numel() // (((ntiles + 1) // 2) * 2 * bb)
+
+    def tiles(t):  # [pair][kb][j][bb] -> [tile][kb][bb]
+        v = t.codes.view(-1, nkb, 2, bb).permute(0, 2, 1, 3).reshape(-1, nkb, bb)
+        return v[:ntiles]
+    f.codes.view(ntiles, nkb, 2, bb).copy_(torch.stack([tiles(a), tiles(b)], dim=2))
+    if a.fmt == FMT_T2:
+        f.centroids = torch.cat([a.centroids, b.centroids]).contiguous()   # one codebook per fused matrix
+        f.norms.view(ntiles, 2, 16).copy_(torch.stack([a.norms.view(-1, 16)[:ntiles], b.norms.view(-1, 16)[:ntiles]], 1))
+    if a.rank > 0:
+        ns = (a.rank + 63) // 64
+        f.sv = torch.zeros(L.glq_sv_bytes(a.N, a.rank, 2), dtype=torch.uint8, device=a.device)
+        f.rank = a.rank
+
+        def svt(t):  # [pair][slice][2][16 rows][128 B] -> [tile][slice][2048 B]
+            v = t.sv.view(-1, ns, 2, 2048).permute(0, 2, 1, 3).reshape(-1, ns, 2048)
+            return v[:ntiles]
+        f.sv.view(ntiles, ns, 2, 2048).copy_(torch.stack([svt(a), svt(b)], dim=2))
+    return f
+
+
+def _table(descs: List[Weight], device) -> torch.Tensor:
+    raw = b"".join(bytes(d) for d in descs)
+    return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+
+
+class GraphCompatibleMoeBlock(nn.Module):
+    """Drop-in replacement for Qwen2MoeSparseMoeBlock running on the fused kernels."""
+
+    def __init__(self, original_block):
+        super().__init__()
+        self.num_experts = original_block.num_experts
+        self.top_k = original_block.top_k
+        self.norm_topk_prob = original_block.norm_topk_prob
+        self.gate = original_block.gate
+        self.experts = original_block.experts
+        self.shared_expert = getattr(original_block, "shared_expert", None)
+        self.shared_expert_gate = getattr(original_block, "shared_expert_gate", None)
+        self.graph_mode = False          # kept for the wrapper; both modes run the same device path
+        self._graph_threshold = 4        # token counts up to this combine in top-k slot order
+        self._built = False
+        self._keep = []                  # tensors the descriptor tables point into
+        self._desc: Optional[MoeDesc] = None
+        self._ws = {}
+        self.last_selected_experts = None
+        self.last_routing_weights = None
+
+    # the reference hands every block the cross-layer U pool; here the pool is tiled.tiled_ut()
+    def set_global_pool(self, pools, id_maps):
+        self._global_pools, self._global_id_maps = pools, id_maps
+
+    # ---- one-time device tables ---------------------------------------------------------------
+    def _build(self, device):
+        E = self.num_experts
+        ex0 = self.experts[0]
+        lins = [(e.gate_proj, e.up_proj, e.down_proj) for e in self.experts]
+        for g, u, dn in lins:
+            for lin in (g, u, dn):
+                if getattr(lin, "_tiled", None) is None:
+                    raise RuntimeError("every expert projection must be a GLoRCQLinear in the tiled layout "
+                                       "(2/4-bit codes with group size 128/64 multiples, or 2-bit codebook)")
+        g0, _, d0 = lins[0]
+        H, I = g0.in_features, g0.out_features
+        fmt, gs = g0._tiled.fmt, g0._tiled.group_size
+        rank = g0._tiled.rank
+        gate_up, down, utg, utu, utd = [], [], [], [], []
+        for g, u, dn in lins:
+            f = _fuse_tiles(g._tiled, u._tiled)
+            if (f.fmt, f.group_size, f.rank, f.N, f.K) != (fmt, gs, rank, I, H) or \
+                    (dn._tiled.fmt, dn._tiled.group_size, dn._tiled.rank, dn._tiled.N, dn._tiled.K) != (fmt, gs, rank, H, I):
+                raise RuntimeError("all experts of a block must share format, group size, rank and shapes")
+            self._keep += [f, dn._tiled]
+            gate_up.append(f.desc)
+            down.append(dn._tiled.desc)
+            if rank > 0:
+                for lin, lst in ((g, utg), (u, utu), (dn, utd)):
+                    ut = tiled.tiled_ut(lin.U)
+                    self._keep.append(ut)
+                    lst.append(Weight(ut.codes.data_ptr(), None, None, None, None, None, ut.N, ut.K, 0, 0))
+        d = MoeDesc()
+        d.H, d.I, d.E, d.top_k = H, I, E, self.top_k
+        d.rank, d.fmt, d.group_size = rank, fmt, gs
+        d.norm_topk_prob = int(bool(self.norm_topk_prob))
+        d.slot_order_max_tokens = self._graph_threshold
+        # router (+ shared expert gate as one more row)
+        rows = [self.gate.weight.detach().to(device=device, dtype=torch.float16)]
+        has_shared = self.shared_expert is not None
+        if has_shared and self.shared_expert_gate is not None:
+            rows.append(self.shared_expert_gate.weight.detach().to(device=device, dtype=torch.float16).reshape(1, H))
+        router = TiledWeight.from_dense(torch.cat(rows, 0).contiguous())
+        self._keep.append(router)
+        d.router_t, d.router_rows = router.codes.data_ptr(), router.N
+        tabs = [_table(gate_up, device), _table(down, device)]
+        d.gate_up, d.down = tabs[0].data_ptr(), tabs[1].data_ptr()
+        if rank > 0:
+            tabs += [_table(utg, device), _table(utu, device), _table(utd, device)]
+            d.ut_gate, d.ut_up, d.ut_down = tabs[2].data_ptr(), tabs[3].data_ptr(), tabs[4].data_ptr()
+        self._keep += tabs
+        # rotations of the codebook format
+        if fmt == FMT_T2:
+            d.rot_in = self._rotation(g0, device)
+            d.rot_mid = self._rotation(d0, device)
+        if has_shared:
+            sg, su, sd = self.shared_expert.gate_proj, self.shared_expert.up_proj, self.shared_expert.down_proj
+            for lin in (sg, su, sd):
+                if getattr(lin, "_tiled", None) is None:
+                    raise RuntimeError("the shared expert must use GLoRCQLinear projections in the tiled layout")
+            f = _fuse_tiles(sg._tiled, su._tiled)
+            if (f.fmt, f.group_size, f.K) != (fmt, gs, H) or f.rank not in (0, rank) or sd._tiled.rank != f.rank:
+                raise RuntimeError("the shared expert must share format, group size and rank with the routed experts")
+            self._keep += [f, sd._tiled]
+            d.I_shared = sg.out_features
+            d.sh_gate_up, d.sh_down = f.desc, sd._tiled.desc
+            if f.rank > 0:
+                uts = [tiled.tiled_ut(lin.U) for lin in (sg, su, sd)]
+                self._keep += uts
+                d.sh_ut_gate, d.sh_ut_up, d.sh_ut_down = (u.codes.data_ptr() for u in uts)
+            if fmt == FMT_T2:
+                d.sh_rot_mid = self._rotation(sd, device)
+        self._desc = d
+        self._built = True
+        _ = ex0
+
+    def _rotation(self, lin, device):
+        """Tiled rotation matrix of a codebook-format layer (None if it has no rotation cache)."""
+        rc = getattr(lin, "_rotation_cache", None)
+        if getattr(lin, "_rht_signs", None) is not None:
+            raise RuntimeError("Hadamard rotation is not supported inside the fused block yet")
+        if rc is None:
+            return None
+        Pi = rc.get_pi(lin.turbo_dim, lin.turbo_bits, lin.turbo_seed)
+        key = ("pi", Pi.data_ptr())
+        cache = GraphCompatibleMoeBlock._PI
+        if key not in cache:
+            cache[key] = TiledWeight.from_dense(Pi.to(device=device, dtype=torch.float16).contiguous())
+        self._keep.append(cache[key])
+        return cache[key].codes.data_ptr()
+
+    _PI = {}
+
+    # ---- forward (inference/moe_block.py:381-436) -----------------------------------------------
+    def forward(self, hidden_states):
+        batch_size, sequence_length, hidden_dim = hidden_states.shape
+        x = hidden_states.reshape(-1, hidden_dim)
+        if x.dtype != torch.float16:
+            x = x.half()
+        x = x.contiguous()
+        if not x.is_cuda:
+            raise RuntimeError("GraphCompatibleMoeBlock runs on a CUDA device only (no CPU path)")
+        if not self._built:
+            self._build(x.device)
+        d = self._desc
+        n = x.shape[0]
+        out = torch.empty(n, d.H, dtype=torch.float16, device=x.device)
+        logits = torch.empty(n, d.E, dtype=torch.float16, device=x.device)
+        sel = torch.empty(n, d.top_k, dtype=torch.int32, device=x.device)
+        wts = torch.empty(n, d.top_k, dtype=torch.float16, device=x.device)
+        if n > 0:
+            L = _lib.lib()
+            with torch.cuda.device(x.device):
+                key = (n, tiled._stream_ptr(x.device))
+                if key not in self._ws:
+                    nbytes = L.glq_moe_workspace_bytes(C.byref(d), n)
+                    nctr = L.glq_moe_counters(C.byref(d), n)
+                    self._ws[key] = (torch.empty(nbytes + 256, dtype=torch.uint8, device=x.device),
+                                     torch.zeros(max(nctr, 1), dtype=torch.int32, device=x.device))
+                ws, ctr = self._ws[key]
+                base = (ws.data_ptr() + 255) // 256 * 256
+                _lib.check(L.glq_moe_forward(C.byref(d), x.data_ptr(), n, out.data_ptr(), logits.data_ptr(),
+                                             sel.data_ptr(), wts.data_ptr(), base, ws.numel() - (base - ws.data_ptr()),
+                                             ctr.data_ptr(), ctr.numel(), tiled._stream_ptr(x.device)), "moe_forward")
+        self.last_selected_experts, self.last_routing_weights = sel, wts
+        return out.reshape(batch_size, sequence_length, hidden_dim), logits

@@ -45,7 +45,7 @@ typedef struct glq_weight {
     const void* codes;      /* tiled codes with their scales (Q2/Q4/T2) or tiled fp16 values (F16) */
     const void* reserved0;
     const float* norms;     /* T2: per-row norms in tile order                                   */
-    const float* centroids; /* T2: (4,) fp32                                                     */
+    const float* centroids; /* T2: (4,) fp32; (8,) for a fused gate|up weight: gate's, then up's  */
     const void* sv;         /* packed output-side low-rank factor, or NULL                       */
     const void* bias;       /* (N,) fp16 or NULL (GLQ_EPI_LINEAR only)                           */
     int32_t N;              /* output features                                                   */
@@ -183,6 +183,47 @@ int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w, const voi
                        int32_t* counters, size_t n_counters, void* stream);
 size_t glq_linear_workspace_bytes(int fmt, int group_size, const glq_weight_t* w, int B);
 size_t glq_linear_counters(int fmt, int group_size, const glq_weight_t* w, int B);
+
+/* ---------------------------------------------------------------------------------------------
+ * MoE block forward (GraphCompatibleMoeBlock.forward, inference/moe_block.py:381-436), entirely on
+ * the device: router matmul, softmax in fp32, top-k, optional renormalisation, per-expert token
+ * lists, x.U per routed expert, fused gate|up with SwiGLU, down projection scaled by the routing
+ * weight, shared expert with its sigmoid gate, combine.  No host synchronisation and fixed launch
+ * shapes, so the whole call can be captured into a CUDA graph; only the routed experts' weights are
+ * read.  The weighted sum over a token's experts is done in fp16 in top-k slot order for up to
+ * `slot_order_max_tokens` tokens (the reference's decode loop, inference/moe_block.py:474-476) and
+ * in expert order above (index_add over experts, inference/moe_block.py:716-739).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct glq_moe_desc {
+    int32_t H, I, E, top_k;
+    int32_t I_shared;        /* 0: no shared expert */
+    int32_t rank;            /* low-rank width of every projection (0: none) */
+    int32_t fmt, group_size; /* format of the expert projections */
+    int32_t norm_topk_prob;
+    int32_t router_rows;     /* E, or E+1 when row E is the shared expert's gate */
+    int32_t slot_order_max_tokens;
+    int32_t reserved;
+    const void* router_t;          /* tiled F16 (router_rows x H) */
+    const glq_weight_t* gate_up;   /* device table [E]: fused gate|up, N = I */
+    const glq_weight_t* down;      /* device table [E]: N = H, K = I */
+    const glq_weight_t* ut_gate;   /* device tables [E] of dense U^T (rank x H / rank x I), or NULL */
+    const glq_weight_t* ut_up;
+    const glq_weight_t* ut_down;
+    glq_weight_t sh_gate_up, sh_down;            /* shared expert (ignored when I_shared == 0) */
+    const void* sh_ut_gate; const void* sh_ut_up; const void* sh_ut_down; /* tiled U^T or NULL */
+    /* codebook format only: rotations applied to the input of the quantized product (the low-rank
+     * term sees the unrotated input), as tiled F16 matrices Pi (y = x . Pi^T), or NULL for identity:
+     * H x H before gate/up, I x I before down, I_shared x I_shared before the shared down */
+    const void* rot_in; const void* rot_mid; const void* sh_rot_mid;
+} glq_moe_desc_t;
+
+size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens);
+size_t glq_moe_counters(const glq_moe_desc_t* d, int n_tokens);
+/* x (n_tokens, H) fp16 -> out (n_tokens, H) fp16; router_logits (n_tokens, E) fp16 may be NULL.
+ * sel_out (n_tokens, top_k) int32 and weight_out (n_tokens, top_k) fp16 may be NULL. */
+int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n_tokens, void* out, void* router_logits,
+                    int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,
+                    size_t n_counters, void* stream);
 
 #ifdef __cplusplus
 }

@@ -174,3 +174,34 @@ def to_b200_linear(d, device="cuda", shared_u=None):
         lin.load_sv(U, d["SV"], device=device)
         lin.cluster_id = d.get("cluster_id")
     return lin
+
+
+class _B200Expert(torch.nn.Module):
+    def __init__(self, ex, device, shared_u):
+        super().__init__()
+        self.gate_proj = to_b200_linear(ex["gate_proj"], device, shared_u)
+        self.up_proj = to_b200_linear(ex["up_proj"], device, shared_u)
+        self.down_proj = to_b200_linear(ex["down_proj"], device, shared_u)
+        self.act_fn = torch.nn.functional.silu
+
+
+class _HFBlock:
+    """Stand-in with the attribute names of a transformers-4.45 Qwen2MoeSparseMoeBlock."""
+
+
+def to_b200_moe(blk, device="cuda"):
+    """glorcq_b200's GraphCompatibleMoeBlock from a case dict."""
+    from glorcq_b200.moe_block import GraphCompatibleMoeBlock
+    shared_u = {}
+    hf = _HFBlock()
+    hf.num_experts, hf.top_k, hf.norm_topk_prob = blk["E"], blk["top_k"], blk["norm_topk_prob"]
+    hf.gate = torch.nn.Linear(blk["H"], blk["E"], bias=False).half().to(device)
+    hf.gate.weight.data.copy_(blk["gate_weight"])
+    hf.experts = torch.nn.ModuleList([_B200Expert(ex, device, shared_u) for ex in blk["experts"]])
+    if blk.get("shared_expert") is not None:
+        hf.shared_expert = _B200Expert(blk["shared_expert"], device, shared_u)
+        hf.shared_expert_gate = torch.nn.Linear(blk["H"], 1, bias=False).half().to(device)
+        hf.shared_expert_gate.weight.data.copy_(blk["shared_gate_weight"])
+    else:
+        hf.shared_expert, hf.shared_expert_gate = None, None
+    return GraphCompatibleMoeBlock(hf)

@@ -1,0 +1,111 @@
+"""MoE block parity: the device-side block (one C-ABI call) against the CPU oracle of the
+reference's GraphCompatibleMoeBlock.forward, and against the golden vectors produced by the
+reference itself.  Bars: routing decisions identical; router logits and routing weights within
+rel-L2 1e-3; block output within rel-L2 2e-3 -- the block chains three fp16-rounded layers (gate/up,
+SwiGLU, down) plus fp16 weighted sums, each of which is held to 1e-3 on its own in test_gpu_linear.py,
+and the oracle rounds its dequantised weights to fp16 where the kernels keep (q - z) * s exact."""
+
+import pytest
+import torch
+
+from oracle import glorcq_oracle as O
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+REL = 1e-3
+REL_BLOCK = 2e-3
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from glorcq_b200 import _build
+    _build.build()
+    return torch.device("cuda:0")
+
+
+def _run(blk, N, dev, seed):
+    mb = cases.to_b200_moe(blk, dev)
+    x = cases.make_x(seed, N, blk["H"]).reshape(1, N, blk["H"])
+    y, logits = mb(x.to(dev))
+    ref, ref_logits = O.moe_forward(cases.to_oracle_moe(blk), x)
+    return mb, y.cpu(), logits.cpu(), ref, ref_logits
+
+
+@pytest.mark.parametrize("N", [1, 2, 3, 4, 5, 8, 9, 20, 33])
+@pytest.mark.parametrize("norm", [False, True])
+def test_small_block(dev, N, norm):
+    blk = cases.make_moe(300 + N, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3, norm_topk_prob=norm)
+    mb, y, logits, ref, ref_logits = _run(blk, N, dev, 1300 + N)
+    assert y.shape == ref.shape and logits.shape == ref_logits.shape
+    assert cases.rel_l2(logits, ref_logits) <= REL
+    # same experts chosen (ties aside, which the seeds avoid)
+    _, w_ref, sel_ref = O.route(cases.to_oracle_moe(blk), cases.make_x(1300 + N, N, 256))
+    assert torch.equal(mb.last_selected_experts.cpu().long(), sel_ref)
+    assert cases.rel_l2(mb.last_routing_weights.cpu(), w_ref) <= REL
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+
+
+@pytest.mark.parametrize("N", [1, 8])
+def test_no_shared_expert_and_top8(dev, N):
+    blk = cases.make_moe(410 + N, 256, 128, 16, 8, I_shared=0, rank=16, experts_per_cluster=4, norm_topk_prob=True)
+    mb, y, logits, ref, _ = _run(blk, N, dev, 1410 + N)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+
+
+@pytest.mark.parametrize("N", [1, 7])
+def test_codebook_format_block(dev, N):
+    blk = cases.make_moe(35, 256, 128, 6, 2, I_shared=256, rank=16, experts_per_cluster=2, fmt="turbo")
+    for ex in blk["experts"] + [blk["shared_expert"]]:
+        for p in ex.values():
+            p["Pi"] = None
+    mb, y, logits, ref, _ = _run(blk, N, dev, 1035)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+
+
+@pytest.mark.parametrize("N", [1, 8])
+def test_qwen_moe_shape(dev, N):
+    """Config 2: hidden 2048, 60 experts top-4, intermediate 1408, shared expert 5632, rank 64,
+    U shared by clusters of 4 experts."""
+    blk = cases.make_moe(2000 + N, 2048, 1408, 60, 4, I_shared=5632, rank=64, experts_per_cluster=4)
+    mb, y, logits, ref, _ = _run(blk, N, dev, 3000 + N)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+
+
+def test_against_golden(dev, golden):
+    from tests.golden.make_golden import MOE_CASES
+    for name, kw, N in MOE_CASES:
+        blk = cases.make_moe(**kw)
+        if blk["fmt"] == "turbo":
+            for ex in blk["experts"] + [blk["shared_expert"]]:
+                for p in ex.values():
+                    p["Pi"] = None
+        mb = cases.to_b200_moe(blk, dev)
+        x = cases.make_x(kw["seed"] + 1000, N, kw["H"]).reshape(1, N, kw["H"])
+        y, logits = mb(x.to(dev))
+        g = golden["moe"][name]
+        assert cases.rel_l2(logits.cpu(), g["router_logits"]) <= REL, name
+        assert cases.rel_l2(y.cpu(), g["y"]) <= REL_BLOCK, name
+
+
+def test_graph_capture_replay(dev):
+    """The whole block is capturable: no host synchronisation, fixed launch shapes."""
+    blk = cases.make_moe(77, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    mb = cases.to_b200_moe(blk, dev)
+    xs = [cases.make_x(500 + i, 1, 256).reshape(1, 1, 256) for i in range(3)]
+    static_x = xs[0].to(dev).clone()
+    mb(static_x)                      # builds tables and workspaces outside the capture
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        mb(static_x)
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_y, _ = mb(static_x)
+    for x in xs:
+        static_x.copy_(x.to(dev))
+        graph.replay()
+        ref, _ = O.moe_forward(cases.to_oracle_moe(blk), x)
+        assert cases.rel_l2(static_y.cpu(), ref) <= REL_BLOCK
