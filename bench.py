@@ -1,0 +1,325 @@
+"""Benchmark of the GLoRCQ real-quant decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+Workload (one GPU): batch-1 decode through the MoE blocks of the Qwen1.5-MoE-A2.7B-shaped model --
+24 layers of {router, 60 experts top-4 (intermediate 1408), shared expert (5632)}, every projection
+2-bit g128 with a rank-64 low-rank correction whose input-side factor U is shared by clustered
+experts across layers -- on seeded synthetic weights.  One step = one token through all layers, the
+output of a block feeding the next, replayed from one CUDA graph.  The weights of the 24 layers
+(5.7 GB) are far larger than L2, and every token touches ~0.67 GB of them.
+
+One JSON line on stdout:
+  value     tokens/s with the hidden state resident in HBM (device-timed with CUDA events)
+  e2e       the same through the public API with pinned host buffers: h2d of the hidden state, graph
+            replay, d2h of the block output, every step
+  roofline  the dominant kernel (the grouped dequant-GEMV) timed alone, live, on 240 distinct
+            expert-projection problems (1408 x 2048, 2-bit g128, rank 64; 240 MB, larger than L2):
+            algorithmic bytes / CUDA-event time against the measured HBM peak
+  cpu_baseline  the CPU restatement of the reference's own path (oracle/), timed on the host cores on
+            a bounded sample (one layer, one token, repeated)
+`--impl reference` times that CPU path as the main line (rank 0 only).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+CFG = dict(H=2048, I=1408, E=60, top_k=4, I_shared=5632, rank=64, experts_per_cluster=4)
+METRIC = "moe_decode_tok_s"
+UNIT = "tok/s"
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ---- clocks ---------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+        sm, smax, reasons = [], 0, set()
+        for ln in self.samples:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(int(float(f[0])))
+                smax = max(smax, int(float(f[1])))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- CPU baseline (reference arm) -----------------------------------------------------------------
+def cpu_layer_seconds(reps_budget_s=12.0, max_reps=200):
+    """One layer, one token, through the CPU oracle (the reference's PyTorch path restated); returns
+    (median seconds per layer-forward, threads, reps)."""
+    from oracle import glorcq_oracle as O
+    from tests import cases
+    torch.set_num_threads(os.cpu_count() or 1)
+    blk = cases.make_moe(2001, CFG["H"], CFG["I"], CFG["E"], CFG["top_k"], I_shared=CFG["I_shared"], rank=CFG["rank"],
+                         experts_per_cluster=CFG["experts_per_cluster"])
+    ob = cases.to_oracle_moe(blk)
+    x = cases.make_x(3001, 1, CFG["H"]).reshape(1, 1, CFG["H"])
+    with torch.no_grad():
+        for _ in range(2):
+            O.moe_forward(ob, x)
+        ts, t_start = [], time.perf_counter()
+        while len(ts) < max_reps and (time.perf_counter() - t_start < reps_budget_s or len(ts) < 3):
+            t0 = time.perf_counter()
+            O.moe_forward(ob, x)
+            ts.append(time.perf_counter() - t0)
+    ts.sort()
+    return ts[len(ts) // 2], torch.get_num_threads(), len(ts)
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    layers = args.layers
+    per = []
+    sec, threads, reps = cpu_layer_seconds(reps_budget_s=3.0, max_reps=5)      # warm-up sample
+    for _ in range(max(1, args.steps)):
+        sec, threads, reps = cpu_layer_seconds(reps_budget_s=8.0 / max(1, args.steps) + 1.0, max_reps=50)
+        per.append(sec)
+    per.sort()
+    sec = per[len(per) // 2]
+    value = 1.0 / (sec * layers)
+    sample = f"1 of {layers} layers, 1 token, median of repeated CPU forwards; tok/s = 1 / ({layers} x layer time)"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * layers * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": workload_config(layers),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(layers):
+    return {"workload": f"Qwen1.5-MoE-A2.7B-shaped MoE decode, batch 1: {layers} MoE blocks (hidden 2048, 60 experts "
+                        "top-4 x 1408, shared expert 5632), 2-bit g128 + rank-64 shared-U correction; attention "
+                        "and lm_head not included", "layers": layers, "batch": 1,
+            "l2": "weights (240 MB per layer) far exceed L2; each token reads other experts' weights of 24 distinct layers"}
+
+
+# ---- GPU arm ----------------------------------------------------------------------------------------
+def gemv_roofline(dev, peak_gbs, peak_kind):
+    """The grouped dequant-GEMV alone: 240 distinct 1408x2048 2-bit g128 rank-64 problems, one row each."""
+    import ctypes as C
+    from glorcq_b200 import _lib
+    from glorcq_b200.tiled import TiledWeight
+    P, N, K, r = 240, 1408, 2048, 64
+    L = _lib.lib()
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    keep, descs = [], []
+    for _ in range(P):
+        tw = TiledWeight.from_gptq(torch.randint(0, 4, (N, K), generator=g, device=dev, dtype=torch.int32),
+                                   (torch.randn(N, K // 128, generator=g, device=dev) * 0.02).abs().half(),
+                                   torch.randint(0, 4, (N, K // 128), generator=g, device=dev).half(), 2, 128)
+        tw.put_sv(0, (torch.randn(N, r, generator=g, device=dev) * 0.01).half())
+        keep.append(tw)
+        descs.append(tw.desc_bytes())
+    table = torch.frombuffer(bytearray(b"".join(descs)), dtype=torch.uint8).to(dev)
+    x = torch.randn(P, K, generator=g, device=dev).half()
+    a = (torch.randn(P, r, generator=g, device=dev) * 0.1).half()
+    y = torch.empty(P, N, dtype=torch.float16, device=dev)
+    m = _lib.MMArgs()
+    m.fmt, m.group_size, m.epilogue, m.n_problems, m.max_rows, m.rows_stride = _lib.FMT_Q2, 128, 0, P, 1, 1
+    m.N, m.K, m.rank = N, K, r
+    m.w_table = table.data_ptr()
+    m.x, m.ldx, m.a0, m.lda, m.y, m.ldy = x.data_ptr(), K, a.data_ptr(), r, y.data_ptr(), N
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(5):
+        _lib.check(L.glq_grouped_matmul(C.byref(m), st))
+    torch.cuda.synchronize()
+    iters = 50
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        _lib.check(L.glq_grouped_matmul(C.byref(m), st))
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / iters * 1e-3
+    # per problem: codes + (scale, zero) pairs + SV + x + a + y  (U is read by the separate x.U kernel)
+    per = N * K // 4 + N * (K // 128) * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
+    achieved = P * per / sec / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+            "traffic": None, "kernel": "stream_kernel<Q2,int8 path> (grouped dequant-GEMV)",
+            "launch_us": sec * 1e6, "bytes_per_launch": P * per, "peak_kind": peak_kind,
+            "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), 1 row each; {P * per / 1e6:.0f} MB > L2"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from glorcq_b200 import _build, synthetic, tiled
+    _build.build()
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    layers = args.layers
+    pools = {}
+    blocks = [synthetic.make_moe_block(1000 + l, dev, pools=pools, **CFG) for l in range(layers)]
+    H = CFG["H"]
+    static_x = torch.randn(1, 1, H, device=dev, dtype=torch.float16)
+    x0 = static_x.clone()
+
+    def token(x):
+        for blk in blocks:
+            x, _ = blk(x)
+            # the decoder's RMS norm between blocks (library op): keeps every layer's input at unit scale
+            x = torch.nn.functional.rms_norm(x, (x.shape[-1],))
+        return x
+
+    # warm-up outside capture (builds workspaces), then capture one token
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s), torch.no_grad():
+        for _ in range(2):
+            token(static_x)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        static_y = token(static_x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ----
+    for _ in range(max(3, args.warmup)):
+        static_x.copy_(static_y)
+        graph.replay()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        static_x.copy_(static_y)     # next token's hidden state stays on the device
+        graph.replay()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # ---- end to end: pinned host in, host out, every step ----
+    hx = torch.empty(1, 1, H, dtype=torch.float16).pin_memory()
+    hy = torch.empty(1, 1, H, dtype=torch.float16).pin_memory()
+    hx.copy_(x0.cpu())
+    for _ in range(3):
+        static_x.copy_(hx, non_blocking=True)
+        graph.replay()
+        hy.copy_(static_y, non_blocking=True)
+        torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        static_x.copy_(hx, non_blocking=True)
+        graph.replay()
+        hy.copy_(static_y, non_blocking=True)
+        torch.cuda.synchronize()
+        hx.copy_(hy)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    err = tiled.debug_error()
+    if rank == 0:
+        peak, kind = measured_peak_gbs()
+        roof = gemv_roofline(dev, peak, kind)
+        sec_layer, threads, reps = cpu_layer_seconds()
+        bytes_tok = synthetic.block_bytes_per_token(**{k: CFG[k] for k in ("H", "I", "top_k", "I_shared", "rank", "E")}) * layers
+        value = world * args.steps / (ms * 1e-3)
+        cfg = workload_config(layers)
+        cfg.update({"parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                    "algorithmic_bytes_per_token": bytes_tok,
+                    "token_hbm_frac_of_peak": bytes_tok * args.steps / (ms * 1e-3) / 1e9 / peak})
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": cfg,
+                "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
+                        "d2h_bytes_per_step": H * 2},
+                "gpu_launches": args.steps * layers * 14,
+                "roofline": roof,
+                "cpu_baseline": {"value": 1.0 / (sec_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
+                                 "sample": f"1 of {layers} layers, 1 token, median of {reps} CPU forwards of the oracle"},
+                "clocks": clocks, "kernel_self_check": err}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=24)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -175,6 +175,19 @@ class GraphCompatibleMoeBlock(nn.Module):
 
     _PI = {}
 
+    def prepare(self, device, release_linear_tiles=False):
+        """Build the device tables now (otherwise done on the first forward).  With
+        release_linear_tiles the per-projection tiled copies of the routed experts' gate/up weights
+        are dropped once they are fused (the expert modules can then no longer run on their own)."""
+        if not self._built:
+            self._build(torch.device(device))
+        if release_linear_tiles:
+            for e in self.experts:
+                e.gate_proj._tiled = e.up_proj._tiled = None
+            if self.shared_expert is not None:
+                self.shared_expert.gate_proj._tiled = self.shared_expert.up_proj._tiled = None
+        return self
+
     # ---- forward (inference/moe_block.py:381-436) -----------------------------------------------
     def forward(self, hidden_states):
         batch_size, sequence_length, hidden_dim = hidden_states.shape

@@ -67,7 +67,7 @@ class GLoRCQLinear(nn.Module):
         self._ut = None              # TiledWeight of U^T (shared through tiled.tiled_ut)
 
     # ---- loaders (inference/quantized_linear.py:195-269) ---------------------------------
-    def load_gptq(self, packed_data, device="cuda", keep_raw=False):
+    def load_gptq(self, packed_data, device="cuda", keep_raw=False, check_range=True):
         """Integer codes + per-group scale/zero.  2- and 4-bit codes with a group size that is a
         multiple of 128 (64 for 4-bit) are re-tiled for the fused kernel; anything else keeps the
         (N,K) codes and runs through the int8 drop-in kernel."""
@@ -79,7 +79,7 @@ class GLoRCQLinear(nn.Module):
         self.gptq_groupsize = packed_data["groupsize"]
         self.gptq_sym = packed_data.get("sym", False)
         in_range = True
-        if _tileable(self.gptq_bits, self.gptq_groupsize):
+        if check_range and _tileable(self.gptq_bits, self.gptq_groupsize):
             in_range = bool(((q >= 0) & (q < 2 ** self.gptq_bits)).all())   # load time only
         if _tileable(self.gptq_bits, self.gptq_groupsize) and in_range:
             self._tiled = TiledWeight.from_gptq(q, self.scales, self.zeros, self.gptq_bits,
