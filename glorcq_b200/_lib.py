@@ -56,6 +56,8 @@ _SIGS = {
     "glq_status_string": (C.c_char_p, [C.c_int]),
     "glq_last_cuda_error": (C.c_int, []),
     "glq_turbo_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
+    "glq_static_scratch_bytes": (C.c_size_t, []),
+    "glq_turbo_dequant_matmul_static": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
     "glq_turbo_dequant_grouped_gemv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
     "glq_gptq_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_int, vp]),

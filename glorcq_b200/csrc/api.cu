@@ -41,7 +41,7 @@ extern "C" const char* glq_status_string(int status) {
         case GLQ_ERR_ALIGN: return "pointer or leading dimension not aligned to 16 bytes";
         case GLQ_ERR_UNSUPPORTED: return "shape, group size or rank not supported by the sm_100a kernels";
         case GLQ_ERR_CUDA: return "CUDA call failed (see glq_last_cuda_error)";
-        case GLQ_ERR_WORKSPACE: return "workspace too small";
+        case GLQ_ERR_WORKSPACE: return "workspace too small (or, for the *_static entry point, the problem needs more scratch than the fixed array holds)";
         default: return "unknown status";
     }
 }
@@ -604,6 +604,66 @@ extern "C" int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const vo
         GLQ_CUDA(cudaGetLastError());
     }
     return GLQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// glq_turbo_dequant_matmul_static: the same product as glq_turbo_dequant_matmul, with k split over
+// CTAs so that a single small matmul fills the machine, for callers that cannot hand over (or
+// allocate) a workspace.  The partial sums and the arrival counters of the split live in a fixed
+// array that is part of the library image.
+// ---------------------------------------------------------------------------------------------
+#define GLQ_STATIC_SCRATCH_BYTES (4u << 20)  /* partial sums */
+#define GLQ_STATIC_COUNTERS 4096             /* arrival counters (ints), in front of the partial sums */
+static __device__ __align__(256) unsigned char g_static_scratch[GLQ_STATIC_COUNTERS * 4 + GLQ_STATIC_SCRATCH_BYTES];
+
+extern "C" size_t glq_static_scratch_bytes(void) { return GLQ_STATIC_SCRATCH_BYTES; }
+
+extern "C" int glq_turbo_dequant_matmul_static(const void* x_rot, const uint8_t* packed, const float* norms,
+                                               const float* centroids, void* y, int B, int N, int K, void* stream) {
+    if (B < 0 || N < 0) return GLQ_ERR_ARG;
+    if (B == 0 || N == 0) return GLQ_OK;
+    if (!x_rot || !packed || !norms || !centroids || !y) return GLQ_ERR_ARG;
+    if (K <= 0 || K % 4 != 0) return GLQ_ERR_UNSUPPORTED;
+    // The array's name is only a host-side handle: its device address is looked up once per device,
+    // with that device current, and it is that address the kernel gets.
+    static unsigned char* dev_ptr[64] = {nullptr};
+    int dev = 0;
+    GLQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return GLQ_ERR_UNSUPPORTED;
+    if (dev_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        GLQ_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (ptr == nullptr) return GLQ_ERR_CUDA;
+        dev_ptr[dev] = reinterpret_cast<unsigned char*>(ptr);
+    }
+    Geometry g;
+    int rc = plan_geometry(GLQ_FMT_T2, GLQ_EPI_LINEAR, N, K, 0, 1, B, true, &g);
+    if (rc != GLQ_OK) return rc;
+    // sizes the fixed array cannot hold are rejected, not truncated
+    if (g.scratch_bytes > GLQ_STATIC_SCRATCH_BYTES || g.n_counters > GLQ_STATIC_COUNTERS) return GLQ_ERR_WORKSPACE;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    // every call shares the array and it keeps the previous call's contents: the counters must start at zero
+    if (g.n_counters > 0) GLQ_CUDA(cudaMemsetAsync(dev_ptr[dev], 0, g.n_counters * sizeof(int), st));
+    SkinnyParams p{};
+    p.w.codes = packed;
+    p.w.norms = norms;
+    p.w.centroids = centroids;
+    p.w.N = N;
+    p.w.K = K;
+    p.sv_slices = 1;
+    p.x = reinterpret_cast<const __half*>(x_rot);
+    p.ldx = K;
+    p.y = reinterpret_cast<__half*>(y);
+    p.ldy = N;
+    p.max_rows = B;
+    p.rows_stride = B;
+    p.x_vec = (aligned16(x_rot) && K % 8 == 0) ? 1 : 0;
+    p.x_extent = (long long)B * K;
+    p.y_extent = (long long)B * N;
+    p.counters = reinterpret_cast<int*>(dev_ptr[dev]);
+    p.scratch = reinterpret_cast<float4*>(dev_ptr[dev] + GLQ_STATIC_COUNTERS * 4);
+    fill_geometry(p, g);
+    return launch_skinny(GLQ_FMT_T2, true, p, g, 1, st);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -85,6 +85,25 @@ int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const void* scales,
                             const float* lora_out, float* y, int B, int N, int K, int groupsize, int n_groups,
                             int sym, void* stream);
 
+/* glq_turbo_dequant_matmul_static -- no counterpart in the reference.
+ * Same operands and result as glq_turbo_dequant_matmul, for hosts that cannot allocate device
+ * memory on this path and have no workspace to lend: for example a serving process that hands all
+ * device memory to one arena at start-up and forbids cudaMalloc afterwards (it synchronises the
+ * device and fragments the arena), or a plugin called from a thread that does not own an allocator.
+ * The k dimension is split over CTAs so that one small matmul still occupies every SM; the partial
+ * sums and arrival counters of that split live in a fixed array inside the library image
+ * (glq_static_scratch_bytes() = 4 MiB plus 16 KiB of counters; every GPU that loads the library
+ * holds it until the process exits).  Nothing is allocated or freed by this call.
+ *   - Problems whose split needs more than that are refused with GLQ_ERR_WORKSPACE.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress with
+ *     that device current); make that first call before any stream capture begins.
+ *   - All calls share the one array, which keeps the previous call's contents; the counters are
+ *     cleared on the stream before each launch, but two calls that overlap on the GPU (different
+ *     streams, or different host threads) race on it: serialise them. */
+size_t glq_static_scratch_bytes(void);
+int glq_turbo_dequant_matmul_static(const void* x_rot, const uint8_t* packed, const float* norms,
+                                    const float* centroids, void* y, int B, int N, int K, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Load-time re-tiling (device to device).  Rows are grouped in tiles of 16, tiles in pairs.
  *   Q2  : [pair][k block of 128][tile in pair][576 B]; a block is 32 lanes x 16 B of codes -- lane
