@@ -151,12 +151,12 @@ def workload_config(layers):
 
 
 # ---- GPU arm ----------------------------------------------------------------------------------------
-def gemv_roofline(dev, peak_gbs, peak_kind):
-    """The grouped dequant-GEMV alone: 240 distinct 1408x2048 2-bit g128 rank-64 problems, one row each."""
+def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
+    """The grouped dequant-GEMV alone: P distinct 1408x2048 2-bit g128 rank-64 problems, one row each."""
     import ctypes as C
     from glorcq_b200 import _lib
     from glorcq_b200.tiled import TiledWeight
-    P, N, K, r = 240, 1408, 2048, 64
+    N, K, r = 1408, 2048, 64
     L = _lib.lib()
     g = torch.Generator(device=dev)
     g.manual_seed(7)
@@ -181,7 +181,6 @@ def gemv_roofline(dev, peak_gbs, peak_kind):
     for _ in range(5):
         _lib.check(L.glq_grouped_matmul(C.byref(m), st))
     torch.cuda.synchronize()
-    iters = 50
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
@@ -294,7 +293,7 @@ def run_ours(args, rank, world, local_rank):
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": cfg,
                 "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
                         "d2h_bytes_per_step": H * 2},
-                "gpu_launches": args.steps * layers * 14,
+                "gpu_launches": args.steps * layers * 10,
                 "roofline": roof,
                 "cpu_baseline": {"value": 1.0 / (sec_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
                                  "sample": f"1 of {layers} layers, 1 token, median of {reps} CPU forwards of the oracle"},
@@ -311,12 +310,22 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--gemv-only", action="store_true",
+                    help="time only the grouped dequant-GEMV roofline case (small enough for an ncu capture)")
+    ap.add_argument("--problems", type=int, default=240)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.gemv_only:
+        from glorcq_b200 import _build
+        _build.build()
+        peak, kind = measured_peak_gbs()
+        print(json.dumps({"roofline": gemv_roofline(torch.device("cuda:0"), peak, kind, P=args.problems,
+                                                     iters=max(1, args.steps))}), flush=True)
         return
     run_ours(args, rank, world, local_rank)
 

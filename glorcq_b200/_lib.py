@@ -45,7 +45,8 @@ class MoeDesc(C.Structure):
                 ("I_shared", C.c_int32), ("rank", C.c_int32), ("fmt", C.c_int32), ("group_size", C.c_int32),
                 ("norm_topk_prob", C.c_int32), ("router_rows", C.c_int32), ("slot_order_max_tokens", C.c_int32),
                 ("reserved", C.c_int32),
-                ("router_t", vp), ("gate_up", vp), ("down", vp), ("ut_gate", vp), ("ut_up", vp), ("ut_down", vp),
+                ("router_t", vp), ("gate_up", vp), ("down", vp), ("ut_gate_up", vp), ("ut_down", vp),
+                ("dense0_rows", C.c_int32), ("sh_a_row", C.c_int32),
                 ("sh_gate_up", Weight), ("sh_down", Weight),
                 ("sh_ut_gate", vp), ("sh_ut_up", vp), ("sh_ut_down", vp),
                 ("rot_in", vp), ("rot_mid", vp), ("sh_rot_mid", vp)]
@@ -81,7 +82,8 @@ _SIGS = {
                                      C.c_int, vp, C.c_size_t, vp, C.c_size_t, vp]),
     "glq_moe_workspace_bytes": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
     "glq_moe_counters": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
-    "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, vp, vp, C.c_size_t, vp, C.c_size_t, vp]),
+    "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, vp, vp, C.c_size_t, vp, C.c_size_t, vp,
+                                  vp, vp, vp]),
 }
 
 _lib = None

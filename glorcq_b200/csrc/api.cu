@@ -283,7 +283,13 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     off = (off + 127) / 128 * 128;
     g.off_ring = (int)off;
     const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.nt * 32 * 16 : 0;
-    const size_t cap = (size_t)(kStreamCtasPerSm == 1 ? 220 : 110) * 1024;
+    // two CTAs per SM when the staged activations leave room for it, else one
+    size_t cap = (size_t)(kStreamCtasPerSm == 1 ? 220 : 110) * 1024;
+    int ctas_per_sm = kStreamCtasPerSm;
+    if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) {
+        cap = 220 * 1024;
+        ctas_per_sm = 1;
+    }
     if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) return false;
     int stages = (int)((cap - off - red) / ((size_t)kWarpsPerCta * g.stage_bytes));
     g.stages = std::min(stages, kMaxStages);
@@ -292,7 +298,7 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     off += red;
     g.smem = off;
     const long iters = (long)n_problems * g.ips;
-    g.grid = (int)std::min<long>(iters, (long)kStreamCtasPerSm * num_sms());
+    g.grid = (int)std::min<long>(iters, (long)ctas_per_sm * num_sms());
     *out = g;
     return g.grid > 0;
 }

@@ -18,7 +18,8 @@ inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 // ---- workspace carve-up ---------------------------------------------------------------------------
 struct MoeLayout {
     size_t logits, sel, wts, active, n_active, slot_count, slot_offset, entry_row, entry_scale, tok_entries;
-    size_t a_gate, a_up, h, b, yd, a_sg, a_su, hs, bs, ysh, xr, hr, hsr, mm;
+    size_t active2, n_active2, slot_count2, slot_offset2;   // gate and up x.U as one launch: 2E slots
+    size_t a_gu, h, b, yd, a_sg, a_su, hs, bs, ysh, xr, hr, hsr, mm, mm2;
     size_t total, mm_bytes, mm_counters;
 };
 
@@ -44,18 +45,21 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
         off += up256(bytes);
         return o;
     };
-    L.logits = take((size_t)n * d->router_rows * 2);
+    L.logits = take((size_t)n * d->dense0_rows * 2);
     L.sel = take(nk * 4);
     L.wts = take(nk * 2);
     L.active = take((size_t)d->E * 4);
     L.n_active = take(4);
     L.slot_count = take((size_t)d->E * 4);
     L.slot_offset = take((size_t)d->E * 4);
-    L.entry_row = take(nk * 4);
+    L.entry_row = take(2 * nk * 4);   // second copy for the up half of the x.U launch
     L.entry_scale = take(nk * 2);
     L.tok_entries = take(nk * 4);
-    L.a_gate = take(nk * R * 2);
-    L.a_up = take(nk * R * 2);
+    L.active2 = take((size_t)2 * d->E * 4);
+    L.n_active2 = take(4);
+    L.slot_count2 = take((size_t)2 * d->E * 4);
+    L.slot_offset2 = take((size_t)2 * d->E * 4);
+    L.a_gu = take(2 * nk * R * 2);
     L.h = take(nk * d->I * 2);
     L.b = take(nk * R * 2);
     L.yd = take(nk * d->H * 2);
@@ -77,12 +81,12 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
         wb = std::max(wb, glq_mm_workspace_bytes(&m));
         wc = std::max(wc, glq_mm_counters(&m));
     };
-    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->router_rows, d->H, 0); acc();
+    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->dense0_rows, d->H, 0); acc();
     if (d->rot_in) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->H, d->H, 0); acc(); }
     if (d->rot_mid) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, (int)nk, d->I, d->I, 0); acc(); }
     if (d->sh_rot_mid && d->I_shared > 0) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->I_shared, d->I_shared, 0); acc(); }
     if (d->rank > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->H, 0); acc();
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, d->rank, d->H, 0); acc();
         set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->I, 0); acc();
     }
     set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, d->rank); acc();
@@ -98,6 +102,7 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
     L.mm_bytes = up256(wb);
     L.mm_counters = wc;
     L.mm = take(L.mm_bytes);
+    L.mm2 = take(L.mm_bytes);   // the shared expert's branch may run concurrently on a second stream
     L.total = off;
     return L;
 }
@@ -112,44 +117,72 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
                                                         int* __restrict__ slot_count, int* __restrict__ slot_offset,
                                                         int* __restrict__ entry_row, __half* __restrict__ entry_scale,
                                                         int* __restrict__ tok_entries, __half* __restrict__ logits_out,
-                                                        int* __restrict__ sel_out, __half* __restrict__ wts_out) {
+                                                        int* __restrict__ sel_out, __half* __restrict__ wts_out,
+                                                        int* __restrict__ active2, int* __restrict__ n_active2,
+                                                        int* __restrict__ slot_count2, int* __restrict__ slot_offset2) {
     extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
     int* sm_off = sm_cnt + E;
-    for (int t = threadIdx.x; t < n; t += blockDim.x) {
+    // Phase A: one warp per token, lanes over experts (E <= 256)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int t = warp; t < n; t += nwarps) {
         const __half* row = logits + (size_t)t * ldl;
+        float lv[8], pv[8];
         float mx = -INFINITY;
-        for (int e = 0; e < E; ++e) mx = fmaxf(mx, __half2float(row[e]));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            lv[i] = e < E ? __half2float(row[e]) : -INFINITY;
+            mx = fmaxf(mx, lv[i]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.f;
-        for (int e = 0; e < E; ++e) sum += expf(__half2float(row[e]) - mx);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            pv[i] = (lane + 32 * i) < E ? expf(lv[i] - mx) : 0.f;
+            sum += pv[i];
+        }
+        sum = warp_sum(sum);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pv[i] = (lane + 32 * i) < E ? pv[i] / sum : -1.f;
         float wk[16];
         int ek[16];
         float wsum = 0.f;
         for (int s = 0; s < k; ++s) {
             float best = -1.f;
-            int be = 0;
-            for (int e = 0; e < E; ++e) {
-                bool taken = false;
-                for (int s2 = 0; s2 < s; ++s2) taken |= (ek[s2] == e);
-                const float pe = expf(__half2float(row[e]) - mx) / sum;
-                if (!taken && pe > best) {
-                    best = pe;
-                    be = e;
+            int be = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (pv[i] > best) {   // increasing i = increasing expert index: first maximum wins
+                    best = pv[i];
+                    be = lane + 32 * i;
+                }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ob > best || (ob == best && oe < be)) {
+                    best = ob;
+                    be = oe;
                 }
             }
             wk[s] = best;
             ek[s] = be;
             wsum += best;
+            if ((be & 31) == lane) pv[be >> 5] = -1.f;   // taken
         }
-        for (int s = 0; s < k; ++s) {
-            const float wv = renorm ? wk[s] / wsum : wk[s];
-            const __half wh = __float2half_rn(wv);
-            sel[t * k + s] = ek[s];
-            wts[t * k + s] = wh;
-            if (sel_out) sel_out[t * k + s] = ek[s];
-            if (wts_out) wts_out[t * k + s] = wh;
+        if (lane == 0) {
+            for (int s = 0; s < k; ++s) {
+                const float wv = renorm ? wk[s] / wsum : wk[s];
+                const __half wh = __float2half_rn(wv);
+                sel[t * k + s] = ek[s];
+                wts[t * k + s] = wh;
+                if (sel_out) sel_out[t * k + s] = ek[s];
+                if (wts_out) wts_out[t * k + s] = wh;
+            }
         }
         if (logits_out)
-            for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = row[e];
+            for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = row[e];
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -171,6 +204,15 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
             off += sm_cnt[e];
         }
         *n_active = j;
+        // the same lists twice, for gate (table entry e, entries 0..nk) and up (entry E+e, entries nk..2nk)
+        for (int i = 0; i < j; ++i) {
+            active2[i] = active[i];
+            active2[j + i] = E + active[i];
+            slot_count2[i] = slot_count2[j + i] = slot_count[i];
+            slot_offset2[i] = slot_offset[i];
+            slot_offset2[j + i] = n * k + slot_offset[i];
+        }
+        *n_active2 = 2 * j;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -179,6 +221,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
         for (int i = 0; i < n * k; ++i)
             if (sel[i] == e) {
                 entry_row[pos] = i / k;
+                entry_row[n * k + pos] = i / k;
                 entry_scale[pos] = wts[i];
                 tok_entries[i] = pos;
                 ++pos;
@@ -241,20 +284,24 @@ extern "C" size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens)
 }
 extern "C" size_t glq_moe_counters(const glq_moe_desc_t* d, int n_tokens) {
     if (!d || n_tokens <= 0) return 0;
-    return moe_layout(d, n_tokens).mm_counters;
+    return 2 * moe_layout(d, n_tokens).mm_counters;
 }
 
 extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, void* out, void* router_logits,
                                int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes,
-                               int32_t* counters, size_t n_counters, void* stream) {
+                               int32_t* counters, size_t n_counters, void* stream, void* aux_stream, void* ev_fork,
+                               void* ev_join) {
     if (!d || !x || !out || n < 0) return GLQ_ERR_ARG;
     if (n == 0) return GLQ_OK;
-    if (d->top_k < 1 || d->top_k > 16 || d->E < d->top_k || d->H % 8 != 0 || d->I % 8 != 0) return GLQ_ERR_UNSUPPORTED;
+    if (d->top_k < 1 || d->top_k > 16 || d->E < d->top_k || d->E > 256 || d->H % 8 != 0 || d->I % 8 != 0)
+        return GLQ_ERR_UNSUPPORTED;
     if (!d->router_t || !d->gate_up || !d->down) return GLQ_ERR_ARG;
-    if (d->rank > 0 && (!d->ut_gate || !d->ut_up || !d->ut_down)) return GLQ_ERR_ARG;
+    if (d->rank > 0 && (!d->ut_gate_up || !d->ut_down)) return GLQ_ERR_ARG;
+    if (d->dense0_rows < d->router_rows || (d->sh_a_row > 0 && (d->sh_a_row % 16 != 0 || d->sh_a_row < d->router_rows)))
+        return GLQ_ERR_ARG;
     const MoeLayout L = moe_layout(d, n);
     if (!workspace || workspace_bytes < L.total) return GLQ_ERR_WORKSPACE;
-    if (L.mm_counters > 0 && (!counters || n_counters < L.mm_counters)) return GLQ_ERR_WORKSPACE;
+    if (L.mm_counters > 0 && (!counters || n_counters < 2 * L.mm_counters)) return GLQ_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return GLQ_ERR_ALIGN;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     char* ws = reinterpret_cast<char*>(workspace);
@@ -273,12 +320,16 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     auto p_tok = reinterpret_cast<int*>(ws + L.tok_entries);
 
     glq_mm_args_t m;
+    // the shared expert's chain runs on aux_stream (forked after the first dense product, joined before
+    // the combine) when the caller provides a stream and two events; it has its own scratch and counters
+    const bool forked = aux_stream != nullptr && ev_fork != nullptr && ev_join != nullptr;
+    bool on_aux = false;
     auto finish = [&](glq_mm_args_t& mm) {
-        mm.workspace = ws + L.mm;
+        mm.workspace = ws + (on_aux ? L.mm2 : L.mm);
         mm.workspace_bytes = L.mm_bytes;
-        mm.counters = counters;
-        mm.n_counters = n_counters;
-        return glq_grouped_matmul(&mm, stream);
+        mm.counters = counters ? counters + (on_aux ? L.mm_counters : 0) : nullptr;
+        mm.n_counters = L.mm_counters;
+        return glq_grouped_matmul(&mm, on_aux && forked ? aux_stream : stream);
     };
     int rc;
     // y = x . Pi^T for a tiled dense Pi (rows x dim -> rows x dim)
@@ -300,20 +351,28 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     }
 
     // 1. router logits (and the shared expert's gate logit): dense fp16 matmul
-    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->router_rows, d->H, 0);
+    //    when the shared expert's U_gate^T / U_up^T are appended to the router rows, the same product
+    //    also yields the shared expert's x.U (columns sh_a_row .. +2R of the output)
+    const int ldl = d->dense0_rows;
+    const bool sh_a_fused = d->sh_a_row > 0 && d->dense0_rows >= d->sh_a_row + 2 * R;
+    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, ldl, d->H, 0);
     m.w.codes = d->router_t;
-    m.w.N = d->router_rows;
+    m.w.N = ldl;
     m.w.K = d->H;
     m.x = x;
     m.ldx = d->H;
     m.y = p_logits;
-    m.ldy = d->router_rows;
+    m.ldy = ldl;
     if ((rc = finish(m)) != GLQ_OK) return rc;
+
+    if (forked && cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_fork), st) != cudaSuccess) return GLQ_ERR_CUDA;
 
     // 2. routing plan
     moe_plan_kernel<<<1, 1024, 2 * d->E * sizeof(int), st>>>(
-        p_logits, d->router_rows, n, d->E, k, d->norm_topk_prob, p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow,
-        p_escale, p_tok, reinterpret_cast<__half*>(router_logits), sel_out, reinterpret_cast<__half*>(weight_out));
+        p_logits, ldl, n, d->E, k, d->norm_topk_prob, p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow,
+        p_escale, p_tok, reinterpret_cast<__half*>(router_logits), sel_out, reinterpret_cast<__half*>(weight_out),
+        reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
+        reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2));
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
 
     auto routed = [&](glq_mm_args_t& mm) {
@@ -323,19 +382,23 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
         mm.slot_offset = p_off;
     };
 
-    // 3. x.U of the routed experts' gate and up clusters
+    // 3. x.U of the routed experts' gate and up clusters: one launch over 2 x (live experts) slots,
+    //    rows 0..nk of the output for gate, nk..2nk for up
+    char* a_gate = ws + L.a_gu;
+    char* a_up = a_gate + (size_t)nk * R * 2;
     if (R > 0) {
-        for (int which = 0; which < 2; ++which) {
-            set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, R, d->H, 0);
-            m.w_table = which == 0 ? d->ut_gate : d->ut_up;
-            routed(m);
-            m.entry_row = p_erow;
-            m.x = x;
-            m.ldx = d->H;
-            m.y = ws + (which == 0 ? L.a_gate : L.a_up);
-            m.ldy = R;
-            if ((rc = finish(m)) != GLQ_OK) return rc;
-        }
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, R, d->H, 0);
+        m.w_table = d->ut_gate_up;
+        m.slot_index = reinterpret_cast<int*>(ws + L.active2);
+        m.n_slots = reinterpret_cast<int*>(ws + L.n_active2);
+        m.slot_count = reinterpret_cast<int*>(ws + L.slot_count2);
+        m.slot_offset = reinterpret_cast<int*>(ws + L.slot_offset2);
+        m.entry_row = p_erow;
+        m.x = x;
+        m.ldx = d->H;
+        m.y = a_gate;
+        m.ldy = R;
+        if ((rc = finish(m)) != GLQ_OK) return rc;
     }
     // 4. h = silu(gate x) * (up x), one row per (token, expert) entry
     set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, R);
@@ -345,8 +408,8 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     m.x = xq;
     m.ldx = d->H;
     if (R > 0) {
-        m.a0 = ws + L.a_gate;
-        m.a1 = ws + L.a_up;
+        m.a0 = a_gate;
+        m.a1 = a_up;
         m.lda = R;
     }
     m.y = ws + L.h;
@@ -387,8 +450,22 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     // 7. shared expert
     const bool shared = d->I_shared > 0 && d->sh_gate_up.codes != nullptr;
     if (shared) {
-        const bool lr = R > 0 && d->sh_ut_gate && d->sh_ut_up && d->sh_ut_down;
-        if (lr) {
+        if (forked) {
+            if (cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(aux_stream), reinterpret_cast<cudaEvent_t>(ev_fork), 0) !=
+                cudaSuccess)
+                return GLQ_ERR_CUDA;
+            on_aux = true;
+        }
+        const bool lr = R > 0 && d->sh_ut_down && (sh_a_fused || (d->sh_ut_gate && d->sh_ut_up));
+        const void* a_sg = ws + L.a_sg;
+        const void* a_su = ws + L.a_su;
+        long long lda_s = R;
+        if (lr && sh_a_fused) {
+            a_sg = reinterpret_cast<const __half*>(p_logits) + d->sh_a_row;
+            a_su = reinterpret_cast<const __half*>(p_logits) + d->sh_a_row + R;
+            lda_s = ldl;
+        }
+        if (lr && !sh_a_fused) {
             for (int which = 0; which < 2; ++which) {
                 set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, R, d->H, 0);
                 m.w.codes = which == 0 ? d->sh_ut_gate : d->sh_ut_up;
@@ -407,9 +484,9 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
         m.x = xq;
         m.ldx = d->H;
         if (lr) {
-            m.a0 = ws + L.a_sg;
-            m.a1 = ws + L.a_su;
-            m.lda = R;
+            m.a0 = a_sg;
+            m.a1 = a_su;
+            m.lda = lda_s;
         }
         m.y = ws + L.hs;
         m.ldy = d->I_shared;
@@ -442,13 +519,20 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
         m.y = ws + L.ysh;
         m.ldy = d->H;
         if ((rc = finish(m)) != GLQ_OK) return rc;
+        if (forked) {
+            on_aux = false;
+            if (cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_join), reinterpret_cast<cudaStream_t>(aux_stream)) !=
+                    cudaSuccess ||
+                cudaStreamWaitEvent(st, reinterpret_cast<cudaEvent_t>(ev_join), 0) != cudaSuccess)
+                return GLQ_ERR_CUDA;
+        }
     }
 
     // 8. combine
     const dim3 grid((d->H / 8 + 255) / 256, n);
     moe_combine_kernel<<<grid, 256, 0, st>>>(
         reinterpret_cast<const __half*>(ws + L.yd), p_tok, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
-        shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, d->router_rows,
+        shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, ldl,
         d->router_rows > d->E ? d->E : -1, reinterpret_cast<__half*>(out));
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
     return GLQ_OK;

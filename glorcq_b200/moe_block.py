@@ -79,6 +79,8 @@ class GraphCompatibleMoeBlock(nn.Module):
         self._keep = []                  # tensors the descriptor tables point into
         self._desc: Optional[MoeDesc] = None
         self._ws = {}
+        self.parallel_shared_expert = True   # shared expert on a side stream, as the reference's side-stream LoRA
+        self._side = None
         self.last_selected_experts = None
         self.last_routing_weights = None
 
@@ -119,19 +121,33 @@ class GraphCompatibleMoeBlock(nn.Module):
         d.rank, d.fmt, d.group_size = rank, fmt, gs
         d.norm_topk_prob = int(bool(self.norm_topk_prob))
         d.slot_order_max_tokens = self._graph_threshold
-        # router (+ shared expert gate as one more row)
+        # router (+ shared expert gate as one more row) (+ the shared expert's U_gate^T, U_up^T, so that
+        # one dense product yields the logits and the shared expert's x.U)
         rows = [self.gate.weight.detach().to(device=device, dtype=torch.float16)]
         has_shared = self.shared_expert is not None
         if has_shared and self.shared_expert_gate is not None:
             rows.append(self.shared_expert_gate.weight.detach().to(device=device, dtype=torch.float16).reshape(1, H))
+        router_rows = sum(r.shape[0] for r in rows)
+        sh_rank = 0
+        if has_shared:
+            sg, su = self.shared_expert.gate_proj, self.shared_expert.up_proj
+            if sg.SV is not None and su.SV is not None and sg.U is not None and su.U is not None:
+                sh_rank = sg.U.shape[1]
+        d.router_rows, d.sh_a_row = router_rows, 0
+        if sh_rank > 0 and sh_rank == rank:
+            pad = (-router_rows) % 16
+            if pad:
+                rows.append(torch.zeros(pad, H, dtype=torch.float16, device=device))
+            d.sh_a_row = router_rows + pad
+            rows += [sg.U.t().to(torch.float16), su.U.t().to(torch.float16)]
         router = TiledWeight.from_dense(torch.cat(rows, 0).contiguous())
         self._keep.append(router)
-        d.router_t, d.router_rows = router.codes.data_ptr(), router.N
+        d.router_t, d.dense0_rows = router.codes.data_ptr(), router.N
         tabs = [_table(gate_up, device), _table(down, device)]
         d.gate_up, d.down = tabs[0].data_ptr(), tabs[1].data_ptr()
         if rank > 0:
-            tabs += [_table(utg, device), _table(utu, device), _table(utd, device)]
-            d.ut_gate, d.ut_up, d.ut_down = tabs[2].data_ptr(), tabs[3].data_ptr(), tabs[4].data_ptr()
+            tabs += [_table(utg + utu, device), _table(utd, device)]
+            d.ut_gate_up, d.ut_down = tabs[2].data_ptr(), tabs[3].data_ptr()
         self._keep += tabs
         # rotations of the codebook format
         if fmt == FMT_T2:
@@ -216,8 +232,20 @@ class GraphCompatibleMoeBlock(nn.Module):
                                      torch.zeros(max(nctr, 1), dtype=torch.int32, device=x.device))
                 ws, ctr = self._ws[key]
                 base = (ws.data_ptr() + 255) // 256 * 256
+                aux = fork = join = None
+                if self.parallel_shared_expert and d.I_shared > 0:
+                    if self._side is None:
+                        self._side = (torch.cuda.Stream(device=x.device), torch.cuda.Event(), torch.cuda.Event())
+                    aux, fork, join = self._side[0].cuda_stream, self._side[1], self._side[2]
+                    # torch creates events lazily: record once so that the handles exist
+                    if not getattr(self, "_events_ready", False):
+                        fork.record()
+                        join.record()
+                        self._events_ready = True
+                    fork, join = fork.cuda_event, join.cuda_event
                 _lib.check(L.glq_moe_forward(C.byref(d), x.data_ptr(), n, out.data_ptr(), logits.data_ptr(),
                                              sel.data_ptr(), wts.data_ptr(), base, ws.numel() - (base - ws.data_ptr()),
-                                             ctr.data_ptr(), ctr.numel(), tiled._stream_ptr(x.device)), "moe_forward")
+                                             ctr.data_ptr(), ctr.numel(), tiled._stream_ptr(x.device), aux, fork, join),
+                           "moe_forward")
         self.last_selected_experts, self.last_routing_weights = sel, wts
         return out.reshape(batch_size, sequence_length, hidden_dim), logits

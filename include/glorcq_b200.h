@@ -222,12 +222,15 @@ typedef struct glq_moe_desc {
     int32_t router_rows;     /* E, or E+1 when row E is the shared expert's gate */
     int32_t slot_order_max_tokens;
     int32_t reserved;
-    const void* router_t;          /* tiled F16 (router_rows x H) */
+    const void* router_t;          /* tiled F16 (dense0_rows x H): the router rows, optionally followed (from row
+                                      sh_a_row, a multiple of 16) by the shared expert's U_gate^T and U_up^T so
+                                      that one dense product yields logits, shared gate logit and both x.U */
     const glq_weight_t* gate_up;   /* device table [E]: fused gate|up, N = I */
     const glq_weight_t* down;      /* device table [E]: N = H, K = I */
-    const glq_weight_t* ut_gate;   /* device tables [E] of dense U^T (rank x H / rank x I), or NULL */
-    const glq_weight_t* ut_up;
-    const glq_weight_t* ut_down;
+    const glq_weight_t* ut_gate_up; /* device table [2E] of dense U^T (rank x H): gate of expert e at e, up at E+e */
+    const glq_weight_t* ut_down;    /* device table [E] of dense U^T (rank x I); both NULL when rank == 0 */
+    int32_t dense0_rows;            /* rows of router_t (== router_rows when nothing is appended) */
+    int32_t sh_a_row;               /* first appended row, 0 when nothing is appended */
     glq_weight_t sh_gate_up, sh_down;            /* shared expert (ignored when I_shared == 0) */
     const void* sh_ut_gate; const void* sh_ut_up; const void* sh_ut_down; /* tiled U^T or NULL */
     /* codebook format only: rotations applied to the input of the quantized product (the low-rank
@@ -240,9 +243,13 @@ size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens);
 size_t glq_moe_counters(const glq_moe_desc_t* d, int n_tokens);
 /* x (n_tokens, H) fp16 -> out (n_tokens, H) fp16; router_logits (n_tokens, E) fp16 may be NULL.
  * sel_out (n_tokens, top_k) int32 and weight_out (n_tokens, top_k) fp16 may be NULL. */
+/* aux_stream (cudaStream_t), ev_fork, ev_join (cudaEvent_t): when all three are given, the shared
+ * expert's launches go to aux_stream, forked from `stream` after the router product and joined before
+ * the combine, so that they overlap the routed experts (captured as a parallel branch of a graph);
+ * NULL runs everything on `stream`. */
 int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n_tokens, void* out, void* router_logits,
                     int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,
-                    size_t n_counters, void* stream);
+                    size_t n_counters, void* stream, void* aux_stream, void* ev_fork, void* ev_join);
 
 #ifdef __cplusplus
 }
