@@ -346,6 +346,7 @@ static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, i
     sp.n_problems = n_problems;
     sp.swiglu = g.swiglu;
     sp.sk = g.sk;
+    sp.sk_log2 = g.sk == 1 ? 0 : (g.sk == 2 ? 1 : (g.sk == 4 ? 2 : 3));
     sp.kb_per_split = g.kb_per_split;
     sp.npairs = g.npairs;
     sp.ips = g.ips;

@@ -44,6 +44,7 @@ struct StreamParams {
     int n_problems;
     int swiglu;        // 1: the weight is a fused gate|up matrix, the output is silu(gate) * up
     int sk;            // k splits (warps of one CTA): 1, 2, 4 or 8
+    int sk_log2;
     int kb_per_split;
     int npairs;        // tile pairs per problem
     int ips;           // iterations (8 warp items) per problem
@@ -141,7 +142,9 @@ __device__ __forceinline__ void stage_x_i8(const SkinnyParams& p, uint4* xs, flo
     using F = Fmt<FMT>;
     constexpr int P8 = F::UPK / 4;  // pieces per block: 2 (2-bit), 1 (4-bit)
     const int nrow = ncol >> 1;
-    const int total = nrow * nkb * F::UPK;
+    // only the live rows are staged; columns of absent rows keep stale (finite or not) data, and the
+    // outputs computed from them are never stored
+    const int total = min(nrow, cnt) * nkb * F::UPK;
     for (int base = 0; base < total; base += kThreads) {
         const int u = base + (int)threadIdx.x;
         const bool valid = u < total;
@@ -366,11 +369,11 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
         int slot, pair, s, kb_lo, kb_hi, ncode, nch;
         bool valid;
     };
-    auto make_item = [&](Item& im, const Slot& sc, int it) {
-        const int local = (it % sp.ips) * kWarpsPerCta + w;
-        im.slot = it / sp.ips;
-        im.pair = local / sk;
-        im.s = local % sk;
+    auto make_item = [&](Item& im, const Slot& sc, int slot, int rem) {   // iteration = slot * ips + rem
+        const int local = rem * kWarpsPerCta + w;
+        im.slot = slot;
+        im.pair = local >> sp.sk_log2;
+        im.s = local & (sk - 1);
         im.valid = im.pair < sp.npairs && sc.cnt > 0;
         im.kb_lo = im.s * sp.kb_per_split;
         im.kb_hi = min(nkb, im.kb_lo + sp.kb_per_split);
@@ -379,25 +382,31 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
     };
 
     // ---- fetch cursor: runs over the same (item, chunk) sequence as the compute loop, S stages ahead
+    bool dead = false;
     Slot fs, cs;
     Item fi;
-    int f_it = it_lo, f_c = 0, fseq = 0, cseq = 0;
+    // cursors keep (iteration, slot, iteration within the slot) and ring positions incrementally: no divisions
+    int f_it = it_lo, f_slot = it_lo / sp.ips, f_rem = it_lo % sp.ips, f_c = 0;
+    int f_stage = 0, f_inflight = 0;      // next stage to fill, chunks issued and not yet consumed
+    int c_stage = 0;                      // next stage to consume
+    uint32_t c_phase = 0;                 // its mbarrier phase parity
     bool f_live = false;
     auto fetch_seek = [&]() {
         f_live = false;
         while (f_it < it_hi) {
-            load_slot(fs, f_it / sp.ips);
-            make_item(fi, fs, f_it);
+            load_slot(fs, f_slot);
+            make_item(fi, fs, f_slot, f_rem);
             if (fi.valid && fi.nch > 0) {
                 f_live = true;
                 return;
             }
             ++f_it;
+            if (++f_rem == sp.ips) f_rem = 0, ++f_slot;
         }
     };
     auto fetch_one = [&]() {
         if (lane == 0) {
-            const int stage = fseq % S;
+            const int stage = f_stage;
             const uint32_t bar = bar_a + 8 * stage;
             const uint32_t dst = ring_a + (uint32_t)(stage * sp.stage_bytes);
             const void* src;
@@ -413,25 +422,38 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
             mbar_expect_tx(bar, bytes);
             bulk_g2s(dst, src, bytes, bar);
         }
-        ++fseq;
+        if (++f_stage == S) f_stage = 0;
+        ++f_inflight;
         if (++f_c >= fi.nch) {
             f_c = 0;
             ++f_it;
+            if (++f_rem == sp.ips) f_rem = 0, ++f_slot;
             fetch_seek();
         }
     };
+    // the consumer side of the ring: wait for the next stage / release it and refill
+    auto ring_wait = [&]() -> uint32_t {
+        mbar_wait(bar_a + 8 * c_stage, c_phase, dead);
+        return ring_a + (uint32_t)(c_stage * sp.stage_bytes);
+    };
+    auto ring_release = [&]() {
+        __syncwarp();
+        if (++c_stage == S) c_stage = 0, c_phase ^= 1u;
+        --f_inflight;
+        if (f_live) fetch_one();
+    };
     fetch_seek();
-    while (f_live && fseq < S) fetch_one();
+    while (f_live && f_inflight < S) fetch_one();
 
     uint32_t TL[2] = {0, 0}, TH[2] = {0, 0};  // codebook tables of the two tiles of a pair
     int staged_slot = -1, red_par = 0;
-    bool dead = false;
     constexpr int ncol_i8 = 2 * kRows;  // digit columns staged on the integer path
 
-    for (int it = it_lo; it < it_hi; ++it) {
-        load_slot(cs, it / sp.ips);
+    int c_slot = it_lo / sp.ips, c_rem = it_lo % sp.ips;
+    for (int it = it_lo; it < it_hi; ++it, c_rem = (c_rem + 1 == sp.ips ? 0 : c_rem + 1), c_slot += (c_rem == 0)) {
+        load_slot(cs, c_slot);
         Item im;
-        make_item(im, cs, it);
+        make_item(im, cs, c_slot, c_rem);
         const int cnt = cs.cnt, e0 = cs.e0;
 
         // ---- activations of a new problem: staged once per CTA ----
@@ -477,9 +499,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
 
         // ---- code chunks ----
         for (int c = 0; c < im.ncode; ++c) {
-            const int stage = cseq % S;
-            mbar_wait(bar_a + 8 * stage, (cseq / S) & 1, dead);
-            const uint32_t st = ring_a + (uint32_t)(stage * sp.stage_bytes);
+            const uint32_t st = ring_wait();
             const int kb0 = im.kb_lo + c * kStreamCB;
             const int nblk = min(kStreamCB, im.kb_hi - kb0);
 #pragma unroll
@@ -561,9 +581,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                     }
                 }
             }
-            __syncwarp();
-            ++cseq;
-            if (f_live) fetch_one();
+            ring_release();
         }
 
         // ---- k splits of this pair: fixed-order reduction through shared memory ----
@@ -607,9 +625,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                 for (int q = 0; q < 4; ++q) lo[j][m][q] = 0.f;
         const int nsv = im.nch - im.ncode;
         for (int c = 0; c < nsv; ++c) {
-            const int stage = cseq % S;
-            mbar_wait(bar_a + 8 * stage, (cseq / S) & 1, dead);
-            const uint32_t st = ring_a + (uint32_t)(stage * sp.stage_bytes);
+            const uint32_t st = ring_wait();
             // every lane runs the (warp-wide) op; lanes beyond the rank feed zeros
             const int cc0 = c * 64 + 16 * t;
             const bool in_rank = cc0 < rank;
@@ -632,9 +648,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                     mma16816(lo[j][m], sa1.z, sb1.z, sa1.w, sb1.w, av1.z, av1.w);
                 }
             }
-            __syncwarp();
-            ++cseq;
-            if (f_live) fetch_one();
+            ring_release();
         }
 
         // ---- epilogue: this lane's activation rows, weight rows g and g+8 of both tiles ----
