@@ -144,7 +144,7 @@ def run_reference(args, rank):
 
 
 def workload_config(layers):
-    return {"workload": f"Qwen1.5-MoE-A2.7B-shaped MoE decode, batch 1: {layers} MoE blocks (hidden 2048, 60 experts "
+    return {"workload": f"Qwen1.5-MoE-A2.7B-shaped MoE decode, one token stream per GPU: {layers} MoE blocks (hidden 2048, 60 experts "
                         "top-4 x 1408, shared expert 5632), 2-bit g128 + rank-64 shared-U correction; attention "
                         "and lm_head not included", "layers": layers, "batch": 1,
             "l2": "weights (240 MB per layer) far exceed L2; each token reads other experts' weights of 24 distinct layers"}
@@ -197,6 +197,11 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
             "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), 1 row each; {P * per / 1e6:.0f} MB > L2"}
 
 
+def _stage(rank, what):
+    if os.environ.get("GLQ_BENCH_VERBOSE"):
+        print(f"[bench rank {rank}] {what}", file=sys.stderr, flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from glorcq_b200 import _build, synthetic, tiled
@@ -207,10 +212,22 @@ def run_ours(args, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=dev)
     layers = args.layers
     pools = {}
-    blocks = [synthetic.make_moe_block(1000 + l, dev, pools=pools, **CFG) for l in range(layers)]
+    # N > 1: the experts of every block are sharded over the ranks (expert e on rank e % N); router and
+    # shared expert are replicated; one all-reduce of the per-entry outputs per block (--replicas: N
+    # independent copies of the whole model instead)
+    ep = world > 1 and not args.replicas
+    blocks = [synthetic.make_moe_block(1000 + l, dev, pools=pools, ep_rank=rank if ep else 0,
+                                       ep_world=world if ep else 1, **CFG) for l in range(layers)]
+    _stage(rank, "blocks built")
     H = CFG["H"]
-    static_x = torch.randn(1, 1, H, device=dev, dtype=torch.float16)
+    # weak scaling: one token stream per rank, so a step decodes `batch` = N tokens; every rank holds all
+    # N hidden states (the replicated router and shared expert see them all) and its share of the experts
+    batch = world if ep and not args.strong else 1
+    gx = torch.Generator(device=dev)
+    gx.manual_seed(4242)
+    static_x = torch.randn(1, batch, H, device=dev, dtype=torch.float16, generator=gx)
     x0 = static_x.clone()
+    mine = rank if batch > 1 else 0
 
     def token(x):
         for blk in blocks:
@@ -227,9 +244,20 @@ def run_ours(args, rank, world, local_rank):
             token(static_x)
     torch.cuda.current_stream().wait_stream(s)
     torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph), torch.no_grad():
-        static_y = token(static_x)
+    _stage(rank, "eager warm-up done")
+    if args.no_graph:
+        class _Eager:
+            def replay(self):
+                with torch.no_grad():
+                    static_y.copy_(token(static_x))
+        with torch.no_grad():
+            static_y = token(static_x).clone()
+        graph = _Eager()
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph), torch.no_grad():
+            static_y = token(static_x)
+    _stage(rank, "captured")
 
     def barrier():
         if world > 1:
@@ -252,23 +280,31 @@ def run_ours(args, rank, world, local_rank):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
+    _stage(rank, f"device timing done: {ms:.2f} ms")
     # ---- end to end: pinned host in, host out, every step ----
-    hx = torch.empty(1, 1, H, dtype=torch.float16).pin_memory()
-    hy = torch.empty(1, 1, H, dtype=torch.float16).pin_memory()
-    hx.copy_(x0.cpu())
-    for _ in range(3):
-        static_x.copy_(hx, non_blocking=True)
+    # every rank owns one token stream: its hidden state comes from its pinned host buffer, the ranks
+    # exchange the rows (all-gather, N > 1), the graph runs, the rank's own output row goes back
+    hx = torch.empty(1, H, dtype=torch.float16).pin_memory()
+    hy = torch.empty(1, H, dtype=torch.float16).pin_memory()
+    hx.copy_(x0[0, mine:mine + 1].cpu())
+    own = torch.empty(1, H, dtype=torch.float16, device=dev)
+
+    def e2e_step():
+        if batch > 1:
+            own.copy_(hx, non_blocking=True)
+            dist.all_gather_into_tensor(static_x.view(batch, H), own)
+        else:
+            static_x.view(1, H).copy_(hx, non_blocking=True)
         graph.replay()
-        hy.copy_(static_y, non_blocking=True)
+        hy.copy_(static_y.view(batch, H)[mine:mine + 1], non_blocking=True)
         torch.cuda.synchronize()
+        hx.copy_(hy)
+    for _ in range(3):
+        e2e_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        static_x.copy_(hx, non_blocking=True)
-        graph.replay()
-        hy.copy_(static_y, non_blocking=True)
-        torch.cuda.synchronize()
-        hx.copy_(hy)
+        e2e_step()
     barrier()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else None
@@ -281,25 +317,43 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         peak, kind = measured_peak_gbs()
         roof = gemv_roofline(dev, peak, kind)
-        sec_layer, threads, reps = cpu_layer_seconds()
+        cpu = None
+        if world == 1:      # the CPU leg is timed at N=1 only
+            sec_layer, threads, reps = cpu_layer_seconds()
+            cpu = {"value": 1.0 / (sec_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"1 of {layers} layers, 1 token, median of {reps} CPU forwards of the oracle"}
         bytes_tok = synthetic.block_bytes_per_token(**{k: CFG[k] for k in ("H", "I", "top_k", "I_shared", "rank", "E")}) * layers
-        value = world * args.steps / (ms * 1e-3)
+        streams = batch if ep else world      # token streams decoded at once
+        value = streams * args.steps / (ms * 1e-3)
         cfg = workload_config(layers)
-        cfg.update({"parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+        cfg.update({"parallelism": "single GPU" if world == 1 else
+                    (f"expert parallel ep{world}: expert e on rank e % {world}, router and shared expert replicated, "
+                     f"NCCL all-reduce of the per-entry outputs once per block; {batch} token stream(s) per step"
+                     if ep else f"replicas x{world}"),
+                    "batch": batch,
                     "algorithmic_bytes_per_token": bytes_tok,
                     "token_hbm_frac_of_peak": bytes_tok * args.steps / (ms * 1e-3) / 1e9 / peak})
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": cfg,
-                "e2e": {"value": world * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
+                "scaling": "strong" if ep and batch == 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": cfg,
+                "e2e": {"value": streams * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
                         "d2h_bytes_per_step": H * 2},
                 "gpu_launches": args.steps * layers * 10,
                 "roofline": roof,
-                "cpu_baseline": {"value": 1.0 / (sec_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
-                                 "sample": f"1 of {layers} layers, 1 token, median of {reps} CPU forwards of the oracle"},
+                "cpu_baseline": cpu,
                 "clocks": clocks, "kernel_self_check": err}
         print(json.dumps(line), flush=True)
     if world > 1:
+        # all ranks leave together (rank 0 was busy with the roofline and CPU legs); a teardown that does
+        # not return must not keep the launcher waiting
+        dist.barrier()
+        del graph
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        t = threading.Timer(20.0, os._exit, (0,))
+        t.daemon = True
+        t.start()
         dist.destroy_process_group()
 
 
@@ -313,6 +367,11 @@ def main():
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the grouped dequant-GEMV roofline case (small enough for an ncu capture)")
     ap.add_argument("--problems", type=int, default=240)
+    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--strong", action="store_true",
+                    help="with --gpus N > 1: one token stream for all ranks (strong scaling) instead of one per rank")
+    ap.add_argument("--replicas", action="store_true",
+                    help="with --gpus N > 1: N independent copies of the model instead of expert parallelism")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

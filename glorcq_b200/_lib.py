@@ -52,6 +52,14 @@ class MoeDesc(C.Structure):
                 ("rot_in", vp), ("rot_mid", vp), ("sh_rot_mid", vp)]
 
 
+class MoeEp(C.Structure):
+    """glq_moe_ep_t"""
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phase", C.c_int32), ("reserved", C.c_int32),
+                ("entry_out", vp)]
+
+
+MOE_PHASE_ALL, MOE_PHASE_EXPERTS, MOE_PHASE_COMBINE = 0, 1, 2
+
 _SIGS = {
     "glq_version": (C.c_int, []),
     "glq_status_string": (C.c_char_p, [C.c_int]),
@@ -84,6 +92,8 @@ _SIGS = {
     "glq_moe_counters": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
     "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, vp, vp, C.c_size_t, vp, C.c_size_t, vp,
                                   vp, vp, vp]),
+    "glq_moe_forward_ep": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, vp, vp, C.c_size_t, vp, C.c_size_t,
+                                     vp, vp, vp, vp, C.POINTER(MoeEp)]),
 }
 
 _lib = None

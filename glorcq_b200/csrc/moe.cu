@@ -119,7 +119,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
                                                         int* __restrict__ tok_entries, __half* __restrict__ logits_out,
                                                         int* __restrict__ sel_out, __half* __restrict__ wts_out,
                                                         int* __restrict__ active2, int* __restrict__ n_active2,
-                                                        int* __restrict__ slot_count2, int* __restrict__ slot_offset2) {
+                                                        int* __restrict__ slot_count2, int* __restrict__ slot_offset2,
+                                                        int ep_rank, int ep_world) {
     extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
     int* sm_off = sm_cnt + E;
     // Phase A: one warp per token, lanes over experts (E <= 256)
@@ -195,7 +196,9 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
         int off = 0, j = 0;
         for (int e = 0; e < E; ++e) {
             sm_off[e] = off;
-            if (sm_cnt[e] > 0) {
+            // entry offsets are global (every rank numbers the entries alike); only the experts this
+            // rank holds (e mod world == rank) become problems of its matmul launches
+            if (sm_cnt[e] > 0 && e % ep_world == ep_rank) {
                 active[j] = e;
                 slot_count[j] = sm_cnt[e];
                 slot_offset[j] = off;
@@ -291,7 +294,19 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
                                int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes,
                                int32_t* counters, size_t n_counters, void* stream, void* aux_stream, void* ev_fork,
                                void* ev_join) {
+    return glq_moe_forward_ep(d, x, n, out, router_logits, sel_out, weight_out, workspace, workspace_bytes, counters,
+                              n_counters, stream, aux_stream, ev_fork, ev_join, nullptr);
+}
+
+extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n, void* out, void* router_logits,
+                                  int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes,
+                                  int32_t* counters, size_t n_counters, void* stream, void* aux_stream, void* ev_fork,
+                                  void* ev_join, const glq_moe_ep_t* ep) {
     if (!d || !x || !out || n < 0) return GLQ_ERR_ARG;
+    const int ep_rank = ep ? ep->rank : 0, ep_world = ep ? ep->world : 1, phase = ep ? ep->phase : GLQ_MOE_PHASE_ALL;
+    if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world || phase < GLQ_MOE_PHASE_ALL || phase > GLQ_MOE_PHASE_COMBINE)
+        return GLQ_ERR_ARG;
+    if (ep_world > 1 && (phase == GLQ_MOE_PHASE_ALL || !ep->entry_out)) return GLQ_ERR_ARG;   // the exchange is the caller's
     if (n == 0) return GLQ_OK;
     if (d->top_k < 1 || d->top_k > 16 || d->E < d->top_k || d->E > 256 || d->H % 8 != 0 || d->I % 8 != 0)
         return GLQ_ERR_UNSUPPORTED;
@@ -307,6 +322,9 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     char* ws = reinterpret_cast<char*>(workspace);
     const int k = d->top_k, nk = n * k, R = d->rank;
     const int P = std::min(nk, d->E);
+    // per-entry down-projection outputs: in the workspace, or in the caller's exchange buffer
+    char* p_yd = ep && ep->entry_out ? reinterpret_cast<char*>(ep->entry_out) : ws + L.yd;
+    const bool shared = d->I_shared > 0 && d->sh_gate_up.codes != nullptr;
 
     auto p_logits = reinterpret_cast<__half*>(ws + L.logits);
     auto p_sel = reinterpret_cast<int*>(ws + L.sel);
@@ -318,7 +336,9 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     auto p_erow = reinterpret_cast<int*>(ws + L.entry_row);
     auto p_escale = reinterpret_cast<__half*>(ws + L.entry_scale);
     auto p_tok = reinterpret_cast<int*>(ws + L.tok_entries);
+    const int ldl = d->dense0_rows;
 
+    if (phase != GLQ_MOE_PHASE_COMBINE) {
     glq_mm_args_t m;
     // the shared expert's chain runs on aux_stream (forked after the first dense product, joined before
     // the combine) when the caller provides a stream and two events; it has its own scratch and counters
@@ -353,7 +373,6 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
     // 1. router logits (and the shared expert's gate logit): dense fp16 matmul
     //    when the shared expert's U_gate^T / U_up^T are appended to the router rows, the same product
     //    also yields the shared expert's x.U (columns sh_a_row .. +2R of the output)
-    const int ldl = d->dense0_rows;
     const bool sh_a_fused = d->sh_a_row > 0 && d->dense0_rows >= d->sh_a_row + 2 * R;
     set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, ldl, d->H, 0);
     m.w.codes = d->router_t;
@@ -372,8 +391,10 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
         p_logits, ldl, n, d->E, k, d->norm_topk_prob, p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow,
         p_escale, p_tok, reinterpret_cast<__half*>(router_logits), sel_out, reinterpret_cast<__half*>(weight_out),
         reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
-        reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2));
+        reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2), ep_rank, ep_world);
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
+    // rows of remote experts' entries stay zero, so that summing the ranks' buffers is exact
+    if (ep_world > 1 && cudaMemsetAsync(p_yd, 0, (size_t)nk * d->H * 2, st) != cudaSuccess) return GLQ_ERR_CUDA;
 
     auto routed = [&](glq_mm_args_t& mm) {
         mm.slot_index = p_active;
@@ -443,12 +464,11 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
         m.a0 = ws + L.b;
         m.lda = R;
     }
-    m.y = ws + L.yd;
+    m.y = p_yd;
     m.ldy = d->H;
     if ((rc = finish(m)) != GLQ_OK) return rc;
 
-    // 7. shared expert
-    const bool shared = d->I_shared > 0 && d->sh_gate_up.codes != nullptr;
+    // 7. shared expert (every rank computes it: no exchange)
     if (shared) {
         if (forked) {
             if (cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(aux_stream), reinterpret_cast<cudaEvent_t>(ev_fork), 0) !=
@@ -527,11 +547,13 @@ extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, vo
                 return GLQ_ERR_CUDA;
         }
     }
+    }   // phases before the combine
+    if (phase == GLQ_MOE_PHASE_EXPERTS) return GLQ_OK;
 
     // 8. combine
     const dim3 grid((d->H / 8 + 255) / 256, n);
     moe_combine_kernel<<<grid, 256, 0, st>>>(
-        reinterpret_cast<const __half*>(ws + L.yd), p_tok, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
+        reinterpret_cast<const __half*>(p_yd), p_tok, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
         shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, ldl,
         d->router_rows > d->E ? d->E : -1, reinterpret_cast<__half*>(out));
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;

@@ -21,8 +21,8 @@ from typing import List, Optional
 import torch
 import torch.nn as nn
 
-from . import _lib, tiled
-from ._lib import FMT_T2, MoeDesc, Weight
+from . import _lib, parallel, tiled
+from ._lib import FMT_T2, MoeDesc, MoeEp, Weight
 from .tiled import TiledWeight
 
 
@@ -83,6 +83,17 @@ class GraphCompatibleMoeBlock(nn.Module):
         self._side = None
         self.last_selected_experts = None
         self.last_routing_weights = None
+        self._ep = (0, 1, None)          # (rank, world, process group)
+        self._exchange = parallel.exchange_entries
+
+    def set_expert_parallel(self, rank: int, world: int, group=None):
+        """Shard the routed experts: this rank keeps experts e with e % world == rank (the other
+        entries of ``experts`` may be None or unloaded).  Call before the first forward."""
+        if self._built:
+            raise RuntimeError("set_expert_parallel must be called before the device tables are built")
+        parallel.local_experts(self.num_experts, rank, world)   # validates
+        self._ep = (int(rank), int(world), group)
+        return self
 
     # the reference hands every block the cross-layer U pool; here the pool is tiled.tiled_ut()
     def set_global_pool(self, pools, id_maps):
@@ -91,31 +102,34 @@ class GraphCompatibleMoeBlock(nn.Module):
     # ---- one-time device tables ---------------------------------------------------------------
     def _build(self, device):
         E = self.num_experts
-        ex0 = self.experts[0]
-        lins = [(e.gate_proj, e.up_proj, e.down_proj) for e in self.experts]
-        for g, u, dn in lins:
+        ep_rank, ep_world, _ = self._ep
+        mine = parallel.local_experts(E, ep_rank, ep_world)
+        if not mine:
+            raise RuntimeError("this rank holds no expert (more ranks than experts)")
+        lins = {e: (self.experts[e].gate_proj, self.experts[e].up_proj, self.experts[e].down_proj) for e in mine}
+        for g, u, dn in lins.values():
             for lin in (g, u, dn):
                 if getattr(lin, "_tiled", None) is None:
                     raise RuntimeError("every expert projection must be a GLoRCQLinear in the tiled layout "
                                        "(2/4-bit codes with group size 128/64 multiples, or 2-bit codebook)")
-        g0, _, d0 = lins[0]
+        g0, _, d0 = lins[mine[0]]
         H, I = g0.in_features, g0.out_features
         fmt, gs = g0._tiled.fmt, g0._tiled.group_size
         rank = g0._tiled.rank
-        gate_up, down, utg, utu, utd = [], [], [], [], []
-        for g, u, dn in lins:
+        gate_up, down, utg, utu, utd = ([Weight() for _ in range(E)] for _ in range(5))
+        for e, (g, u, dn) in lins.items():
             f = _fuse_tiles(g._tiled, u._tiled)
             if (f.fmt, f.group_size, f.rank, f.N, f.K) != (fmt, gs, rank, I, H) or \
                     (dn._tiled.fmt, dn._tiled.group_size, dn._tiled.rank, dn._tiled.N, dn._tiled.K) != (fmt, gs, rank, H, I):
                 raise RuntimeError("all experts of a block must share format, group size, rank and shapes")
             self._keep += [f, dn._tiled]
-            gate_up.append(f.desc)
-            down.append(dn._tiled.desc)
+            gate_up[e] = f.desc
+            down[e] = dn._tiled.desc
             if rank > 0:
                 for lin, lst in ((g, utg), (u, utu), (dn, utd)):
                     ut = tiled.tiled_ut(lin.U)
                     self._keep.append(ut)
-                    lst.append(Weight(ut.codes.data_ptr(), None, None, None, None, None, ut.N, ut.K, 0, 0))
+                    lst[e] = Weight(ut.codes.data_ptr(), None, None, None, None, None, ut.N, ut.K, 0, 0)
         d = MoeDesc()
         d.H, d.I, d.E, d.top_k = H, I, E, self.top_k
         d.rank, d.fmt, d.group_size = rank, fmt, gs
@@ -172,7 +186,6 @@ class GraphCompatibleMoeBlock(nn.Module):
                 d.sh_rot_mid = self._rotation(sd, device)
         self._desc = d
         self._built = True
-        _ = ex0
 
     def _rotation(self, lin, device):
         """Tiled rotation matrix of a codebook-format layer (None if it has no rotation cache)."""
@@ -198,7 +211,8 @@ class GraphCompatibleMoeBlock(nn.Module):
         if not self._built:
             self._build(torch.device(device))
         if release_linear_tiles:
-            for e in self.experts:
+            for i in parallel.local_experts(self.num_experts, self._ep[0], self._ep[1]):
+                e = self.experts[i]
                 e.gate_proj._tiled = e.up_proj._tiled = None
             if self.shared_expert is not None:
                 self.shared_expert.gate_proj._tiled = self.shared_expert.up_proj._tiled = None
@@ -243,9 +257,25 @@ class GraphCompatibleMoeBlock(nn.Module):
                         join.record()
                         self._events_ready = True
                     fork, join = fork.cuda_event, join.cuda_event
-                _lib.check(L.glq_moe_forward(C.byref(d), x.data_ptr(), n, out.data_ptr(), logits.data_ptr(),
-                                             sel.data_ptr(), wts.data_ptr(), base, ws.numel() - (base - ws.data_ptr()),
-                                             ctr.data_ptr(), ctr.numel(), tiled._stream_ptr(x.device), aux, fork, join),
-                           "moe_forward")
+                ep_rank, ep_world, group = self._ep
+
+                def call(ep):
+                    _lib.check(L.glq_moe_forward_ep(C.byref(d), x.data_ptr(), n, out.data_ptr(), logits.data_ptr(),
+                                                    sel.data_ptr(), wts.data_ptr(), base,
+                                                    ws.numel() - (base - ws.data_ptr()), ctr.data_ptr(), ctr.numel(),
+                                                    tiled._stream_ptr(x.device), aux, fork, join, ep),
+                               "moe_forward")
+                if ep_world == 1:
+                    call(None)
+                else:
+                    ekey = ("entries", n)
+                    if ekey not in self._ws:
+                        self._ws[ekey] = torch.empty(n * d.top_k, d.H, dtype=torch.float16, device=x.device)
+                    entries = self._ws[ekey]
+                    ep = MoeEp(ep_rank, ep_world, _lib.MOE_PHASE_EXPERTS, 0, entries.data_ptr())
+                    call(C.byref(ep))
+                    self._exchange(entries, group)
+                    ep.phase = _lib.MOE_PHASE_COMBINE
+                    call(C.byref(ep))
         self.last_selected_experts, self.last_routing_weights = sel, wts
         return out.reshape(batch_size, sequence_length, hidden_dim), logits

@@ -41,17 +41,26 @@ class _SparseBlock:
 
 
 def make_moe_block(seed, device, H=2048, I=1408, E=60, top_k=4, I_shared=5632, rank=64, experts_per_cluster=4,
-                   norm_topk_prob=False, release_linear_tiles=True, pools=None, n_clusters=None):
+                   norm_topk_prob=False, release_linear_tiles=True, pools=None, n_clusters=None,
+                   ep_rank=0, ep_world=1, ep_group=None):
     """One MoE block of the Qwen1.5-MoE shape.  `pools` (dict) lets several blocks share the cluster U
-    factors across layers, as the cross-layer clustering of the reference does."""
-    gen = torch.Generator(device=device)
-    gen.manual_seed(seed)
+    factors across layers, as the cross-layer clustering of the reference does.  With ep_world > 1
+    only the experts of rank ep_rank are materialised; every tensor is drawn from its own seeded
+    generator, so all ranks see the same router, shared expert and (for the experts they hold) weights."""
+    def generator(index):
+        g = torch.Generator(device=device)
+        g.manual_seed(seed * 100003 + index)
+        return g
+    gen = generator(0)
     pools = {} if pools is None else pools
+    kinds = {"gate": 1, "up": 2, "down": 3, "sgate": 4, "sup": 5, "sdown": 6}
 
     def U(kind, c, K):
         key = (kind, c)
         if key not in pools:
-            pools[key] = (torch.randn(K, rank, generator=gen, device=device) * 0.01).half()
+            g = torch.Generator(device=device)
+            g.manual_seed(7919 * kinds[kind] + int(c))        # the pool is shared by blocks: not seeded per block
+            pools[key] = (torch.randn(K, rank, generator=g, device=device) * 0.01).half()
         return pools[key]
 
     if n_clusters:   # cross-layer clusters assigned at random per (expert, projection)
@@ -63,17 +72,19 @@ def make_moe_block(seed, device, H=2048, I=1408, E=60, top_k=4, I_shared=5632, r
     hf.num_experts, hf.top_k, hf.norm_topk_prob = E, top_k, norm_topk_prob
     hf.gate = nn.Linear(H, E, bias=False).half().to(device)
     hf.gate.weight.data.copy_((torch.randn(E, H, generator=gen, device=device) * 0.02).half())
-    hf.experts = nn.ModuleList([
-        _Expert(gen, H, I, rank, U("gate", assign[0][e], H), U("up", assign[1][e], H),
-                U("down", assign[2][e], I), device) for e in range(E)])
+    hf.experts = [
+        _Expert(generator(1 + e), H, I, rank, U("gate", assign[0][e], H), U("up", assign[1][e], H),
+                U("down", assign[2][e], I), device) if e % ep_world == ep_rank else None for e in range(E)]
     if I_shared:
-        hf.shared_expert = _Expert(gen, H, I_shared, rank, U("sgate", seed, H), U("sup", seed, H),
+        hf.shared_expert = _Expert(generator(100001), H, I_shared, rank, U("sgate", seed, H), U("sup", seed, H),
                                    U("sdown", seed, I_shared), device)
         hf.shared_expert_gate = nn.Linear(H, 1, bias=False).half().to(device)
         hf.shared_expert_gate.weight.data.copy_((torch.randn(1, H, generator=gen, device=device) * 0.02).half())
     else:
         hf.shared_expert, hf.shared_expert_gate = None, None
     blk = GraphCompatibleMoeBlock(hf)
+    if ep_world > 1:
+        blk.set_expert_parallel(ep_rank, ep_world, ep_group)
     blk.prepare(device, release_linear_tiles=release_linear_tiles)
     return blk
 

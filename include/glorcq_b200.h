@@ -251,6 +251,26 @@ int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n_tokens, void* 
                     int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,
                     size_t n_counters, void* stream, void* aux_stream, void* ev_fork, void* ev_join);
 
+/* Expert-parallel form of the same block.  The reference runs every expert on one device; its call
+ * site is still GraphCompatibleMoeBlock.forward (inference/moe_block.py:381-436).  Rank r of `world`
+ * holds the experts e with e mod world == r (the other entries of the gate_up / down / ut tables are
+ * never read); router and shared expert are replicated.  Every rank numbers the (token, expert)
+ * entries alike, writes the weighted down-projection rows of its own experts into `entry_out`
+ * ((n_tokens*top_k, H) fp16, caller-owned) and leaves the others zero, so that a sum all-reduce of
+ * the ranks' buffers is exact (one non-zero term per row) and the combine that follows gives
+ * bit-identical results for every world size.  The exchange itself is the caller's:
+ *   phase EXPERTS  -> all-reduce(entry_out) on `stream` -> phase COMBINE.
+ * ep == NULL, or world == 1 with phase ALL, is glq_moe_forward. */
+enum { GLQ_MOE_PHASE_ALL = 0, GLQ_MOE_PHASE_EXPERTS = 1, GLQ_MOE_PHASE_COMBINE = 2 };
+typedef struct glq_moe_ep {
+    int32_t rank, world, phase, reserved;
+    void* entry_out; /* NULL: use the workspace (world == 1 only) */
+} glq_moe_ep_t;
+int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n_tokens, void* out, void* router_logits,
+                       int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,
+                       size_t n_counters, void* stream, void* aux_stream, void* ev_fork, void* ev_join,
+                       const glq_moe_ep_t* ep);
+
 #ifdef __cplusplus
 }
 #endif

@@ -109,3 +109,79 @@ def test_graph_capture_replay(dev):
         graph.replay()
         ref, _ = O.moe_forward(cases.to_oracle_moe(blk), x)
         assert cases.rel_l2(static_y.cpu(), ref) <= REL_BLOCK
+
+
+# ---- expert parallelism ---------------------------------------------------------------------------
+@pytest.mark.parametrize("N,world", [(1, 2), (3, 2), (9, 2), (9, 4), (33, 3)])
+def test_expert_parallel_emulated_on_one_gpu(dev, N, world):
+    """Every rank's block (its own experts only) run in turn on one device; the exchange is emulated by
+    summing the ranks' entry buffers.  The result must equal the single-device block bit for bit."""
+    blk = cases.make_moe(900 + N, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    x = cases.make_x(1900 + N, N, 256).reshape(1, N, 256).to(dev)
+    single, logits1 = cases.to_b200_moe(blk, dev)(x)
+    bufs = {}
+    outs = []
+    for rank in list(range(world)) + [0]:        # second pass of rank 0 sees every other rank's rows
+        mb = cases.to_b200_moe(blk, dev).set_expert_parallel(rank, world)
+        second = rank == 0 and 0 in bufs
+
+        def hook(entries, group, rank=rank, second=second):
+            if second:
+                for r, b in bufs.items():
+                    if r != 0:
+                        entries += b
+            else:
+                bufs[rank] = entries.clone()
+            return entries
+        mb._exchange = hook
+        y, logits = mb(x)
+        outs.append(y)
+        assert torch.equal(logits, logits1)
+    # each entry row is non-zero on exactly one rank
+    nz = torch.stack([(b != 0).any(1) for b in bufs.values()]).sum(0)
+    assert int(nz.max()) <= 1
+    assert torch.equal(outs[-1], single)
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
+def _nccl_worker(rank, world, port, q):
+    import os
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        d = torch.device("cuda", rank)
+        blk = cases.make_moe(950, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+        res = []
+        for N in (1, 9):
+            x = cases.make_x(1950 + N, N, 256).reshape(1, N, 256).to(d)
+            single, _ = cases.to_b200_moe(blk, d)(x)
+            y, _ = cases.to_b200_moe(blk, d).set_expert_parallel(rank, world)(x)
+            torch.cuda.synchronize()
+            res.append(bool(torch.equal(y, single)))
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_two_gpus_nccl(dev):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=170) for _ in procs]
+    for p in procs:
+        p.join(30)
+    for rank, oks in res:
+        assert all(oks), f"rank {rank}: expert-parallel output differs from the single-device block"
