@@ -30,7 +30,7 @@ class MMArgs(C.Structure):
     """glq_mm_args_t"""
     _fields_ = [("fmt", C.c_int32), ("group_size", C.c_int32), ("epilogue", C.c_int32), ("n_problems", C.c_int32),
                 ("max_rows", C.c_int32), ("rows_stride", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
-                ("rank", C.c_int32), ("reserved", C.c_int32),
+                ("rank", C.c_int32), ("total_rows", C.c_int32),
                 ("w", Weight), ("w_table", vp),
                 ("slot_index", vp), ("n_slots", vp), ("slot_count", vp), ("slot_offset", vp), ("entry_row", vp),
                 ("entry_scale", vp),

@@ -10,6 +10,7 @@
 #include "aux_kernels.cuh"
 #include "skinny_mm.cuh"
 #include "stream_mm.cuh"
+#include "tc_mm.cuh"
 
 using namespace glq;
 
@@ -368,8 +369,97 @@ static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, i
 // ---------------------------------------------------------------------------------------------
 // glq_grouped_matmul
 // ---------------------------------------------------------------------------------------------
+// ---------------------------------------------------------------------------------------------
+// tensor-core path (tc_mm.cuh): many rows per problem
+// ---------------------------------------------------------------------------------------------
+struct TcGeom {
+    int tn, nkb, ns, na, tiles_max;
+    long long tile_bytes;
+    size_t xp_bytes;
+};
+static bool tc_disabled() {
+    static const bool v = std::getenv("GLQ_NO_TC") != nullptr;
+    return v;
+}
+// true when the tcgen05 kernel takes the call: 2-bit affine codes, more rows than the streaming kernel stages
+static bool plan_tc(const glq_mm_args_t* a, TcGeom* out) {
+    if (tc_disabled() || a->fmt != GLQ_FMT_Q2 || a->max_rows <= 32) return false;
+    if (a->N <= 0 || a->K <= 0 || a->n_problems <= 0 || a->rank < 0 || a->rank % 16 != 0) return false;
+    if (a->group_size <= 0 || a->group_size % 128 != 0) return false;
+    TcGeom g{};
+    const long long stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
+    long long total = a->total_rows > 0 ? a->total_rows : (long long)a->n_problems * (a->slot_offset ? a->max_rows : stride);
+    if (!a->slot_offset) total = std::max(total, (long long)(a->n_problems - 1) * stride + a->max_rows);
+    g.tn = (total / a->n_problems > 64) ? 128 : 64;
+    g.nkb = cdiv(a->K, 128);
+    g.ns = a->rank > 0 ? cdiv(a->rank, 64) : 0;
+    g.na = a->epilogue == GLQ_EPI_SWIGLU ? 2 : 1;
+    const long long tiles = total / g.tn + a->n_problems + 1;
+    if (tiles > 65535) return false;
+    g.tiles_max = (int)tiles;
+    g.tile_bytes = (long long)g.nkb * g.tn * 256 + (long long)g.ns * g.na * g.tn * 128;
+    g.xp_bytes = (size_t)g.tiles_max * (size_t)g.tile_bytes;
+    *out = g;
+    return true;
+}
+
+template <int TN, bool SW>
+static int launch_tc_t(const TcParams& p, int N, cudaStream_t st) {
+    using C = TcCfg<TN, SW>;
+    static bool configured[64] = {};
+    int dev = 0;
+    GLQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        GLQ_CUDA(cudaFuncSetAttribute(tc_kernel<TN, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    tc_pack_b_kernel<TN><<<dim3(p.tiles_max, p.nkb + p.ns), 256, 0, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    tc_kernel<TN, SW><<<dim3(cdiv(N, kTcFeat), p.tiles_max), kTcThreads, C::SMEM, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st) {
+    if (!a->workspace || a->workspace_bytes < g.xp_bytes) return GLQ_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(a->workspace) & 127u) != 0) return GLQ_ERR_ALIGN;
+    TcParams p{};
+    p.w = a->w;
+    p.table = a->w_table;
+    p.slot_index = a->slot_index;
+    p.n_slots = a->n_slots;
+    p.slot_count = a->slot_count;
+    p.slot_offset = a->slot_offset;
+    p.entry_row = a->entry_row;
+    p.entry_scale = reinterpret_cast<const __half*>(a->entry_scale);
+    p.x = reinterpret_cast<const __half*>(a->x);
+    p.ldx = a->ldx;
+    p.a[0] = reinterpret_cast<const __half*>(a->a0);
+    p.a[1] = reinterpret_cast<const __half*>(a->a1);
+    p.lda = a->lda;
+    p.y = reinterpret_cast<__half*>(a->y);
+    p.ldy = a->ldy;
+    p.xp = reinterpret_cast<unsigned char*>(a->workspace);
+    p.tile_bytes = g.tile_bytes;
+    p.n_problems = a->n_problems;
+    p.max_rows = a->max_rows;
+    p.rows_stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
+    p.K = a->K;
+    p.rank = (a->a0 != nullptr) ? a->rank : 0;
+    p.nkb = g.nkb;
+    p.ns = p.rank > 0 ? g.ns : 0;
+    p.na = g.na;
+    p.tiles_max = g.tiles_max;
+    p.x_vec = ((reinterpret_cast<uintptr_t>(a->x) & 7u) == 0 && a->ldx % 4 == 0) ? 1 : 0;
+    const bool sw = a->epilogue == GLQ_EPI_SWIGLU;
+    if (g.tn == 128) return sw ? launch_tc_t<128, true>(p, a->N, st) : launch_tc_t<128, false>(p, a->N, st);
+    return sw ? launch_tc_t<64, true>(p, a->N, st) : launch_tc_t<64, false>(p, a->N, st);
+}
+
 extern "C" size_t glq_mm_workspace_bytes(const glq_mm_args_t* a) {
     if (!a) return 0;
+    TcGeom tg;
+    if (plan_tc(a, &tg)) return tg.xp_bytes;
     StreamGeom sg;
     if (plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg)) return 0;
     Geometry g;
@@ -380,6 +470,8 @@ extern "C" size_t glq_mm_workspace_bytes(const glq_mm_args_t* a) {
 
 extern "C" size_t glq_mm_counters(const glq_mm_args_t* a) {
     if (!a) return 0;
+    TcGeom tg;
+    if (plan_tc(a, &tg)) return 0;
     StreamGeom sg;
     if (plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg)) return 0;
     Geometry g;
@@ -395,6 +487,11 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     if (a->rank < 0 || a->rank % 16 != 0) return GLQ_ERR_UNSUPPORTED;
     if (a->rank > 0 && (a->a0 || a->a1) && (a->lda % 8 != 0 || !aligned16(a->a0) || !aligned16(a->a1)))
         return GLQ_ERR_ALIGN;
+    TcGeom tg;
+    if (plan_tc(a, &tg)) {
+        if (!a->w_table && !a->w.codes) return GLQ_ERR_ARG;
+        return launch_tc(a, tg, reinterpret_cast<cudaStream_t>(stream));
+    }
     StreamGeom sg;
     const bool use_stream =
         plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg);

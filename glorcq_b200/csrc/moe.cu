@@ -23,7 +23,8 @@ struct MoeLayout {
     size_t total, mm_bytes, mm_counters;
 };
 
-void set_mm(glq_mm_args_t* m, int fmt, int group_size, int epi, int P, int rows, int N, int K, int rank) {
+void set_mm(glq_mm_args_t* m, int fmt, int group_size, int epi, int P, int rows, int N, int K, int rank,
+            int total_rows = 0) {
     std::memset(m, 0, sizeof(*m));
     m->fmt = fmt;
     m->group_size = group_size;
@@ -34,6 +35,7 @@ void set_mm(glq_mm_args_t* m, int fmt, int group_size, int epi, int P, int rows,
     m->N = N;
     m->K = K;
     m->rank = rank;
+    m->total_rows = total_rows;   // entries of all problems together (0: P * rows)
 }
 
 MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
@@ -89,8 +91,8 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
         set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, d->rank, d->H, 0); acc();
         set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->I, 0); acc();
     }
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, d->rank); acc();
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, d->rank); acc();
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, d->rank, (int)nk); acc();
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, d->rank, (int)nk); acc();
     if (d->I_shared > 0) {
         if (d->rank > 0) {
             set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->rank, d->H, 0); acc();
@@ -422,7 +424,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         if ((rc = finish(m)) != GLQ_OK) return rc;
     }
     // 4. h = silu(gate x) * (up x), one row per (token, expert) entry
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, R);
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, R, nk);
     m.w_table = d->gate_up;
     routed(m);
     m.entry_row = p_erow;
@@ -454,7 +456,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         if ((rc = rotate(d->rot_mid, ws + L.h, nk, d->I, ws + L.hr)) != GLQ_OK) return rc;
         hq = ws + L.hr;
     }
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, R);
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, R, nk);
     m.w_table = d->down;
     routed(m);
     m.entry_scale = p_escale;

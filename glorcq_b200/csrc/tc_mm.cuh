@@ -1,0 +1,512 @@
+// Grouped dequant-GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for
+// problems with many activation rows (prefill, large decode batches).
+//
+//   D[feature, token] = sum_k W[feature, k] * X[token, k]   (+ sum_r SV[feature, r] * a[token, r])
+//
+// The weights are the M operand ("swap AB"): a CTA owns 128 output features of one problem and TN
+// tokens; producer warps unpack the 2-bit codes of the pair-interleaved tiled layout to the exact
+// fp16 values fp16((q - z) * s) and store them as a K-major, 128-byte-swizzled UMMA operand in shared
+// memory; the token operand arrives ready-made: a pre-pass (tc_pack_b_kernel) gathers the problem's
+// activation rows, orders k like the unpack does and writes swizzled tiles, so the main kernel fetches
+// each k stage of it with one bulk copy.  One thread issues the MMAs; the low-rank term is folded in
+// as extra k steps (A = SV rows, B = the entries' x.U rows), so the epilogue only rounds, applies
+// SwiGLU / routing weight / bias and stores.
+//
+// k order inside every group of 16 input channels: position 2j holds channel j, position 2j+1 holds
+// channel j+8 (the order in which one shift-and-mask yields two codes); both operands use it, so the
+// dot products are unchanged.
+//
+// Every mbarrier wait is bounded (about 2 ms); a wait that runs out records error 100/101, marks the
+// CTA dead, and all roles fall through to the common exit, which frees the tensor memory.
+#pragma once
+
+#include "stream_mm.cuh"
+
+namespace glq {
+
+constexpr int kTcFeat = 128;          // output features per CTA (UMMA M)
+constexpr int kTcProducers = 8;       // producer (and epilogue) warps
+constexpr int kTcThreads = (kTcProducers + 2) * 32;
+
+struct TcParams {
+    glq_weight_t w;
+    const glq_weight_t* table;
+    const int* slot_index;
+    const int* n_slots;
+    const int* slot_count;
+    const int* slot_offset;
+    const int* entry_row;
+    const __half* entry_scale;
+    const __half* x;
+    long long ldx;
+    const __half* a[2];
+    long long lda;
+    __half* y;
+    long long ldy;
+    unsigned char* xp;        // packed token operand: [token tile][k stages | low-rank stages]
+    long long tile_bytes;     // bytes of one token tile in xp
+    int n_problems, max_rows, rows_stride;
+    int K, rank, nkb, ns, na; // ns: 64-wide low-rank slices, na: x.U operands per entry (1, or 2 for gate|up)
+    int tiles_max;
+    int x_vec;                // x rows allow 8-byte loads
+};
+
+// ---- token tile -> (problem slot, local tile) -----------------------------------------------------
+// Problem p (slot position) with entries [off_p, off_p + cnt_p) owns the global token tiles
+// [off_p / TN + p, off_p / TN + p + ceil(cnt_p / TN)): disjoint for consecutive problems, and at most
+// total / TN + P + 1 tiles in all.  Warp-uniform result; every warp scans the (few) slots itself.
+template <int TN>
+__device__ __forceinline__ bool tc_find_tile(const TcParams& p, int gt, int& slot, int& lt, int& cnt, int& e0) {
+    const int lane = threadIdx.x & 31;
+    int P = p.n_problems;
+    if (p.n_slots) P = min(P, __ldg(p.n_slots));
+    for (int base = 0; base < P; base += 32) {
+        const int pp = base + lane;
+        int off = 0, c = 0;
+        if (pp < P) {
+            c = p.slot_count ? __ldg(p.slot_count + pp) : p.max_rows;
+            off = p.slot_offset ? __ldg(p.slot_offset + pp) : pp * p.rows_stride;
+        }
+        const int start = off / TN + pp;
+        const bool hit = pp < P && c > 0 && gt >= start && gt < start + (c + TN - 1) / TN;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (m) {
+            const int src = __ffs(m) - 1;
+            slot = base + src;
+            lt = gt - __shfl_sync(0xffffffffu, start, src);
+            cnt = __shfl_sync(0xffffffffu, c, src);
+            e0 = __shfl_sync(0xffffffffu, off, src);
+            return true;
+        }
+    }
+    return false;
+}
+
+// ---- pre-pass: token operand in UMMA layout ---------------------------------------------------------
+// Tile layout in xp (TN rows): per k stage (128 input channels) two atoms [TN][128 B], then per
+// low-rank slice `na` atoms [TN][128 B].  Inside an atom row r keeps its 16-byte chunk c at chunk
+// position c ^ (r & 7) (the 128-byte swizzle).  grid = (tiles_max, nkb + ns), 256 threads.
+template <int TN>
+__global__ void __launch_bounds__(256) tc_pack_b_kernel(const TcParams p) {
+    int slot, lt, cnt, e0;
+    if (!tc_find_tile<TN>(p, blockIdx.x, slot, lt, cnt, e0)) return;
+    unsigned char* tile = p.xp + (size_t)blockIdx.x * p.tile_bytes;
+    const int st = blockIdx.y;
+    if (st < p.nkb) {
+        uint4* dst = reinterpret_cast<uint4*>(tile + (size_t)st * TN * 256);
+        for (int ci = threadIdx.x; ci < TN * 16; ci += 256) {
+            const int atom = ci / (TN * 8), r = (ci >> 3) % TN, cpos = ci & 7;
+            const int c = cpos ^ (r & 7);
+            const int k0 = st * 128 + atom * 64 + (c >> 1) * 16, h = c & 1;
+            const int rr = lt * TN + r;
+            __align__(16) __half v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __float2half(0.f);
+            if (rr < cnt) {
+                const long long row = p.entry_row ? __ldg(p.entry_row + e0 + rr) : (long long)(e0 + rr);
+                const __half* src = p.x + row * p.ldx;
+                const int ka = k0 + 4 * h, kb = k0 + 8 + 4 * h;     // channels j and j+8, j = 4h..4h+3
+                if (p.x_vec && kb + 4 <= p.K) {
+                    __align__(8) __half lo[4], hi[4];
+                    *reinterpret_cast<uint2*>(lo) = __ldg(reinterpret_cast<const uint2*>(src + ka));
+                    *reinterpret_cast<uint2*>(hi) = __ldg(reinterpret_cast<const uint2*>(src + kb));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        v[2 * i] = lo[i];
+                        v[2 * i + 1] = hi[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (ka + i < p.K) v[2 * i] = __ldg(src + ka + i);
+                        if (kb + i < p.K) v[2 * i + 1] = __ldg(src + kb + i);
+                    }
+                }
+            }
+            dst[ci] = *reinterpret_cast<const uint4*>(v);
+        }
+    } else {
+        const int sl = st - p.nkb;
+        uint4* dst = reinterpret_cast<uint4*>(tile + (size_t)p.nkb * TN * 256 + (size_t)sl * p.na * TN * 128);
+        for (int ci = threadIdx.x; ci < p.na * TN * 8; ci += 256) {
+            const int ai = ci / (TN * 8), r = (ci >> 3) % TN, cpos = ci & 7;
+            const int c = cpos ^ (r & 7);
+            const int col = sl * 64 + c * 8;
+            const int rr = lt * TN + r;
+            __align__(16) __half v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __float2half(0.f);
+            const __half* a = p.a[ai];
+            if (rr < cnt && a != nullptr) {
+                const __half* src = a + (long long)(e0 + rr) * p.lda + col;
+                if (col + 8 <= p.rank) {
+                    *reinterpret_cast<uint4*>(v) = __ldg(reinterpret_cast<const uint4*>(src));   // lda % 8 == 0, a 16-byte aligned
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (col + i < p.rank) v[i] = __ldg(src + i);
+                }
+            }
+            dst[ci] = *reinterpret_cast<const uint4*>(v);
+        }
+    }
+}
+
+// ---- tcgen05 primitives -----------------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns: thread i of the warp gets lane (base lane + i)
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+// K-major operand, 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart, version 1
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// kind::f16: D fp32, A and B fp16, both K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t tc_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcFeat >> 4) << 24);
+}
+
+// bounded wait shared by all roles; `dead` lives in shared memory so that every role sees it
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* dead, int code) {
+    if (*dead) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    while (!mbar_test_wait(bar, parity)) {
+        if (*dead) return false;
+        if (global_ns() - t0 > 2000000ull) {
+            glq_ok(false, code, bar, parity);
+            *dead = 1;
+            return false;
+        }
+        __nanosleep(32);
+    }
+    return true;
+}
+
+template <int TN, bool SW> struct TcCfg {
+    static constexpr int A_BYTES = (SW ? 2 : 1) * kTcFeat * 256;   // 128 rows x 128 channels fp16 (x2: gate, up)
+    static constexpr int B_BYTES = TN * 256;
+    static constexpr int STAGE = A_BYTES + B_BYTES;
+    static constexpr int S = (200 * 1024) / STAGE >= 4 ? 4 : (200 * 1024) / STAGE;
+    static constexpr int COLS = SW ? 2 * TN : TN;                 // fp32 accumulator columns in TMEM
+    static constexpr size_t SMEM = (size_t)S * STAGE + 1024;
+};
+
+// 2-bit codes of one row and 32 channels (two words of 16) -> 4 chunks of 8 fp16 in k-pair order
+__device__ __forceinline__ void tc_unpack_row_q2(uint32_t w0, uint32_t w1, uint32_t sz, uint32_t (&out)[16]) {
+    const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xffffu)));
+    const __half zh = __ushort_as_half((unsigned short)(sz >> 16));
+    const float zf = __half2float(zh);
+    const __half2 k1024 = __float2half2_rn(1024.f);
+    // the exponent trick yields 1024 + code.  Integer zero points (what the quantizer writes) fold into
+    // one exact subtraction of 1024 + z; any other zero point takes (1024 + code - 1024) - z, which is
+    // the fp16 rounding of fp16(code) - z.  Either way the value is fp16(fp16(q - z) * s).
+    const bool integral = zf == rintf(zf) && zf >= -1024.f && zf <= 1023.f;
+    const __half2 z2 = __half2half2(zh);
+    const __half2 zc = __hadd2(z2, k1024);
+#pragma unroll
+    for (int wi = 0; wi < 2; ++wi) {
+        const uint32_t w = wi ? w1 : w0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t h = and_or(w >> (2 * j), 0x00030003u, 0x64006400u);   // 1024 + code
+            const __half2 hv = *reinterpret_cast<const __half2*>(&h);
+            const __half2 d = integral ? __hsub2(hv, zc) : __hsub2(__hsub2(hv, k1024), z2);
+            const __half2 v = __hmul2(d, s2);
+            out[wi * 8 + j] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+    }
+}
+
+template <int TN, bool SW>
+__global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
+    using C = TcCfg<TN, SW>;
+    constexpr int S = C::S;
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * S + 1];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_dead;
+
+    int slot, lt, cnt, e0;
+    if (!tc_find_tile<TN>(p, blockIdx.y, slot, lt, cnt, e0)) return;    // uniform: a padding tile
+    const int widx = p.slot_index ? __ldg(p.slot_index + slot) : slot;
+    const glq_weight_t W = p.table ? p.table[widx] : p.w;
+    const int N = W.N;
+    const int ft = blockIdx.x;
+    if (ft * kTcFeat >= N) return;
+    const bool has_lr = p.rank > 0 && W.sv != nullptr && p.a[0] != nullptr;
+    const int nst = p.nkb + (has_lr ? p.ns : 0);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sraw = smem_u32(tc_smem_raw);
+    const uint32_t sbase = (sraw + 1023u) & ~1023u;
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_acc = bar_full + 16 * S;
+    volatile int* dead = &s_dead;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, kTcProducers + 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        s_dead = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kTcProducers) tc_alloc(smem_u32(&s_tmem), C::COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    if (warp < kTcProducers) {
+        // ================= producers: dequantise the weight operand =================
+        const int g = lane >> 2, t = lane & 3;
+        const int tile16 = ft * 8 + warp;                       // 16-row tile of the matrix (of gate and of up)
+        constexpr int NM = SW ? 2 : 1;
+        const unsigned char* blk[NM];
+        // fused gate|up: pair = tile16, j = matrix; plain: destination tile d = tile16
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+            const int d = SW ? tile16 * 2 + m : tile16;
+            blk[m] = reinterpret_cast<const unsigned char*>(W.codes) + ((size_t)(d >> 1) * p.nkb * 2 + (d & 1)) * 576;
+        }
+        const int ntiles16 = (N + 15) / 16;
+        const bool live = tile16 < ntiles16;                    // tiles past the matrix contribute zero rows
+        constexpr int D = 4;                                    // register prefetch depth (k stages)
+        uint4 cq[D][NM];
+        uint2 csz[D][NM];
+        auto fetch = [&](int kb, uint4 (&q)[NM], uint2 (&z)[NM]) {
+#pragma unroll
+            for (int m = 0; m < NM; ++m) {
+                if (live && kb < p.nkb) {
+                    const unsigned char* b = blk[m] + (size_t)kb * 2 * 576;
+                    q[m] = __ldg(reinterpret_cast<const uint4*>(b) + lane);
+                    z[m] = __ldg(reinterpret_cast<const uint2*>(b + 512) + g);
+                } else {
+                    q[m] = make_uint4(0, 0, 0, 0);
+                    z[m] = make_uint2(0, 0);
+                }
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < D; ++d) fetch(d, cq[d], csz[d]);
+
+        int s = 0;
+        uint32_t ph = 0;
+        // swizzled position of this lane's chunks: row g (and g+8) of the warp's 16 rows
+        const uint32_t row_off = (uint32_t)(warp * 16 + g) * 128u;
+        for (int st0 = 0; st0 < nst; st0 += D) {
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                const int st = st0 + d;
+                if (st < nst) {
+                    const bool ok = tc_wait(bar_empty + 8 * s, ph ^ 1u, dead, 100);
+                    const uint32_t abase = sbase + (uint32_t)s * C::STAGE;
+                    if (ok && st < p.nkb) {
+#pragma unroll
+                        for (int m = 0; m < NM; ++m) {
+#pragma unroll
+                            for (int hrow = 0; hrow < 2; ++hrow) {
+                                uint32_t o[16];
+                                tc_unpack_row_q2(hrow ? cq[d][m].z : cq[d][m].x, hrow ? cq[d][m].w : cq[d][m].y,
+                                                 hrow ? csz[d][m].y : csz[d][m].x, o);
+                                // channels 32t .. 32t+31: atom t/2, chunks 4(t%2) .. 4(t%2)+3
+                                const uint32_t base = abase + (uint32_t)m * (kTcFeat * 256) + (uint32_t)(t >> 1) * (kTcFeat * 128) +
+                                                      row_off + (uint32_t)hrow * (8 * 128);
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) {
+                                    const uint32_t chunk = (uint32_t)((4 * (t & 1) + c) ^ g);
+                                    sts128(base + chunk * 16u, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                                }
+                            }
+                        }
+                        fetch(st + D, cq[d], csz[d]);
+                    } else if (ok) {
+                        // low-rank stage: rows of the packed SV slice -> atom 0 of the A buffer
+                        const int sl = st - p.nkb;
+#pragma unroll
+                        for (int m = 0; m < NM; ++m) {
+                            const int dt = SW ? tile16 * 2 + m : tile16;
+                            const int r = lane >> 1, hb = lane & 1;       // row of the tile, 64-byte half of its 128 B
+                            const uint4* src = reinterpret_cast<const uint4*>(
+                                reinterpret_cast<const unsigned char*>(W.sv) +
+                                ((((size_t)(dt >> 1) * p.ns + sl) * 32) + (dt & 1) * 16 + r) * 128 + hb * 64);
+                            const uint32_t base = abase + (uint32_t)m * (kTcFeat * 256) + (uint32_t)(warp * 16 + r) * 128u;
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                uint4 v = make_uint4(0, 0, 0, 0);
+                                if (live) v = __ldg(src + c);
+                                const uint32_t chunk = (uint32_t)((4 * hb + c) ^ (r & 7));
+                                sts128(base + chunk * 16u, v.x, v.y, v.z, v.w);
+                            }
+                        }
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                    if (++s == S) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+        }
+
+        // ================= epilogue: TMEM -> registers -> global =================
+        const bool acc_ok = tc_wait(bar_acc, 0, dead, 101);
+        tc_fence_after();
+        const int q = warp & 3, half = warp >> 2;
+        const int f = ft * kTcFeat + q * 32 + lane;
+        const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+        const __half* bias = reinterpret_cast<const __half*>(W.bias);
+        const float bv = (!SW && bias && f < N) ? __half2float(__ldg(bias + f)) : 0.f;
+        for (int c0 = half * (TN / 2); c0 < (half + 1) * (TN / 2); c0 += 16) {
+            uint32_t vg[16], vu[16];
+            tc_ld16(trow + (uint32_t)c0, vg);
+            if (SW) tc_ld16(trow + (uint32_t)(TN + c0), vu);
+            tc_ld_wait();
+            if (acc_ok && f < N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int rr = lt * TN + c0 + j;
+                    if (rr < cnt) {
+                        float v = round16(__uint_as_float(vg[j]));
+                        if (SW) {
+                            v = round16(silu16(v) * round16(__uint_as_float(vu[j])));
+                        } else {
+                            if (bias) v = round16(v + bv);
+                            if (p.entry_scale) v = round16(__half2float(__ldg(p.entry_scale + e0 + rr)) * v);
+                        }
+                        p.y[(size_t)(e0 + rr) * p.ldy + f] = __float2half_rn(v);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else if (warp == kTcProducers) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc_idesc(TN);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int st = 0; st < nst && ok; ++st) {
+                ok = tc_wait(bar_full + 8 * s, ph, dead, 100);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t abase = sbase + (uint32_t)s * C::STAGE, bbase = abase + C::A_BYTES;
+                if (st < p.nkb) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t ao = (uint32_t)(kk >> 2) * (kTcFeat * 128) + (uint32_t)(kk & 3) * 32u;
+                        const uint32_t bo = (uint32_t)(kk >> 2) * (TN * 128) + (uint32_t)(kk & 3) * 32u;
+                        const uint64_t bd = tc_smem_desc(bbase + bo);
+                        tc_mma_f16(tmem, tc_smem_desc(abase + ao), bd, idesc, (st | kk) != 0);
+                        if (SW) tc_mma_f16(tmem + TN, tc_smem_desc(abase + kTcFeat * 256 + ao), bd, idesc, (st | kk) != 0);
+                    }
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint32_t o = (uint32_t)kk * 32u;
+                        tc_mma_f16(tmem, tc_smem_desc(abase + o), tc_smem_desc(bbase + o), idesc, 1);
+                        if (SW)
+                            tc_mma_f16(tmem + TN, tc_smem_desc(abase + kTcFeat * 256 + o), tc_smem_desc(bbase + TN * 128 + o),
+                                       idesc, 1);
+                    }
+                }
+                tc_commit(bar_empty + 8 * s);
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            if (ok) tc_commit(bar_acc);
+        }
+        __syncwarp();
+    } else {
+        // ================= loader of the token operand =================
+        if (lane == 0) {
+            const unsigned char* tile = p.xp + (size_t)blockIdx.y * p.tile_bytes;
+            int s = 0;
+            uint32_t ph = 0;
+            int issued = 0;
+            for (int st = 0; st < nst; ++st) {
+                if (!tc_wait(bar_empty + 8 * s, ph ^ 1u, dead, 100)) break;
+                const uint32_t bbase = sbase + (uint32_t)s * C::STAGE + C::A_BYTES;
+                const unsigned char* src;
+                uint32_t bytes;
+                if (st < p.nkb) {
+                    src = tile + (size_t)st * TN * 256;
+                    bytes = TN * 256;
+                } else {
+                    src = tile + (size_t)p.nkb * TN * 256 + (size_t)(st - p.nkb) * p.na * TN * 128;
+                    bytes = (uint32_t)p.na * TN * 128;
+                }
+                mbar_expect_tx(bar_full + 8 * s, bytes);
+                bulk_g2s(bbase, src, bytes, bar_full + 8 * s);
+                ++issued;
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            // a CTA that gave up must not leave while its copies are in flight: wait (bounded) for the
+            // barriers of the last copies issued
+            if (*dead) {
+                int s2 = s;
+                uint32_t ph2 = ph;
+                for (int i = 0; i < S && i < issued; ++i) {
+                    if (--s2 < 0) {
+                        s2 = S - 1;
+                        ph2 ^= 1u;
+                    }
+                    const unsigned long long t0 = global_ns();
+                    while (!mbar_test_wait(bar_full + 8 * s2, ph2) && global_ns() - t0 < 2000000ull) __nanosleep(64);
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    __syncthreads();
+    if (warp == kTcProducers) {
+        tc_fence_after();
+        tc_dealloc(tmem, C::COLS);
+    }
+}
+
+}  // namespace glq

@@ -165,7 +165,8 @@ typedef struct glq_mm_args {
     int32_t max_rows;    /* upper bound of rows per slot (sizes shared memory and passes) */
     int32_t rows_stride; /* entries reserved per slot when slot_offset is NULL */
     int32_t N, K, rank;  /* shape shared by all slots */
-    int32_t reserved;
+    int32_t total_rows;  /* upper bound of the entries of all slots together (sizes the workspace of the
+                            many-row path); 0: n_problems * max_rows */
     glq_weight_t w;              /* inline descriptor */
     const glq_weight_t* w_table; /* device array indexed by slot_index[], or NULL */
     const int32_t* slot_index;  /* device, NULL: identity */
@@ -177,7 +178,8 @@ typedef struct glq_mm_args {
     const void* x;  int64_t ldx;   /* fp16 */
     const void* a0; const void* a1; int64_t lda; /* fp16 x.U per entry, NULL: no low-rank term */
     void* y;        int64_t ldy;   /* fp16 */
-    void* workspace; size_t workspace_bytes; /* scratch for split-k partial sums (contents irrelevant)   */
+    void* workspace; size_t workspace_bytes; /* scratch: split-k partial sums, or the re-tiled activations
+                                                of the many-row path (contents irrelevant)               */
     int32_t* counters; size_t n_counters;    /* arrival counters: zero before the first use, left zero   */
 } glq_mm_args_t;
 

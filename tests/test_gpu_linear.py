@@ -78,6 +78,22 @@ def test_linear_forward(dev, N, K, rank, fmt, bits, gs, sym, B):
         assert cases.rel_l2(y2, ref) <= REL
 
 
+@pytest.mark.parametrize("N,K,rank,B,int_zeros", [(1408, 2048, 64, 128, True), (2048, 1408, 64, 300, True),
+                                                   (100, 392, 16, 200, True), (256, 256, 16, 64, False),
+                                                   (24, 128, 0, 40, True), (5632, 2048, 64, 96, True)])
+def test_many_rows_tensor_core_path(dev, N, K, rank, B, int_zeros):
+    """More than 32 rows of 2-bit affine codes go to the tcgen05 kernel: ragged feature and channel
+    counts, token counts that do not fill a tile, non-integer zero points."""
+    d = cases.make_linear(11 * N + K + B, N, K, rank=max(rank, 16), with_lora=rank > 0, int_zeros=int_zeros)
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(N + 3 * K + B, B, K)
+    y = lin(x.to(dev)).cpu()
+    ref = O.linear_forward(cases.to_oracle_linear(d), x)
+    assert cases.rel_l2(y, ref) <= REL
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
 def test_linear_batch_dims_and_empty(dev):
     d = cases.make_linear(5, 96, 256, rank=16)
     lin = cases.to_b200_linear(d, dev)

@@ -111,6 +111,23 @@ def test_graph_capture_replay(dev):
         assert cases.rel_l2(static_y.cpu(), ref) <= REL_BLOCK
 
 
+@pytest.mark.parametrize("N", [64, 200, 515])
+def test_prefill_block_many_rows(dev, N):
+    """Token counts that give experts more than 32 rows: the grouped tcgen05 path with device-side
+    token lists, gather of the activation rows, SwiGLU and routing-weight epilogues."""
+    blk = cases.make_moe(700 + N, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    mb, y, logits, ref, ref_logits = _run(blk, N, dev, 1700 + N)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
+def test_qwen_moe_shape_prefill(dev):
+    blk = cases.make_moe(4242, 2048, 1408, 60, 4, I_shared=5632, rank=64, experts_per_cluster=4)
+    mb, y, logits, ref, ref_logits = _run(blk, 128, dev, 4243)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+
+
 # ---- expert parallelism ---------------------------------------------------------------------------
 @pytest.mark.parametrize("N,world", [(1, 2), (3, 2), (9, 2), (9, 4), (33, 3)])
 def test_expert_parallel_emulated_on_one_gpu(dev, N, world):
