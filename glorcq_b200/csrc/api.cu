@@ -383,9 +383,15 @@ static bool tc_disabled() {
 }
 // true when the tcgen05 kernel takes the call: 2-bit affine codes, more rows than the streaming kernel stages
 static bool plan_tc(const glq_mm_args_t* a, TcGeom* out) {
-    if (tc_disabled() || a->fmt != GLQ_FMT_Q2 || a->max_rows <= 32) return false;
+    if (tc_disabled() || a->max_rows <= 32) return false;
     if (a->N <= 0 || a->K <= 0 || a->n_problems <= 0 || a->rank < 0 || a->rank % 16 != 0) return false;
-    if (a->group_size <= 0 || a->group_size % 128 != 0) return false;
+    if (a->fmt == GLQ_FMT_Q2 || a->fmt == GLQ_FMT_Q4) {
+        if (a->group_size <= 0 || a->group_size % fmt_kb(a->fmt) != 0) return false;
+    } else if (a->fmt == GLQ_FMT_F16) {
+        if (a->epilogue != GLQ_EPI_LINEAR) return false;
+    } else if (a->fmt != GLQ_FMT_T2) {
+        return false;
+    }
     TcGeom g{};
     const long long stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
     long long total = a->total_rows > 0 ? a->total_rows : (long long)a->n_problems * (a->slot_offset ? a->max_rows : stride);
@@ -403,19 +409,19 @@ static bool plan_tc(const glq_mm_args_t* a, TcGeom* out) {
     return true;
 }
 
-template <int TN, bool SW>
+template <int FMT, int TN, bool SW>
 static int launch_tc_t(const TcParams& p, int N, cudaStream_t st) {
     using C = TcCfg<TN, SW>;
     static bool configured[64] = {};
     int dev = 0;
     GLQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        GLQ_CUDA(cudaFuncSetAttribute(tc_kernel<TN, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        GLQ_CUDA(cudaFuncSetAttribute(tc_kernel<FMT, TN, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     tc_pack_b_kernel<TN><<<dim3(p.tiles_max, p.nkb + p.ns), 256, 0, st>>>(p);
     GLQ_CUDA(cudaGetLastError());
-    tc_kernel<TN, SW><<<dim3(cdiv(N, kTcFeat), p.tiles_max), kTcThreads, C::SMEM, st>>>(p);
+    tc_kernel<FMT, TN, SW><<<dim3(cdiv(N, kTcFeat), p.tiles_max), kTcThreads, C::SMEM, st>>>(p);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
 }
@@ -451,9 +457,22 @@ static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st) {
     p.na = g.na;
     p.tiles_max = g.tiles_max;
     p.x_vec = ((reinterpret_cast<uintptr_t>(a->x) & 7u) == 0 && a->ldx % 4 == 0) ? 1 : 0;
+    p.fmt = a->fmt;
     const bool sw = a->epilogue == GLQ_EPI_SWIGLU;
-    if (g.tn == 128) return sw ? launch_tc_t<128, true>(p, a->N, st) : launch_tc_t<128, false>(p, a->N, st);
-    return sw ? launch_tc_t<64, true>(p, a->N, st) : launch_tc_t<64, false>(p, a->N, st);
+    const bool big = g.tn == 128;
+    switch (a->fmt) {
+#define GLQ_TC_CASE(F)                                                                                       \
+    case F:                                                                                                  \
+        if (big) return sw ? launch_tc_t<F, 128, true>(p, a->N, st) : launch_tc_t<F, 128, false>(p, a->N, st); \
+        return sw ? launch_tc_t<F, 64, true>(p, a->N, st) : launch_tc_t<F, 64, false>(p, a->N, st);
+        GLQ_TC_CASE(GLQ_FMT_Q2)
+        GLQ_TC_CASE(GLQ_FMT_Q4)
+        GLQ_TC_CASE(GLQ_FMT_T2)
+#undef GLQ_TC_CASE
+        case GLQ_FMT_F16:
+            return big ? launch_tc_t<GLQ_FMT_F16, 128, false>(p, a->N, st) : launch_tc_t<GLQ_FMT_F16, 64, false>(p, a->N, st);
+    }
+    return GLQ_ERR_UNSUPPORTED;
 }
 
 extern "C" size_t glq_mm_workspace_bytes(const glq_mm_args_t* a) {

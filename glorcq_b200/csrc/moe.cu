@@ -88,8 +88,8 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
     if (d->rot_mid) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, (int)nk, d->I, d->I, 0); acc(); }
     if (d->sh_rot_mid && d->I_shared > 0) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->I_shared, d->I_shared, 0); acc(); }
     if (d->rank > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, d->rank, d->H, 0); acc();
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->I, 0); acc();
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, d->rank, d->H, 0, (int)(2 * nk)); acc();
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->I, 0, (int)nk); acc();
     }
     set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, d->rank, (int)nk); acc();
     set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, d->rank, (int)nk); acc();
@@ -410,7 +410,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     char* a_gate = ws + L.a_gu;
     char* a_up = a_gate + (size_t)nk * R * 2;
     if (R > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, R, d->H, 0);
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, R, d->H, 0, 2 * nk);
         m.w_table = d->ut_gate_up;
         m.slot_index = reinterpret_cast<int*>(ws + L.active2);
         m.n_slots = reinterpret_cast<int*>(ws + L.n_active2);
@@ -440,7 +440,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if ((rc = finish(m)) != GLQ_OK) return rc;
     // 5. h.U of the down clusters
     if (R > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, R, d->I, 0);
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, R, d->I, 0, nk);
         m.w_table = d->ut_down;
         routed(m);
         m.x = ws + L.h;

@@ -49,6 +49,7 @@ struct TcParams {
     int K, rank, nkb, ns, na; // ns: 64-wide low-rank slices, na: x.U operands per entry (1, or 2 for gate|up)
     int tiles_max;
     int x_vec;                // x rows allow 8-byte loads
+    int fmt;                  // GLQ_FMT_*: fixes the channel order inside a group of 16
 };
 
 // ---- token tile -> (problem slot, local tile) -----------------------------------------------------
@@ -82,6 +83,17 @@ __device__ __forceinline__ bool tc_find_tile(const TcParams& p, int gt, int& slo
     return false;
 }
 
+// Order of the input channels inside a group of 16, per format (the order in which the format's
+// unpack yields its values); the pre-pass stores the token operand in the same order.
+__host__ __device__ __forceinline__ int tc_channel_of(int fmt, int pos) {
+    switch (fmt) {
+        case GLQ_FMT_Q2: return (pos >> 1) + 8 * (pos & 1);                              // (j, j+8)
+        case GLQ_FMT_Q4: return (pos & 8) + ((pos & 7) >> 1) + 4 * (pos & 1);             // (j, j+4) per 8
+        case GLQ_FMT_T2: return ((pos & 7) >> 1) * 4 + (pos & 1) * 2 + (pos >> 3);        // (0,2)(4,6)..(1,3)(5,7)..
+        default: return 2 * (pos >> 2) + (pos & 1) + 8 * ((pos >> 1) & 1);                // F16 fragment order
+    }
+}
+
 // ---- pre-pass: token operand in UMMA layout ---------------------------------------------------------
 // Tile layout in xp (TN rows): per k stage (128 input channels) two atoms [TN][128 B], then per
 // low-rank slice `na` atoms [TN][128 B].  Inside an atom row r keeps its 16-byte chunk c at chunk
@@ -106,7 +118,13 @@ __global__ void __launch_bounds__(256) tc_pack_b_kernel(const TcParams p) {
                 const long long row = p.entry_row ? __ldg(p.entry_row + e0 + rr) : (long long)(e0 + rr);
                 const __half* src = p.x + row * p.ldx;
                 const int ka = k0 + 4 * h, kb = k0 + 8 + 4 * h;     // channels j and j+8, j = 4h..4h+3
-                if (p.x_vec && kb + 4 <= p.K) {
+                if (p.fmt != GLQ_FMT_Q2) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int k = k0 + tc_channel_of(p.fmt, 8 * h + i);
+                        if (k < p.K) v[i] = __ldg(src + k);
+                    }
+                } else if (p.x_vec && kb + 4 <= p.K) {
                     __align__(8) __half lo[4], hi[4];
                     *reinterpret_cast<uint2*>(lo) = __ldg(reinterpret_cast<const uint2*>(src + ka));
                     *reinterpret_cast<uint2*>(hi) = __ldg(reinterpret_cast<const uint2*>(src + kb));
@@ -226,36 +244,35 @@ template <int TN, bool SW> struct TcCfg {
     static constexpr size_t SMEM = (size_t)S * STAGE + 1024;
 };
 
-// 2-bit codes of one row and 32 channels (two words of 16) -> 4 chunks of 8 fp16 in k-pair order
-__device__ __forceinline__ void tc_unpack_row_q2(uint32_t w0, uint32_t w1, uint32_t sz, uint32_t (&out)[16]) {
-    const __half2 s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xffffu)));
-    const __half zh = __ushort_as_half((unsigned short)(sz >> 16));
-    const float zf = __half2float(zh);
-    const __half2 k1024 = __float2half2_rn(1024.f);
-    // the exponent trick yields 1024 + code.  Integer zero points (what the quantizer writes) fold into
-    // one exact subtraction of 1024 + z; any other zero point takes (1024 + code - 1024) - z, which is
-    // the fp16 rounding of fp16(code) - z.  Either way the value is fp16(fp16(q - z) * s).
-    const bool integral = zf == rintf(zf) && zf >= -1024.f && zf <= 1023.f;
-    const __half2 z2 = __half2half2(zh);
-    const __half2 zc = __hadd2(z2, k1024);
-#pragma unroll
-    for (int wi = 0; wi < 2; ++wi) {
-        const uint32_t w = wi ? w1 : w0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t h = and_or(w >> (2 * j), 0x00030003u, 0x64006400u);   // 1024 + code
-            const __half2 hv = *reinterpret_cast<const __half2*>(&h);
-            const __half2 d = integral ? __hsub2(hv, zc) : __hsub2(__hsub2(hv, k1024), z2);
-            const __half2 v = __hmul2(d, s2);
-            out[wi * 8 + j] = *reinterpret_cast<const uint32_t*>(&v);
-        }
+// (1024 + code) or (64 + code) pairs -> fp16(fp16(q - z) * s).  Integer zero points (what the
+// quantizer writes) fold into one exact subtraction of offset + z; any other zero point takes
+// (offset + code - offset) - z, the fp16 rounding of fp16(code) - z.
+struct TcAffine {
+    __half2 s2, z2, zc, koff;
+    bool integral;
+    __device__ __forceinline__ TcAffine(uint32_t sz, float off) {
+        s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xffffu)));
+        const __half zh = __ushort_as_half((unsigned short)(sz >> 16));
+        const float zf = __half2float(zh);
+        koff = __float2half2_rn(off);
+        integral = zf == rintf(zf) && zf >= -1024.f && zf <= 900.f;
+        z2 = __half2half2(zh);
+        zc = __hadd2(z2, koff);
     }
-}
+    __device__ __forceinline__ uint32_t operator()(uint32_t h) const {
+        const __half2 hv = *reinterpret_cast<const __half2*>(&h);
+        const __half2 d = integral ? __hsub2(hv, zc) : __hsub2(__hsub2(hv, koff), z2);
+        const __half2 v = __hmul2(d, s2);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+};
 
-template <int TN, bool SW>
+template <int FMT, int TN, bool SW>
 __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
     using C = TcCfg<TN, SW>;
     constexpr int S = C::S;
+    constexpr bool AFFINE = FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4;
+    static_assert(!(SW && FMT == GLQ_FMT_F16), "dense weights have no fused gate|up form");
     extern __shared__ unsigned char tc_smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * S + 1];
     __shared__ uint32_t s_tmem;
@@ -268,7 +285,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
     const int N = W.N;
     const int ft = blockIdx.x;
     if (ft * kTcFeat >= N) return;
-    const bool has_lr = p.rank > 0 && W.sv != nullptr && p.a[0] != nullptr;
+    const bool has_lr = FMT != GLQ_FMT_F16 && p.rank > 0 && W.sv != nullptr && p.a[0] != nullptr;
     const int nst = p.nkb + (has_lr ? p.ns : 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -293,41 +310,62 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
     const uint32_t tmem = s_tmem;
 
     if (warp < kTcProducers) {
-        // ================= producers: dequantise the weight operand =================
+        // ================= producers: the weight operand =================
         const int g = lane >> 2, t = lane & 3;
         const int tile16 = ft * 8 + warp;                       // 16-row tile of the matrix (of gate and of up)
         constexpr int NM = SW ? 2 : 1;
-        const unsigned char* blk[NM];
-        // fused gate|up: pair = tile16, j = matrix; plain: destination tile d = tile16
-#pragma unroll
-        for (int m = 0; m < NM; ++m) {
-            const int d = SW ? tile16 * 2 + m : tile16;
-            blk[m] = reinterpret_cast<const unsigned char*>(W.codes) + ((size_t)(d >> 1) * p.nkb * 2 + (d & 1)) * 576;
-        }
         const int ntiles16 = (N + 15) / 16;
         const bool live = tile16 < ntiles16;                    // tiles past the matrix contribute zero rows
-        constexpr int D = 4;                                    // register prefetch depth (k stages)
-        uint4 cq[D][NM];
-        uint2 csz[D][NM];
-        auto fetch = [&](int kb, uint4 (&q)[NM], uint2 (&z)[NM]) {
+        // blocks of the tiled layouts per 128-channel stage, 16-byte loads per lane and block
+        constexpr int BPS = (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) ? 1 : 2;
+        constexpr int LPB = FMT == GLQ_FMT_F16 ? 4 : 1;
+        constexpr int BB = FMT == GLQ_FMT_T2 ? 512 : 576;
+        constexpr int REGS = NM * BPS * (LPB * 4 + (AFFINE ? 2 : 0));
+        constexpr int D = REGS <= 12 ? 4 : (REGS <= 32 ? 2 : 1);   // register prefetch depth (stages)
+        const int nblk = FMT == GLQ_FMT_F16 ? (p.K + 63) / 64 : (FMT == GLQ_FMT_Q4 ? (p.K + 63) / 64 : p.nkb);
+        const unsigned char* blk[NM];
 #pragma unroll
-            for (int m = 0; m < NM; ++m) {
-                if (live && kb < p.nkb) {
-                    const unsigned char* b = blk[m] + (size_t)kb * 2 * 576;
-                    q[m] = __ldg(reinterpret_cast<const uint4*>(b) + lane);
-                    z[m] = __ldg(reinterpret_cast<const uint2*>(b + 512) + g);
-                } else {
-                    q[m] = make_uint4(0, 0, 0, 0);
-                    z[m] = make_uint2(0, 0);
-                }
+        for (int m = 0; m < NM; ++m) {
+            if constexpr (FMT == GLQ_FMT_F16) {
+                blk[m] = reinterpret_cast<const unsigned char*>(W.codes) + (size_t)tile16 * nblk * 2048;
+            } else {
+                // fused gate|up: destination tile d = 2 * tile16 + matrix; plain: d = tile16; pair d/2, slot d%2
+                const int d = SW ? tile16 * 2 + m : tile16;
+                blk[m] = reinterpret_cast<const unsigned char*>(W.codes) + ((size_t)(d >> 1) * nblk * 2 + (d & 1)) * BB;
             }
+        }
+        uint32_t TL[NM], TH[NM];
+        if constexpr (FMT == GLQ_FMT_T2) {
+#pragma unroll
+            for (int m = 0; m < NM; ++m) make_t2_tables(W.centroids + 4 * m, TL[m], TH[m]);
+        }
+        uint4 cq[D][NM][BPS][LPB];
+        uint2 csz[D][NM][BPS];
+        auto fetch = [&](int st, uint4 (&q)[NM][BPS][LPB], uint2 (&z)[NM][BPS]) {
+#pragma unroll
+            for (int m = 0; m < NM; ++m)
+#pragma unroll
+                for (int b = 0; b < BPS; ++b) {
+                    const int kb = st * BPS + b;
+                    const bool in = live && st < p.nkb && kb < nblk;
+                    if constexpr (FMT == GLQ_FMT_F16) {
+                        const uint4* src = reinterpret_cast<const uint4*>(blk[m] + (size_t)kb * 2048) + lane;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) q[m][b][ks] = in ? __ldg(src + 32 * ks) : make_uint4(0, 0, 0, 0);
+                    } else {
+                        const unsigned char* src = blk[m] + (size_t)kb * 2 * BB;
+                        q[m][b][0] = in ? __ldg(reinterpret_cast<const uint4*>(src) + lane) : make_uint4(0, 0, 0, 0);
+                        if constexpr (AFFINE)
+                            z[m][b] = in ? __ldg(reinterpret_cast<const uint2*>(src + 512) + g) : make_uint2(0, 0);
+                    }
+                }
         };
 #pragma unroll
         for (int d = 0; d < D; ++d) fetch(d, cq[d], csz[d]);
 
         int s = 0;
         uint32_t ph = 0;
-        // swizzled position of this lane's chunks: row g (and g+8) of the warp's 16 rows
+        // this lane's rows of the A tile: g and g + 8 of the warp's 16; swizzle key (row & 7) = g
         const uint32_t row_off = (uint32_t)(warp * 16 + g) * 128u;
         for (int st0 = 0; st0 < nst; st0 += D) {
 #pragma unroll
@@ -339,19 +377,68 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                     if (ok && st < p.nkb) {
 #pragma unroll
                         for (int m = 0; m < NM; ++m) {
+                            const uint32_t mbase = abase + (uint32_t)m * (kTcFeat * 256) + row_off;
+                            if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) {
+                                // lane t holds channels 32t .. 32t+31 of the stage: atom t/2, chunks 4(t%2) .. +3
 #pragma unroll
-                            for (int hrow = 0; hrow < 2; ++hrow) {
-                                uint32_t o[16];
-                                tc_unpack_row_q2(hrow ? cq[d][m].z : cq[d][m].x, hrow ? cq[d][m].w : cq[d][m].y,
-                                                 hrow ? csz[d][m].y : csz[d][m].x, o);
-                                // channels 32t .. 32t+31: atom t/2, chunks 4(t%2) .. 4(t%2)+3
-                                const uint32_t base = abase + (uint32_t)m * (kTcFeat * 256) + (uint32_t)(t >> 1) * (kTcFeat * 128) +
-                                                      row_off + (uint32_t)hrow * (8 * 128);
+                                for (int hrow = 0; hrow < 2; ++hrow) {
+                                    const uint4 q = cq[d][m][0][0];
+                                    uint32_t o[16];
+                                    if constexpr (FMT == GLQ_FMT_Q2) {
+                                        const TcAffine af(hrow ? csz[d][m][0].y : csz[d][m][0].x, 1024.f);
 #pragma unroll
-                                for (int c = 0; c < 4; ++c) {
-                                    const uint32_t chunk = (uint32_t)((4 * (t & 1) + c) ^ g);
-                                    sts128(base + chunk * 16u, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                                        for (int wi = 0; wi < 2; ++wi) {
+                                            const uint32_t w = hrow ? (wi ? q.w : q.z) : (wi ? q.y : q.x);
+#pragma unroll
+                                            for (int j = 0; j < 8; ++j)
+                                                o[wi * 8 + j] = af(and_or(w >> (2 * j), 0x00030003u, 0x64006400u));
+                                        }
+                                    } else {
+                                        uint32_t h0[8], h1[8];
+                                        unpack_t2(hrow ? q.z : q.x, TL[m], TH[m], h0);
+                                        unpack_t2(hrow ? q.w : q.y, TL[m], TH[m], h1);
+#pragma unroll
+                                        for (int j = 0; j < 8; ++j) {
+                                            o[j] = h0[j];
+                                            o[8 + j] = h1[j];
+                                        }
+                                    }
+                                    const uint32_t base = mbase + (uint32_t)(t >> 1) * (kTcFeat * 128) + (uint32_t)hrow * (8 * 128);
+#pragma unroll
+                                    for (int c = 0; c < 4; ++c) {
+                                        const uint32_t chunk = (uint32_t)((4 * (t & 1) + c) ^ g);
+                                        sts128(base + chunk * 16u, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                                    }
                                 }
+                            } else if constexpr (FMT == GLQ_FMT_Q4) {
+                                // block b = atom b; lane t holds channels 16t .. 16t+15 of it: chunks 2t, 2t+1
+#pragma unroll
+                                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                                    for (int hrow = 0; hrow < 2; ++hrow) {
+                                        const uint4 q = cq[d][m][b][0];
+                                        const TcAffine af(hrow ? csz[d][m][b].y : csz[d][m][b].x, kQ4Offset);
+                                        uint32_t h0[4], h1[4];
+                                        unpack_q4(hrow ? q.z : q.x, h0);
+                                        unpack_q4(hrow ? q.w : q.y, h1);
+                                        const uint32_t base = mbase + (uint32_t)b * (kTcFeat * 128) + (uint32_t)hrow * (8 * 128);
+                                        sts128(base + (uint32_t)((2 * t) ^ g) * 16u, af(h0[0]), af(h0[1]), af(h0[2]), af(h0[3]));
+                                        sts128(base + (uint32_t)((2 * t + 1) ^ g) * 16u, af(h1[0]), af(h1[1]), af(h1[2]), af(h1[3]));
+                                    }
+                            } else {
+                                // dense fp16 fragments: block b = atom b; (ks, lane) holds, per row, channels
+                                // 16ks + {2t, 2t+1, 2t+8, 2t+9}: 8 bytes at chunk 2ks + t/2, half t%2
+#pragma unroll
+                                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                                    for (int ks = 0; ks < 4; ++ks) {
+                                        const uint4 q = cq[d][m][b][ks];
+                                        const uint32_t base = mbase + (uint32_t)b * (kTcFeat * 128) +
+                                                              (uint32_t)((2 * ks + (t >> 1)) ^ g) * 16u + (uint32_t)(t & 1) * 8u;
+                                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(base), "r"(q.x), "r"(q.z) : "memory");
+                                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(base + 8 * 128), "r"(q.y), "r"(q.w)
+                                                     : "memory");
+                                    }
                             }
                         }
                         fetch(st + D, cq[d], csz[d]);
@@ -366,10 +453,27 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                                 reinterpret_cast<const unsigned char*>(W.sv) +
                                 ((((size_t)(dt >> 1) * p.ns + sl) * 32) + (dt & 1) * 16 + r) * 128 + hb * 64);
                             const uint32_t base = abase + (uint32_t)m * (kTcFeat * 256) + (uint32_t)(warp * 16 + r) * 128u;
+                            // codebook format: the accumulator is scaled by the row norm in the epilogue,
+                            // so the low-rank rows go in divided by it
+                            float inv = 1.f;
+                            if constexpr (FMT == GLQ_FMT_T2) {
+                                if (live) {
+                                    const float nv = __ldg(W.norms + (size_t)dt * 16 + r);
+                                    inv = nv != 0.f ? 1.f / nv : 0.f;
+                                }
+                            }
 #pragma unroll
                             for (int c = 0; c < 4; ++c) {
                                 uint4 v = make_uint4(0, 0, 0, 0);
                                 if (live) v = __ldg(src + c);
+                                if constexpr (FMT == GLQ_FMT_T2) {
+                                    __half2* hp = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        const float2 f2 = __half22float2(hp[i]);
+                                        hp[i] = __floats2half2_rn(f2.x * inv, f2.y * inv);
+                                    }
+                                }
                                 const uint32_t chunk = (uint32_t)((4 * hb + c) ^ (r & 7));
                                 sts128(base + chunk * 16u, v.x, v.y, v.z, v.w);
                             }
@@ -394,6 +498,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
         const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
         const __half* bias = reinterpret_cast<const __half*>(W.bias);
         const float bv = (!SW && bias && f < N) ? __half2float(__ldg(bias + f)) : 0.f;
+        float nrm_g = 1.f, nrm_u = 1.f;     // codebook format: per-row norms, in tile order
+        if constexpr (FMT == GLQ_FMT_T2) {
+            if (f < N) {
+                const int t16 = f >> 4, r16 = f & 15;
+                nrm_g = __ldg(W.norms + (size_t)(SW ? 2 * t16 : t16) * 16 + r16);
+                if (SW) nrm_u = __ldg(W.norms + (size_t)(2 * t16 + 1) * 16 + r16);
+            }
+        }
         for (int c0 = half * (TN / 2); c0 < (half + 1) * (TN / 2); c0 += 16) {
             uint32_t vg[16], vu[16];
             tc_ld16(trow + (uint32_t)c0, vg);
@@ -404,9 +516,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                 for (int j = 0; j < 16; ++j) {
                     const int rr = lt * TN + c0 + j;
                     if (rr < cnt) {
-                        float v = round16(__uint_as_float(vg[j]));
+                        float v = round16(__uint_as_float(vg[j]) * nrm_g);
                         if (SW) {
-                            v = round16(silu16(v) * round16(__uint_as_float(vu[j])));
+                            v = round16(silu16(v) * round16(__uint_as_float(vu[j]) * nrm_u));
                         } else {
                             if (bias) v = round16(v + bv);
                             if (p.entry_scale) v = round16(__half2float(__ldg(p.entry_scale + e0 + rr)) * v);

@@ -53,7 +53,7 @@ def test_no_shared_expert_and_top8(dev, N):
     assert cases.rel_l2(y, ref) <= REL_BLOCK
 
 
-@pytest.mark.parametrize("N", [1, 7])
+@pytest.mark.parametrize("N", [1, 7, 150])
 def test_codebook_format_block(dev, N):
     blk = cases.make_moe(35, 256, 128, 6, 2, I_shared=256, rank=16, experts_per_cluster=2, fmt="turbo")
     for ex in blk["experts"] + [blk["shared_expert"]]:
