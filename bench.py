@@ -202,6 +202,65 @@ def _stage(rank, what):
         print(f"[bench rank {rank}] {what}", file=sys.stderr, flush=True)
 
 
+def measured_peak_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def gemm_roofline(dev, P=8, rows=1024, iters=20):
+    """The grouped dequant-GEMM (tcgen05 path) alone: P distinct 1408x2048 2-bit g128 rank-64 problems of
+    `rows` activation rows each (a prefill-sized grouped launch), x.U given."""
+    import ctypes as C
+    from glorcq_b200 import _lib
+    from glorcq_b200.tiled import TiledWeight
+    N, K, r = 1408, 2048, 64
+    L = _lib.lib()
+    g = torch.Generator(device=dev)
+    g.manual_seed(11)
+    keep, descs = [], []
+    for _ in range(P):
+        tw = TiledWeight.from_gptq(torch.randint(0, 4, (N, K), generator=g, device=dev, dtype=torch.int32),
+                                   (torch.randn(N, K // 128, generator=g, device=dev) * 0.02).abs().half(),
+                                   torch.randint(0, 4, (N, K // 128), generator=g, device=dev).half(), 2, 128)
+        tw.put_sv(0, (torch.randn(N, r, generator=g, device=dev) * 0.01).half())
+        keep.append(tw)
+        descs.append(tw.desc_bytes())
+    table = torch.frombuffer(bytearray(b"".join(descs)), dtype=torch.uint8).to(dev)
+    x = torch.randn(P * rows, K, generator=g, device=dev).half()
+    a = (torch.randn(P * rows, r, generator=g, device=dev) * 0.1).half()
+    y = torch.empty(P * rows, N, dtype=torch.float16, device=dev)
+    m = _lib.MMArgs()
+    m.fmt, m.group_size, m.epilogue, m.n_problems, m.max_rows, m.rows_stride = _lib.FMT_Q2, 128, 0, P, rows, rows
+    m.N, m.K, m.rank, m.total_rows = N, K, r, P * rows
+    m.w_table = table.data_ptr()
+    m.x, m.ldx, m.a0, m.lda, m.y, m.ldy = x.data_ptr(), K, a.data_ptr(), r, y.data_ptr(), N
+    ws = torch.empty(L.glq_mm_workspace_bytes(C.byref(m)) + 256, dtype=torch.uint8, device=dev)
+    m.workspace, m.workspace_bytes = (ws.data_ptr() + 255) // 256 * 256, ws.numel() - 256
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        _lib.check(L.glq_grouped_matmul(C.byref(m), st))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        _lib.check(L.glq_grouped_matmul(C.byref(m), st))
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / iters * 1e-3
+    flops = P * rows * (2.0 * N * K + 2.0 * N * r)
+    peak, kind = measured_peak_tflops()
+    ach = flops / sec / 1e12
+    return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+            "kernel": "tc_pack_b_kernel + tc_kernel<Q2> (grouped dequant-GEMM, tcgen05)", "launch_us": sec * 1e6,
+            "flops_per_launch": flops, "peak_kind": kind,
+            "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), {rows} rows each"}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from glorcq_b200 import _build, synthetic, tiled
@@ -317,6 +376,7 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         peak, kind = measured_peak_gbs()
         roof = gemv_roofline(dev, peak, kind)
+        roof_gemm = gemm_roofline(dev)
         cpu = None
         if world == 1:      # the CPU leg is timed at N=1 only
             sec_layer, threads, reps = cpu_layer_seconds()
@@ -340,7 +400,7 @@ def run_ours(args, rank, world, local_rank):
                 "e2e": {"value": streams * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
                         "d2h_bytes_per_step": H * 2},
                 "gpu_launches": args.steps * layers * 10,
-                "roofline": roof,
+                "roofline": roof, "roofline_gemm": roof_gemm,
                 "cpu_baseline": cpu,
                 "clocks": clocks, "kernel_self_check": err}
         print(json.dumps(line), flush=True)
@@ -366,6 +426,9 @@ def main():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the grouped dequant-GEMV roofline case (small enough for an ncu capture)")
+    ap.add_argument("--gemm-only", action="store_true",
+                    help="time only the grouped tcgen05 dequant-GEMM roofline case (small enough for an ncu capture)")
+    ap.add_argument("--rows", type=int, default=1024)
     ap.add_argument("--problems", type=int, default=240)
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--strong", action="store_true",
@@ -385,6 +448,13 @@ def main():
         peak, kind = measured_peak_gbs()
         print(json.dumps({"roofline": gemv_roofline(torch.device("cuda:0"), peak, kind, P=args.problems,
                                                      iters=max(1, args.steps))}), flush=True)
+        return
+    if args.gemm_only:
+        from glorcq_b200 import _build
+        _build.build()
+        P = args.problems if args.problems != 240 else 8
+        print(json.dumps({"roofline_gemm": gemm_roofline(torch.device("cuda:0"), P=P, rows=args.rows,
+                                                          iters=max(1, args.steps))}), flush=True)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -49,7 +49,8 @@ class MoeDesc(C.Structure):
                 ("dense0_rows", C.c_int32), ("sh_a_row", C.c_int32),
                 ("sh_gate_up", Weight), ("sh_down", Weight),
                 ("sh_ut_gate", vp), ("sh_ut_up", vp), ("sh_ut_down", vp),
-                ("rot_in", vp), ("rot_mid", vp), ("sh_rot_mid", vp)]
+                ("rot_in", vp), ("rot_mid", vp), ("sh_rot_mid", vp),
+                ("rht_in", vp), ("rht_mid", vp), ("sh_rht_mid", vp)]
 
 
 class MoeEp(C.Structure):
@@ -81,6 +82,7 @@ _SIGS = {
     "glq_pack_f16": (C.c_int, [vp, C.c_long, C.c_long, C.c_int, C.c_int, vp, vp]),
     "glq_dequant_tiled": (C.c_int, [C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
     "glq_debug_error": (C.c_int, [vp, C.c_int]),
+    "glq_rht_forward": (C.c_int, [vp, C.c_int, C.c_int64, vp, C.c_int, C.c_int, C.c_float, vp, C.c_int, C.c_int64, vp]),
     "glq_mm_workspace_bytes": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_mm_counters": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_grouped_matmul": (C.c_int, [C.POINTER(MMArgs), vp]),

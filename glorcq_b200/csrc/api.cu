@@ -869,6 +869,34 @@ extern "C" int glq_dequant_tiled(int fmt, const void* tiled, const float* norms_
 // First bounds violation recorded by a self-checking kernel: {code, index, limit, block<<32|thread};
 // all zero when there was none.  Synchronises the device.
 // ---------------------------------------------------------------------------------------------
+// ---------------------------------------------------------------------------------------------
+// randomized Hadamard rotation
+// ---------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+static int launch_rht(const void* x, int64_t ldx, const float* signs, int rows, int d, int n, float scale, void* y,
+                      int64_t ldy, cudaStream_t st) {
+    const size_t smem = (size_t)n * sizeof(float);
+    auto kern = rht_kernel<TI, TO>;
+    if (smem > 48 * 1024) GLQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<rows, 256, smem, st>>>(reinterpret_cast<const TI*>(x), ldx, signs, d, n, scale, reinterpret_cast<TO*>(y), ldy);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+extern "C" int glq_rht_forward(const void* x, int x_is_f32, int64_t ldx, const float* signs, int rows, int d, float scale,
+                               void* y, int y_is_f32, int64_t ldy, void* stream) {
+    if (!x || !y || !signs || rows < 0 || d <= 0) return GLQ_ERR_ARG;
+    if (rows == 0) return GLQ_OK;
+    int n = 1;
+    while (n < d) n <<= 1;
+    if (n > 32768) return GLQ_ERR_UNSUPPORTED;       // n floats of shared memory per row
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (x_is_f32 && y_is_f32) return launch_rht<float, float>(x, ldx, signs, rows, d, n, scale, y, ldy, st);
+    if (!x_is_f32 && !y_is_f32) return launch_rht<__half, __half>(x, ldx, signs, rows, d, n, scale, y, ldy, st);
+    if (x_is_f32) return launch_rht<float, __half>(x, ldx, signs, rows, d, n, scale, y, ldy, st);
+    return launch_rht<__half, float>(x, ldx, signs, rows, d, n, scale, y, ldy, st);
+}
+
 extern "C" int glq_debug_error(unsigned long long* out4, int clear) {
     if (!out4) return GLQ_ERR_ARG;
     GLQ_CUDA(cudaMemcpyFromSymbol(out4, g_glq_err, 4 * sizeof(unsigned long long)));

@@ -215,4 +215,29 @@ __global__ void __launch_bounds__(kThreads) gptq_i8_kernel(const float* __restri
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Randomized Hadamard rotation: y = scale * H_n * (signs . x) over one row, H_n the Sylvester-ordered
+// Walsh-Hadamard matrix of the next power of two n >= d; the input is zero-padded to n and the first d
+// outputs are kept.  One CTA per row; the butterflies run in fp32 in shared memory (n floats).
+// ---------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) rht_kernel(const TI* __restrict__ x, long long ldx, const float* __restrict__ signs,
+                                                  int d, int n, float scale, TO* __restrict__ y, long long ldy) {
+    extern __shared__ float rht_buf[];
+    const TI* xr = x + (size_t)blockIdx.x * ldx;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) rht_buf[i] = i < d ? (float)xr[i] * __ldg(signs + i) : 0.f;
+    __syncthreads();
+    for (int h = 1; h < n; h <<= 1) {
+        for (int p = threadIdx.x; p < (n >> 1); p += blockDim.x) {
+            const int i = ((p / h) * 2 * h) + (p % h);
+            const float a = rht_buf[i], b = rht_buf[i + h];
+            rht_buf[i] = a + b;
+            rht_buf[i + h] = a - b;
+        }
+        __syncthreads();
+    }
+    TO* yr = y + (size_t)blockIdx.x * ldy;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) yr[i] = (TO)(rht_buf[i] * scale);
+}
+
 }  // namespace glq

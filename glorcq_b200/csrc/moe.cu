@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 
 #include "glq_common.cuh"
@@ -72,9 +73,9 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
         L.bs = take((size_t)n * R * 2);
         L.ysh = take((size_t)n * d->H * 2);
     }
-    if (d->rot_in) L.xr = take((size_t)n * d->H * 2);
-    if (d->rot_mid) L.hr = take(nk * d->I * 2);
-    if (d->sh_rot_mid && d->I_shared > 0) L.hsr = take((size_t)n * d->I_shared * 2);
+    if (d->rot_in || d->rht_in) L.xr = take((size_t)n * d->H * 2);
+    if (d->rot_mid || d->rht_mid) L.hr = take(nk * d->I * 2);
+    if ((d->sh_rot_mid || d->sh_rht_mid) && d->I_shared > 0) L.hsr = take((size_t)n * d->I_shared * 2);
     // scratch / counters of the matmul calls: they run one after the other, so they share
     const int P = (int)std::min<size_t>(nk, (size_t)d->E);
     glq_mm_args_t m;
@@ -355,7 +356,10 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     };
     int rc;
     // y = x . Pi^T for a tiled dense Pi (rows x dim -> rows x dim)
-    auto rotate = [&](const void* pi_t, const void* src, int rows, int dim, void* dst) {
+    auto rotate = [&](const void* pi_t, const float* signs, const void* src, int rows, int dim, void* dst) {
+        if (signs)
+            return glq_rht_forward(src, 0, dim, signs, rows, dim, 1.0f / sqrtf((float)dim), dst, 0, dim,
+                                   on_aux && forked ? aux_stream : stream);
         set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, rows, dim, dim, 0);
         m.w.codes = pi_t;
         m.w.N = dim;
@@ -367,8 +371,8 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         return finish(m);
     };
     const void* xq = x;  // input of the quantized gate/up products
-    if (d->rot_in) {
-        if ((rc = rotate(d->rot_in, x, n, d->H, ws + L.xr)) != GLQ_OK) return rc;
+    if (d->rot_in || d->rht_in) {
+        if ((rc = rotate(d->rot_in, d->rht_in, x, n, d->H, ws + L.xr)) != GLQ_OK) return rc;
         xq = ws + L.xr;
     }
 
@@ -451,9 +455,9 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     }
     // 6. down projection, scaled by the routing weight
     const void* hq = ws + L.h;
-    if (d->rot_mid) {
+    if (d->rot_mid || d->rht_mid) {
         // rotates every entry row (rows beyond the live entries hold stale but finite data)
-        if ((rc = rotate(d->rot_mid, ws + L.h, nk, d->I, ws + L.hr)) != GLQ_OK) return rc;
+        if ((rc = rotate(d->rot_mid, d->rht_mid, ws + L.h, nk, d->I, ws + L.hr)) != GLQ_OK) return rc;
         hq = ws + L.hr;
     }
     set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, R, nk);
@@ -525,8 +529,8 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
             if ((rc = finish(m)) != GLQ_OK) return rc;
         }
         const void* hsq = ws + L.hs;
-        if (d->sh_rot_mid) {
-            if ((rc = rotate(d->sh_rot_mid, ws + L.hs, n, d->I_shared, ws + L.hsr)) != GLQ_OK) return rc;
+        if (d->sh_rot_mid || d->sh_rht_mid) {
+            if ((rc = rotate(d->sh_rot_mid, d->sh_rht_mid, ws + L.hs, n, d->I_shared, ws + L.hsr)) != GLQ_OK) return rc;
             hsq = ws + L.hsr;
         }
         set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, 1, n, d->H, d->I_shared, lr ? R : 0);

@@ -25,7 +25,7 @@
 namespace glq {
 
 constexpr int kTcFeat = 128;          // output features per CTA (UMMA M)
-constexpr int kTcProducers = 8;       // producer (and epilogue) warps
+constexpr int kTcProducers = 16;      // producer (and epilogue) warps: 8 tiles of 16 rows x 2 row halves
 constexpr int kTcThreads = (kTcProducers + 2) * 32;
 
 struct TcParams {
@@ -259,10 +259,12 @@ struct TcAffine {
         z2 = __half2half2(zh);
         zc = __hadd2(z2, koff);
     }
-    __device__ __forceinline__ uint32_t operator()(uint32_t h) const {
-        const __half2 hv = *reinterpret_cast<const __half2*>(&h);
-        const __half2 d = integral ? __hsub2(hv, zc) : __hsub2(__hsub2(hv, koff), z2);
-        const __half2 v = __hmul2(d, s2);
+    __device__ __forceinline__ uint32_t exact(uint32_t h) const {
+        const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&h), zc), s2);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    __device__ __forceinline__ uint32_t general(uint32_t h) const {
+        const __half2 v = __hmul2(__hsub2(__hsub2(*reinterpret_cast<const __half2*>(&h), koff), z2), s2);
         return *reinterpret_cast<const uint32_t*>(&v);
     }
 };
@@ -311,18 +313,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
 
     if (warp < kTcProducers) {
         // ================= producers: the weight operand =================
+        // warp = (row half, 16-row tile): lane (g, t) owns row 8*hrow + g of tile `warp & 7`
         const int g = lane >> 2, t = lane & 3;
-        const int tile16 = ft * 8 + warp;                       // 16-row tile of the matrix (of gate and of up)
+        const int hrow = warp >> 3;
+        const int tile16 = ft * 8 + (warp & 7);                 // 16-row tile of the matrix (of gate and of up)
         constexpr int NM = SW ? 2 : 1;
         const int ntiles16 = (N + 15) / 16;
         const bool live = tile16 < ntiles16;                    // tiles past the matrix contribute zero rows
-        // blocks of the tiled layouts per 128-channel stage, 16-byte loads per lane and block
+        // blocks of the tiled layouts per 128-channel stage, 32-bit words per lane, row and block
         constexpr int BPS = (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) ? 1 : 2;
-        constexpr int LPB = FMT == GLQ_FMT_F16 ? 4 : 1;
+        constexpr int WPB = FMT == GLQ_FMT_F16 ? 8 : 2;
         constexpr int BB = FMT == GLQ_FMT_T2 ? 512 : 576;
-        constexpr int REGS = NM * BPS * (LPB * 4 + (AFFINE ? 2 : 0));
-        constexpr int D = REGS <= 12 ? 4 : (REGS <= 32 ? 2 : 1);   // register prefetch depth (stages)
-        const int nblk = FMT == GLQ_FMT_F16 ? (p.K + 63) / 64 : (FMT == GLQ_FMT_Q4 ? (p.K + 63) / 64 : p.nkb);
+        constexpr int REGS = NM * BPS * (WPB + (AFFINE ? 1 : 0));
+        constexpr int D = REGS <= 6 ? 4 : (REGS <= 16 ? 2 : 1);    // register prefetch depth (stages)
+        const int nblk = (FMT == GLQ_FMT_F16 || FMT == GLQ_FMT_Q4) ? (p.K + 63) / 64 : p.nkb;
         const unsigned char* blk[NM];
 #pragma unroll
         for (int m = 0; m < NM; ++m) {
@@ -339,9 +343,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
 #pragma unroll
             for (int m = 0; m < NM; ++m) make_t2_tables(W.centroids + 4 * m, TL[m], TH[m]);
         }
-        uint4 cq[D][NM][BPS][LPB];
-        uint2 csz[D][NM][BPS];
-        auto fetch = [&](int st, uint4 (&q)[NM][BPS][LPB], uint2 (&z)[NM][BPS]) {
+        uint32_t cq[D][NM][BPS][WPB];
+        uint32_t csz[D][NM][BPS];
+        auto fetch = [&](int st, uint32_t (&q)[NM][BPS][WPB], uint32_t (&z)[NM][BPS]) {
 #pragma unroll
             for (int m = 0; m < NM; ++m)
 #pragma unroll
@@ -349,14 +353,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                     const int kb = st * BPS + b;
                     const bool in = live && st < p.nkb && kb < nblk;
                     if constexpr (FMT == GLQ_FMT_F16) {
-                        const uint4* src = reinterpret_cast<const uint4*>(blk[m] + (size_t)kb * 2048) + lane;
+                        // fragment (ks, lane): words 0,2 = row g (channels 2t,2t+1 | 2t+8,2t+9), words 1,3 = row g+8
+                        const uint32_t* src = reinterpret_cast<const uint32_t*>(blk[m] + (size_t)kb * 2048) + lane * 4 + hrow;
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) q[m][b][ks] = in ? __ldg(src + 32 * ks) : make_uint4(0, 0, 0, 0);
+                        for (int ks = 0; ks < 4; ++ks) {
+                            q[m][b][2 * ks] = in ? __ldg(src + 128 * ks) : 0u;
+                            q[m][b][2 * ks + 1] = in ? __ldg(src + 128 * ks + 2) : 0u;
+                        }
                     } else {
+                        // words 0,1 of the lane's 16 bytes = row g, words 2,3 = row g + 8
                         const unsigned char* src = blk[m] + (size_t)kb * 2 * BB;
-                        q[m][b][0] = in ? __ldg(reinterpret_cast<const uint4*>(src) + lane) : make_uint4(0, 0, 0, 0);
-                        if constexpr (AFFINE)
-                            z[m][b] = in ? __ldg(reinterpret_cast<const uint2*>(src + 512) + g) : make_uint2(0, 0);
+                        const uint2 v = in ? __ldg(reinterpret_cast<const uint2*>(src) + 2 * lane + hrow) : make_uint2(0, 0);
+                        q[m][b][0] = v.x;
+                        q[m][b][1] = v.y;
+                        if constexpr (AFFINE) z[m][b] = in ? __ldg(reinterpret_cast<const uint32_t*>(src + 512) + 2 * g + hrow) : 0u;
                     }
                 }
         };
@@ -365,8 +375,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
 
         int s = 0;
         uint32_t ph = 0;
-        // this lane's rows of the A tile: g and g + 8 of the warp's 16; swizzle key (row & 7) = g
-        const uint32_t row_off = (uint32_t)(warp * 16 + g) * 128u;
+        // this lane's row of the A tile; its swizzle key (row & 7) is g
+        const uint32_t row_off = (uint32_t)((warp & 7) * 16 + hrow * 8 + g) * 128u;
         for (int st0 = 0; st0 < nst; st0 += D) {
 #pragma unroll
             for (int d = 0; d < D; ++d) {
@@ -379,80 +389,94 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                         for (int m = 0; m < NM; ++m) {
                             const uint32_t mbase = abase + (uint32_t)m * (kTcFeat * 256) + row_off;
                             if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) {
-                                // lane t holds channels 32t .. 32t+31 of the stage: atom t/2, chunks 4(t%2) .. +3
-#pragma unroll
-                                for (int hrow = 0; hrow < 2; ++hrow) {
-                                    const uint4 q = cq[d][m][0][0];
-                                    uint32_t o[16];
-                                    if constexpr (FMT == GLQ_FMT_Q2) {
-                                        const TcAffine af(hrow ? csz[d][m][0].y : csz[d][m][0].x, 1024.f);
-#pragma unroll
-                                        for (int wi = 0; wi < 2; ++wi) {
-                                            const uint32_t w = hrow ? (wi ? q.w : q.z) : (wi ? q.y : q.x);
-#pragma unroll
-                                            for (int j = 0; j < 8; ++j)
-                                                o[wi * 8 + j] = af(and_or(w >> (2 * j), 0x00030003u, 0x64006400u));
-                                        }
-                                    } else {
-                                        uint32_t h0[8], h1[8];
-                                        unpack_t2(hrow ? q.z : q.x, TL[m], TH[m], h0);
-                                        unpack_t2(hrow ? q.w : q.y, TL[m], TH[m], h1);
+                                // lane t holds channels 32t .. 32t+31 of the stage: atom t/2, chunks 4(t%2) .. +3.
+                                // Lanes of atom 1 take their two words in the other order, so that the lanes
+                                // of one store instruction that differ only in the atom hit different banks.
+                                const bool flip = (t >> 1) != 0;
+                                const uint32_t wa = flip ? cq[d][m][0][1] : cq[d][m][0][0];
+                                const uint32_t wb = flip ? cq[d][m][0][0] : cq[d][m][0][1];
+                                uint32_t o[16];
+                                if constexpr (FMT == GLQ_FMT_Q2) {
+                                    const TcAffine af(csz[d][m][0], 1024.f);
+                                    if (af.integral) {
 #pragma unroll
                                         for (int j = 0; j < 8; ++j) {
-                                            o[j] = h0[j];
-                                            o[8 + j] = h1[j];
+                                            o[j] = af.exact(and_or(wa >> (2 * j), 0x00030003u, 0x64006400u));
+                                            o[8 + j] = af.exact(and_or(wb >> (2 * j), 0x00030003u, 0x64006400u));
+                                        }
+                                    } else {
+#pragma unroll
+                                        for (int j = 0; j < 8; ++j) {
+                                            o[j] = af.general(and_or(wa >> (2 * j), 0x00030003u, 0x64006400u));
+                                            o[8 + j] = af.general(and_or(wb >> (2 * j), 0x00030003u, 0x64006400u));
                                         }
                                     }
-                                    const uint32_t base = mbase + (uint32_t)(t >> 1) * (kTcFeat * 128) + (uint32_t)hrow * (8 * 128);
+                                } else {
+                                    uint32_t h0[8], h1[8];
+                                    unpack_t2(wa, TL[m], TH[m], h0);
+                                    unpack_t2(wb, TL[m], TH[m], h1);
 #pragma unroll
-                                    for (int c = 0; c < 4; ++c) {
-                                        const uint32_t chunk = (uint32_t)((4 * (t & 1) + c) ^ g);
-                                        sts128(base + chunk * 16u, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                                    for (int j = 0; j < 8; ++j) {
+                                        o[j] = h0[j];
+                                        o[8 + j] = h1[j];
                                     }
+                                }
+                                const uint32_t base = mbase + (uint32_t)(t >> 1) * (kTcFeat * 128);
+                                const uint32_t fx = flip ? 2u : 0u;
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) {
+                                    const uint32_t chunk = ((uint32_t)(4 * (t & 1) + c) ^ fx) ^ (uint32_t)g;
+                                    sts128(base + chunk * 16u, o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
                                 }
                             } else if constexpr (FMT == GLQ_FMT_Q4) {
                                 // block b = atom b; lane t holds channels 16t .. 16t+15 of it: chunks 2t, 2t+1
 #pragma unroll
-                                for (int b = 0; b < 2; ++b)
-#pragma unroll
-                                    for (int hrow = 0; hrow < 2; ++hrow) {
-                                        const uint4 q = cq[d][m][b][0];
-                                        const TcAffine af(hrow ? csz[d][m][b].y : csz[d][m][b].x, kQ4Offset);
-                                        uint32_t h0[4], h1[4];
-                                        unpack_q4(hrow ? q.z : q.x, h0);
-                                        unpack_q4(hrow ? q.w : q.y, h1);
-                                        const uint32_t base = mbase + (uint32_t)b * (kTcFeat * 128) + (uint32_t)hrow * (8 * 128);
-                                        sts128(base + (uint32_t)((2 * t) ^ g) * 16u, af(h0[0]), af(h0[1]), af(h0[2]), af(h0[3]));
-                                        sts128(base + (uint32_t)((2 * t + 1) ^ g) * 16u, af(h1[0]), af(h1[1]), af(h1[2]), af(h1[3]));
+                                for (int b = 0; b < 2; ++b) {
+                                    const TcAffine af(csz[d][m][b], kQ4Offset);
+                                    uint32_t h0[4], h1[4];
+                                    unpack_q4(cq[d][m][b][0], h0);
+                                    unpack_q4(cq[d][m][b][1], h1);
+                                    const uint32_t base = mbase + (uint32_t)b * (kTcFeat * 128);
+                                    if (af.integral) {
+                                        sts128(base + (uint32_t)((2 * t) ^ g) * 16u, af.exact(h0[0]), af.exact(h0[1]), af.exact(h0[2]),
+                                               af.exact(h0[3]));
+                                        sts128(base + (uint32_t)((2 * t + 1) ^ g) * 16u, af.exact(h1[0]), af.exact(h1[1]),
+                                               af.exact(h1[2]), af.exact(h1[3]));
+                                    } else {
+                                        sts128(base + (uint32_t)((2 * t) ^ g) * 16u, af.general(h0[0]), af.general(h0[1]),
+                                               af.general(h0[2]), af.general(h0[3]));
+                                        sts128(base + (uint32_t)((2 * t + 1) ^ g) * 16u, af.general(h1[0]), af.general(h1[1]),
+                                               af.general(h1[2]), af.general(h1[3]));
                                     }
+                                }
                             } else {
-                                // dense fp16 fragments: block b = atom b; (ks, lane) holds, per row, channels
-                                // 16ks + {2t, 2t+1, 2t+8, 2t+9}: 8 bytes at chunk 2ks + t/2, half t%2
+                                // dense fp16 fragments: block b = atom b; (ks, lane) holds channels
+                                // 16ks + {2t, 2t+1, 2t+8, 2t+9} of its row: 8 bytes at chunk 2ks + t/2, half t%2
 #pragma unroll
                                 for (int b = 0; b < 2; ++b)
 #pragma unroll
                                     for (int ks = 0; ks < 4; ++ks) {
-                                        const uint4 q = cq[d][m][b][ks];
-                                        const uint32_t base = mbase + (uint32_t)b * (kTcFeat * 128) +
-                                                              (uint32_t)((2 * ks + (t >> 1)) ^ g) * 16u + (uint32_t)(t & 1) * 8u;
-                                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(base), "r"(q.x), "r"(q.z) : "memory");
-                                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(base + 8 * 128), "r"(q.y), "r"(q.w)
+                                        const uint32_t a = mbase + (uint32_t)b * (kTcFeat * 128) +
+                                                           (uint32_t)((2 * ks + (t >> 1)) ^ g) * 16u + (uint32_t)(t & 1) * 8u;
+                                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(cq[d][m][b][2 * ks]),
+                                                     "r"(cq[d][m][b][2 * ks + 1])
                                                      : "memory");
                                     }
                             }
                         }
                         fetch(st + D, cq[d], csz[d]);
                     } else if (ok) {
-                        // low-rank stage: rows of the packed SV slice -> atom 0 of the A buffer
+                        // low-rank stage: rows of the packed SV slice -> atom 0 of the A buffer;
+                        // four lanes per row, two 16-byte chunks each
                         const int sl = st - p.nkb;
 #pragma unroll
                         for (int m = 0; m < NM; ++m) {
                             const int dt = SW ? tile16 * 2 + m : tile16;
-                            const int r = lane >> 1, hb = lane & 1;       // row of the tile, 64-byte half of its 128 B
+                            const int r = hrow * 8 + g;                   // row of the tile
                             const uint4* src = reinterpret_cast<const uint4*>(
                                 reinterpret_cast<const unsigned char*>(W.sv) +
-                                ((((size_t)(dt >> 1) * p.ns + sl) * 32) + (dt & 1) * 16 + r) * 128 + hb * 64);
-                            const uint32_t base = abase + (uint32_t)m * (kTcFeat * 256) + (uint32_t)(warp * 16 + r) * 128u;
+                                ((((size_t)(dt >> 1) * p.ns + sl) * 32) + (dt & 1) * 16 + r) * 128 + t * 32);
+                            const uint32_t base = abase + (uint32_t)m * (kTcFeat * 256) + row_off;
                             // codebook format: the accumulator is scaled by the row norm in the epilogue,
                             // so the low-rank rows go in divided by it
                             float inv = 1.f;
@@ -463,7 +487,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                                 }
                             }
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
+                            for (int c = 0; c < 2; ++c) {
                                 uint4 v = make_uint4(0, 0, 0, 0);
                                 if (live) v = __ldg(src + c);
                                 if constexpr (FMT == GLQ_FMT_T2) {
@@ -474,7 +498,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                                         hp[i] = __floats2half2_rn(f2.x * inv, f2.y * inv);
                                     }
                                 }
-                                const uint32_t chunk = (uint32_t)((4 * hb + c) ^ (r & 7));
+                                const uint32_t chunk = (uint32_t)((2 * t + c) ^ g);
                                 sts128(base + chunk * 16u, v.x, v.y, v.z, v.w);
                             }
                         }
@@ -493,7 +517,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
         // ================= epilogue: TMEM -> registers -> global =================
         const bool acc_ok = tc_wait(bar_acc, 0, dead, 101);
         tc_fence_after();
-        const int q = warp & 3, half = warp >> 2;
+        const int q = warp & 3, part = warp >> 2;      // TMEM lane quarter, quarter of the token columns
         const int f = ft * kTcFeat + q * 32 + lane;
         const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
         const __half* bias = reinterpret_cast<const __half*>(W.bias);
@@ -506,7 +530,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
                 if (SW) nrm_u = __ldg(W.norms + (size_t)(2 * t16 + 1) * 16 + r16);
             }
         }
-        for (int c0 = half * (TN / 2); c0 < (half + 1) * (TN / 2); c0 += 16) {
+        for (int c0 = part * (TN / 4); c0 < (part + 1) * (TN / 4); c0 += 16) {
             uint32_t vg[16], vu[16];
             tc_ld16(trow + (uint32_t)c0, vg);
             if (SW) tc_ld16(trow + (uint32_t)(TN + c0), vu);

@@ -1,0 +1,231 @@
+"""A decoder assembled from the quantized layers: the host model the reference borrows from
+transformers (inference/model_builder.py:234-243 instantiates ``AutoModelForCausalLM`` and swaps its
+linear layers; inference/graph_wrapper.py:84-127 calls it with ``input_ids, cache_position,
+past_key_values, use_cache, return_dict``).  It is written here so that the path does not depend on
+the transformers version: RMSNorm, rotary embedding, grouped-query attention over a static key/value
+cache, and per layer either a ``GraphCompatibleMoeBlock`` or a dense SwiGLU MLP, all built from
+``GLoRCQLinear`` modules.  Covers the Qwen2-MoE (shared expert, optional top-k renormalisation),
+Mixtral (w1/w3/w2 naming, top-2 renormalised, no shared expert) and Qwen3-MoE (per-head q/k norms, no
+shared expert) layouts.
+
+The quantized projections and the MoE block run on this package's kernels.  Norms, rotary embedding,
+the attention core (``scaled_dot_product_attention`` over the static cache with a position mask),
+embedding lookup and the fp16 ``lm_head`` product are plain library calls: small or dense-fp16 work
+outside the quantized path.
+"""
+
+from __future__ import annotations
+
+from types import SimpleNamespace
+from typing import Dict, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .moe_block import GraphCompatibleMoeBlock
+from .quantized_linear import GLoRCQLinear
+
+
+class StaticKVCache:
+    """Fixed-size key/value cache, one (B, kv_heads, max_len, head_dim) pair per layer: the role of
+    transformers' StaticCache in inference/graph_wrapper.py:41-47 (``reset`` included)."""
+
+    def __init__(self, config, max_batch_size, max_cache_len, device, dtype=torch.float16):
+        c = config
+        self.max_batch_size, self.max_cache_len = max_batch_size, max_cache_len
+        shape = (c.num_hidden_layers, max_batch_size, c.num_key_value_heads, max_cache_len, c.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+
+    def reset(self):
+        self.k.zero_()
+        self.v.zero_()
+
+    def update(self, layer, k_new, v_new, cache_position):
+        """Write (B, kv_heads, T, D) at positions cache_position (T,) and return the layer's full buffers."""
+        b = k_new.shape[0]
+        self.k[layer, :b].index_copy_(2, cache_position, k_new)
+        self.v[layer, :b].index_copy_(2, cache_position, v_new)
+        return self.k[layer, :b], self.v[layer, :b]
+
+
+def _rope_tables(head_dim, max_len, theta, device):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    freqs = torch.outer(torch.arange(max_len, device=device, dtype=torch.float32), inv)
+    emb = torch.cat([freqs, freqs], dim=-1)
+    return emb.cos().half(), emb.sin().half()
+
+
+def _rotate_half(x):
+    h = x.shape[-1] // 2
+    return torch.cat([-x[..., h:], x[..., :h]], dim=-1)
+
+
+class _Attention(nn.Module):
+    def __init__(self, cfg, layer_idx, mods: Dict[str, GLoRCQLinear], dense, prefix, device):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        self.q_proj, self.k_proj = mods["self_attn.q_proj"], mods["self_attn.k_proj"]
+        self.v_proj, self.o_proj = mods["self_attn.v_proj"], mods["self_attn.o_proj"]
+        for nm, lin in (("q_proj", self.q_proj), ("k_proj", self.k_proj), ("v_proj", self.v_proj)):
+            b = dense.get(f"{prefix}.self_attn.{nm}.bias")
+            if b is not None:
+                lin.set_bias(b.to(device))
+        self.q_norm = dense.get(f"{prefix}.self_attn.q_norm.weight")
+        self.k_norm = dense.get(f"{prefix}.self_attn.k_norm.weight")
+        if self.q_norm is not None:
+            self.q_norm, self.k_norm = self.q_norm.to(device).half(), self.k_norm.to(device).half()
+
+    def forward(self, x, cache_position, cache: StaticKVCache, cos, sin):
+        c = self.cfg
+        B, T, _ = x.shape
+        q = self.q_proj(x).view(B, T, c.num_attention_heads, c.head_dim)
+        k = self.k_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
+        v = self.v_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
+        if self.q_norm is not None:
+            q = F.rms_norm(q, (c.head_dim,), self.q_norm, c.rms_norm_eps)
+            k = F.rms_norm(k, (c.head_dim,), self.k_norm, c.rms_norm_eps)
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        cs, sn = cos[cache_position][None, None], sin[cache_position][None, None]
+        q = q * cs + _rotate_half(q) * sn
+        k = k * cs + _rotate_half(k) * sn
+        k_all, v_all = cache.update(self.layer_idx, k, v, cache_position)
+        # position mask over the whole static cache: key j is visible to query t when j <= position(t)
+        mask = torch.arange(cache.max_cache_len, device=x.device)[None, :] <= cache_position[:, None]
+        y = F.scaled_dot_product_attention(q, k_all, v_all, attn_mask=mask[None, None],
+                                           enable_gqa=c.num_key_value_heads != c.num_attention_heads)
+        return self.o_proj(y.transpose(1, 2).reshape(B, T, c.num_attention_heads * c.head_dim))
+
+
+class _DenseMLP(nn.Module):
+    def __init__(self, gate, up, down):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate, up, down
+        self.act_fn = F.silu
+
+    def forward(self, x):
+        return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+
+
+class _Expert(nn.Module):
+    def __init__(self, gate, up, down):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = gate, up, down
+        self.act_fn = F.silu
+
+
+def _config(hf: dict):
+    c = SimpleNamespace(**hf)
+    c.num_key_value_heads = hf.get("num_key_value_heads") or hf["num_attention_heads"]
+    c.head_dim = hf.get("head_dim") or hf["hidden_size"] // hf["num_attention_heads"]
+    c.rms_norm_eps = hf.get("rms_norm_eps", 1e-6)
+    c.rope_theta = hf.get("rope_theta", 10000.0)
+    c.num_experts = hf.get("num_experts", hf.get("num_local_experts", 0))
+    c.num_experts_per_tok = hf.get("num_experts_per_tok", 0)
+    mixtral = "num_local_experts" in hf
+    c.norm_topk_prob = True if mixtral else hf.get("norm_topk_prob", False)
+    c.moe_prefix = "block_sparse_moe" if mixtral else "mlp"
+    c.expert_names = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+    c.max_position_embeddings = hf.get("max_position_embeddings", 4096)
+    return c
+
+
+class GLoRCQDecoder(nn.Module):
+    """``layers``: {layer_idx: {module_name: GLoRCQLinear}} from ``model_builder.build_layers``.
+    ``dense``: fp16 tensors under their state-dict names (model.embed_tokens.weight,
+    model.layers.N.input_layernorm.weight, model.layers.N.post_attention_layernorm.weight,
+    model.layers.N.mlp.gate.weight, model.layers.N.mlp.shared_expert_gate.weight, model.norm.weight,
+    lm_head.weight, attention biases and q/k norms); what is missing is zero, as the reference's loader
+    leaves every parameter it does not replace (inference/model_builder.py:314-330, 431-447)."""
+
+    def __init__(self, hf_config: dict, layers, dense: Optional[dict] = None, device="cuda:0"):
+        super().__init__()
+        c = self.config = _config(hf_config)
+        dense = dense or {}
+        dev = torch.device(device)
+        H = c.hidden_size
+
+        def dense_param(name, shape):
+            t = dense.get(name)
+            if t is None:
+                t = torch.zeros(shape, dtype=torch.float16)
+            return nn.Parameter(t.to(dev).half(), requires_grad=False)
+
+        self.embed_tokens = dense_param("model.embed_tokens.weight", (c.vocab_size, H))
+        self.norm = dense_param("model.norm.weight", (H,))
+        lm = dense.get("lm_head.weight")
+        self.lm_head = self.embed_tokens if lm is None else nn.Parameter(lm.to(dev).half(), requires_grad=False)
+        self.ln1, self.ln2 = nn.ParameterList(), nn.ParameterList()
+        self.attn, self.mlp = nn.ModuleList(), nn.ModuleList()
+        for l in range(c.num_hidden_layers):
+            mods = layers[l]
+            pre = f"model.layers.{l}"
+            self.ln1.append(dense_param(f"{pre}.input_layernorm.weight", (H,)))
+            self.ln2.append(dense_param(f"{pre}.post_attention_layernorm.weight", (H,)))
+            self.attn.append(_Attention(c, l, mods, dense, pre, dev))
+            mp, (gn, un, dn) = c.moe_prefix, c.expert_names
+            if f"{mp}.experts.0.{gn}" in mods:
+                blk = SimpleNamespace()
+                blk.num_experts, blk.top_k, blk.norm_topk_prob = c.num_experts, c.num_experts_per_tok, c.norm_topk_prob
+                blk.gate = nn.Linear(H, c.num_experts, bias=False, device=dev, dtype=torch.float16)
+                blk.gate.weight.data.copy_(dense_param(f"{pre}.{mp}.gate.weight", (c.num_experts, H)))
+                blk.experts = nn.ModuleList([_Expert(mods[f"{mp}.experts.{e}.{gn}"], mods[f"{mp}.experts.{e}.{un}"],
+                                                     mods[f"{mp}.experts.{e}.{dn}"]) for e in range(c.num_experts)])
+                if f"{mp}.shared_expert.gate_proj" in mods:
+                    blk.shared_expert = _Expert(mods[f"{mp}.shared_expert.gate_proj"], mods[f"{mp}.shared_expert.up_proj"],
+                                                mods[f"{mp}.shared_expert.down_proj"])
+                    blk.shared_expert_gate = nn.Linear(H, 1, bias=False, device=dev, dtype=torch.float16)
+                    blk.shared_expert_gate.weight.data.copy_(dense_param(f"{pre}.{mp}.shared_expert_gate.weight", (1, H)))
+                else:
+                    blk.shared_expert, blk.shared_expert_gate = None, None
+                moe = GraphCompatibleMoeBlock(blk)
+                moe.prepare(dev, release_linear_tiles=True)
+                self.mlp.append(moe)
+            else:
+                self.mlp.append(_DenseMLP(mods["mlp.gate_proj"], mods["mlp.up_proj"], mods["mlp.down_proj"]))
+        self._rope = None
+        self._own_cache = None
+
+    def _tables(self, need, device):
+        if self._rope is None or self._rope[0].shape[0] < need:
+            n = max(need, self.config.max_position_embeddings)
+            self._rope = _rope_tables(self.config.head_dim, n, self.config.rope_theta, device)
+        return self._rope
+
+    def forward(self, input_ids=None, cache_position=None, past_key_values=None, use_cache=True, return_dict=False,
+                **_unused):
+        c = self.config
+        B, T = input_ids.shape
+        if past_key_values is None:
+            if self._own_cache is None or self._own_cache.max_batch_size < B:
+                self._own_cache = StaticKVCache(c, B, c.max_position_embeddings, input_ids.device)
+            past_key_values = self._own_cache
+        if cache_position is None:
+            cache_position = torch.arange(T, device=input_ids.device)
+        cos, sin = self._tables(past_key_values.max_cache_len, input_ids.device)
+        x = F.embedding(input_ids, self.embed_tokens)
+        for l in range(c.num_hidden_layers):
+            h = F.rms_norm(x, (c.hidden_size,), self.ln1[l], c.rms_norm_eps)
+            x = x + self.attn[l](h, cache_position, past_key_values, cos, sin)
+            h = F.rms_norm(x, (c.hidden_size,), self.ln2[l], c.rms_norm_eps)
+            m = self.mlp[l](h)
+            x = x + (m[0] if isinstance(m, tuple) else m)
+        x = F.rms_norm(x, (c.hidden_size,), self.norm, c.rms_norm_eps)
+        logits = x @ self.lm_head.t()
+        return (logits, past_key_values)
+
+    @torch.no_grad()
+    def generate(self, input_ids, max_new_tokens=100, do_sample=False):
+        """Greedy generation without a graph (the comparison leg of run_speed_benchmark)."""
+        B, T = input_ids.shape
+        cache = StaticKVCache(self.config, B, T + max_new_tokens, input_ids.device)
+        logits = self(input_ids=input_ids, cache_position=torch.arange(T, device=input_ids.device), past_key_values=cache)[0]
+        out = input_ids
+        for i in range(max_new_tokens):
+            nxt = torch.argmax(logits[:, -1, :], dim=-1, keepdim=True)
+            out = torch.cat([out, nxt], dim=1)
+            if i + 1 < max_new_tokens:
+                pos = torch.full((1,), T + i, device=input_ids.device, dtype=torch.long)
+                logits = self(input_ids=nxt, cache_position=pos, past_key_values=cache)[0]
+        return out

@@ -165,8 +165,8 @@ class GraphCompatibleMoeBlock(nn.Module):
         self._keep += tabs
         # rotations of the codebook format
         if fmt == FMT_T2:
-            d.rot_in = self._rotation(g0, device)
-            d.rot_mid = self._rotation(d0, device)
+            d.rot_in, d.rht_in = self._rotation(g0, device)
+            d.rot_mid, d.rht_mid = self._rotation(d0, device)
         if has_shared:
             sg, su, sd = self.shared_expert.gate_proj, self.shared_expert.up_proj, self.shared_expert.down_proj
             for lin in (sg, su, sd):
@@ -183,24 +183,30 @@ class GraphCompatibleMoeBlock(nn.Module):
                 self._keep += uts
                 d.sh_ut_gate, d.sh_ut_up, d.sh_ut_down = (u.codes.data_ptr() for u in uts)
             if fmt == FMT_T2:
-                d.sh_rot_mid = self._rotation(sd, device)
+                d.sh_rot_mid, d.sh_rht_mid = self._rotation(sd, device)
         self._desc = d
         self._built = True
 
     def _rotation(self, lin, device):
-        """Tiled rotation matrix of a codebook-format layer (None if it has no rotation cache)."""
+        """(tiled rotation matrix, Hadamard sign vector) of a codebook-format layer: one of them is set, or
+        neither when the layer has no rotation.  Sign vectors (``_rht_signs``, attached by the loader for
+        rotation_type "hadamard", inference/model_builder.py:277-286) take precedence, as in the reference
+        block (inference/moe_block.py:349-351)."""
+        signs = getattr(lin, "_rht_signs", None)
+        if signs is not None:
+            sg = signs.to(device=device, dtype=torch.float32).contiguous()
+            self._keep.append(sg)
+            return None, sg.data_ptr()
         rc = getattr(lin, "_rotation_cache", None)
-        if getattr(lin, "_rht_signs", None) is not None:
-            raise RuntimeError("Hadamard rotation is not supported inside the fused block yet")
         if rc is None:
-            return None
+            return None, None
         Pi = rc.get_pi(lin.turbo_dim, lin.turbo_bits, lin.turbo_seed)
         key = ("pi", Pi.data_ptr())
         cache = GraphCompatibleMoeBlock._PI
         if key not in cache:
             cache[key] = TiledWeight.from_dense(Pi.to(device=device, dtype=torch.float16).contiguous())
         self._keep.append(cache[key])
-        return cache[key].codes.data_ptr()
+        return cache[key].codes.data_ptr(), None
 
     _PI = {}
 

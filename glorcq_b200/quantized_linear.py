@@ -149,8 +149,8 @@ class GLoRCQLinear(nn.Module):
     # ---- forward (inference/quantized_linear.py:286-355) ------------------------------------
     def _rotate(self, x):
         if self._rht_signs is not None:
-            from .rotation import rht_forward
-            return rht_forward(x, self._rht_signs)
+            from .hadamard_rotation import rht_forward_half
+            return rht_forward_half(x, self._rht_signs)
         Pi = self._rotation_cache.get_pi(self.turbo_dim, self.turbo_bits, self.turbo_seed)
         return (x.float() @ Pi.float().T).half()
 

@@ -98,3 +98,114 @@ def block_bytes_per_token(H=2048, I=1408, top_k=4, I_shared=5632, rank=64, E=60,
     shared = (2 * lin(I_shared, H) + lin(H, I_shared)) if I_shared else 0
     router = (E + (1 if I_shared else 0)) * H * 2
     return routed + shared + router
+
+
+# ---- synthetic checkpoints in the reference's on-disk format ---------------------------------------
+def make_checkpoint(hf_config: dict, seed=0, qbit=2, attn_bits=4, rank=64, attn_rank=None, groupsize=128,
+                    n_clusters=8, u_format="int4", sv_format="int4", uv_bits=8):
+    """Seeded random model in the format ``load_glorcq_model`` reads (CPU tensors):
+    returns (model_data, cross_layer_info, dense) = the contents of glorcq_model.pt,
+    cross_layer_info.pt and dense_weights.pt.  Codes uniform, scales |N(0, 0.02)|, integer zero points,
+    low-rank factors N(0, 0.01) quantised to `u_format` / `sv_format` ("fp16", "int4", "int8"), cluster
+    of every (layer, expert, projection) drawn at random from `n_clusters`; attention projections carry
+    `attn_bits` codes and their own clusters (expert index -1); the shared expert has no low-rank term,
+    as in the reference's loader."""
+    from .model_builder import _pack_int4
+    g = torch.Generator()
+    g.manual_seed(seed)
+    c = hf_config
+    H, L = c["hidden_size"], c["num_hidden_layers"]
+    nh, nkv = c["num_attention_heads"], c.get("num_key_value_heads") or c["num_attention_heads"]
+    hd = c.get("head_dim") or H // nh
+    E = c.get("num_experts", c.get("num_local_experts", 0))
+    mixtral = "num_local_experts" in c
+    I = c.get("moe_intermediate_size", c.get("intermediate_size"))
+    Ish = c.get("shared_expert_intermediate_size", 0)
+    mp = "block_sparse_moe" if mixtral else "mlp"
+    names = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+    attn_rank = attn_rank or rank
+
+    def codes(N, K, bits):
+        G = (K + groupsize - 1) // groupsize
+        return {"qweight_int": torch.randint(0, 2 ** bits, (N, K), generator=g, dtype=torch.int32),
+                "scales": (torch.randn(N, G, generator=g) * 0.02).abs().half(),
+                "zeros": torch.randint(0, 2 ** bits, (N, G), generator=g).half(),
+                "bits": bits, "groupsize": groupsize, "sym": False}
+
+    def quant(M, fmt, prefix):
+        """(rows, r) fp32 factor -> stored form with a per-column scale."""
+        if fmt == "fp16":
+            return {f"{prefix}_fp16": M.half()}
+        bits = 4 if fmt == "int4" else uv_bits
+        maxval = 2 ** (bits - 1) - 1
+        scale = M.abs().amax(0).clamp_min(1e-8)
+        q = torch.round(M / scale * maxval).clamp(-maxval, maxval).to(torch.int8)
+        if fmt == "int4":
+            return {f"{prefix}_int4_packed": _pack_int4(q), f"{prefix}_scale": scale.half(),
+                    f"{prefix}_orig_rows": torch.tensor(M.shape[0])}
+        return {f"{prefix}_int8": q, f"{prefix}_scale": scale.half()}
+
+    layers, dense = {}, {}
+    assignments = {w: [] for w in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")}
+    per_v = {w: [] for w in assignments}
+    shapes = {"q_proj": (nh * hd, H), "k_proj": (nkv * hd, H), "v_proj": (nkv * hd, H), "o_proj": (H, nh * hd),
+              "gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}
+    wt_of = dict(zip(names, ("gate_proj", "up_proj", "down_proj")))
+
+    def add(layer, expert, wtype, r):
+        gid = int(torch.randint(0, n_clusters, (1,), generator=g))
+        assignments[wtype].append({"layer": layer, "expert": expert, "group_id": gid})
+        per_v[wtype].append(quant(torch.randn(shapes[wtype][0], r, generator=g) * 0.01, sv_format, "SV"))
+
+    for l in range(L):
+        mods = {}
+        for w in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            mods[f"self_attn.{w}"] = codes(*shapes[w], attn_bits)
+            add(l, -1, w, attn_rank)
+        if E:
+            for e in range(E):
+                for nm in names:
+                    mods[f"{mp}.experts.{e}.{nm}"] = codes(*shapes[wt_of[nm]], qbit)
+                    add(l, e, wt_of[nm], rank)
+            if Ish:
+                mods[f"{mp}.shared_expert.gate_proj"] = codes(Ish, H, qbit)
+                mods[f"{mp}.shared_expert.up_proj"] = codes(Ish, H, qbit)
+                mods[f"{mp}.shared_expert.down_proj"] = codes(H, Ish, qbit)
+                dense[f"model.layers.{l}.{mp}.shared_expert_gate.weight"] = (torch.randn(1, H, generator=g) * 0.02).half()
+            dense[f"model.layers.{l}.{mp}.gate.weight"] = (torch.randn(E, H, generator=g) * 0.02).half()
+        else:
+            for nm in ("gate_proj", "up_proj", "down_proj"):
+                mods[f"mlp.{nm}"] = codes(*shapes[nm], qbit)
+                add(l, -1, nm, rank)
+        layers[l] = mods
+        dense[f"model.layers.{l}.input_layernorm.weight"] = torch.ones(H).half()
+        dense[f"model.layers.{l}.post_attention_layernorm.weight"] = torch.ones(H).half()
+    shared = {}
+    for w, (N, K) in shapes.items():
+        r = attn_rank if w.endswith(("q_proj", "k_proj", "v_proj", "o_proj")) else rank
+        shared[w] = {gid: quant(torch.randn(K, r, generator=g) * 0.01, u_format, "U") for gid in range(n_clusters)}
+    dense["model.embed_tokens.weight"] = (torch.randn(c["vocab_size"], H, generator=g) * 0.02).half()
+    dense["lm_head.weight"] = (torch.randn(c["vocab_size"], H, generator=g) * 0.02).half()
+    dense["model.norm.weight"] = torch.ones(H).half()
+    model_data = {"model_config": {"model_path": "synthetic", "qbit": qbit, "rank": rank, "groupsize": groupsize,
+                                   "n_iter": 0, "use_turboquant": False, "act_alpha": 0.0, "uv_bits": uv_bits,
+                                   "rotation_type": "qr"},
+                  "layers": layers}
+    cross = {"config": {"uv_bits": uv_bits, "u_bits": 4 if u_format == "int4" else uv_bits,
+                        "sv_bits": 4 if sv_format == "int4" else uv_bits},
+             "assignments": assignments, "shared_matrices": shared, "per_expert_V": per_v}
+    return model_data, cross, dense
+
+
+def write_checkpoint(path, hf_config: dict, **kw):
+    """make_checkpoint written as config.json, glorcq_model.pt, cross_layer_info.pt and dense_weights.pt."""
+    import json
+    import os
+    os.makedirs(path, exist_ok=True)
+    model_data, cross, dense = make_checkpoint(hf_config, **kw)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(hf_config, f)
+    torch.save(model_data, os.path.join(path, "glorcq_model.pt"))
+    torch.save(cross, os.path.join(path, "cross_layer_info.pt"))
+    torch.save(dense, os.path.join(path, "dense_weights.pt"))
+    return model_data, cross, dense

@@ -191,6 +191,14 @@ size_t glq_mm_workspace_bytes(const glq_mm_args_t* args);
 size_t glq_mm_counters(const glq_mm_args_t* args);
 int glq_grouped_matmul(const glq_mm_args_t* args, void* stream);
 
+/* Randomized Hadamard rotation of activation rows (rht_forward, hadamard_rotation.py:50-65, which
+ * multiplies by the signs and calls the third-party fast-hadamard-transform):
+ *   y[row] = scale * H_n * (signs . x[row]),  H_n in natural (Sylvester) order, n = next power of two >= d;
+ * x is zero-padded to n and the first d outputs are kept.  x / y are fp16 or fp32 ((rows, d), leading
+ * dimensions in elements), signs (d,) fp32; the butterflies run in fp32.  n <= 32768. */
+int glq_rht_forward(const void* x, int x_is_f32, int64_t ldx, const float* signs, int rows, int d, float scale, void* y,
+                    int y_is_f32, int64_t ldy, void* stream);
+
 /* First bounds violation or timed-out wait recorded by a kernel: {code, index, limit,
  * block<<32|thread}, all zero when there was none.  Synchronises the device; clear != 0 resets it. */
 int glq_debug_error(unsigned long long* out4, int clear);
@@ -239,6 +247,9 @@ typedef struct glq_moe_desc {
      * term sees the unrotated input), as tiled F16 matrices Pi (y = x . Pi^T), or NULL for identity:
      * H x H before gate/up, I x I before down, I_shared x I_shared before the shared down */
     const void* rot_in; const void* rot_mid; const void* sh_rot_mid;
+    /* the same three rotations as randomized Hadamard transforms: (dim,) fp32 sign vectors, or NULL; a sign
+     * vector takes precedence over the dense matrix of the same position (scale 1/sqrt(dim)) */
+    const float* rht_in; const float* rht_mid; const float* sh_rht_mid;
 } glq_moe_desc_t;
 
 size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens);

@@ -129,6 +129,42 @@ def gptq_matmul(x: torch.Tensor, q: torch.Tensor, scales: torch.Tensor, zeros: t
 
 
 # --------------------------------------------------------------------------------------
+# Randomized Hadamard rotation (hadamard_rotation.py:33-65)
+# --------------------------------------------------------------------------------------
+def generate_rht_signs(d: int, seed: int = 42) -> torch.Tensor:
+    """(d,) float32 of +-1 from a CPU generator seeded with `seed` (hadamard_rotation.py:33-47)."""
+    rng = torch.Generator(device="cpu")
+    rng.manual_seed(seed)
+    return (torch.randint(0, 2, (d,), generator=rng) * 2 - 1).float()
+
+
+def sylvester_hadamard(n: int) -> torch.Tensor:
+    """H_n for n a power of two, by the Sylvester construction: H_1 = [1], H_2n = [[H, H], [H, -H]]."""
+    assert n > 0 and n & (n - 1) == 0
+    H = torch.ones(1, 1, dtype=torch.float64)
+    while H.shape[0] < n:
+        H = torch.cat([torch.cat([H, H], 1), torch.cat([H, -H], 1)], 0)
+    return H
+
+
+def rht_forward(x: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
+    """y = (1/sqrt(d)) H diag(signs) x over the last dimension (hadamard_rotation.py:50-65).
+
+    The reference delegates H to the third-party fast-hadamard-transform 1.1.0, which is absent here
+    (parity unpinned for it).  Restated from its published behaviour: the Walsh-Hadamard transform in
+    natural (Sylvester) order; a dimension that is not a power of two is zero-padded to the next one
+    and the result is cut back to d, while the scale stays 1/sqrt(d) as the caller passes it.
+    """
+    d = x.shape[-1]
+    n = 1 << max(0, (d - 1).bit_length())
+    xs = (x.double() * signs.double())
+    if n != d:
+        xs = torch.nn.functional.pad(xs, (0, n - d))
+    y = xs @ sylvester_hadamard(n).T
+    return (y[..., :d] * (1.0 / d ** 0.5)).to(x.dtype)
+
+
+# --------------------------------------------------------------------------------------
 # Quantized linear layer
 # --------------------------------------------------------------------------------------
 @dataclass
@@ -150,6 +186,7 @@ class QuantLinear:
     norms: Optional[torch.Tensor] = None           # (N,) fp32
     centroids: Optional[torch.Tensor] = None       # (4,) fp32
     Pi: Optional[torch.Tensor] = None              # (K, K) fp16 rotation, or None = identity
+    rht_signs: Optional[torch.Tensor] = None       # (K,) +-1: randomized Hadamard rotation instead of Pi
     # low-rank correction
     U: Optional[torch.Tensor] = None               # (K, r) fp16, shared by a cluster
     SV: Optional[torch.Tensor] = None              # (N, r) fp16, per layer
@@ -175,7 +212,10 @@ def linear_forward(p: QuantLinear, x: torch.Tensor, precomputed_xU: Optional[tor
         W = gptq_tile_fp16(p.qweight_int, p.scales, p.zeros, p.gptq_groupsize, p.gptq_sym)
         y = x2 @ W.to(x2.dtype).T
     elif p.quant_type == "turbo":
-        xr = x2.float() if p.Pi is None else x2.float() @ p.Pi.float().T
+        if p.rht_signs is not None:          # inference/moe_block.py:349-351, 523-525
+            xr = rht_forward(x2.float(), p.rht_signs).to(torch.float16).float()
+        else:
+            xr = x2.float() if p.Pi is None else x2.float() @ p.Pi.float().T
         if x_rot_half:
             xr = xr.to(torch.float16).float()
         y = turbo_matmul(xr, p.packed_indices, p.norms, p.centroids).to(torch.float16)
@@ -319,3 +359,149 @@ def experts_forward(experts: List[Expert], hidden: torch.Tensor, top_k_index: to
         y = y * top_k_weights[tok, slot, None]
         out.index_add_(0, tok, y.to(out.dtype))
     return out
+
+
+# --------------------------------------------------------------------------------------
+# On-disk format -> layers (inference/model_builder.py:27-80, 335-450, 465-544)
+# --------------------------------------------------------------------------------------
+def dequant_intN(q: torch.Tensor, scale: torch.Tensor, nbits: int) -> torch.Tensor:
+    """q / (2^(nbits-1) - 1) * scale in fp32, per-column scale (inference/model_builder.py:69-72)."""
+    return q.float() / (2 ** (nbits - 1) - 1) * scale.float()
+
+
+def unpack_int4(packed: torch.Tensor, orig_rows: int) -> torch.Tensor:
+    """Two rows per byte: low nibble = even row, high nibble = odd row, stored value = q + 7
+    (inference/model_builder.py:75-80)."""
+    lo = (packed & 0xF).to(torch.int8) - 7
+    hi = ((packed >> 4) & 0xF).to(torch.int8) - 7
+    return torch.stack([lo, hi], dim=1).reshape(-1, packed.shape[1])[:orig_rows]
+
+
+def _decode_factor(d: dict, prefix: str, bits: int) -> torch.Tensor:
+    if f"{prefix}_fp16" in d:
+        return d[f"{prefix}_fp16"].half()
+    if f"{prefix}_int4_packed" in d:
+        rows = int(d[f"{prefix}_orig_rows"].item())
+        return dequant_intN(unpack_int4(d[f"{prefix}_int4_packed"], rows), d[f"{prefix}_scale"], 4).half()
+    return dequant_intN(d[f"{prefix}_int8"], d[f"{prefix}_scale"], bits).half()
+
+
+def checkpoint_layers(model_data: dict, cross: dict) -> Dict[int, Dict[str, QuantLinear]]:
+    """{layer: {module name: QuantLinear}} as the loader builds them: U from the cluster the
+    (projection type, layer, expert) record assigns (expert -1 for attention / dense projections, the
+    shared expert gets no low-rank term), SV from per_expert_V at the record's list position; Mixtral's
+    w1/w2/w3 are gate/down/up (inference/model_builder.py:345-351, 473-544)."""
+    mc, cc = model_data["model_config"], cross["config"]
+    uv_bits = cc.get("uv_bits", mc.get("uv_bits", 8))
+    u_bits, sv_bits = cc.get("u_bits", uv_bits), cc.get("sv_bits", uv_bits)
+    lookup = {}
+    for wtype, recs in cross["assignments"].items():
+        for li, rec in enumerate(recs):
+            lookup[(wtype, rec["layer"], rec["expert"])] = (rec["group_id"], li)
+    U_cache = {}
+    out = {}
+    for l, mods in model_data["layers"].items():
+        out[l] = {}
+        for name, D in mods.items():
+            N, K = D["qweight_int"].shape
+            ql = QuantLinear(in_features=K, out_features=N, quant_type="gptq", qweight_int=D["qweight_int"],
+                             scales=D["scales"], zeros=D["zeros"], gptq_bits=D["bits"],
+                             gptq_groupsize=D["groupsize"], gptq_sym=D.get("sym", False))
+            parts = name.split(".")
+            if "shared_expert" in name:
+                expert = -2
+            elif "experts" in parts:
+                expert = int(parts[parts.index("experts") + 1])
+            else:
+                expert = -1
+            wt = {"w1": "gate_proj", "w2": "down_proj", "w3": "up_proj"}.get(parts[-1], parts[-1])
+            if expert != -2 and (wt, l, expert) in lookup:
+                gid, li = lookup[(wt, l, expert)]
+                if (wt, gid) not in U_cache:
+                    U_cache[(wt, gid)] = _decode_factor(cross["shared_matrices"][wt][gid], "U", u_bits)
+                v = cross["per_expert_V"][wt][li]
+                ql.U = U_cache[(wt, gid)]
+                if "V_int8" in v:   # old format: S kept with the cluster, fused here (quantized_linear.py:249-259)
+                    V = dequant_intN(v["V_int8"], v["V_scale"], uv_bits).half()
+                    ql.SV = (V * cross["shared_matrices"][wt][gid]["S"].half().unsqueeze(0)).half()
+                else:
+                    ql.SV = _decode_factor(v, "SV", sv_bits)
+                ql.cluster_id = (wt, gid)
+            out[l][name] = ql
+    return out
+
+
+# --------------------------------------------------------------------------------------
+# Decoder around the layers: what the transformers Qwen2-MoE / Mixtral / Qwen3-MoE models compute
+# (the reference borrows them, inference/model_builder.py:234-243), restated with plain tensor ops
+# --------------------------------------------------------------------------------------
+def _rms_norm(x, w, eps):
+    v = x.float()
+    v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+    return (w.float() * v).to(x.dtype)
+
+
+def decoder_forward(cfg: dict, layers: Dict[int, Dict[str, QuantLinear]], dense: Dict[str, torch.Tensor],
+                    input_ids: torch.Tensor) -> torch.Tensor:
+    """Logits (B, T, V) of a full causal forward without a cache, fp16 activations: embedding, per
+    layer RMSNorm -> attention (rotary embedding, grouped-query, softmax in fp32) -> residual -> RMSNorm
+    -> MoE block (moe_forward) or dense SwiGLU MLP -> residual, final RMSNorm, lm_head."""
+    H, nh = cfg["hidden_size"], cfg["num_attention_heads"]
+    nkv = cfg.get("num_key_value_heads") or nh
+    hd = cfg.get("head_dim") or H // nh
+    eps, theta = cfg.get("rms_norm_eps", 1e-6), cfg.get("rope_theta", 10000.0)
+    mixtral = "num_local_experts" in cfg
+    E = cfg.get("num_experts", cfg.get("num_local_experts", 0))
+    mp = "block_sparse_moe" if mixtral else "mlp"
+    gn, un, dn = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+    B, T = input_ids.shape
+    x = dense["model.embed_tokens.weight"][input_ids]
+    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    fr = torch.outer(torch.arange(T, dtype=torch.float32), inv)
+    emb = torch.cat([fr, fr], -1)
+    cos, sin = emb.cos().half()[None, None], emb.sin().half()[None, None]
+
+    def rot(v):
+        h = v.shape[-1] // 2
+        return torch.cat([-v[..., h:], v[..., :h]], -1)
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    for l in range(cfg["num_hidden_layers"]):
+        m = layers[l]
+        pre = f"model.layers.{l}"
+        h = _rms_norm(x, dense[f"{pre}.input_layernorm.weight"], eps)
+        q = linear_forward(m["self_attn.q_proj"], h).view(B, T, nh, hd)
+        k = linear_forward(m["self_attn.k_proj"], h).view(B, T, nkv, hd)
+        v = linear_forward(m["self_attn.v_proj"], h).view(B, T, nkv, hd)
+        if f"{pre}.self_attn.q_norm.weight" in dense:
+            q = _rms_norm(q, dense[f"{pre}.self_attn.q_norm.weight"], eps)
+            k = _rms_norm(k, dense[f"{pre}.self_attn.k_norm.weight"], eps)
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        q = q * cos + rot(q) * sin
+        k = k * cos + rot(k) * sin
+        k = k.repeat_interleave(nh // nkv, dim=1)
+        v = v.repeat_interleave(nh // nkv, dim=1)
+        s = (q.float() @ k.float().transpose(-1, -2)) / hd ** 0.5
+        s = s.masked_fill(~causal, float("-inf"))
+        p = torch.softmax(s, dim=-1).to(x.dtype)
+        a = (p @ v).transpose(1, 2).reshape(B, T, nh * hd)
+        x = x + linear_forward(m["self_attn.o_proj"], a)
+        h = _rms_norm(x, dense[f"{pre}.post_attention_layernorm.weight"], eps)
+        if f"{mp}.experts.0.{gn}" in m:
+            experts = [Expert(m[f"{mp}.experts.{e}.{gn}"], m[f"{mp}.experts.{e}.{un}"], m[f"{mp}.experts.{e}.{dn}"])
+                       for e in range(E)]
+            shared = None
+            if f"{mp}.shared_expert.gate_proj" in m:
+                shared = Expert(m[f"{mp}.shared_expert.gate_proj"], m[f"{mp}.shared_expert.up_proj"],
+                                m[f"{mp}.shared_expert.down_proj"])
+            blk = MoeBlock(num_experts=E, top_k=cfg["num_experts_per_tok"],
+                           norm_topk_prob=True if mixtral else cfg.get("norm_topk_prob", False),
+                           gate_weight=dense[f"{pre}.{mp}.gate.weight"], experts=experts, shared_expert=shared,
+                           shared_gate_weight=dense.get(f"{pre}.{mp}.shared_expert_gate.weight"))
+            y, _ = moe_forward(blk, h)
+        else:
+            g = linear_forward(m["mlp.gate_proj"], h)
+            u = linear_forward(m["mlp.up_proj"], h)
+            y = linear_forward(m["mlp.down_proj"], F.silu(g) * u)
+        x = x + y
+    x = _rms_norm(x, dense["model.norm.weight"], eps)
+    return x @ dense.get("lm_head.weight", dense["model.embed_tokens.weight"]).T

@@ -107,6 +107,8 @@ def to_oracle_linear(d):
     else:
         kw.update(packed_indices=d["packed_indices"], norms=d["norms"], centroids=d["centroids"],
                   Pi=d.get("Pi"))
+        if d.get("rht_seed") is not None:     # rotation_type "hadamard": signs from the layer's seed
+            kw.update(rht_signs=O.generate_rht_signs(d["K"], d["rht_seed"]))
     return O.QuantLinear(**kw)
 
 
@@ -163,6 +165,9 @@ def to_b200_linear(d, device="cuda", shared_u=None):
         lin.load_turbo({"packed_indices": d["packed_indices"], "norms": d["norms"], "bits": 2,
                         "dim": d["K"], "seed": 42},
                        FixedRotationCache(Pi.to(device), d["centroids"].to(device)), device=device)
+        if d.get("rht_seed") is not None:
+            from glorcq_b200.hadamard_rotation import generate_rht_signs
+            lin._rht_signs = generate_rht_signs(d["K"], seed=d["rht_seed"], device=device)
     if "SV" in d:
         U = d["U"]
         if shared_u is not None:

@@ -145,6 +145,13 @@ MOE_CASES = [
 ]
 
 
+RHT_SIGN_CASES = [(2048, 42), (1408, 42), (768, 7), (64, 0)]
+LOADER_CFG = dict(hidden_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, vocab_size=32,
+                  num_experts=2, num_experts_per_tok=1, moe_intermediate_size=32, shared_expert_intermediate_size=32)
+LOADER_FORMATS = ("int4", "fp16", "int8")
+LOADER_MODULES = ("self_attn.q_proj", "mlp.experts.1.down_proj", "mlp.experts.0.gate_proj", "mlp.shared_expert.up_proj")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
@@ -242,6 +249,42 @@ def main():
         y = ge(x, idx, w)
     gold["experts"]["experts_10"] = {"args": kw, "T": T, "digest": moe_digest(blk), "idx": idx, "w": w, "y": y,
                                       "x_seed": 52}
+
+    # ---- Hadamard sign vectors (hadamard_rotation.py:33-47) ----
+    import hadamard_rotation as RH                                   # noqa: E402
+    gold["rht_signs"] = {f"{d}_{seed}": RH.generate_rht_signs(d, seed=seed, device="cpu").to(torch.int8)
+                         for d, seed in RHT_SIGN_CASES}
+
+    # ---- loader: integer decoders, SharedUCache, _load_lora_for_module (inference/model_builder.py) ----
+    from inference import model_builder as RMB                       # noqa: E402
+    from glorcq_b200 import synthetic                                # noqa: E402
+    gold["loader"] = {}
+    g = torch.Generator().manual_seed(61)
+    packed = torch.randint(0, 256, (5, 6), generator=g, dtype=torch.int32).to(torch.uint8)
+    gold["loader"]["unpack_int4"] = {"packed": packed, "rows": 9, "out": RMB._unpack_int4(packed, 9)}
+    q = torch.randint(-127, 128, (7, 4), generator=g, dtype=torch.int32).to(torch.int8)
+    sc = torch.rand(4, generator=g).half()
+    gold["loader"]["dequant_intN"] = {"q": q, "scale": sc, "out8": RMB._dequant_intN(q, sc, 8),
+                                      "out4": RMB._dequant_intN(q.clamp(-7, 7), sc, 4)}
+    for fmt in LOADER_FORMATS:
+        md, cr, _ = synthetic.make_checkpoint(LOADER_CFG, seed=62, rank=8, attn_rank=8, n_clusters=2, u_format=fmt,
+                                              sv_format=fmt)
+        cc = cr["config"]
+        uc = RMB.SharedUCache(cr["shared_matrices"], cc["uv_bits"], device="cpu", u_bits=cc["u_bits"])
+        lookup = {}
+        for wtype, recs in cr["assignments"].items():
+            for li, rec in enumerate(recs):
+                lookup[(wtype, rec["layer"], rec["expert"])] = (rec["group_id"], wtype, li)
+        mods = {}
+        for name in LOADER_MODULES:
+            D = md["layers"][0][name]
+            N, K = D["qweight_int"].shape
+            ql = GLoRCQLinear(K, N)
+            ql.load_gptq(D, device="cpu")
+            RMB._load_lora_for_module(ql, 0, name, lookup, uc, cr["per_expert_V"], cc["uv_bits"], "cpu",
+                                      sv_bits=cc["sv_bits"])
+            mods[name] = {"U": ql.U, "SV": ql.SV, "cluster_id": getattr(ql, "cluster_id", None)}
+        gold["loader"][fmt] = mods
 
     torch.save(gold, args.out)
     print("wrote", args.out, os.path.getsize(args.out), "bytes")

@@ -1,0 +1,148 @@
+"""Rotation kernel, loader, decoder and graph wrapper on the GPU against the CPU oracle.
+
+Bars: low-rank factors read from a checkpoint bit-identical to the oracle's; rotated activations
+within 1e-6 (fp32) / one fp16 rounding; logits of a two-layer decoder within rel-L2 5e-3 of the
+oracle's full causal forward (each quantized layer is held to 1e-3 on its own; attention runs
+through the library's fused kernel with fp32 accumulation where the oracle rounds the probabilities
+to fp16)."""
+
+import pytest
+import torch
+
+from oracle import glorcq_oracle as O
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+REL_LOGITS = 5e-3
+
+CFG = dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=512,
+           num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=256,
+           norm_topk_prob=False, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=64)
+MIXTRAL = dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=300,
+               num_local_experts=4, num_experts_per_tok=2, intermediate_size=384, rms_norm_eps=1e-5,
+               rope_theta=1e6, max_position_embeddings=64)
+QWEN3 = dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+             vocab_size=300, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, norm_topk_prob=True,
+             rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=64)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available()
+    from glorcq_b200 import _build
+    _build.build()
+    return torch.device("cuda:0")
+
+
+@pytest.mark.parametrize("d", [2048, 1408, 768, 64, 48])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_rht_forward(dev, d, dtype):
+    from glorcq_b200.hadamard_rotation import generate_rht_signs, rht_backward, rht_forward, rht_forward_half
+    x = cases.make_x(900 + d, 5, d, dtype)
+    signs = generate_rht_signs(d, seed=d, device=dev)
+    ref = O.rht_forward(x.float(), O.generate_rht_signs(d, d))
+    y = rht_forward(x.to(dev), signs)
+    assert y.dtype == dtype and y.shape == x.shape
+    if dtype == torch.float32:
+        assert torch.allclose(y.cpu(), ref, atol=2e-6 * d ** 0.5)
+        if d & (d - 1) == 0:
+            assert torch.allclose(rht_backward(y, signs).cpu(), x, atol=1e-5)
+    else:
+        assert cases.rel_l2(y.cpu(), ref) <= 5e-4
+    yh = rht_forward_half(x.to(dev), signs)
+    assert yh.dtype == torch.float16 and cases.rel_l2(yh.cpu(), ref) <= 5e-4
+    assert rht_forward(x[:0].to(dev), signs).shape == (0, d)
+
+
+@pytest.mark.parametrize("N", [1, 6, 70])
+def test_codebook_block_with_hadamard_rotation(dev, N):
+    blk = cases.make_moe(36, 256, 128, 6, 2, I_shared=256, rank=16, experts_per_cluster=2, fmt="turbo")
+    for ex in blk["experts"] + [blk["shared_expert"]]:
+        for p in ex.values():
+            p["Pi"] = None
+            p["rht_seed"] = 42
+    mb = cases.to_b200_moe(blk, dev)
+    x = cases.make_x(1036 + N, N, 256).reshape(1, N, 256)
+    y, _ = mb(x.to(dev))
+    ref, _ = O.moe_forward(cases.to_oracle_moe(blk), x)
+    assert cases.rel_l2(y.cpu(), ref) <= 2e-3
+
+
+def _models(cfg, dev, seed, **kw):
+    from glorcq_b200 import model_builder as MB
+    from glorcq_b200 import synthetic
+    from glorcq_b200.decoder import GLoRCQDecoder
+    md, cr, dense = synthetic.make_checkpoint(cfg, seed=seed, rank=16, attn_rank=32, n_clusters=3, **kw)
+    layers, u_cache = MB.build_layers(md["model_config"], md["layers"], cr, device=dev)
+    return GLoRCQDecoder(cfg, layers, dense=dense, device=dev), layers, O.checkpoint_layers(md, cr), dense
+
+
+@pytest.mark.parametrize("fmt", ["int4", "fp16", "int8"])
+def test_build_layers_matches_oracle(dev, fmt):
+    model, layers, olayers, _ = _models(CFG, dev, 21, u_format=fmt, sv_format=fmt)
+    for name in ("self_attn.q_proj", "mlp.experts.3.down_proj", "mlp.experts.0.gate_proj", "mlp.shared_expert.up_proj"):
+        ql, oq = layers[1][name], olayers[1][name]
+        if oq.U is None:
+            assert ql.U is None and ql.SV is None
+        else:
+            assert torch.equal(ql.U.cpu(), oq.U) and torch.equal(ql.SV.cpu(), oq.SV)
+            assert tuple(ql.cluster_id) == tuple(oq.cluster_id)
+    # layers of one cluster share one U tensor (and so one tiled copy)
+    by_cluster = {}
+    for mods in layers.values():
+        for ql in mods.values():
+            if ql.U is not None:
+                by_cluster.setdefault(ql.cluster_id, set()).add(ql.U.data_ptr())
+    assert all(len(v) == 1 for v in by_cluster.values())
+    x = cases.make_x(5, 3, 256)
+    ql, oq = layers[0]["self_attn.o_proj"], olayers[0]["self_attn.o_proj"]
+    assert cases.rel_l2(ql(x.to(dev)).cpu(), O.linear_forward(oq, x)) <= 1e-3
+
+
+@pytest.mark.parametrize("cfg", [CFG, MIXTRAL, QWEN3], ids=["qwen2moe", "mixtral", "qwen3moe"])
+def test_decoder_logits_prefill_and_decode(dev, cfg):
+    from glorcq_b200.decoder import StaticKVCache
+    model, _, olayers, dense = _models(cfg, dev, 31)
+    if cfg is QWEN3:   # per-head q/k norms
+        g = torch.Generator().manual_seed(7)
+        for l in range(2):
+            dense[f"model.layers.{l}.self_attn.q_norm.weight"] = (1 + 0.1 * torch.randn(32, generator=g)).half()
+            dense[f"model.layers.{l}.self_attn.k_norm.weight"] = (1 + 0.1 * torch.randn(32, generator=g)).half()
+        from glorcq_b200 import model_builder as MB
+        from glorcq_b200 import synthetic
+        from glorcq_b200.decoder import GLoRCQDecoder
+        md, cr, _ = synthetic.make_checkpoint(cfg, seed=31, rank=16, attn_rank=32, n_clusters=3)
+        layers, _ = MB.build_layers(md["model_config"], md["layers"], cr, device=dev)
+        model = GLoRCQDecoder(cfg, layers, dense=dense, device=dev)
+    T = 12
+    ids = torch.randint(0, cfg["vocab_size"], (1, T + 1), generator=torch.Generator().manual_seed(3))
+    ref = O.decoder_forward(cfg, olayers, dense, ids)
+    cache = StaticKVCache(model.config, 1, 32, dev)
+    with torch.no_grad():
+        lg = model(input_ids=ids[:, :T].to(dev), cache_position=torch.arange(T, device=dev), past_key_values=cache)[0]
+        assert cases.rel_l2(lg.cpu(), ref[:, :T]) <= REL_LOGITS
+        step = model(input_ids=ids[:, T:].to(dev), cache_position=torch.tensor([T], device=dev), past_key_values=cache)[0]
+    assert step.shape == (1, 1, cfg["vocab_size"])
+    assert cases.rel_l2(step.cpu(), ref[:, T:]) <= REL_LOGITS
+
+
+def test_graph_wrapper_generate_matches_eager(dev, tmp_path):
+    from glorcq_b200 import synthetic
+    from glorcq_b200.graph_wrapper import GLoRCQGraphWrapper, run_speed_benchmark
+    from glorcq_b200.model_builder import load_glorcq_model
+    synthetic.write_checkpoint(str(tmp_path), CFG, seed=41, rank=16, attn_rank=32, n_clusters=3)
+    model = load_glorcq_model(str(tmp_path), device="cuda:0")
+    ids = torch.randint(0, 512, (1, 9), generator=torch.Generator().manual_seed(4)).to(dev)
+    eager = model.generate(ids, max_new_tokens=8)
+    w = GLoRCQGraphWrapper(model, max_batch_size=1, max_seq_len=32)
+    out, seconds = w.generate(ids, max_new_tokens=8)          # captures on first use
+    assert out.shape == (1, 17) and seconds > 0
+    assert torch.equal(out, eager)
+    out2, _ = w.generate(ids, max_new_tokens=8)               # replay of the captured graph only
+    assert torch.equal(out2, eager)
+    assert w.static_input_ids.shape == (1, 1) and w.static_cache_position.shape == (1,)
+    assert w.static_logits.shape == (1, 1, 512)
+    r = run_speed_benchmark(model, max_seq_len=32, gen_len=6, input_ids=ids)
+    assert set(r) == {"standard_tps", "graph_tps", "speedup"} and r["graph_tps"] > 0
+    with pytest.raises(AssertionError):
+        w.generate(torch.cat([ids, ids]), max_new_tokens=2)
