@@ -56,7 +56,7 @@ class MoeDesc(C.Structure):
 class MoeEp(C.Structure):
     """glq_moe_ep_t"""
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phase", C.c_int32), ("reserved", C.c_int32),
-                ("entry_out", vp)]
+                ("entry_out", vp), ("sel_in", vp), ("weight_in", vp)]
 
 
 MOE_PHASE_ALL, MOE_PHASE_EXPERTS, MOE_PHASE_COMBINE = 0, 1, 2

@@ -123,12 +123,22 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
                                                         int* __restrict__ sel_out, __half* __restrict__ wts_out,
                                                         int* __restrict__ active2, int* __restrict__ n_active2,
                                                         int* __restrict__ slot_count2, int* __restrict__ slot_offset2,
-                                                        int ep_rank, int ep_world) {
+                                                        int ep_rank, int ep_world, const int* __restrict__ sel_in,
+                                                        const __half* __restrict__ wts_in) {
     extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
     int* sm_off = sm_cnt + E;
     // Phase A: one warp per token, lanes over experts (E <= 256)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int t = warp; t < n; t += nwarps) {
+    if (sel_in) {
+        // routing decided by the caller: copy it; an index outside [0, E) marks a dropped slot
+        for (int i = threadIdx.x; i < n * k; i += blockDim.x) {
+            const int e = sel_in[i];
+            sel[i] = e;
+            wts[i] = wts_in[i];
+            if (e < 0 || e >= E) tok_entries[i] = -1;
+        }
+    }
+    for (int t = warp; t < n && !sel_in; t += nwarps) {
         const __half* row = logits + (size_t)t * ldl;
         float lv[8], pv[8];
         float mx = -INFINITY;
@@ -264,6 +274,7 @@ __global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __r
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int s = 0; s < k; ++s) {
         const int entry = tok_entries[t * k + order[s]];
+        if (entry < 0) continue;     // dropped slot
         __align__(16) __half v[8];
         *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(yd + (size_t)entry * H + c0);
 #pragma unroll
@@ -313,9 +324,11 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if (n == 0) return GLQ_OK;
     if (d->top_k < 1 || d->top_k > 16 || d->E < d->top_k || d->E > 256 || d->H % 8 != 0 || d->I % 8 != 0)
         return GLQ_ERR_UNSUPPORTED;
-    if (!d->router_t || !d->gate_up || !d->down) return GLQ_ERR_ARG;
+    const bool given = ep && ep->sel_in != nullptr;     // routing supplied by the caller: no router, no shared expert
+    if (given && (!ep->weight_in || d->I_shared > 0 || router_logits)) return GLQ_ERR_ARG;
+    if ((!given && !d->router_t) || !d->gate_up || !d->down) return GLQ_ERR_ARG;
     if (d->rank > 0 && (!d->ut_gate_up || !d->ut_down)) return GLQ_ERR_ARG;
-    if (d->dense0_rows < d->router_rows || (d->sh_a_row > 0 && (d->sh_a_row % 16 != 0 || d->sh_a_row < d->router_rows)))
+    if (!given && (d->dense0_rows < d->router_rows || (d->sh_a_row > 0 && (d->sh_a_row % 16 != 0 || d->sh_a_row < d->router_rows))))
         return GLQ_ERR_ARG;
     const MoeLayout L = moe_layout(d, n);
     if (!workspace || workspace_bytes < L.total) return GLQ_ERR_WORKSPACE;
@@ -380,15 +393,17 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     //    when the shared expert's U_gate^T / U_up^T are appended to the router rows, the same product
     //    also yields the shared expert's x.U (columns sh_a_row .. +2R of the output)
     const bool sh_a_fused = d->sh_a_row > 0 && d->dense0_rows >= d->sh_a_row + 2 * R;
-    set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, ldl, d->H, 0);
-    m.w.codes = d->router_t;
-    m.w.N = ldl;
-    m.w.K = d->H;
-    m.x = x;
-    m.ldx = d->H;
-    m.y = p_logits;
-    m.ldy = ldl;
-    if ((rc = finish(m)) != GLQ_OK) return rc;
+    if (!given) {
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, ldl, d->H, 0);
+        m.w.codes = d->router_t;
+        m.w.N = ldl;
+        m.w.K = d->H;
+        m.x = x;
+        m.ldx = d->H;
+        m.y = p_logits;
+        m.ldy = ldl;
+        if ((rc = finish(m)) != GLQ_OK) return rc;
+    }
 
     if (forked && cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_fork), st) != cudaSuccess) return GLQ_ERR_CUDA;
 
@@ -397,7 +412,8 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         p_logits, ldl, n, d->E, k, d->norm_topk_prob, p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow,
         p_escale, p_tok, reinterpret_cast<__half*>(router_logits), sel_out, reinterpret_cast<__half*>(weight_out),
         reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
-        reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2), ep_rank, ep_world);
+        reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2), ep_rank, ep_world,
+        given ? ep->sel_in : nullptr, given ? reinterpret_cast<const __half*>(ep->weight_in) : nullptr);
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
     // rows of remote experts' entries stay zero, so that summing the ranks' buffers is exact
     if (ep_world > 1 && cudaMemsetAsync(p_yd, 0, (size_t)nk * d->H * 2, st) != cudaSuccess) return GLQ_ERR_CUDA;

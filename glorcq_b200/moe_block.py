@@ -137,8 +137,25 @@ class GraphCompatibleMoeBlock(nn.Module):
         d.slot_order_max_tokens = self._graph_threshold
         # router (+ shared expert gate as one more row) (+ the shared expert's U_gate^T, U_up^T, so that
         # one dense product yields the logits and the shared expert's x.U)
-        rows = [self.gate.weight.detach().to(device=device, dtype=torch.float16)]
         has_shared = self.shared_expert is not None
+        if self.gate is None:
+            # experts only, routing supplied per call (GLoRCQExperts): no router product
+            if has_shared:
+                raise RuntimeError("a block without a router cannot have a shared expert")
+            d.router_rows = d.dense0_rows = d.sh_a_row = 0
+            tabs = [_table(gate_up, device), _table(down, device)]
+            d.gate_up, d.down = tabs[0].data_ptr(), tabs[1].data_ptr()
+            if rank > 0:
+                tabs += [_table(utg + utu, device), _table(utd, device)]
+                d.ut_gate_up, d.ut_down = tabs[2].data_ptr(), tabs[3].data_ptr()
+            self._keep += tabs
+            if fmt == FMT_T2:
+                d.rot_in, d.rht_in = self._rotation(g0, device)
+                d.rot_mid, d.rht_mid = self._rotation(d0, device)
+            self._desc = d
+            self._built = True
+            return
+        rows = [self.gate.weight.detach().to(device=device, dtype=torch.float16)]
         if has_shared and self.shared_expert_gate is not None:
             rows.append(self.shared_expert_gate.weight.detach().to(device=device, dtype=torch.float16).reshape(1, H))
         router_rows = sum(r.shape[0] for r in rows)
@@ -225,7 +242,9 @@ class GraphCompatibleMoeBlock(nn.Module):
         return self
 
     # ---- forward (inference/moe_block.py:381-436) -----------------------------------------------
-    def forward(self, hidden_states):
+    def forward(self, hidden_states, top_k_index=None, top_k_weights=None):
+        """(B, S, H) -> ((B, S, H), router logits).  With top_k_index / top_k_weights ((B*S, k)) the routing
+        is the caller's and no logits are returned (the fused-experts adapter)."""
         batch_size, sequence_length, hidden_dim = hidden_states.shape
         x = hidden_states.reshape(-1, hidden_dim)
         if x.dtype != torch.float16:
@@ -238,7 +257,15 @@ class GraphCompatibleMoeBlock(nn.Module):
         d = self._desc
         n = x.shape[0]
         out = torch.empty(n, d.H, dtype=torch.float16, device=x.device)
-        logits = torch.empty(n, d.E, dtype=torch.float16, device=x.device)
+        given = top_k_index is not None
+        if given != (self.gate is None):
+            raise RuntimeError("routing must be passed exactly when the block has no router")
+        logits = None if given else torch.empty(n, d.E, dtype=torch.float16, device=x.device)
+        if given:
+            sel_in = top_k_index.to(device=x.device, dtype=torch.int32).contiguous()
+            wts_in = top_k_weights.to(device=x.device, dtype=torch.float16).contiguous()
+            if sel_in.shape != (n, d.top_k) or wts_in.shape != (n, d.top_k):
+                raise RuntimeError(f"top_k_index / top_k_weights must have shape ({n}, {d.top_k})")
         sel = torch.empty(n, d.top_k, dtype=torch.int32, device=x.device)
         wts = torch.empty(n, d.top_k, dtype=torch.float16, device=x.device)
         if n > 0:
@@ -266,10 +293,16 @@ class GraphCompatibleMoeBlock(nn.Module):
                 ep_rank, ep_world, group = self._ep
 
                 def call(ep):
-                    _lib.check(L.glq_moe_forward_ep(C.byref(d), x.data_ptr(), n, out.data_ptr(), logits.data_ptr(),
+                    if given:
+                        if ep is None:
+                            ep = MoeEp(0, 1, _lib.MOE_PHASE_ALL, 0, None, None, None)
+                        ep.sel_in, ep.weight_in = sel_in.data_ptr(), wts_in.data_ptr()
+                    _lib.check(L.glq_moe_forward_ep(C.byref(d), x.data_ptr(), n, out.data_ptr(),
+                                                    None if logits is None else logits.data_ptr(),
                                                     sel.data_ptr(), wts.data_ptr(), base,
                                                     ws.numel() - (base - ws.data_ptr()), ctr.data_ptr(), ctr.numel(),
-                                                    tiled._stream_ptr(x.device), aux, fork, join, ep),
+                                                    tiled._stream_ptr(x.device), aux, fork, join,
+                                                    None if ep is None else C.byref(ep)),
                                "moe_forward")
                 if ep_world == 1:
                     call(None)
@@ -278,10 +311,10 @@ class GraphCompatibleMoeBlock(nn.Module):
                     if ekey not in self._ws:
                         self._ws[ekey] = torch.empty(n * d.top_k, d.H, dtype=torch.float16, device=x.device)
                     entries = self._ws[ekey]
-                    ep = MoeEp(ep_rank, ep_world, _lib.MOE_PHASE_EXPERTS, 0, entries.data_ptr())
-                    call(C.byref(ep))
+                    ep = MoeEp(ep_rank, ep_world, _lib.MOE_PHASE_EXPERTS, 0, entries.data_ptr(), None, None)
+                    call(ep)
                     self._exchange(entries, group)
                     ep.phase = _lib.MOE_PHASE_COMBINE
-                    call(C.byref(ep))
+                    call(ep)
         self.last_selected_experts, self.last_routing_weights = sel, wts
         return out.reshape(batch_size, sequence_length, hidden_dim), logits

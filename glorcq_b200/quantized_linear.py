@@ -202,3 +202,53 @@ class GLoRCQLinear(nn.Module):
         if self.U is not None:
             s += f", lora_rank={self.U.shape[1]}"
         return s
+
+
+# ---------------------------------------------------------------------------------------------
+# GLoRCQExperts: fused-experts adapter (inference/quantized_linear.py:368-428)
+# ---------------------------------------------------------------------------------------------
+class GLoRCQExperts(nn.Module):
+    """Drop-in for the transformers-5.x style ``XxxExperts`` modules: three per-expert lists of
+    ``GLoRCQLinear`` (gate, up, down) and ``forward(hidden_states (T,H), top_k_index (T,k), top_k_weights
+    (T,k)) -> (T,H)``.
+
+    The reference loops over the experts that were hit on the host (one-hot mask, ``nonzero``, three
+    linears per expert, ``index_add_``).  Here the routing tensors go to the device-side block path
+    (per-expert token lists, grouped gate|up + SwiGLU and down kernels, sum in expert order) in one call;
+    nothing is read back and the call can be captured into a graph.  ``act_fn`` must be SiLU.
+    """
+
+    def __init__(self, num_experts, hidden_dim, intermediate_dim, act_fn):
+        super().__init__()
+        self.num_experts = num_experts
+        self.hidden_dim = hidden_dim
+        self.intermediate_dim = intermediate_dim
+        self.gate_experts = nn.ModuleList([GLoRCQLinear(hidden_dim, intermediate_dim) for _ in range(num_experts)])
+        self.up_experts = nn.ModuleList([GLoRCQLinear(hidden_dim, intermediate_dim) for _ in range(num_experts)])
+        self.down_experts = nn.ModuleList([GLoRCQLinear(intermediate_dim, hidden_dim) for _ in range(num_experts)])
+        self.act_fn = act_fn
+        self._block = None
+
+    def _routed(self, top_k):
+        if self._block is None or self._block.top_k != top_k:
+            import torch.nn.functional as F
+            from types import SimpleNamespace
+            from .moe_block import GraphCompatibleMoeBlock
+            if self.act_fn not in (F.silu,) and not isinstance(self.act_fn, nn.SiLU):
+                raise RuntimeError("the fused expert kernels implement SiLU gating only")
+            shim = SimpleNamespace(num_experts=self.num_experts, top_k=top_k, norm_topk_prob=False, gate=None,
+                                   experts=[SimpleNamespace(gate_proj=g, up_proj=u, down_proj=d) for g, u, d in
+                                            zip(self.gate_experts, self.up_experts, self.down_experts)],
+                                   shared_expert=None, shared_expert_gate=None)
+            blk = GraphCompatibleMoeBlock(shim)
+            blk._graph_threshold = 0          # always the expert-order sum of index_add_
+            self._block = blk
+        return self._block
+
+    def forward(self, hidden_states, top_k_index, top_k_weights):
+        if not hidden_states.is_cuda:
+            raise RuntimeError("GLoRCQExperts runs on a CUDA device only (no CPU path)")
+        T, H = hidden_states.shape
+        blk = self._routed(top_k_index.shape[1])
+        out, _ = blk(hidden_states.reshape(1, T, H), top_k_index=top_k_index, top_k_weights=top_k_weights)
+        return out.reshape(T, H).to(hidden_states.dtype)

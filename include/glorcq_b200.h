@@ -278,6 +278,11 @@ enum { GLQ_MOE_PHASE_ALL = 0, GLQ_MOE_PHASE_EXPERTS = 1, GLQ_MOE_PHASE_COMBINE =
 typedef struct glq_moe_ep {
     int32_t rank, world, phase, reserved;
     void* entry_out; /* NULL: use the workspace (world == 1 only) */
+    /* Routing decided by the caller instead of the block's router (the fused-experts adapter
+     * GLoRCQExperts.forward, inference/quantized_linear.py:395-428): sel_in (n_tokens, top_k) int32 expert
+     * indices (an index outside [0, E) drops the slot), weight_in (n_tokens, top_k) fp16; both NULL for
+     * the block's own router.  Needs I_shared == 0 and router_logits == NULL; router_t is not read. */
+    const int32_t* sel_in; const void* weight_in;
 } glq_moe_ep_t;
 int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n_tokens, void* out, void* router_logits,
                        int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,

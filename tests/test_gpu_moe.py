@@ -202,3 +202,50 @@ def test_expert_parallel_two_gpus_nccl(dev):
         p.join(30)
     for rank, oks in res:
         assert all(oks), f"rank {rank}: expert-parallel output differs from the single-device block"
+
+
+# ---- fused-experts adapter --------------------------------------------------------------------------
+def _b200_experts(blk, dev):
+    import torch.nn.functional as F
+    from glorcq_b200.quantized_linear import GLoRCQExperts
+    ge = GLoRCQExperts(blk["E"], blk["H"], blk["I"], F.silu)
+    shared_u = {}
+    for e, ex in enumerate(blk["experts"]):
+        ge.gate_experts[e] = cases.to_b200_linear(ex["gate_proj"], dev, shared_u)
+        ge.up_experts[e] = cases.to_b200_linear(ex["up_proj"], dev, shared_u)
+        ge.down_experts[e] = cases.to_b200_linear(ex["down_proj"], dev, shared_u)
+    return ge
+
+
+def test_experts_adapter_against_golden_and_oracle(dev, golden):
+    g = golden["experts"]["experts_10"]
+    blk = cases.make_moe(**g["args"])
+    ge = _b200_experts(blk, dev)
+    x = cases.make_x(g["x_seed"], g["T"], g["args"]["H"])
+    y = ge(x.to(dev), g["idx"].to(dev), g["w"].to(dev)).cpu()
+    assert y.shape == g["y"].shape and y.dtype == torch.float16
+    assert cases.rel_l2(y, g["y"]) <= REL_BLOCK
+    ob = cases.to_oracle_moe(blk)
+    assert cases.rel_l2(y, O.experts_forward(ob.experts, x, g["idx"], g["w"])) <= REL_BLOCK
+
+
+@pytest.mark.parametrize("T", [1, 3, 50])
+def test_experts_adapter_token_counts_and_dropped_slots(dev, T):
+    kw = dict(seed=61, H=256, I=128, E=6, top_k=2, I_shared=0, rank=16, experts_per_cluster=2)
+    blk = cases.make_moe(**kw)
+    ge = _b200_experts(blk, dev)
+    x = cases.make_x(62 + T, T, 256)
+    gen = torch.Generator().manual_seed(63 + T)
+    idx = torch.stack([torch.randperm(6, generator=gen)[:2] for _ in range(T)])
+    w = torch.rand(T, 2, generator=gen).to(torch.float16)
+    ref = O.experts_forward(cases.to_oracle_moe(blk).experts, x, idx, w)
+    assert cases.rel_l2(ge(x.to(dev), idx.to(dev), w.to(dev)).cpu(), ref) <= REL_BLOCK
+    # index == num_experts marks a dropped slot: it contributes nothing
+    idx2 = idx.clone()
+    idx2[0, 1] = 6
+    w2 = w.clone()
+    w2[0, 1] = 0
+    idx_ref = idx2.clone()
+    idx_ref[0, 1] = idx2[0, 0] ^ 1          # any other expert, weight zero
+    ref2 = O.experts_forward(cases.to_oracle_moe(blk).experts, x, idx_ref, w2)
+    assert cases.rel_l2(ge(x.to(dev), idx2.to(dev), w2.to(dev)).cpu(), ref2) <= REL_BLOCK
