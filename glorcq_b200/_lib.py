@@ -36,7 +36,7 @@ class MMArgs(C.Structure):
                 ("entry_scale", vp),
                 ("x", vp), ("ldx", C.c_int64), ("a0", vp), ("a1", vp), ("lda", C.c_int64),
                 ("y", vp), ("ldy", C.c_int64), ("workspace", vp), ("workspace_bytes", C.c_size_t),
-                ("counters", vp), ("n_counters", C.c_size_t)]
+                ("counters", vp), ("n_counters", C.c_size_t), ("flags", C.c_int32), ("reserved", C.c_int32)]
 
 
 class MoeDesc(C.Structure):

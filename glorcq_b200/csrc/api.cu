@@ -205,6 +205,10 @@ struct StreamGeom {
     int grid;
 };
 
+static bool pdl_disabled() {
+    static const bool v = std::getenv("GLQ_NO_PDL") != nullptr;
+    return v;
+}
 static bool stream_disabled() {
     static int v = -1;
     if (v < 0) {
@@ -314,6 +318,21 @@ static int launch_stream_one(const StreamParams& sp, const StreamGeom& g, cudaSt
         GLQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
         if (dev >= 0 && dev < 16) configured[dev] = g.smem;
     }
+    if (sp.a_late) {
+        // programmatic dependent launch: may start while the previous launch of the stream still runs
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(g.grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = g.smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        GLQ_CUDA(cudaLaunchKernelEx(&cfg, kern, sp));
+        return GLQ_OK;
+    }
     kern<<<g.grid, kThreads, g.smem, st>>>(sp);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
@@ -333,8 +352,9 @@ static int launch_stream_fmt(const StreamParams& sp, const StreamGeom& g, cudaSt
 }
 
 static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, int K, int rank, int n_problems,
-                         cudaStream_t st) {
+                         cudaStream_t st, bool a_late = false) {
     StreamParams sp{};
+    sp.a_late = (a_late && rank > 0 && p.a[0] != nullptr && !pdl_disabled()) ? 1 : 0;
     p.nkb = g.nkb;
     p.ntc = g.ntc;
     p.kb_chunk = g.nkb;
@@ -550,7 +570,8 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     p.epilogue = a->epilogue;
     p.x_vec = (aligned16(a->x) && a->ldx % 8 == 0) ? 1 : 0;
     if (use_stream)
-        return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
+        return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, reinterpret_cast<cudaStream_t>(stream),
+                             (a->flags & GLQ_MM_A_FROM_PREVIOUS_LAUNCH) != 0);
     fill_geometry(p, g);
     return launch_skinny(a->fmt, false, p, g, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
 }

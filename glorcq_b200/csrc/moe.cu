@@ -454,6 +454,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         m.a0 = a_gate;
         m.a1 = a_up;
         m.lda = R;
+        m.flags = GLQ_MM_A_FROM_PREVIOUS_LAUNCH;    // the x.U launch directly before; x and the lists are older
     }
     m.y = ws + L.h;
     m.ldy = d->I;
@@ -485,6 +486,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if (R > 0) {
         m.a0 = ws + L.b;
         m.lda = R;
+        if (hq == ws + L.h) m.flags = GLQ_MM_A_FROM_PREVIOUS_LAUNCH;   // h.U directly before; not when a rotation sits between
     }
     m.y = p_yd;
     m.ldy = d->H;
@@ -557,6 +559,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         if (lr) {
             m.a0 = ws + L.bs;
             m.lda = R;
+            if (hsq == ws + L.hs) m.flags = GLQ_MM_A_FROM_PREVIOUS_LAUNCH;
         }
         m.y = ws + L.ysh;
         m.ldy = d->H;

@@ -335,6 +335,9 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
     constexpr int kDepth = F::DEPTH;
     extern __shared__ uint4 smem_u4[];
     __shared__ int s_last;
+    // lets a successor launched with programmatic stream serialization start its independent part now
+    // (it still waits for this grid to finish before it reads what this grid writes); no effect otherwise
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     int bid = blockIdx.x;
     const int s = bid % p.sk;

@@ -51,6 +51,7 @@ struct StreamParams {
     int stages;        // ring depth
     int stage_bytes;
     int off_xs, off_ox, off_as, off_ring, off_red;  // shared memory carve-up (bytes)
+    int a_late;   // 1: the x.U operand is still being written when this kernel starts (programmatic dependent launch)
 };
 
 // ---- shared memory, mbarrier and bulk copy primitives ------------------------------------------
@@ -108,6 +109,11 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, bool& d
         }
         __nanosleep(64);
     }
+}
+__device__ __forceinline__ uint4 ld_global_u4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -447,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
 
     uint32_t TL[2] = {0, 0}, TH[2] = {0, 0};  // codebook tables of the two tiles of a pair
     int staged_slot = -1, red_par = 0;
+    bool dep_waited = false;
     constexpr int ncol_i8 = 2 * kRows;  // digit columns staged on the integer path
 
     int c_slot = it_lo / sp.ips, c_rem = it_lo % sp.ips;
@@ -464,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                     stage_x_i8<FMT>(p, xs, ox, nkb, ncol_i8, e0, cnt, K);
                 else
                     stage_x<FMT>(p, xs, ox, 0, nkb, e0, 0, cnt, K);
-                if (cs.sv != nullptr) {
+                if (cs.sv != nullptr && !sp.a_late) {
                     const int na = swiglu ? 2 : 1, r8 = rank / 8;
                     for (int idx = tid; idx < na * kRows * r8; idx += kThreads) {
                         const int i = idx / (kRows * r8), rem = idx % (kRows * r8);
@@ -624,6 +631,11 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
 #pragma unroll
                 for (int q = 0; q < 4; ++q) lo[j][m][q] = 0.f;
         const int nsv = im.nch - im.ncode;
+        if (sp.a_late && nsv > 0 && !dep_waited) {
+            // programmatic dependent launch: everything up to here overlapped the launch that produces x.U
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            dep_waited = true;
+        }
         for (int c = 0; c < nsv; ++c) {
             const uint32_t st = ring_wait();
             // every lane runs the (warp-wide) op; lanes beyond the rank feed zeros
@@ -639,9 +651,17 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                 for (int m = 0; m < NM; ++m) {
                     const int row = m * 8 + g;
                     const bool ok = in_rank && row < kRows;
-                    const uint4* pav = reinterpret_cast<const uint4*>(
-                        as + ((size_t)(swiglu ? j : 0) * kRows + (ok ? row : 0)) * rank + (ok ? cc0 : 0));
-                    const uint4 av0 = ok ? pav[0] : z4, av1 = ok ? pav[1] : z4;
+                    uint4 av0 = z4, av1 = z4;
+                    if (!sp.a_late) {
+                        const uint4* pav = reinterpret_cast<const uint4*>(
+                            as + ((size_t)(swiglu ? j : 0) * kRows + (ok ? row : 0)) * rank + (ok ? cc0 : 0));
+                        if (ok) av0 = pav[0], av1 = pav[1];
+                    } else if (ok && row < cnt) {
+                        // written by the launch before this one, which has completed by now (see the wait above)
+                        const uint4* pav = reinterpret_cast<const uint4*>(p.a[swiglu ? j : 0] + (size_t)(e0 + row) * p.lda + cc0);
+                        av0 = ld_global_u4(pav);
+                        av1 = ld_global_u4(pav + 1);
+                    }
                     mma16816(lo[j][m], sa0.x, sb0.x, sa0.y, sb0.y, av0.x, av0.y);
                     mma16816(lo[j][m], sa0.z, sb0.z, sa0.w, sb0.w, av0.z, av0.w);
                     mma16816(lo[j][m], sa1.x, sb1.x, sa1.y, sb1.y, av1.x, av1.y);

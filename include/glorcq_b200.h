@@ -181,7 +181,13 @@ typedef struct glq_mm_args {
     void* workspace; size_t workspace_bytes; /* scratch: split-k partial sums, or the re-tiled activations
                                                 of the many-row path (contents irrelevant)               */
     int32_t* counters; size_t n_counters;    /* arrival counters: zero before the first use, left zero   */
+    int32_t flags;    /* GLQ_MM_* */
+    int32_t reserved;
 } glq_mm_args_t;
+/* a0 / a1 are written by the launch issued on this stream immediately before this call, and nothing
+ * else this call reads is: the kernel may then be launched programmatically dependent (it starts while
+ * that launch still runs and waits for it only before the low-rank term). */
+#define GLQ_MM_A_FROM_PREVIOUS_LAUNCH 1
 
 /* Scratch bytes / arrival counters a call with these args needs (both 0 when no CTA-level k split is
  * used).  The counters must be zero when a call starts and are zero again when it ends, so one
