@@ -135,6 +135,25 @@ static int plan_geometry(int fmt, int epilogue, int N, int K, int group_size, in
     return GLQ_OK;
 }
 
+// launch with programmatic stream serialization: the grid may be scheduled while the previous kernel of
+// the stream still runs; the kernels wait for it (griddepcontrol.wait) before they read its results
+static thread_local bool t_dependent_launch = false;
+template <typename Kern, typename Params>
+static int launch_dependent(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, const Params& p) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    GLQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return GLQ_OK;
+}
+
 template <int FMT, int NW, int NTT, bool RM>
 static int launch_one(const SkinnyParams& p, int grid, size_t smem, cudaStream_t st) {
     auto kern = skinny_kernel<FMT, NW, NTT, RM>;
@@ -147,6 +166,7 @@ static int launch_one(const SkinnyParams& p, int grid, size_t smem, cudaStream_t
             if (dev >= 0 && dev < 16) configured[dev] = smem;
         }
     }
+    if (t_dependent_launch) return launch_dependent(kern, dim3(grid), dim3(kThreads), smem, st, p);
     kern<<<grid, kThreads, smem, st>>>(p);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
@@ -318,21 +338,7 @@ static int launch_stream_one(const StreamParams& sp, const StreamGeom& g, cudaSt
         GLQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
         if (dev >= 0 && dev < 16) configured[dev] = g.smem;
     }
-    if (sp.a_late) {
-        // programmatic dependent launch: may start while the previous launch of the stream still runs
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(g.grid);
-        cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = g.smem;
-        cfg.stream = st;
-        cudaLaunchAttribute attr{};
-        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr.val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        GLQ_CUDA(cudaLaunchKernelEx(&cfg, kern, sp));
-        return GLQ_OK;
-    }
+    if (sp.a_late || sp.dependent) return launch_dependent(kern, dim3(g.grid), dim3(kThreads), g.smem, st, sp);
     kern<<<g.grid, kThreads, g.smem, st>>>(sp);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
@@ -352,9 +358,10 @@ static int launch_stream_fmt(const StreamParams& sp, const StreamGeom& g, cudaSt
 }
 
 static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, int K, int rank, int n_problems,
-                         cudaStream_t st, bool a_late = false) {
+                         cudaStream_t st, bool a_late = false, bool dependent = false) {
     StreamParams sp{};
     sp.a_late = (a_late && rank > 0 && p.a[0] != nullptr && !pdl_disabled()) ? 1 : 0;
+    sp.dependent = ((dependent || a_late) && !pdl_disabled()) ? 1 : 0;
     p.nkb = g.nkb;
     p.ntc = g.ntc;
     p.kb_chunk = g.nkb;
@@ -571,9 +578,12 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     p.x_vec = (aligned16(a->x) && a->ldx % 8 == 0) ? 1 : 0;
     if (use_stream)
         return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, reinterpret_cast<cudaStream_t>(stream),
-                             (a->flags & GLQ_MM_A_FROM_PREVIOUS_LAUNCH) != 0);
+                             (a->flags & GLQ_MM_A_FROM_PREVIOUS_LAUNCH) != 0, (a->flags & GLQ_MM_AFTER_KERNEL) != 0);
     fill_geometry(p, g);
-    return launch_skinny(a->fmt, false, p, g, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
+    t_dependent_launch = (a->flags & (GLQ_MM_AFTER_KERNEL | GLQ_MM_A_FROM_PREVIOUS_LAUNCH)) != 0 && !pdl_disabled();
+    rc = launch_skinny(a->fmt, false, p, g, a->n_problems, reinterpret_cast<cudaStream_t>(stream));
+    t_dependent_launch = false;
+    return rc;
 }
 
 // ---------------------------------------------------------------------------------------------

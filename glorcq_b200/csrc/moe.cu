@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "glq_common.cuh"
@@ -15,6 +16,10 @@ using namespace glq;
 namespace {
 
 inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+inline bool no_dependent_launch() {
+    static const bool v = std::getenv("GLQ_NO_PDL") != nullptr;
+    return v;
+}
 
 // ---- workspace carve-up ---------------------------------------------------------------------------
 struct MoeLayout {
@@ -111,9 +116,10 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
 }
 
 // ---- routing plan -----------------------------------------------------------------------------------
-// One CTA.  Phase A, thread per token: softmax over the fp16 router logits in fp32, top-k (ties to
-// the lower expert index), optional renormalisation, weights rounded to fp16.  Phase B, thread per
-// expert: the expert's entry list in token order (deterministic), then the list of live experts.
+// One CTA.  Phase A, warp per token: softmax over the fp16 router logits in fp32, top-k (ties to
+// the lower expert index), optional renormalisation, weights rounded to fp16.  Phase B, warp per
+// expert: entry counts, offsets and the expert's entry list in token order (ballot scans:
+// deterministic), and the compacted list of live experts.
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict__ logits, int ldl, int n, int E, int k,
                                                         int renorm, int* __restrict__ sel, __half* __restrict__ wts,
                                                         int* __restrict__ active, int* __restrict__ n_active,
@@ -127,6 +133,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
                                                         const __half* __restrict__ wts_in) {
     extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
     int* sm_off = sm_cnt + E;
+    asm volatile("griddepcontrol.wait;" ::: "memory");              // no-ops for a plain launch
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // Phase A: one warp per token, lanes over experts (E <= 256)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     if (sel_in) {
@@ -199,49 +207,77 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
             for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = row[e];
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int nk = n * k;
+    const unsigned lt = (1u << lane) - 1u;
+    // Phase B1: entries per expert, one warp per expert (ballot counts: no atomics, any order gives the same sum)
+    for (int e = warp; e < E; e += nwarps) {
         int c = 0;
-        for (int i = 0; i < n * k; ++i) c += (sel[i] == e);
-        sm_cnt[e] = c;
+        for (int i0 = 0; i0 < nk; i0 += 32) {
+            const int i = i0 + lane;
+            c += __popc(__ballot_sync(0xffffffffu, i < nk && sel[i] == e));
+        }
+        if (lane == 0) sm_cnt[e] = c;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, j = 0;
-        for (int e = 0; e < E; ++e) {
-            sm_off[e] = off;
-            // entry offsets are global (every rank numbers the entries alike); only the experts this
-            // rank holds (e mod world == rank) become problems of its matmul launches
-            if (sm_cnt[e] > 0 && e % ep_world == ep_rank) {
-                active[j] = e;
-                slot_count[j] = sm_cnt[e];
-                slot_offset[j] = off;
-                ++j;
+    // Phase B2, warp 0: exclusive prefix of the counts (entry offsets are global: every rank numbers the
+    // entries alike) and the compacted list of live experts this rank holds (e mod world == rank)
+    if (warp == 0) {
+        int base = 0, j = 0;
+        for (int e0 = 0; e0 < E; e0 += 32) {
+            const int e = e0 + lane;
+            const int c = e < E ? sm_cnt[e] : 0;
+            int v = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int tv = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += tv;
             }
-            off += sm_cnt[e];
+            const int off = base + v - c;
+            if (e < E) sm_off[e] = off;
+            const bool act = e < E && c > 0 && e % ep_world == ep_rank;
+            const unsigned m = __ballot_sync(0xffffffffu, act);
+            if (act) {
+                const int pos = j + __popc(m & lt);
+                active[pos] = e;
+                slot_count[pos] = c;
+                slot_offset[pos] = off;
+                // the same lists twice, for gate (table entry e, entries 0..nk) and up (entry E+e, entries nk..2nk)
+                active2[pos] = e;
+                slot_count2[pos] = c;
+                slot_offset2[pos] = off;
+            }
+            j += __popc(m);
+            base += __shfl_sync(0xffffffffu, v, 31);
         }
-        *n_active = j;
-        // the same lists twice, for gate (table entry e, entries 0..nk) and up (entry E+e, entries nk..2nk)
-        for (int i = 0; i < j; ++i) {
-            active2[i] = active[i];
+        __syncwarp();
+        for (int i = lane; i < j; i += 32) {
             active2[j + i] = E + active[i];
-            slot_count2[i] = slot_count2[j + i] = slot_count[i];
-            slot_offset2[i] = slot_offset[i];
-            slot_offset2[j + i] = n * k + slot_offset[i];
+            slot_count2[j + i] = slot_count[i];
+            slot_offset2[j + i] = nk + slot_offset[i];
         }
-        *n_active2 = 2 * j;
+        if (lane == 0) {
+            *n_active = j;
+            *n_active2 = 2 * j;
+        }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int pos = sm_off[e];
+    // Phase B3: each expert's entries in token order, one warp per expert
+    for (int e = warp; e < E; e += nwarps) {
         if (sm_cnt[e] == 0) continue;
-        for (int i = 0; i < n * k; ++i)
-            if (sel[i] == e) {
-                entry_row[pos] = i / k;
-                entry_row[n * k + pos] = i / k;
-                entry_scale[pos] = wts[i];
-                tok_entries[i] = pos;
-                ++pos;
+        int pos = sm_off[e];
+        for (int i0 = 0; i0 < nk; i0 += 32) {
+            const int i = i0 + lane;
+            const bool hit = i < nk && sel[i] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int q = pos + __popc(m & lt);
+                entry_row[q] = i / k;
+                entry_row[nk + q] = i / k;
+                entry_scale[q] = wts[i];
+                tok_entries[i] = q;
             }
+            pos += __popc(m);
+        }
     }
 }
 
@@ -252,6 +288,7 @@ __global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __r
                                    const int* __restrict__ sel, int k, int H, int by_expert,
                                    const __half* __restrict__ ysh, const __half* __restrict__ logits, int ldl,
                                    int gate_col, __half* __restrict__ out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");              // no-op for a plain launch
     const int t = blockIdx.y;
     const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c0 >= H) return;
@@ -360,7 +397,14 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     // the combine) when the caller provides a stream and two events; it has its own scratch and counters
     const bool forked = aux_stream != nullptr && ev_fork != nullptr && ev_join != nullptr;
     bool on_aux = false;
+    // programmatic dependent launches: allowed when the previous operation on the stream was one of this
+    // library's launches (not the first launch of the call, not after an event wait)
+    bool after_kernel[2] = {false, false};
     auto finish = [&](glq_mm_args_t& mm) {
+        // (chaining every launch this way, GLQ_MM_AFTER_KERNEL, measured no faster than plain launches
+        // inside a graph: only the two x.U edges, whose consumers have real independent work, are used)
+        if (!after_kernel[on_aux ? 1 : 0]) mm.flags &= ~GLQ_MM_A_FROM_PREVIOUS_LAUNCH;
+        after_kernel[on_aux ? 1 : 0] = true;
         mm.workspace = ws + (on_aux ? L.mm2 : L.mm);
         mm.workspace_bytes = L.mm_bytes;
         mm.counters = counters ? counters + (on_aux ? L.mm_counters : 0) : nullptr;
@@ -408,13 +452,27 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if (forked && cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_fork), st) != cudaSuccess) return GLQ_ERR_CUDA;
 
     // 2. routing plan
-    moe_plan_kernel<<<1, 1024, 2 * d->E * sizeof(int), st>>>(
-        p_logits, ldl, n, d->E, k, d->norm_topk_prob, p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow,
-        p_escale, p_tok, reinterpret_cast<__half*>(router_logits), sel_out, reinterpret_cast<__half*>(weight_out),
-        reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
-        reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2), ep_rank, ep_world,
-        given ? ep->sel_in : nullptr, given ? reinterpret_cast<const __half*>(ep->weight_in) : nullptr);
-    if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
+    {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(1);
+        cfg.blockDim = dim3(1024);
+        cfg.dynamicSmemBytes = 2 * d->E * sizeof(int);
+        cfg.stream = st;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 0;   // plain launch (a dependent launch after the router product measured no faster)
+        if (cudaLaunchKernelEx(&cfg, moe_plan_kernel, (const __half*)p_logits, ldl, n, (int)d->E, k, (int)d->norm_topk_prob,
+                               p_sel, p_wts, p_active, p_nact, p_cnt, p_off, p_erow, p_escale, p_tok,
+                               reinterpret_cast<__half*>(router_logits), (int*)sel_out, reinterpret_cast<__half*>(weight_out),
+                               reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
+                               reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2),
+                               ep_rank, ep_world, given ? (const int*)ep->sel_in : (const int*)nullptr,
+                               given ? reinterpret_cast<const __half*>(ep->weight_in) : (const __half*)nullptr) != cudaSuccess)
+            return GLQ_ERR_CUDA;
+        after_kernel[0] = true;
+    }
     // rows of remote experts' entries stay zero, so that summing the ranks' buffers is exact
     if (ep_world > 1 && cudaMemsetAsync(p_yd, 0, (size_t)nk * d->H * 2, st) != cudaSuccess) return GLQ_ERR_CUDA;
 

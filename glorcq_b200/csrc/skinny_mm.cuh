@@ -335,8 +335,10 @@ __global__ void __launch_bounds__(kThreads, 2) skinny_kernel(const SkinnyParams 
     constexpr int kDepth = F::DEPTH;
     extern __shared__ uint4 smem_u4[];
     __shared__ int s_last;
-    // lets a successor launched with programmatic stream serialization start its independent part now
-    // (it still waits for this grid to finish before it reads what this grid writes); no effect otherwise
+    // Programmatic dependent launch, both no-ops for a plain launch: wait for the preceding grid of the
+    // stream (this kernel reads its results from the first load on), then let the next grid be scheduled
+    // (it waits for this one in the same way before it reads what this one writes).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     int bid = blockIdx.x;

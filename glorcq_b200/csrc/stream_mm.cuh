@@ -51,6 +51,7 @@ struct StreamParams {
     int stages;        // ring depth
     int stage_bytes;
     int off_xs, off_ox, off_as, off_ring, off_red;  // shared memory carve-up (bytes)
+    int dependent;  // 1: launched with programmatic stream serialization
     int a_late;   // 1: the x.U operand is still being written when this kernel starts (programmatic dependent launch)
 };
 
@@ -326,6 +327,10 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
     const bool swiglu = sp.swiglu != 0;
     const int ns = (rank + 63) / 64;
 
+    // Programmatic dependent launch (no-ops for a plain launch).  a_late: only the x.U operand comes from
+    // the preceding grid, the wait sits in front of the low-rank term; otherwise wait here.
+    if (!sp.a_late) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int n_live = p.n_slots ? min(__ldg(p.n_slots), sp.n_problems) : sp.n_problems;
     const long total = (long)n_live * sp.ips;
     const int it_lo = (int)((long)blockIdx.x * total / gridDim.x);

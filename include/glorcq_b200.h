@@ -188,6 +188,10 @@ typedef struct glq_mm_args {
  * else this call reads is: the kernel may then be launched programmatically dependent (it starts while
  * that launch still runs and waits for it only before the low-rank term). */
 #define GLQ_MM_A_FROM_PREVIOUS_LAUNCH 1
+/* The operation issued on this stream immediately before this call is a kernel launch of this library
+ * (no event wait or foreign work in between): the launch may be programmatically dependent on it; the
+ * kernel waits for that launch before its first load. */
+#define GLQ_MM_AFTER_KERNEL 2
 
 /* Scratch bytes / arrival counters a call with these args needs (both 0 when no CTA-level k split is
  * used).  The counters must be zero when a call starts and are zero again when it ends, so one
