@@ -261,6 +261,32 @@ def gemm_roofline(dev, P=8, rows=1024, iters=20):
             "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), {rows} rows each"}
 
 
+def run_full_model(args):
+    """BASELINE config 3: the whole Qwen1.5-MoE-A2.7B-shaped decoder (attention 4-bit g128, experts 2-bit
+    rank 64 with 128 random cross-layer U clusters, fp16 lm_head), 512-token prefill then 256 greedy decode
+    steps replayed from one CUDA graph.  Printed as its own JSON line (not the driver's metric line)."""
+    from glorcq_b200 import _build, synthetic
+    from glorcq_b200.graph_wrapper import GLoRCQGraphWrapper
+    _build.build()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    cfg = dict(synthetic.QWEN15_MOE_A27B)
+    cfg["num_hidden_layers"] = args.layers
+    model = synthetic.make_decoder(cfg, dev, seed=77)
+    w = GLoRCQGraphWrapper(model, max_batch_size=1, max_seq_len=1024)
+    ids = torch.randint(0, cfg["vocab_size"], (1, args.prompt), generator=torch.Generator().manual_seed(5)).to(dev)
+    w.capture_graph()
+    w.generate(ids, max_new_tokens=8)                   # warm-up of prefill and replay
+    out, seconds = w.generate(ids, max_new_tokens=args.new_tokens)
+    line = {"full_model": {"workload": f"Qwen1.5-MoE-A2.7B-shaped decoder, {args.layers} layers, prompt {args.prompt}, "
+                                       f"{args.new_tokens} greedy tokens, CUDA graph decode",
+                           "decode_tok_s": (args.new_tokens - 1) / w.last_decode_seconds,
+                           "prefill_tok_s": args.prompt / w.last_prefill_seconds,
+                           "prefill_s": w.last_prefill_seconds, "decode_s": w.last_decode_seconds, "total_s": seconds,
+                           "generated": int(out.shape[1] - ids.shape[1])}}
+    print(json.dumps(line), flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from glorcq_b200 import _build, synthetic, tiled
@@ -426,6 +452,10 @@ def main():
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the grouped dequant-GEMV roofline case (small enough for an ncu capture)")
+    ap.add_argument("--full-model", action="store_true",
+                    help="time the whole decoder (prefill + graph decode) instead of the MoE-block metric line")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--gemm-only", action="store_true",
                     help="time only the grouped tcgen05 dequant-GEMM roofline case (small enough for an ncu capture)")
     ap.add_argument("--rows", type=int, default=1024)
@@ -448,6 +478,9 @@ def main():
         peak, kind = measured_peak_gbs()
         print(json.dumps({"roofline": gemv_roofline(torch.device("cuda:0"), peak, kind, P=args.problems,
                                                      iters=max(1, args.steps))}), flush=True)
+        return
+    if args.full_model:
+        run_full_model(args)
         return
     if args.gemm_only:
         from glorcq_b200 import _build

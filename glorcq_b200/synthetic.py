@@ -209,3 +209,69 @@ def write_checkpoint(path, hf_config: dict, **kw):
     torch.save(cross, os.path.join(path, "cross_layer_info.pt"))
     torch.save(dense, os.path.join(path, "dense_weights.pt"))
     return model_data, cross, dense
+
+
+def make_decoder(hf_config: dict, device, seed=0, qbit=2, attn_bits=4, rank=64, attn_rank=64, groupsize=128,
+                 n_clusters=128):
+    """A whole random decoder of the given shape built directly on the device (no files: the int32 code
+    tensors of the on-disk format would be 4 bytes per weight).  Same distributions and cluster rule as
+    make_checkpoint: every (layer, expert, projection) draws its U cluster from `n_clusters`; attention
+    projections are `attn_bits` codes with their own clusters; the shared expert has no low-rank term."""
+    from .decoder import GLoRCQDecoder
+    c = hf_config
+    H, L = c["hidden_size"], c["num_hidden_layers"]
+    nh, nkv = c["num_attention_heads"], c.get("num_key_value_heads") or c["num_attention_heads"]
+    hd = c.get("head_dim") or H // nh
+    E = c.get("num_experts", c.get("num_local_experts", 0))
+    mixtral = "num_local_experts" in c
+    I = c.get("moe_intermediate_size", c.get("intermediate_size"))
+    Ish = c.get("shared_expert_intermediate_size", 0)
+    mp = "block_sparse_moe" if mixtral else "mlp"
+    names = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+    wt_of = dict(zip(names, ("gate_proj", "up_proj", "down_proj")))
+    shapes = {"q_proj": (nh * hd, H), "k_proj": (nkv * hd, H), "v_proj": (nkv * hd, H), "o_proj": (H, nh * hd),
+              "gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    pools = {}
+
+    def U(wtype, r):
+        gid = int(torch.randint(0, n_clusters, (1,), generator=gen, device=device))
+        if (wtype, gid) not in pools:
+            pools[(wtype, gid)] = (torch.randn(shapes[wtype][1], r, generator=gen, device=device) * 0.01).half()
+        return pools[(wtype, gid)]
+
+    layers, dense = {}, {}
+    for l in range(L):
+        mods = {}
+        for w in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            mods[f"self_attn.{w}"] = _linear(gen, *shapes[w], attn_rank, U(w, attn_rank), device, bits=attn_bits,
+                                             groupsize=groupsize)
+        if E:
+            for e in range(E):
+                for nm in names:
+                    w = wt_of[nm]
+                    mods[f"{mp}.experts.{e}.{nm}"] = _linear(gen, *shapes[w], rank, U(w, rank), device, bits=qbit,
+                                                             groupsize=groupsize)
+            if Ish:
+                mods[f"{mp}.shared_expert.gate_proj"] = _linear(gen, Ish, H, 0, None, device, bits=qbit, groupsize=groupsize)
+                mods[f"{mp}.shared_expert.up_proj"] = _linear(gen, Ish, H, 0, None, device, bits=qbit, groupsize=groupsize)
+                mods[f"{mp}.shared_expert.down_proj"] = _linear(gen, H, Ish, 0, None, device, bits=qbit, groupsize=groupsize)
+                dense[f"model.layers.{l}.{mp}.shared_expert_gate.weight"] = (torch.randn(1, H, generator=gen, device=device) * 0.02).half()
+            dense[f"model.layers.{l}.{mp}.gate.weight"] = (torch.randn(E, H, generator=gen, device=device) * 0.02).half()
+        else:
+            for nm in ("gate_proj", "up_proj", "down_proj"):
+                mods[f"mlp.{nm}"] = _linear(gen, *shapes[nm], rank, U(nm, rank), device, bits=qbit, groupsize=groupsize)
+        layers[l] = mods
+        dense[f"model.layers.{l}.input_layernorm.weight"] = torch.ones(H, device=device).half()
+        dense[f"model.layers.{l}.post_attention_layernorm.weight"] = torch.ones(H, device=device).half()
+    dense["model.embed_tokens.weight"] = (torch.randn(c["vocab_size"], H, generator=gen, device=device) * 0.02).half()
+    dense["lm_head.weight"] = (torch.randn(c["vocab_size"], H, generator=gen, device=device) * 0.02).half()
+    dense["model.norm.weight"] = torch.ones(H, device=device).half()
+    return GLoRCQDecoder(hf_config, layers, dense=dense, device=device)
+
+
+QWEN15_MOE_A27B = dict(hidden_size=2048, num_hidden_layers=24, num_attention_heads=16, num_key_value_heads=16,
+                       vocab_size=151936, num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408,
+                       shared_expert_intermediate_size=5632, norm_topk_prob=False, rms_norm_eps=1e-6,
+                       rope_theta=1000000.0, max_position_embeddings=8192)
