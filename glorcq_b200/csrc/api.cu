@@ -358,8 +358,11 @@ static int launch_stream_fmt(const StreamParams& sp, const StreamGeom& g, cudaSt
 }
 
 static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, int K, int rank, int n_problems,
-                         cudaStream_t st, bool a_late = false, bool dependent = false) {
+                         cudaStream_t st, bool a_late = false, bool dependent = false, int cnt_lo = 0,
+                         int cnt_hi = 0x7fffffff) {
     StreamParams sp{};
+    sp.cnt_lo = cnt_lo;
+    sp.cnt_hi = cnt_hi;
     sp.a_late = (a_late && rank > 0 && p.a[0] != nullptr && !pdl_disabled()) ? 1 : 0;
     sp.dependent = ((dependent || a_late) && !pdl_disabled()) ? 1 : 0;
     p.nkb = g.nkb;
@@ -401,9 +404,14 @@ static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, i
 // ---------------------------------------------------------------------------------------------
 struct TcGeom {
     int tn, nkb, ns, na, tiles_max;
+    bool hybrid;
     long long tile_bytes;
     size_t xp_bytes;
 };
+static bool hybrid_disabled() {
+    static const bool v = std::getenv("GLQ_NO_HYBRID") != nullptr;
+    return v;
+}
 static bool tc_disabled() {
     static const bool v = std::getenv("GLQ_NO_TC") != nullptr;
     return v;
@@ -432,6 +440,10 @@ static bool plan_tc(const glq_mm_args_t* a, TcGeom* out) {
     g.tiles_max = (int)tiles;
     g.tile_bytes = (long long)g.nkb * g.tn * 256 + (long long)g.ns * g.na * g.tn * 128;
     g.xp_bytes = (size_t)g.tiles_max * (size_t)g.tile_bytes;
+    // device-side row counts with few rows per problem on average: the streaming kernels take the
+    // problems with up to 32 rows (one launch for <= 8 rows on the integer path, one for 9..32), this
+    // kernel only the larger ones
+    g.hybrid = a->slot_count != nullptr && a->fmt != GLQ_FMT_F16 && total / a->n_problems <= 24 && !hybrid_disabled();
     *out = g;
     return true;
 }
@@ -453,7 +465,7 @@ static int launch_tc_t(const TcParams& p, int N, cudaStream_t st) {
     return GLQ_OK;
 }
 
-static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st) {
+static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st, int min_rows = 0) {
     if (!a->workspace || a->workspace_bytes < g.xp_bytes) return GLQ_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(a->workspace) & 127u) != 0) return GLQ_ERR_ALIGN;
     TcParams p{};
@@ -485,6 +497,7 @@ static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st) {
     p.tiles_max = g.tiles_max;
     p.x_vec = ((reinterpret_cast<uintptr_t>(a->x) & 7u) == 0 && a->ldx % 4 == 0) ? 1 : 0;
     p.fmt = a->fmt;
+    p.min_rows = min_rows;
     const bool sw = a->epilogue == GLQ_EPI_SWIGLU;
     const bool big = g.tn == 128;
     switch (a->fmt) {
@@ -534,13 +547,23 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     if (a->rank > 0 && (a->a0 || a->a1) && (a->lda % 8 != 0 || !aligned16(a->a0) || !aligned16(a->a1)))
         return GLQ_ERR_ALIGN;
     TcGeom tg;
-    if (plan_tc(a, &tg)) {
+    const bool use_tc = plan_tc(a, &tg);
+    if (use_tc && !tg.hybrid) {
         if (!a->w_table && !a->w.codes) return GLQ_ERR_ARG;
         return launch_tc(a, tg, reinterpret_cast<cudaStream_t>(stream));
     }
     StreamGeom sg;
-    const bool use_stream =
-        plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, a->max_rows, &sg);
+    StreamGeom sg8;
+    bool use_stream =
+        plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, std::min(a->max_rows, 32), &sg);
+    // device-side row counts: slots with at most 8 rows go to the integer path in a launch of their own
+    const bool split8 = use_stream && a->slot_count != nullptr && a->max_rows > 8 && !sg.i8 && !hybrid_disabled() &&
+                        plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, 8, &sg8) &&
+                        sg8.i8;
+    if (use_tc && !use_stream) {
+        if (!a->w_table && !a->w.codes) return GLQ_ERR_ARG;
+        return launch_tc(a, tg, reinterpret_cast<cudaStream_t>(stream));
+    }
     Geometry g{};
     int rc = use_stream ? GLQ_OK
                         : plan_geometry(a->fmt, a->epilogue, a->N, a->K, a->group_size, a->n_problems, a->max_rows,
@@ -576,9 +599,28 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     p.rows_stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
     p.epilogue = a->epilogue;
     p.x_vec = (aligned16(a->x) && a->ldx % 8 == 0) ? 1 : 0;
-    if (use_stream)
-        return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, reinterpret_cast<cudaStream_t>(stream),
-                             (a->flags & GLQ_MM_A_FROM_PREVIOUS_LAUNCH) != 0, (a->flags & GLQ_MM_AFTER_KERNEL) != 0);
+    if (use_stream) {
+        cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+        const bool a_late = (a->flags & GLQ_MM_A_FROM_PREVIOUS_LAUNCH) != 0, dep = (a->flags & GLQ_MM_AFTER_KERNEL) != 0;
+        if (!split8 && !use_tc) return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, st, a_late, dep);
+        // one launch per range of rows; only the first may depend programmatically on the producer of x.U
+        // (the later ones start after it has finished)
+        int lo = 0;
+        if (split8) {
+            SkinnyParams p8 = p;
+            p8.max_rows = 8;
+            if ((rc = launch_stream(a->fmt, p8, sg8, a->N, a->K, a->rank, a->n_problems, st, a_late, dep, 0, 8)) != GLQ_OK)
+                return rc;
+            lo = 8;
+        }
+        SkinnyParams p32 = p;
+        p32.max_rows = std::min(a->max_rows, 32);
+        if ((rc = launch_stream(a->fmt, p32, sg, a->N, a->K, a->rank, a->n_problems, st, lo == 0 && a_late, lo == 0 && dep,
+                                lo, 32)) != GLQ_OK)
+            return rc;
+        if (use_tc) return launch_tc(a, tg, st, 32);
+        return GLQ_OK;
+    }
     fill_geometry(p, g);
     t_dependent_launch = (a->flags & (GLQ_MM_AFTER_KERNEL | GLQ_MM_A_FROM_PREVIOUS_LAUNCH)) != 0 && !pdl_disabled();
     rc = launch_skinny(a->fmt, false, p, g, a->n_problems, reinterpret_cast<cudaStream_t>(stream));

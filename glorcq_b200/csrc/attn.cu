@@ -1,0 +1,158 @@
+// One decode step of grouped-query attention over a static key/value cache, in one launch: optional
+// per-head RMS norm of q and k, rotary embedding (rotate-half convention) of q and of the new key at
+// the current position, cache write, softmax(q k^T / sqrt(hd)) v over positions 0..pos.
+// The position is read from device memory, so a captured launch serves every step of a replayed graph
+// and only the live part of the cache is read.  Host model code around the quantized projections
+// (inference/graph_wrapper.py:84-127 drives the transformers attention modules for this).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "glq_common.cuh"
+
+using namespace glq;
+
+namespace {
+
+constexpr int kAttnWarps = 8;
+
+// EPL: head_dim / 32 elements per lane; lane l owns elements [l*EPL, (l+1)*EPL); its rotate-half partner
+// (element +- hd/2) sits in lane l ^ 16 at the same offset.
+template <int EPL>
+__device__ __forceinline__ void rope_norm(float (&v)[EPL], const __half* __restrict__ norm_w, float eps, int hd,
+                                          const __half* __restrict__ cs, const __half* __restrict__ sn, int lane) {
+    if (norm_w) {   // RMS norm over the head, weight applied, rounded to fp16 as a tensor op does
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float r = rsqrtf(ss / hd + eps);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) v[i] = round16(__half2float(norm_w[lane * EPL + i]) * (v[i] * r));
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+        const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        const float rot = lane < 16 ? -partner : partner;          // rotate_half: (-x2, x1)
+        const float c = __half2float(cs[lane * EPL + i]), s = __half2float(sn[lane * EPL + i]);
+        v[i] = round16(round16(v[i] * c) + round16(rot * s));
+    }
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
+    const __half* __restrict__ q, const __half* __restrict__ k_new, const __half* __restrict__ v_new,
+    const __half* __restrict__ cos_t, const __half* __restrict__ sin_t, const long long* __restrict__ pos_p,
+    __half* __restrict__ k_cache, __half* __restrict__ v_cache, __half* __restrict__ out, int n_heads, int n_kv, int max_len,
+    const __half* __restrict__ q_norm_w, const __half* __restrict__ k_norm_w, float eps) {
+    constexpr int HD = EPL * 32;
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = n_heads / n_kv, kvh = h / group;
+    long long pos = *pos_p;
+    if (pos < 0) pos = 0;
+    if (pos >= max_len) pos = max_len - 1;
+    const __half* cs = cos_t + (size_t)pos * HD;
+    const __half* sn = sin_t + (size_t)pos * HD;
+
+    float qv[EPL], kn[EPL], vn[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+        qv[i] = __half2float(q[((size_t)b * n_heads + h) * HD + lane * EPL + i]);
+        kn[i] = __half2float(k_new[((size_t)b * n_kv + kvh) * HD + lane * EPL + i]);
+        vn[i] = __half2float(v_new[((size_t)b * n_kv + kvh) * HD + lane * EPL + i]);
+    }
+    rope_norm<EPL>(qv, q_norm_w, eps, HD, cs, sn, lane);
+    rope_norm<EPL>(kn, k_norm_w, eps, HD, cs, sn, lane);
+    __half* kc = k_cache + ((size_t)b * n_kv + kvh) * max_len * HD;
+    __half* vc = v_cache + ((size_t)b * n_kv + kvh) * max_len * HD;
+    if (h % group == 0 && warp == 0) {     // one CTA per key/value head stores the new entry
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            kc[(size_t)pos * HD + lane * EPL + i] = __float2half_rn(kn[i]);
+            vc[(size_t)pos * HD + lane * EPL + i] = __float2half_rn(vn[i]);
+        }
+    }
+    const float scale = rsqrtf((float)HD);
+    // online softmax per warp over its share of positions 0..pos-1 (the new position is warp 0's, from
+    // registers: other CTAs of the group may not have stored it yet)
+    float m = -INFINITY, l = 0.f, o[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) o[i] = 0.f;
+    auto visit = [&](const float (&kk)[EPL], const float (&vv)[EPL]) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) s += qv[i] * kk[i];
+        s = warp_sum(s) * scale;
+        const float mn = fmaxf(m, s);
+        const float a = __expf(m - mn), p = __expf(s - mn);
+        l = l * a + p;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) o[i] = o[i] * a + p * vv[i];
+        m = mn;
+    };
+    for (long long t = warp; t < pos; t += kAttnWarps) {
+        float kk[EPL], vv[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            kk[i] = __half2float(kc[(size_t)t * HD + lane * EPL + i]);
+            vv[i] = __half2float(vc[(size_t)t * HD + lane * EPL + i]);
+        }
+        visit(kk, vv);
+    }
+    if (warp == 0) visit(kn, vn);
+    // combine the warps
+    __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_o[kAttnWarps][HD];
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) sm_o[warp][lane * EPL + i] = o[i];
+    __syncthreads();
+    if (warp == 0) {
+        float mm = -INFINITY;
+        for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm_m[w]);
+        float ll = 0.f, oo[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) oo[i] = 0.f;
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float a = sm_m[w] == -INFINITY ? 0.f : __expf(sm_m[w] - mm);
+            ll += sm_l[w] * a;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) oo[i] += sm_o[w][lane * EPL + i] * a;
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) out[((size_t)b * n_heads + h) * HD + lane * EPL + i] = __float2half_rn(oo[i] / ll);
+    }
+}
+
+}  // namespace
+
+extern "C" int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const void* cos_t, const void* sin_t,
+                               const int64_t* pos, void* k_cache, void* v_cache, void* out, int B, int n_heads, int n_kv,
+                               int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps,
+                               void* stream) {
+    if (!q || !k_new || !v_new || !cos_t || !sin_t || !pos || !k_cache || !v_cache || !out) return GLQ_ERR_ARG;
+    if (B < 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || max_len <= 0) return GLQ_ERR_ARG;
+    if (B == 0) return GLQ_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const dim3 grid(n_heads, B), block(kAttnWarps * 32);
+#define GLQ_ATTN(EPL)                                                                                              \
+    attn_decode_kernel<EPL><<<grid, block, 0, st>>>(                                                               \
+        reinterpret_cast<const __half*>(q), reinterpret_cast<const __half*>(k_new), reinterpret_cast<const __half*>(v_new), \
+        reinterpret_cast<const __half*>(cos_t), reinterpret_cast<const __half*>(sin_t),                           \
+        reinterpret_cast<const long long*>(pos), reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache), \
+        reinterpret_cast<__half*>(out), n_heads, n_kv, max_len, reinterpret_cast<const __half*>(q_norm_w),         \
+        reinterpret_cast<const __half*>(k_norm_w), eps)
+    switch (head_dim) {
+        case 32: GLQ_ATTN(1); break;
+        case 64: GLQ_ATTN(2); break;
+        case 128: GLQ_ATTN(4); break;
+        case 256: GLQ_ATTN(8); break;
+        default: return GLQ_ERR_UNSUPPORTED;
+    }
+#undef GLQ_ATTN
+    return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
+}

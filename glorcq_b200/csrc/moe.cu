@@ -166,7 +166,12 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
         }
         sum = warp_sum(sum);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) pv[i] = (lane + 32 * i) < E ? pv[i] / sum : -1.f;
+        // a probability that is not a number (non-finite hidden state) counts as zero: the top-k below then
+        // still selects k distinct experts and no index leaves the tables
+        for (int i = 0; i < 8; ++i) {
+            const float pr = pv[i] / sum;
+            pv[i] = (lane + 32 * i) < E ? (pr >= 0.f ? pr : 0.f) : -1.f;
+        }
         float wk[16];
         int ek[16];
         float wsum = 0.f;
@@ -284,7 +289,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
 // ---- combine ------------------------------------------------------------------------------------------
 // out[t] = sum over the token's experts of (already weighted, fp16) down outputs, accumulated in fp16
 // in slot order or in expert order, + sigmoid(shared gate) * shared expert output.  8 columns/thread.
-__global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __restrict__ tok_entries,
+__global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __restrict__ tok_entries, int n_entries,
                                    const int* __restrict__ sel, int k, int H, int by_expert,
                                    const __half* __restrict__ ysh, const __half* __restrict__ logits, int ldl,
                                    int gate_col, __half* __restrict__ out) {
@@ -311,7 +316,7 @@ __global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __r
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int s = 0; s < k; ++s) {
         const int entry = tok_entries[t * k + order[s]];
-        if (entry < 0) continue;     // dropped slot
+        if (entry < 0 || entry >= n_entries) continue;     // dropped slot
         __align__(16) __half v[8];
         *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(yd + (size_t)entry * H + c0);
 #pragma unroll
@@ -636,7 +641,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     // 8. combine
     const dim3 grid((d->H / 8 + 255) / 256, n);
     moe_combine_kernel<<<grid, 256, 0, st>>>(
-        reinterpret_cast<const __half*>(p_yd), p_tok, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
+        reinterpret_cast<const __half*>(p_yd), p_tok, nk, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
         shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, ldl,
         d->router_rows > d->E ? d->E : -1, reinterpret_cast<__half*>(out));
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;

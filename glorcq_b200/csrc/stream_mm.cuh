@@ -51,6 +51,7 @@ struct StreamParams {
     int stages;        // ring depth
     int stage_bytes;
     int off_xs, off_ox, off_as, off_ring, off_red;  // shared memory carve-up (bytes)
+    int cnt_lo, cnt_hi;  // only slots with cnt_lo < rows <= cnt_hi are this launch's (others belong to a sibling launch)
     int dependent;  // 1: launched with programmatic stream serialization
     int a_late;   // 1: the x.U operand is still being written when this kernel starts (programmatic dependent launch)
 };
@@ -232,7 +233,7 @@ __device__ __forceinline__ void stage_x_i8(const SkinnyParams& p, uint4* xs, flo
 // ---- fp16 path: one k block of one tile against preloaded activation fragments --------------------
 template <int FMT, int NTT>
 __device__ __forceinline__ void tile_block(const uint4 q, const uint4 (&bx)[NTT][4], uint32_t TL, uint32_t TH,
-                                           float (&c)[NTT][4]) {
+                                           float (&c)[NTT][4], int nt_live = NTT) {
     const uint32_t wa[2] = {q.x, q.y}, wb[2] = {q.z, q.w};
     if constexpr (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_T2) {
 #pragma unroll
@@ -247,6 +248,7 @@ __device__ __forceinline__ void tile_block(const uint4 q, const uint4 (&bx)[NTT]
             }
 #pragma unroll
             for (int tt = 0; tt < NTT; ++tt) {
+                if (tt >= nt_live) continue;      // activation tiles beyond the problem's rows (warp-uniform)
                 const uint4 b0 = bx[tt][2 * u], b1 = bx[tt][2 * u + 1];
                 mma16816(c[tt], ha[0], hb[0], ha[1], hb[1], b0.x, b0.y);
                 mma16816(c[tt], ha[2], hb[2], ha[3], hb[3], b0.z, b0.w);
@@ -262,6 +264,7 @@ __device__ __forceinline__ void tile_block(const uint4 q, const uint4 (&bx)[NTT]
             unpack_q4(wb[u], hb);
 #pragma unroll
             for (int tt = 0; tt < NTT; ++tt) {
+                if (tt >= nt_live) continue;
                 const uint4 b = bx[tt][u];
                 mma16816(c[tt], ha[0], hb[0], ha[1], hb[1], b.x, b.y);
                 mma16816(c[tt], ha[2], hb[2], ha[3], hb[3], b.z, b.w);
@@ -335,7 +338,12 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
     const long total = (long)n_live * sp.ips;
     const int it_lo = (int)((long)blockIdx.x * total / gridDim.x);
     const int it_hi = (int)((long)(blockIdx.x + 1) * total / gridDim.x);
-    if (it_lo >= it_hi) return;
+    if (it_lo >= it_hi) {
+        // a dependent launch must not end before the launch it depends on has: later launches of the
+        // stream order themselves after this grid only
+        if (sp.a_late) asm volatile("griddepcontrol.wait;" ::: "memory");
+        return;
+    }
 
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem);
     uint4* xs = reinterpret_cast<uint4*>(smem + sp.off_xs);
@@ -365,7 +373,9 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
     auto load_slot = [&](Slot& sc, int slot) {
         if (slot == sc.slot) return;
         sc.slot = slot;
-        sc.cnt = min(p.slot_count ? __ldg(p.slot_count + slot) : p.max_rows, p.max_rows);
+        sc.cnt = p.slot_count ? __ldg(p.slot_count + slot) : p.max_rows;
+        if (sc.cnt <= sp.cnt_lo || sc.cnt > sp.cnt_hi) sc.cnt = 0;     // not this launch's slot: skipped like an empty one
+        sc.cnt = min(sc.cnt, p.max_rows);
         sc.e0 = p.slot_offset ? __ldg(p.slot_offset + slot) : slot * p.rows_stride;
         const int widx = p.slot_index ? __ldg(p.slot_index + slot) : slot;
         const glq_weight_t* W = p.table ? p.table + widx : &p.w;
@@ -497,6 +507,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
             }
         }
         if (!im.valid) continue;
+        const int nt_live = I8 ? NT : min(NT, (cnt + 7) >> 3);     // fp16 path: activation tiles that hold rows
 
         // accumulators [tile in pair][activation tile]: {row g: 2 values, row g+8: 2 values}.
         // fp16 path: the two values are activation rows 2t, 2t+1 of the tile; integer path: only
@@ -556,7 +567,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                         const int col = (nt * 8 + g) & (ntc - 1);
 #pragma unroll
                         for (int i = 0; i < kPieces; ++i)
-                            bx[nt][i] = (NT > 1 || g < ntc)
+                            bx[nt][i] = (nt < nt_live && (NT > 1 || g < ntc))
                                             ? lds128(xs_a + (uint32_t)(((kb * kPieces + i) * ntc + col) * 4 + t) * 16u)
                                             : make_uint4(0, 0, 0, 0);
                     }
@@ -571,13 +582,14 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                             for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                                 for (int q4 = 0; q4 < 4; ++q4) cc[nt][q4] = 0.f;
-                            tile_block<FMT, NT>(q, bx, 0, 0, cc);
+                            tile_block<FMT, NT>(q, bx, 0, 0, cc, nt_live);
                             const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv.x);
                             const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv.y);
                             const float s0 = __low2float(sz0), z0 = __high2float(sz0);
                             const float s1 = __low2float(sz1), z1 = __high2float(sz1);
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt) {
+                                if (nt >= nt_live) continue;
                                 const int col = (nt * 8 + 2 * t) & (ntc - 1);
                                 const uint4 ov = lds128(ox_a + (uint32_t)(kb * ntc + col) * 8u);
                                 const float ox0 = __uint_as_float(ov.x), xx0 = __uint_as_float(ov.y);
@@ -588,7 +600,7 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                                 acc[j][nt][3] = fmaf(s1, fmaf(-z1, xx1, cc[nt][3] - ox1), acc[j][nt][3]);
                             }
                         } else {
-                            tile_block<FMT, NT>(q, bx, TL[j], TH[j], acc[j]);
+                            tile_block<FMT, NT>(q, bx, TL[j], TH[j], acc[j], nt_live);
                         }
                     }
                 }
@@ -740,6 +752,8 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
             }
         }
     }
+    // see the early exit above: a dependent grid ends only after the grid it depends on
+    if (sp.a_late && !dep_waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace glq

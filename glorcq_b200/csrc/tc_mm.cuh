@@ -50,6 +50,7 @@ struct TcParams {
     int tiles_max;
     int x_vec;                // x rows allow 8-byte loads
     int fmt;                  // GLQ_FMT_*: fixes the channel order inside a group of 16
+    int min_rows;             // only problems with more rows than this are this launch's
 };
 
 // ---- token tile -> (problem slot, local tile) -----------------------------------------------------
@@ -69,7 +70,7 @@ __device__ __forceinline__ bool tc_find_tile(const TcParams& p, int gt, int& slo
             off = p.slot_offset ? __ldg(p.slot_offset + pp) : pp * p.rows_stride;
         }
         const int start = off / TN + pp;
-        const bool hit = pp < P && c > 0 && gt >= start && gt < start + (c + TN - 1) / TN;
+        const bool hit = pp < P && c > p.min_rows && gt >= start && gt < start + (c + TN - 1) / TN;
         const unsigned m = __ballot_sync(0xffffffffu, hit);
         if (m) {
             const int src = __ffs(m) - 1;

@@ -8,10 +8,11 @@ cache, and per layer either a ``GraphCompatibleMoeBlock`` or a dense SwiGLU MLP,
 Mixtral (w1/w3/w2 naming, top-2 renormalised, no shared expert) and Qwen3-MoE (per-head q/k norms, no
 shared expert) layouts.
 
-The quantized projections and the MoE block run on this package's kernels.  Norms, rotary embedding,
-the attention core (``scaled_dot_product_attention`` over the static cache with a position mask),
-embedding lookup and the fp16 ``lm_head`` product are plain library calls: small or dense-fp16 work
-outside the quantized path.
+The quantized projections and the MoE block run on this package's kernels, and so does the attention
+of a decode step (``glq_attn_decode``: q/k norms, rotary embedding, cache write and attention over the
+live positions in one launch).  Layer norms, the prefill attention (``scaled_dot_product_attention``
+over the static cache with a position mask), embedding lookup and the fp16 ``lm_head`` product are plain
+library calls: small or dense-fp16 work outside the quantized path.
 """
 
 from __future__ import annotations
@@ -23,6 +24,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import _lib, tiled
 from .moe_block import GraphCompatibleMoeBlock
 from .quantized_linear import GLoRCQLinear
 
@@ -76,10 +78,34 @@ class _Attention(nn.Module):
         self.k_norm = dense.get(f"{prefix}.self_attn.k_norm.weight")
         if self.q_norm is not None:
             self.q_norm, self.k_norm = self.q_norm.to(device).half(), self.k_norm.to(device).half()
+        # q, k and v of one shape (no grouped-query sharing): one grouped launch pair for the decode step
+        self._qkv = None
+        tl = [getattr(m, "_tiled", None) for m in (self.q_proj, self.k_proj, self.v_proj)]
+        uts = [getattr(m, "_ut", None) for m in (self.q_proj, self.k_proj, self.v_proj)]
+        if all(t is not None for t in tl) and len({(t.fmt, t.N, t.K, t.group_size, t.rank) for t in tl}) == 1 and \
+                (all(u is not None for u in uts) or all(u is None for u in uts)):
+            self._qkv = tiled.GroupedLinear(tl, uts if uts[0] is not None else None)
 
     def forward(self, x, cache_position, cache: StaticKVCache, cos, sin):
         c = self.cfg
         B, T, _ = x.shape
+        if T == 1 and cache_position.numel() == 1 and c.head_dim in (32, 64, 128, 256):
+            # decode step: norms, rotary embedding, cache write and attention over the live positions in
+            # one launch; the position stays on the device (graph replay)
+            if self._qkv is not None:
+                q, k, v = self._qkv.forward(x.view(B, -1).contiguous())
+            else:
+                q, k, v = self.q_proj(x).view(B, -1), self.k_proj(x).view(B, -1), self.v_proj(x).view(B, -1)
+            y = torch.empty_like(q)
+            kc, vc = cache.k[self.layer_idx], cache.v[self.layer_idx]
+            with torch.cuda.device(x.device):
+                _lib.check(_lib.lib().glq_attn_decode(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), cache_position.data_ptr(),
+                    kc.data_ptr(), vc.data_ptr(), y.data_ptr(), B, c.num_attention_heads, c.num_key_value_heads,
+                    c.head_dim, cache.max_cache_len, None if self.q_norm is None else self.q_norm.data_ptr(),
+                    None if self.k_norm is None else self.k_norm.data_ptr(), float(c.rms_norm_eps),
+                    tiled._stream_ptr(x.device)), "attn_decode")
+            return self.o_proj(y.view(B, 1, -1))
         q = self.q_proj(x).view(B, T, c.num_attention_heads, c.head_dim)
         k = self.k_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
         v = self.v_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)

@@ -270,3 +270,58 @@ def linear_forward(w: TiledWeight, x: torch.Tensor, ut: Optional[TiledWeight] = 
 def dense_matmul(w: TiledWeight, x: torch.Tensor) -> torch.Tensor:
     """y = x . W^T for a dense tiled weight (used for a = x . U with W = U^T)."""
     return linear_forward(w, x)
+
+
+class GroupedLinear:
+    """Several quantized layers of one shape applied to the same activation rows in two launches (x.U of
+    all of them, then the quantized products with the low-rank term), through ``glq_grouped_matmul``:
+    e.g. the q, k and v projections of an attention layer.  ``forward(x (B,K))`` returns (P, B, N)."""
+
+    def __init__(self, weights, uts):
+        w0 = weights[0]
+        for w in weights:
+            if (w.fmt, w.N, w.K, w.group_size, w.rank) != (w0.fmt, w0.N, w0.K, w0.group_size, w0.rank):
+                raise RuntimeError("grouped layers must share format, shape, group size and rank")
+        self.weights, self.uts = list(weights), list(uts) if uts else None
+        dev = w0.device
+        self._table = torch.frombuffer(bytearray(b"".join(w.desc_bytes() for w in weights)), dtype=torch.uint8).to(dev)
+        self._ut_table = None
+        if self.uts:
+            descs = [_lib.Weight(u.codes.data_ptr(), None, None, None, None, None, u.N, u.K, 0, 0) for u in self.uts]
+            self._ut_table = torch.frombuffer(bytearray(b"".join(bytes(d) for d in descs)), dtype=torch.uint8).to(dev)
+        self._rows = {}
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w0, P = self.weights[0], len(self.weights)
+        B = x.shape[0]
+        dev = x.device
+        L = _lib.lib()
+        if B not in self._rows:     # every problem reads the same B activation rows
+            self._rows[B] = torch.arange(B, dtype=torch.int32, device=dev).repeat(P)
+        rows = self._rows[B]
+        y = torch.empty(P, B, w0.N, dtype=torch.float16, device=dev)
+        st = _stream_ptr(dev)
+
+        def call(fmt, gs, table, N, K, rank, out, a):
+            m = _lib.MMArgs()
+            m.fmt, m.group_size, m.epilogue, m.n_problems, m.max_rows, m.rows_stride = fmt, gs, 0, P, B, B
+            m.N, m.K, m.rank, m.total_rows = N, K, rank, P * B
+            m.w_table = table.data_ptr()
+            m.entry_row = rows.data_ptr()
+            m.x, m.ldx = x.data_ptr(), x.stride(0)
+            if a is not None:
+                m.a0, m.lda = a.data_ptr(), a.shape[-1]
+            m.y, m.ldy = out.data_ptr(), N
+            nbytes, nctr = L.glq_mm_workspace_bytes(C.byref(m)), L.glq_mm_counters(C.byref(m))
+            ws, ctr = workspace(dev, nbytes, nctr)
+            m.workspace, m.workspace_bytes = ws.data_ptr(), ws.numel()
+            m.counters, m.n_counters = ctr.data_ptr(), ctr.numel()
+            _lib.check(L.glq_grouped_matmul(C.byref(m), st), "grouped_matmul")
+
+        with torch.cuda.device(dev):
+            a = None
+            if self._ut_table is not None and w0.rank > 0:
+                a = torch.empty(P, B, w0.rank, dtype=torch.float16, device=dev)
+                call(_lib.FMT_F16, 0, self._ut_table, w0.rank, w0.K, 0, a, None)
+            call(w0.fmt, w0.group_size, self._table, w0.N, w0.K, w0.rank if a is not None else 0, y, a)
+        return y

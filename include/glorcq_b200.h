@@ -299,6 +299,20 @@ int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n_tokens, voi
                        size_t n_counters, void* stream, void* aux_stream, void* ev_fork, void* ev_join,
                        const glq_moe_ep_t* ep);
 
+/* ---------------------------------------------------------------------------------------------
+ * One decode step of grouped-query attention over a static key/value cache, in one launch.  The
+ * reference leaves attention to the transformers modules it wraps (inference/graph_wrapper.py:84-127
+ * calls the model with a StaticCache); this entry point serves the host model of this package.
+ * q (B, n_heads*head_dim), k_new / v_new (B, n_kv*head_dim) fp16 as the projections produce them;
+ * optional per-head RMS-norm weights (head_dim,) fp16 for q and k; rotary embedding in the rotate-half
+ * convention from cos / sin tables (max positions, head_dim) fp16 at position *pos (device int64, so a
+ * captured launch follows the replayed position); the new key / value are stored into the caches
+ * (B, n_kv, max_len, head_dim) fp16 at that position; out (B, n_heads*head_dim) fp16 =
+ * softmax(q k^T / sqrt(head_dim)) v over positions 0..*pos.  head_dim in {32, 64, 128, 256}. */
+int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const void* cos_t, const void* sin_t,
+                    const int64_t* pos, void* k_cache, void* v_cache, void* out, int B, int n_heads, int n_kv,
+                    int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

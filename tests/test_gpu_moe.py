@@ -128,6 +128,24 @@ def test_qwen_moe_shape_prefill(dev):
     assert cases.rel_l2(y, ref) <= REL_BLOCK
 
 
+def test_non_finite_hidden_state_keeps_indices_in_range(dev):
+    """Overflowed activations give NaN router probabilities; routing must still pick k distinct experts
+    (probabilities that are not numbers count as zero) so that no table index leaves its range."""
+    blk = cases.make_moe(808, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    mb = cases.to_b200_moe(blk, dev)
+    x = cases.make_x(809, 5, 256).reshape(1, 5, 256).to(dev)
+    x[0, 1, :] = float("inf")
+    x[0, 3, 7] = float("nan")
+    y, _ = mb(x)
+    torch.cuda.synchronize()
+    sel = mb.last_selected_experts.cpu()
+    assert int(sel.min()) >= 0 and int(sel.max()) < 8
+    assert all(len(set(r.tolist())) == 2 for r in sel)
+    assert torch.isfinite(y[0, [0, 2, 4]]).all()          # the other tokens are untouched
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
 # ---- expert parallelism ---------------------------------------------------------------------------
 @pytest.mark.parametrize("N,world", [(1, 2), (3, 2), (9, 2), (9, 4), (33, 3)])
 def test_expert_parallel_emulated_on_one_gpu(dev, N, world):
