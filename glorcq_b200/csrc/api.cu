@@ -553,13 +553,18 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
         return launch_tc(a, tg, reinterpret_cast<cudaStream_t>(stream));
     }
     StreamGeom sg;
-    StreamGeom sg8;
-    bool use_stream =
-        plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, std::min(a->max_rows, 32), &sg);
-    // device-side row counts: slots with at most 8 rows go to the integer path in a launch of their own
-    const bool split8 = use_stream && a->slot_count != nullptr && a->max_rows > 8 && !sg.i8 && !hybrid_disabled() &&
-                        plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, 8, &sg8) &&
+    // Row-count classes (device-side counts): slots with <= 8 rows go to the integer path, 9..16 to the
+    // fp16 path with two activation tiles, and above that to the tcgen05 kernel when the call may have
+    // more than 32 rows per slot, else to the fp16 path with four tiles.  Each class is one launch that
+    // skips the slots of the others.
+    StreamGeom sg8, sg16;
+    const int cap = use_tc ? 16 : std::min(a->max_rows, 32);
+    bool use_stream = plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, cap, &sg);
+    const bool classes = use_stream && a->slot_count != nullptr && a->max_rows > 8 && !sg.i8 && !hybrid_disabled();
+    const bool split8 = classes && plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, 8, &sg8) &&
                         sg8.i8;
+    const bool split16 = classes && cap > 16 &&
+                         plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, 16, &sg16);
     if (use_tc && !use_stream) {
         if (!a->w_table && !a->w.codes) return GLQ_ERR_ARG;
         return launch_tc(a, tg, reinterpret_cast<cudaStream_t>(stream));
@@ -602,23 +607,24 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     if (use_stream) {
         cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
         const bool a_late = (a->flags & GLQ_MM_A_FROM_PREVIOUS_LAUNCH) != 0, dep = (a->flags & GLQ_MM_AFTER_KERNEL) != 0;
-        if (!split8 && !use_tc) return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, st, a_late, dep);
-        // one launch per range of rows; only the first may depend programmatically on the producer of x.U
-        // (the later ones start after it has finished)
+        if (!split8 && !split16 && !use_tc) return launch_stream(a->fmt, p, sg, a->N, a->K, a->rank, a->n_problems, st, a_late, dep);
+        // one launch per class; only the first may depend programmatically on the producer of x.U (the
+        // later ones start after it has finished)
         int lo = 0;
-        if (split8) {
-            SkinnyParams p8 = p;
-            p8.max_rows = 8;
-            if ((rc = launch_stream(a->fmt, p8, sg8, a->N, a->K, a->rank, a->n_problems, st, a_late, dep, 0, 8)) != GLQ_OK)
-                return rc;
-            lo = 8;
-        }
-        SkinnyParams p32 = p;
-        p32.max_rows = std::min(a->max_rows, 32);
-        if ((rc = launch_stream(a->fmt, p32, sg, a->N, a->K, a->rank, a->n_problems, st, lo == 0 && a_late, lo == 0 && dep,
-                                lo, 32)) != GLQ_OK)
-            return rc;
-        if (use_tc) return launch_tc(a, tg, st, 32);
+        bool first = true;
+        auto one = [&](const StreamGeom& gg, int rows, int hi) {
+            SkinnyParams pp = p;
+            pp.max_rows = rows;
+            const int r2 = launch_stream(a->fmt, pp, gg, a->N, a->K, a->rank, a->n_problems, st, first && a_late, first && dep,
+                                         lo, hi);
+            first = false;
+            lo = hi;
+            return r2;
+        };
+        if (split8 && (rc = one(sg8, 8, 8)) != GLQ_OK) return rc;
+        if (split16 && (rc = one(sg16, 16, 16)) != GLQ_OK) return rc;
+        if ((rc = one(sg, cap, cap)) != GLQ_OK) return rc;
+        if (use_tc) return launch_tc(a, tg, st, cap);
         return GLQ_OK;
     }
     fill_geometry(p, g);
