@@ -29,6 +29,22 @@ struct MoeLayout {
     size_t total, mm_bytes, mm_counters;
 };
 
+// Rows per problem slot of the routed products.  With 9 or more tokens but few rows per expert on
+// average, an expert's entries are cut into slots of at most 8 rows (consecutive entries, so nothing
+// else changes): every routed product then stays on the integer streaming path in one launch, and the
+// repeated reads of an expert's weights are served by L2.  0: one slot per expert.
+inline int moe_chunk(const glq_moe_desc_t* d, int n) {
+    static const bool off = std::getenv("GLQ_NO_CHUNK") != nullptr;
+    const long long nk = (long long)n * d->top_k;
+    const bool affine = d->fmt == GLQ_FMT_Q2 || d->fmt == GLQ_FMT_Q4;
+    return (!off && affine && n > 8 && nk <= 24ll * d->E) ? 8 : 0;
+}
+inline int moe_slots(const glq_moe_desc_t* d, int n) {
+    const long long nk = (long long)n * d->top_k;
+    const int chunk = moe_chunk(d, n);
+    return (int)std::min<long long>(nk, chunk ? d->E + nk / chunk : d->E);
+}
+
 void set_mm(glq_mm_args_t* m, int fmt, int group_size, int epi, int P, int rows, int N, int K, int rank,
             int total_rows = 0) {
     std::memset(m, 0, sizeof(*m));
@@ -56,17 +72,18 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
     L.logits = take((size_t)n * d->dense0_rows * 2);
     L.sel = take(nk * 4);
     L.wts = take(nk * 2);
-    L.active = take((size_t)d->E * 4);
+    const size_t PS = (size_t)moe_slots(d, n);
+    L.active = take(PS * 4);
     L.n_active = take(4);
-    L.slot_count = take((size_t)d->E * 4);
-    L.slot_offset = take((size_t)d->E * 4);
+    L.slot_count = take(PS * 4);
+    L.slot_offset = take(PS * 4);
     L.entry_row = take(2 * nk * 4);   // second copy for the up half of the x.U launch
     L.entry_scale = take(nk * 2);
     L.tok_entries = take(nk * 4);
-    L.active2 = take((size_t)2 * d->E * 4);
+    L.active2 = take(2 * PS * 4);
     L.n_active2 = take(4);
-    L.slot_count2 = take((size_t)2 * d->E * 4);
-    L.slot_offset2 = take((size_t)2 * d->E * 4);
+    L.slot_count2 = take(2 * PS * 4);
+    L.slot_offset2 = take(2 * PS * 4);
     L.a_gu = take(2 * nk * R * 2);
     L.h = take(nk * d->I * 2);
     L.b = take(nk * R * 2);
@@ -82,7 +99,8 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
     if (d->rot_mid || d->rht_mid) L.hr = take(nk * d->I * 2);
     if ((d->sh_rot_mid || d->sh_rht_mid) && d->I_shared > 0) L.hsr = take((size_t)n * d->I_shared * 2);
     // scratch / counters of the matmul calls: they run one after the other, so they share
-    const int P = (int)std::min<size_t>(nk, (size_t)d->E);
+    const int P = moe_slots(d, n);
+    const int rows = moe_chunk(d, n) ? std::min(n, moe_chunk(d, n)) : n;   // rows per routed slot
     glq_mm_args_t m;
     size_t wb = 0, wc = 0;
     auto acc = [&]() {
@@ -94,11 +112,11 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
     if (d->rot_mid) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, (int)nk, d->I, d->I, 0); acc(); }
     if (d->sh_rot_mid && d->I_shared > 0) { set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->I_shared, d->I_shared, 0); acc(); }
     if (d->rank > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, d->rank, d->H, 0, (int)(2 * nk)); acc();
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, d->rank, d->I, 0, (int)nk); acc();
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, rows, d->rank, d->H, 0, (int)(2 * nk)); acc();
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, rows, d->rank, d->I, 0, (int)nk); acc();
     }
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, d->rank, (int)nk); acc();
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, d->rank, (int)nk); acc();
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, rows, d->I, d->H, d->rank, (int)nk); acc();
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, rows, d->H, d->I, d->rank, (int)nk); acc();
     if (d->I_shared > 0) {
         if (d->rank > 0) {
             set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 1, n, d->rank, d->H, 0); acc();
@@ -130,7 +148,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
                                                         int* __restrict__ active2, int* __restrict__ n_active2,
                                                         int* __restrict__ slot_count2, int* __restrict__ slot_offset2,
                                                         int ep_rank, int ep_world, const int* __restrict__ sel_in,
-                                                        const __half* __restrict__ wts_in) {
+                                                        const __half* __restrict__ wts_in, int chunk) {
     extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
     int* sm_off = sm_cnt + E;
     asm volatile("griddepcontrol.wait;" ::: "memory");              // no-ops for a plain launch
@@ -240,18 +258,27 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
             const int off = base + v - c;
             if (e < E) sm_off[e] = off;
             const bool act = e < E && c > 0 && e % ep_world == ep_rank;
-            const unsigned m = __ballot_sync(0xffffffffu, act);
-            if (act) {
-                const int pos = j + __popc(m & lt);
+            // slots of this expert: one, or ceil(c / chunk) of at most `chunk` consecutive entries each
+            const int ns = act ? (chunk > 0 ? (c + chunk - 1) / chunk : 1) : 0;
+            int sv = ns;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int tv = __shfl_up_sync(0xffffffffu, sv, o);
+                if (lane >= o) sv += tv;
+            }
+            for (int i = 0; i < ns; ++i) {
+                const int pos = j + sv - ns + i;
+                const int cc = chunk > 0 ? min(chunk, c - i * chunk) : c;
+                const int oo = off + (chunk > 0 ? i * chunk : 0);
                 active[pos] = e;
-                slot_count[pos] = c;
-                slot_offset[pos] = off;
+                slot_count[pos] = cc;
+                slot_offset[pos] = oo;
                 // the same lists twice, for gate (table entry e, entries 0..nk) and up (entry E+e, entries nk..2nk)
                 active2[pos] = e;
-                slot_count2[pos] = c;
-                slot_offset2[pos] = off;
+                slot_count2[pos] = cc;
+                slot_offset2[pos] = oo;
             }
-            j += __popc(m);
+            j += __shfl_sync(0xffffffffu, sv, 31);
             base += __shfl_sync(0xffffffffu, v, 31);
         }
         __syncwarp();
@@ -379,7 +406,8 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     char* ws = reinterpret_cast<char*>(workspace);
     const int k = d->top_k, nk = n * k, R = d->rank;
-    const int P = std::min(nk, d->E);
+    const int P = moe_slots(d, n), chunk = moe_chunk(d, n);
+    const int rows = chunk ? std::min(n, chunk) : n;     // rows per routed slot
     // per-entry down-projection outputs: in the workspace, or in the caller's exchange buffer
     char* p_yd = ep && ep->entry_out ? reinterpret_cast<char*>(ep->entry_out) : ws + L.yd;
     const bool shared = d->I_shared > 0 && d->sh_gate_up.codes != nullptr;
@@ -474,7 +502,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
                                reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
                                reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2),
                                ep_rank, ep_world, given ? (const int*)ep->sel_in : (const int*)nullptr,
-                               given ? reinterpret_cast<const __half*>(ep->weight_in) : (const __half*)nullptr) != cudaSuccess)
+                               given ? reinterpret_cast<const __half*>(ep->weight_in) : (const __half*)nullptr, chunk) != cudaSuccess)
             return GLQ_ERR_CUDA;
         after_kernel[0] = true;
     }
@@ -493,7 +521,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     char* a_gate = ws + L.a_gu;
     char* a_up = a_gate + (size_t)nk * R * 2;
     if (R > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, n, R, d->H, 0, 2 * nk);
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, 2 * P, rows, R, d->H, 0, 2 * nk);
         m.w_table = d->ut_gate_up;
         m.slot_index = reinterpret_cast<int*>(ws + L.active2);
         m.n_slots = reinterpret_cast<int*>(ws + L.n_active2);
@@ -507,7 +535,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         if ((rc = finish(m)) != GLQ_OK) return rc;
     }
     // 4. h = silu(gate x) * (up x), one row per (token, expert) entry
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, n, d->I, d->H, R, nk);
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_SWIGLU, P, rows, d->I, d->H, R, nk);
     m.w_table = d->gate_up;
     routed(m);
     m.entry_row = p_erow;
@@ -524,7 +552,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if ((rc = finish(m)) != GLQ_OK) return rc;
     // 5. h.U of the down clusters
     if (R > 0) {
-        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, n, R, d->I, 0, nk);
+        set_mm(&m, GLQ_FMT_F16, 0, GLQ_EPI_LINEAR, P, rows, R, d->I, 0, nk);
         m.w_table = d->ut_down;
         routed(m);
         m.x = ws + L.h;
@@ -540,7 +568,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         if ((rc = rotate(d->rot_mid, d->rht_mid, ws + L.h, nk, d->I, ws + L.hr)) != GLQ_OK) return rc;
         hq = ws + L.hr;
     }
-    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, n, d->H, d->I, R, nk);
+    set_mm(&m, d->fmt, d->group_size, GLQ_EPI_LINEAR, P, rows, d->H, d->I, R, nk);
     m.w_table = d->down;
     routed(m);
     m.entry_scale = p_escale;
