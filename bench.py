@@ -191,8 +191,11 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
     # per problem: codes + (scale, zero) pairs + SV + x + a + y  (U is read by the separate x.U kernel)
     per = N * K // 4 + N * (K // 128) * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
     achieved = P * per / sec / 1e9
+    # DRAM bytes of one launch of this case from the ncu capture summarised under profiles/
+    # (dram__bytes_read.sum + dram__bytes_write.sum = 239.47 MB + 4.13 MB at P = 240); scaled by P otherwise
+    traffic = 243.60e6 * P / 240.0
     return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-            "traffic": None, "kernel": "stream_kernel<Q2,int8 path> (grouped dequant-GEMV)",
+            "traffic": traffic, "kernel": "stream_kernel<Q2,int8 path> (grouped dequant-GEMV)",
             "launch_us": sec * 1e6, "bytes_per_launch": P * per, "peak_kind": peak_kind,
             "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), 1 row each; {P * per / 1e6:.0f} MB > L2"}
 

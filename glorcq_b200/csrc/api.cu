@@ -735,6 +735,8 @@ extern "C" int glq_linear_forward(int fmt, int group_size, const glq_weight_t* w
     m.counters = counters;
     m.n_counters = main_ctr;
     if (!a_use) m.w.rank = 0, m.rank = 0;
+    // x.U was just launched above and is needed only in the epilogue; x itself is older
+    if (a_use != nullptr && a_use != a) m.flags = GLQ_MM_A_FROM_PREVIOUS_LAUNCH;
     return glq_grouped_matmul(&m, stream);
 }
 

@@ -304,6 +304,8 @@ class GroupedLinear:
 
         def call(fmt, gs, table, N, K, rank, out, a):
             m = _lib.MMArgs()
+            if a is not None:
+                m.flags = 1      # GLQ_MM_A_FROM_PREVIOUS_LAUNCH: x.U was launched directly before
             m.fmt, m.group_size, m.epilogue, m.n_problems, m.max_rows, m.rows_stride = fmt, gs, 0, P, B, B
             m.N, m.K, m.rank, m.total_rows = N, K, rank, P * B
             m.w_table = table.data_ptr()
