@@ -99,7 +99,7 @@ class ClockSampler:
 
 
 # ---- CPU baseline (reference arm) -----------------------------------------------------------------
-def cpu_layer_seconds(reps_budget_s=12.0, max_reps=200):
+def cpu_layer_seconds(sample_seconds=12.0, max_reps=200):
     """One layer, one token, through the CPU oracle (the reference's PyTorch path restated); returns
     (median seconds per layer-forward, threads, reps)."""
     from oracle import glorcq_oracle as O
@@ -113,7 +113,7 @@ def cpu_layer_seconds(reps_budget_s=12.0, max_reps=200):
         for _ in range(2):
             O.moe_forward(ob, x)
         ts, t_start = [], time.perf_counter()
-        while len(ts) < max_reps and (time.perf_counter() - t_start < reps_budget_s or len(ts) < 3):
+        while len(ts) < max_reps and (time.perf_counter() - t_start < sample_seconds or len(ts) < 3):
             t0 = time.perf_counter()
             O.moe_forward(ob, x)
             ts.append(time.perf_counter() - t0)
@@ -126,9 +126,9 @@ def run_reference(args, rank):
         return
     layers = args.layers
     per = []
-    sec, threads, reps = cpu_layer_seconds(reps_budget_s=3.0, max_reps=5)      # warm-up sample
+    sec, threads, reps = cpu_layer_seconds(sample_seconds=3.0, max_reps=5)      # warm-up sample
     for _ in range(max(1, args.steps)):
-        sec, threads, reps = cpu_layer_seconds(reps_budget_s=8.0 / max(1, args.steps) + 1.0, max_reps=50)
+        sec, threads, reps = cpu_layer_seconds(sample_seconds=8.0 / max(1, args.steps) + 1.0, max_reps=50)
         per.append(sec)
     per.sort()
     sec = per[len(per) // 2]

@@ -2,7 +2,7 @@
 
 Run where the unmodified reference tree is mounted (it cannot travel with the repository):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <checkout of the reference>
 
 It imports the reference's own modules (``inference.kernels`` falls back to its pure-PyTorch
 functions when its CUDA extensions are absent; ``inference.quantized_linear.GLoRCQLinear``;
@@ -154,7 +154,8 @@ LOADER_MODULES = ("self_attn.q_proj", "mlp.experts.1.down_proj", "mlp.experts.0.
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("GLORCQ_REFERENCE"), required=os.environ.get("GLORCQ_REFERENCE") is None,
+                    help="checkout of the unmodified reference (or set GLORCQ_REFERENCE)")
     ap.add_argument("--out", default=os.path.join(HERE, "golden.pt"))
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
