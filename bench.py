@@ -215,7 +215,7 @@ def measured_peak_tflops():
     return 1590.0, "fallback"
 
 
-def gemm_roofline(dev, P=8, rows=1024, iters=20):
+def gemm_roofline(dev, P=8, rows=2048, iters=20):
     """The grouped dequant-GEMM (tcgen05 path) alone: P distinct 1408x2048 2-bit g128 rank-64 problems of
     `rows` activation rows each (a prefill-sized grouped launch), x.U given."""
     import ctypes as C
@@ -259,7 +259,7 @@ def gemm_roofline(dev, P=8, rows=1024, iters=20):
     peak, kind = measured_peak_tflops()
     ach = flops / sec / 1e12
     return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-            "kernel": "tc_pack_b_kernel + tc_kernel<Q2> (grouped dequant-GEMM, tcgen05)", "launch_us": sec * 1e6,
+            "kernel": "tc_pack_b_kernel + tc_ts_kernel<Q2> (grouped dequant-GEMM, tcgen05, weights unpacked into TMEM)", "launch_us": sec * 1e6,
             "flops_per_launch": flops, "peak_kind": kind,
             "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), {rows} rows each"}
 
@@ -461,7 +461,7 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--gemm-only", action="store_true",
                     help="time only the grouped tcgen05 dequant-GEMM roofline case (small enough for an ncu capture)")
-    ap.add_argument("--rows", type=int, default=1024)
+    ap.add_argument("--rows", type=int, default=2048)
     ap.add_argument("--problems", type=int, default=240)
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--strong", action="store_true",

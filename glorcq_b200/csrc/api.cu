@@ -408,6 +408,10 @@ struct TcGeom {
     long long tile_bytes;
     size_t xp_bytes;
 };
+static bool ts_disabled() {
+    static const bool v = std::getenv("GLQ_NO_TS") != nullptr;
+    return v;
+}
 static bool hybrid_disabled() {
     static const bool v = std::getenv("GLQ_NO_HYBRID") != nullptr;
     return v;
@@ -432,6 +436,11 @@ static bool plan_tc(const glq_mm_args_t* a, TcGeom* out) {
     long long total = a->total_rows > 0 ? a->total_rows : (long long)a->n_problems * (a->slot_offset ? a->max_rows : stride);
     if (!a->slot_offset) total = std::max(total, (long long)(a->n_problems - 1) * stride + a->max_rows);
     g.tn = (total / a->n_problems > 64) ? 128 : 64;
+    // 256-token tiles: tensor-memory variant, plain epilogue (2-bit codes), long problems only
+    static const char* tn_env = std::getenv("GLQ_TC_TN");
+    const bool wide_ok = a->fmt == GLQ_FMT_Q2 && a->epilogue == GLQ_EPI_LINEAR && !ts_disabled();
+    const int wide_from = tn_env ? std::atoi(tn_env) : 512;      // rows per problem from which the wide tile is used
+    if (wide_ok && wide_from > 0 && total / a->n_problems >= wide_from) g.tn = 256;
     g.nkb = cdiv(a->K, 128);
     g.ns = a->rank > 0 ? cdiv(a->rank, 64) : 0;
     g.na = a->epilogue == GLQ_EPI_SWIGLU ? 2 : 1;
@@ -461,6 +470,24 @@ static int launch_tc_t(const TcParams& p, int N, cudaStream_t st) {
     tc_pack_b_kernel<TN><<<dim3(p.tiles_max, p.nkb + p.ns), 256, 0, st>>>(p);
     GLQ_CUDA(cudaGetLastError());
     tc_kernel<FMT, TN, SW><<<dim3(cdiv(N, kTcFeat), p.tiles_max), kTcThreads, C::SMEM, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
+// variant with the weight operand in tensor memory (2-bit affine codes)
+template <int TN, bool SW>
+static int launch_tc_ts_t(const TcParams& p, int N, cudaStream_t st) {
+    using C = TcTsCfg<TN, SW>;
+    static bool configured[64] = {};
+    int dev = 0;
+    GLQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        GLQ_CUDA(cudaFuncSetAttribute(tc_ts_kernel<TN, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    tc_pack_b_kernel<TN><<<dim3(p.tiles_max, p.nkb + p.ns), 256, 0, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    tc_ts_kernel<TN, SW><<<dim3(cdiv(N, kTcFeat), p.tiles_max), kTcThreads, C::SMEM, st>>>(p);
     GLQ_CUDA(cudaGetLastError());
     return GLQ_OK;
 }
@@ -500,6 +527,12 @@ static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st, i
     p.min_rows = min_rows;
     const bool sw = a->epilogue == GLQ_EPI_SWIGLU;
     const bool big = g.tn == 128;
+    if (a->fmt == GLQ_FMT_Q2 && !ts_disabled()) {
+        p.ts = 1;
+        if (g.tn == 256) return launch_tc_ts_t<256, false>(p, a->N, st);
+        if (big) return sw ? launch_tc_ts_t<128, true>(p, a->N, st) : launch_tc_ts_t<128, false>(p, a->N, st);
+        return sw ? launch_tc_ts_t<64, true>(p, a->N, st) : launch_tc_ts_t<64, false>(p, a->N, st);
+    }
     switch (a->fmt) {
 #define GLQ_TC_CASE(F)                                                                                       \
     case F:                                                                                                  \

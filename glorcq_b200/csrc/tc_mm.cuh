@@ -51,6 +51,7 @@ struct TcParams {
     int x_vec;                // x rows allow 8-byte loads
     int fmt;                  // GLQ_FMT_*: fixes the channel order inside a group of 16
     int min_rows;             // only problems with more rows than this are this launch's
+    int ts;                   // 1: K positions of a stage in the order of the tensor-memory variant
 };
 
 // ---- token tile -> (problem slot, local tile) -----------------------------------------------------
@@ -95,6 +96,12 @@ __host__ __device__ __forceinline__ int tc_channel_of(int fmt, int pos) {
     }
 }
 
+// K position -> channel of the tensor-memory variant (see tc_ts_kernel)
+__host__ __device__ __forceinline__ int tc_ts_channel_of(int P) {
+    const int w = P >> 6, n = (P >> 4) & 3, t = (P >> 2) & 3, i = P & 3;
+    return 32 * t + 16 * w + 2 * n + (i >> 1) + 8 * (i & 1);
+}
+
 // ---- pre-pass: token operand in UMMA layout ---------------------------------------------------------
 // Tile layout in xp (TN rows): per k stage (128 input channels) two atoms [TN][128 B], then per
 // low-rank slice `na` atoms [TN][128 B].  Inside an atom row r keeps its 16-byte chunk c at chunk
@@ -119,7 +126,13 @@ __global__ void __launch_bounds__(256) tc_pack_b_kernel(const TcParams p) {
                 const long long row = p.entry_row ? __ldg(p.entry_row + e0 + rr) : (long long)(e0 + rr);
                 const __half* src = p.x + row * p.ldx;
                 const int ka = k0 + 4 * h, kb = k0 + 8 + 4 * h;     // channels j and j+8, j = 4h..4h+3
-                if (p.fmt != GLQ_FMT_Q2) {
+                if (p.ts) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int k = st * 128 + tc_ts_channel_of(atom * 64 + c * 8 + i);
+                        if (k < p.K) v[i] = __ldg(src + k);
+                    }
+                } else if (p.fmt != GLQ_FMT_Q2) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int k = k0 + tc_channel_of(p.fmt, 8 * h + i);
@@ -643,6 +656,310 @@ __global__ void __launch_bounds__(kTcThreads, 1) tc_kernel(const TcParams p) {
     if (warp == kTcProducers) {
         tc_fence_after();
         tc_dealloc(tmem, C::COLS);
+    }
+}
+
+// =====================================================================================================
+// Variant with the weight operand in tensor memory (2-bit affine codes).
+//
+// An SS-operand MMA reads both operands from shared memory (8 KB per 128x128x16 instruction, the whole
+// 128 B/clk port) while the producers store the unpacked weights and the bulk copy writes the token
+// operand through the same port.  Here the producers write the unpacked fp16 values straight into
+// tensor memory (tcgen05.st, 16 lanes x 256 bit shape, which matches the (g, t) ownership of the code
+// tiles: lane (g, t) holds rows g and g+8 and four consecutive K positions of every 16) and the MMA
+// takes A from there (tcgen05.mma with a TMEM A operand); only the token operand uses shared memory.
+//
+// Tensor memory (512 columns): accumulators first (TN columns, twice for gate|up), then a ring of S
+// stages of 64 columns (128 K positions x fp16) per matrix.
+//
+// K positions of a 128-channel stage: position P = 64*w + 16*n + 4*t + i (w: word of the lane's 32
+// channels, n: repeat of the store = k step inside the word's half, t: lane mod 4, i: 0..3) holds channel
+// 32*t + 16*w + 2*n + (i >> 1) + 8*(i & 1); the pre-pass lays the token operand out the same way.
+// =====================================================================================================
+__device__ __forceinline__ void tc_st_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_x2(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D (TMEM) += A (TMEM, 128 lanes x 8 columns = 16 fp16 per row) * B (shared memory descriptor)
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+template <int TN, bool SW> struct TcTsCfg {
+    static constexpr int NM = SW ? 2 : 1;
+    static constexpr int ACC = NM * TN;                       // accumulator columns
+    static constexpr int S = SW ? 2 : (TN > 128 ? 3 : 4);     // ring stages: tensor memory and shared memory both fit
+    static constexpr int B_BYTES = TN * 256;
+    static constexpr size_t SMEM = (size_t)S * B_BYTES + 1024;
+    static_assert(ACC + S * NM * 64 <= 512, "tensor memory holds 512 columns");
+};
+
+template <int TN, bool SW>
+__global__ void __launch_bounds__(kTcThreads, 1) tc_ts_kernel(const TcParams p) {
+    using C = TcTsCfg<TN, SW>;
+    constexpr int S = C::S, NM = C::NM;
+    extern __shared__ unsigned char tc_smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * S + 1];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_dead;
+
+    int slot, lt, cnt, e0;
+    if (!tc_find_tile<TN>(p, blockIdx.y, slot, lt, cnt, e0)) return;    // uniform: a padding tile
+    const int widx = p.slot_index ? __ldg(p.slot_index + slot) : slot;
+    const glq_weight_t W = p.table ? p.table[widx] : p.w;
+    const int N = W.N;
+    const int ft = blockIdx.x;
+    if (ft * kTcFeat >= N) return;
+    const bool has_lr = p.rank > 0 && W.sv != nullptr && p.a[0] != nullptr;
+    const int nst = p.nkb + (has_lr ? p.ns : 0);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sbase = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * S, bar_acc = bar_full + 16 * S;
+    volatile int* dead = &s_dead;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(bar_full + 8 * s, kTcProducers + 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        s_dead = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kTcProducers) tc_alloc(smem_u32(&s_tmem), 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t ring = tmem + C::ACC;      // first column of the weight ring
+
+    if (warp < kTcProducers) {
+        // ================= producers: unpack into tensor memory =================
+        // warp = (lane quarter q, sub): tiles 2q and 2q+1 of the CTA's eight 16-row tiles live in TMEM lanes
+        // 32q .. 32q+31, the only ones this warp may touch; sub picks the tile and the word (K half)
+        const int g = lane >> 2, t = lane & 3;
+        const int q = warp & 3, sub = warp >> 2;
+        const int tl = 2 * q + (sub & 1), wh = sub >> 1;
+        const int tile16 = ft * 8 + tl;
+        const bool live = tile16 < (N + 15) / 16;
+        const uint32_t lane_base = (uint32_t)(16 * tl) << 16;
+        const unsigned char* blk[NM];
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+            const int d = SW ? tile16 * 2 + m : tile16;
+            blk[m] = reinterpret_cast<const unsigned char*>(W.codes) + ((size_t)(d >> 1) * p.nkb * 2 + (d & 1)) * 576;
+        }
+        constexpr int D = 4;
+        uint32_t cq[D][NM][2], csz[D][NM][2];     // word `wh` of row g and of row g+8; their (scale, zero) pairs
+        auto fetch = [&](int st, uint32_t (&qv)[NM][2], uint32_t (&zv)[NM][2]) {
+#pragma unroll
+            for (int m = 0; m < NM; ++m) {
+                const bool in = live && st < p.nkb;
+                const unsigned char* src = blk[m] + (size_t)st * 2 * 576;
+                const uint32_t* wsrc = reinterpret_cast<const uint32_t*>(src) + lane * 4 + wh;
+                qv[m][0] = in ? __ldg(wsrc) : 0u;
+                qv[m][1] = in ? __ldg(wsrc + 2) : 0u;
+                const uint2 z = in ? __ldg(reinterpret_cast<const uint2*>(src + 512) + g) : make_uint2(0, 0);
+                zv[m][0] = z.x;
+                zv[m][1] = z.y;
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < D; ++d) fetch(d, cq[d], csz[d]);
+
+        int s = 0;
+        uint32_t ph = 0;
+        for (int st0 = 0; st0 < nst; st0 += D) {
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                const int st = st0 + d;
+                if (st < nst) {
+                    const bool ok = tc_wait(bar_empty + 8 * s, ph ^ 1u, dead, 100);
+                    tc_fence_after();
+                    const uint32_t acol = ring + (uint32_t)(s * NM * 64);
+                    if (ok && st < p.nkb) {
+#pragma unroll
+                        for (int m = 0; m < NM; ++m) {
+                            // regs of repeat n: {row g: positions 4t..4t+3 of k step 4*wh + n}, {row g+8: the same}
+                            uint32_t r[16];
+#pragma unroll
+                            for (int hrow = 0; hrow < 2; ++hrow) {
+                                const TcAffine af(csz[d][m][hrow], 1024.f);
+                                const uint32_t w = cq[d][m][hrow];
+#pragma unroll
+                                for (int n = 0; n < 4; ++n)
+#pragma unroll
+                                    for (int e = 0; e < 2; ++e) {
+                                        const uint32_t h = and_or(w >> (2 * (2 * n + e)), 0x00030003u, 0x64006400u);
+                                        r[4 * n + 2 * hrow + e] = af.integral ? af.exact(h) : af.general(h);
+                                    }
+                            }
+                            tc_st_x4(acol + (uint32_t)(m * 64 + wh * 32) + lane_base, r);
+                        }
+                        fetch(st + D, cq[d], csz[d]);
+                    } else if (ok) {
+                        // low-rank stage: SV rows in natural K order; this warp stores k steps 2*wh, 2*wh+1
+                        const int sl = st - p.nkb;
+#pragma unroll
+                        for (int m = 0; m < NM; ++m) {
+                            const int dt = SW ? tile16 * 2 + m : tile16;
+                            uint32_t r[8];
+#pragma unroll
+                            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                                for (int hrow = 0; hrow < 2; ++hrow) {
+                                    const int row = g + 8 * hrow;
+                                    const uint2* src = reinterpret_cast<const uint2*>(
+                                        reinterpret_cast<const unsigned char*>(W.sv) +
+                                        ((((size_t)(dt >> 1) * p.ns + sl) * 32) + (dt & 1) * 16 + row) * 128 +
+                                        (2 * wh + n) * 32 + t * 8);
+                                    const uint2 v = live ? __ldg(src) : make_uint2(0, 0);
+                                    r[4 * n + 2 * hrow] = v.x;
+                                    r[4 * n + 2 * hrow + 1] = v.y;
+                                }
+                            tc_st_x2(acol + (uint32_t)(m * 64 + wh * 16) + lane_base, r);
+                        }
+                    }
+                    tc_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                    if (++s == S) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
+                }
+            }
+        }
+
+        // ================= epilogue: TMEM -> registers -> global =================
+        const bool acc_ok = tc_wait(bar_acc, 0, dead, 101);
+        tc_fence_after();
+        const int part = warp >> 2;                                // quarter of the token columns
+        const int f = ft * kTcFeat + q * 32 + lane;
+        const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+        const __half* bias = reinterpret_cast<const __half*>(W.bias);
+        const float bv = (!SW && bias && f < N) ? __half2float(__ldg(bias + f)) : 0.f;
+        for (int c0 = part * (TN / 4); c0 < (part + 1) * (TN / 4); c0 += 16) {
+            uint32_t vg[16], vu[16];
+            tc_ld16(trow + (uint32_t)c0, vg);
+            if (SW) tc_ld16(trow + (uint32_t)(TN + c0), vu);
+            tc_ld_wait();
+            if (acc_ok && f < N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int rr = lt * TN + c0 + j;
+                    if (rr < cnt) {
+                        float v = round16(__uint_as_float(vg[j]));
+                        if (SW) {
+                            v = round16(silu16(v) * round16(__uint_as_float(vu[j])));
+                        } else {
+                            if (bias) v = round16(v + bv);
+                            if (p.entry_scale) v = round16(__half2float(__ldg(p.entry_scale + e0 + rr)) * v);
+                        }
+                        p.y[(size_t)(e0 + rr) * p.ldy + f] = __float2half_rn(v);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else if (warp == kTcProducers) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc_idesc(TN);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int st = 0; st < nst && ok; ++st) {
+                ok = tc_wait(bar_full + 8 * s, ph, dead, 100);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acol = ring + (uint32_t)(s * NM * 64);
+                const uint32_t bbase = sbase + (uint32_t)s * C::B_BYTES;
+                if (st < p.nkb) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint64_t bd = tc_smem_desc(bbase + (uint32_t)(kk >> 2) * (TN * 128) + (uint32_t)(kk & 3) * 32u);
+                        tc_mma_f16_ts(tmem, acol + 8 * kk, bd, idesc, (st | kk) != 0);
+                        if (SW) tc_mma_f16_ts(tmem + TN, acol + 64 + 8 * kk, bd, idesc, (st | kk) != 0);
+                    }
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        tc_mma_f16_ts(tmem, acol + 8 * kk, tc_smem_desc(bbase + (uint32_t)kk * 32u), idesc, 1);
+                        if (SW) tc_mma_f16_ts(tmem + TN, acol + 64 + 8 * kk, tc_smem_desc(bbase + TN * 128 + (uint32_t)kk * 32u), idesc, 1);
+                    }
+                }
+                tc_commit(bar_empty + 8 * s);
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            if (ok) tc_commit(bar_acc);
+        }
+        __syncwarp();
+    } else {
+        // ================= loader of the token operand =================
+        if (lane == 0) {
+            const unsigned char* tile = p.xp + (size_t)blockIdx.y * p.tile_bytes;
+            int s = 0;
+            uint32_t ph = 0;
+            int issued = 0;
+            for (int st = 0; st < nst; ++st) {
+                if (!tc_wait(bar_empty + 8 * s, ph ^ 1u, dead, 100)) break;
+                const uint32_t bbase = sbase + (uint32_t)s * C::B_BYTES;
+                const unsigned char* src;
+                uint32_t bytes;
+                if (st < p.nkb) {
+                    src = tile + (size_t)st * TN * 256;
+                    bytes = TN * 256;
+                } else {
+                    src = tile + (size_t)p.nkb * TN * 256 + (size_t)(st - p.nkb) * p.na * TN * 128;
+                    bytes = (uint32_t)p.na * TN * 128;
+                }
+                mbar_expect_tx(bar_full + 8 * s, bytes);
+                bulk_g2s(bbase, src, bytes, bar_full + 8 * s);
+                ++issued;
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1u;
+                }
+            }
+            if (*dead) {      // do not leave while copies are in flight
+                int s2 = s;
+                uint32_t ph2 = ph;
+                for (int i = 0; i < S && i < issued; ++i) {
+                    if (--s2 < 0) {
+                        s2 = S - 1;
+                        ph2 ^= 1u;
+                    }
+                    const unsigned long long t0 = global_ns();
+                    while (!mbar_test_wait(bar_full + 8 * s2, ph2) && global_ns() - t0 < 2000000ull) __nanosleep(64);
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    __syncthreads();
+    if (warp == kTcProducers) {
+        tc_fence_after();
+        tc_dealloc(tmem, 512);
     }
 }
 
