@@ -103,13 +103,13 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, bool& d
     if (dead) return;
     if (mbar_try_wait(bar, parity)) return;
     const unsigned long long t0 = global_ns();
-    while (!mbar_test_wait(bar, parity)) {
+    // try_wait suspends the thread in hardware for a bounded time: a waiting warp takes no issue slots
+    while (!mbar_try_wait(bar, parity)) {
         if (global_ns() - t0 > 2000000ull) {
             glq_ok(false, 100, bar, parity);
             dead = true;
             return;
         }
-        __nanosleep(64);
     }
 }
 __device__ __forceinline__ uint4 ld_global_u4(const uint4* p) {

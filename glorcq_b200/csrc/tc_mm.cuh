@@ -237,14 +237,15 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     if (*dead) return false;
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
-    while (!mbar_test_wait(bar, parity)) {
+    // try_wait suspends the thread in hardware for a bounded time, so a waiting warp takes no issue slots
+    // from the working ones; the loop only re-arms it and enforces the overall limit
+    while (!mbar_try_wait(bar, parity)) {
         if (*dead) return false;
         if (global_ns() - t0 > 2000000ull) {
             glq_ok(false, code, bar, parity);
             *dead = 1;
             return false;
         }
-        __nanosleep(32);
     }
     return true;
 }
