@@ -82,8 +82,9 @@ _SIGS = {
     "glq_pack_f16": (C.c_int, [vp, C.c_long, C.c_long, C.c_int, C.c_int, vp, vp]),
     "glq_dequant_tiled": (C.c_int, [C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
     "glq_debug_error": (C.c_int, [vp, C.c_int]),
+    "glq_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "glq_attn_decode": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
-                                  C.c_float, vp]),
+                                  C.c_float, vp, C.c_size_t, vp, C.c_size_t, vp]),
     "glq_rht_forward": (C.c_int, [vp, C.c_int, C.c_int64, vp, C.c_int, C.c_int, C.c_float, vp, C.c_int, C.c_int64, vp]),
     "glq_mm_workspace_bytes": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_mm_counters": (C.c_size_t, [C.POINTER(MMArgs)]),

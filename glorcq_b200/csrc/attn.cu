@@ -7,6 +7,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 
 #include "glq_common.cuh"
@@ -45,9 +46,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
     const __half* __restrict__ q, const __half* __restrict__ k_new, const __half* __restrict__ v_new,
     const __half* __restrict__ cos_t, const __half* __restrict__ sin_t, const long long* __restrict__ pos_p,
     __half* __restrict__ k_cache, __half* __restrict__ v_cache, __half* __restrict__ out, int n_heads, int n_kv, int max_len,
-    const __half* __restrict__ q_norm_w, const __half* __restrict__ k_norm_w, float eps) {
+    const __half* __restrict__ q_norm_w, const __half* __restrict__ k_norm_w, float eps, float* __restrict__ partial,
+    int* __restrict__ arrivals) {
     constexpr int HD = EPL * 32;
-    const int h = blockIdx.x, b = blockIdx.y;
+    const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int group = n_heads / n_kv, kvh = h / group;
     long long pos = *pos_p;
@@ -67,7 +69,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
     rope_norm<EPL>(kn, k_norm_w, eps, HD, cs, sn, lane);
     __half* kc = k_cache + ((size_t)b * n_kv + kvh) * max_len * HD;
     __half* vc = v_cache + ((size_t)b * n_kv + kvh) * max_len * HD;
-    if (h % group == 0 && warp == 0) {     // one CTA per key/value head stores the new entry
+    if (h % group == 0 && warp == 0 && z == 0) {     // one CTA per key/value head stores the new entry
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
             kc[(size_t)pos * HD + lane * EPL + i] = __float2half_rn(kn[i]);
@@ -92,7 +94,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
         for (int i = 0; i < EPL; ++i) o[i] = o[i] * a + p * vv[i];
         m = mn;
     };
-    for (long long t = warp; t < pos; t += kAttnWarps) {
+    // this CTA's share of the cached positions (the grid's z dimension splits them)
+    const long long per = (pos + nsplit - 1) / nsplit;
+    const long long t_lo = (long long)z * per, t_hi = t_lo + per < pos ? t_lo + per : pos;
+    for (long long t = t_lo + warp; t < t_hi; t += kAttnWarps) {
         float kk[EPL], vv[EPL];
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
@@ -101,7 +106,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
         }
         visit(kk, vv);
     }
-    if (warp == 0) visit(kn, vn);
+    if (warp == 0 && z == 0) visit(kn, vn);
     // combine the warps
     __shared__ float sm_m[kAttnWarps], sm_l[kAttnWarps], sm_o[kAttnWarps][HD];
     if (lane == 0) {
@@ -111,6 +116,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
 #pragma unroll
     for (int i = 0; i < EPL; ++i) sm_o[warp][lane * EPL + i] = o[i];
     __syncthreads();
+    __shared__ int s_last;
     if (warp == 0) {
         float mm = -INFINITY;
         for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm_m[w]);
@@ -123,29 +129,85 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
 #pragma unroll
             for (int i = 0; i < EPL; ++i) oo[i] += sm_o[w][lane * EPL + i] * a;
         }
+        if (nsplit == 1) {
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) out[((size_t)b * n_heads + h) * HD + lane * EPL + i] = __float2half_rn(oo[i] / ll);
+            for (int i = 0; i < EPL; ++i) out[((size_t)b * n_heads + h) * HD + lane * EPL + i] = __float2half_rn(oo[i] / ll);
+            return;
+        }
+        // several CTAs per head: leave (max, sum, weighted values) of this share; the CTA that arrives last
+        // (counter per head, reset by it) merges the shares in a fixed order
+        float* mine = partial + (((size_t)b * n_heads + h) * nsplit + z) * (HD + 2);
+        if (lane == 0) {
+            mine[0] = mm;
+            mine[1] = ll;
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) mine[2 + lane * EPL + i] = oo[i];
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) s_last = atomicAdd(arrivals + (size_t)b * n_heads + h, 1) == nsplit - 1;
+        __syncwarp();
+        if (!s_last) return;
+        __threadfence();
+        const float* all = partial + ((size_t)b * n_heads + h) * nsplit * (HD + 2);
+        float gm = -INFINITY;
+        for (int s2 = 0; s2 < nsplit; ++s2) gm = fmaxf(gm, __ldcg(all + (size_t)s2 * (HD + 2)));
+        float gl = 0.f, go[EPL];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) go[i] = 0.f;
+        for (int s2 = 0; s2 < nsplit; ++s2) {
+            const float* pp = all + (size_t)s2 * (HD + 2);
+            const float pm = __ldcg(pp);
+            const float a = pm == -INFINITY ? 0.f : __expf(pm - gm);
+            gl += __ldcg(pp + 1) * a;
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) go[i] += __ldcg(pp + 2 + lane * EPL + i) * a;
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) out[((size_t)b * n_heads + h) * HD + lane * EPL + i] = __float2half_rn(go[i] / gl);
+        if (lane == 0) arrivals[(size_t)b * n_heads + h] = 0;
     }
 }
 
 }  // namespace
 
+// position splits per head: enough CTAs to fill the device for long caches
+static int attn_splits(int B, int n_heads, int max_len) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int s = (2 * sms + B * n_heads - 1) / (B * n_heads);
+    s = std::max(1, std::min(s, 16));
+    return std::min(s, std::max(1, max_len / 64));
+}
+
+extern "C" size_t glq_attn_decode_workspace_bytes(int B, int n_heads, int head_dim, int max_len) {
+    if (B <= 0 || n_heads <= 0 || head_dim <= 0) return 0;
+    const int s = attn_splits(B, n_heads, max_len);
+    return s == 1 ? 0 : (size_t)B * n_heads * s * (head_dim + 2) * sizeof(float);
+}
+
 extern "C" int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const void* cos_t, const void* sin_t,
                                const int64_t* pos, void* k_cache, void* v_cache, void* out, int B, int n_heads, int n_kv,
                                int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps,
+                               void* workspace, size_t workspace_bytes, int32_t* counters, size_t n_counters,
                                void* stream) {
     if (!q || !k_new || !v_new || !cos_t || !sin_t || !pos || !k_cache || !v_cache || !out) return GLQ_ERR_ARG;
     if (B < 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || max_len <= 0) return GLQ_ERR_ARG;
     if (B == 0) return GLQ_OK;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const dim3 grid(n_heads, B), block(kAttnWarps * 32);
+    const int nsplit = attn_splits(B, n_heads, max_len);
+    if (nsplit > 1) {
+        if (!workspace || workspace_bytes < glq_attn_decode_workspace_bytes(B, n_heads, head_dim, max_len)) return GLQ_ERR_WORKSPACE;
+        if (!counters || n_counters < (size_t)B * n_heads) return GLQ_ERR_WORKSPACE;
+    }
+    const dim3 grid(n_heads, B, nsplit), block(kAttnWarps * 32);
 #define GLQ_ATTN(EPL)                                                                                              \
     attn_decode_kernel<EPL><<<grid, block, 0, st>>>(                                                               \
         reinterpret_cast<const __half*>(q), reinterpret_cast<const __half*>(k_new), reinterpret_cast<const __half*>(v_new), \
         reinterpret_cast<const __half*>(cos_t), reinterpret_cast<const __half*>(sin_t),                           \
         reinterpret_cast<const long long*>(pos), reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache), \
         reinterpret_cast<__half*>(out), n_heads, n_kv, max_len, reinterpret_cast<const __half*>(q_norm_w),         \
-        reinterpret_cast<const __half*>(k_norm_w), eps)
+        reinterpret_cast<const __half*>(k_norm_w), eps, reinterpret_cast<float*>(workspace), counters)
     switch (head_dim) {
         case 32: GLQ_ATTN(1); break;
         case 64: GLQ_ATTN(2); break;

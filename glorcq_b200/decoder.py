@@ -99,12 +99,15 @@ class _Attention(nn.Module):
             y = torch.empty_like(q)
             kc, vc = cache.k[self.layer_idx], cache.v[self.layer_idx]
             with torch.cuda.device(x.device):
-                _lib.check(_lib.lib().glq_attn_decode(
+                L = _lib.lib()
+                ws, ctr = tiled.workspace(x.device, L.glq_attn_decode_workspace_bytes(
+                    B, c.num_attention_heads, c.head_dim, cache.max_cache_len), B * c.num_attention_heads)
+                _lib.check(L.glq_attn_decode(
                     q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(), cache_position.data_ptr(),
                     kc.data_ptr(), vc.data_ptr(), y.data_ptr(), B, c.num_attention_heads, c.num_key_value_heads,
                     c.head_dim, cache.max_cache_len, None if self.q_norm is None else self.q_norm.data_ptr(),
                     None if self.k_norm is None else self.k_norm.data_ptr(), float(c.rms_norm_eps),
-                    tiled._stream_ptr(x.device)), "attn_decode")
+                    ws.data_ptr(), ws.numel(), ctr.data_ptr(), ctr.numel(), tiled._stream_ptr(x.device)), "attn_decode")
             return self.o_proj(y.view(B, 1, -1))
         q = self.q_proj(x).view(B, T, c.num_attention_heads, c.head_dim)
         k = self.k_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)

@@ -308,10 +308,16 @@ int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n_tokens, voi
  * convention from cos / sin tables (max positions, head_dim) fp16 at position *pos (device int64, so a
  * captured launch follows the replayed position); the new key / value are stored into the caches
  * (B, n_kv, max_len, head_dim) fp16 at that position; out (B, n_heads*head_dim) fp16 =
- * softmax(q k^T / sqrt(head_dim)) v over positions 0..*pos.  head_dim in {32, 64, 128, 256}. */
+ * softmax(q k^T / sqrt(head_dim)) v over positions 0..*pos.  head_dim in {32, 64, 128, 256}.
+ * The cached positions of a head are split over several CTAs when the cache is long; their partial
+ * results go through `workspace` (glq_attn_decode_workspace_bytes; contents irrelevant) and are merged
+ * by the CTA that arrives last; `counters` (B * n_heads ints) must be zero before the first call and are
+ * left zero. */
+size_t glq_attn_decode_workspace_bytes(int B, int n_heads, int head_dim, int max_len);
 int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const void* cos_t, const void* sin_t,
                     const int64_t* pos, void* k_cache, void* v_cache, void* out, int B, int n_heads, int n_kv,
-                    int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps, void* stream);
+                    int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps, void* workspace,
+                    size_t workspace_bytes, int32_t* counters, size_t n_counters, void* stream);
 
 #ifdef __cplusplus
 }

@@ -99,8 +99,9 @@ def test_build_layers_matches_oracle(dev, fmt):
     assert cases.rel_l2(ql(x.to(dev)).cpu(), O.linear_forward(oq, x)) <= 1e-3
 
 
+@pytest.mark.parametrize("cache_len", [32, 320])     # 320: the decode attention splits the positions over CTAs
 @pytest.mark.parametrize("cfg", [CFG, MIXTRAL, QWEN3], ids=["qwen2moe", "mixtral", "qwen3moe"])
-def test_decoder_logits_prefill_and_decode(dev, cfg):
+def test_decoder_logits_prefill_and_decode(dev, cfg, cache_len):
     from glorcq_b200.decoder import StaticKVCache
     model, _, olayers, dense = _models(cfg, dev, 31)
     if cfg is QWEN3:   # per-head q/k norms
@@ -114,10 +115,10 @@ def test_decoder_logits_prefill_and_decode(dev, cfg):
         md, cr, _ = synthetic.make_checkpoint(cfg, seed=31, rank=16, attn_rank=32, n_clusters=3)
         layers, _ = MB.build_layers(md["model_config"], md["layers"], cr, device=dev)
         model = GLoRCQDecoder(cfg, layers, dense=dense, device=dev)
-    T = 12
+    T = 12 if cache_len == 32 else 45
     ids = torch.randint(0, cfg["vocab_size"], (1, T + 1), generator=torch.Generator().manual_seed(3))
     ref = O.decoder_forward(cfg, olayers, dense, ids)
-    cache = StaticKVCache(model.config, 1, 32, dev)
+    cache = StaticKVCache(model.config, 1, cache_len, dev)
     with torch.no_grad():
         lg = model(input_ids=ids[:, :T].to(dev), cache_position=torch.arange(T, device=dev), past_key_values=cache)[0]
         assert cases.rel_l2(lg.cpu(), ref[:, :T]) <= REL_LOGITS
