@@ -94,6 +94,21 @@ def test_many_rows_tensor_core_path(dev, N, K, rank, B, int_zeros):
     assert tiled.debug_error() is None
 
 
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("B", [1, 40])
+def test_mixtral_expert_projection_shapes(dev, N, K, B):
+    """The largest projections of the benchmark configurations (expert up / down of a Mixtral-8x7B-shaped
+    layer): long reductions (112 k blocks) and many row tiles."""
+    d = cases.make_linear(3 * N + K + B, N, K, rank=64)
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(N + K + B, B, K)
+    y = lin(x.to(dev)).cpu()
+    ref = O.linear_forward(cases.to_oracle_linear(d), x)
+    assert cases.rel_l2(y, ref) <= REL
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
 def test_linear_batch_dims_and_empty(dev):
     d = cases.make_linear(5, 96, 256, rank=16)
     lin = cases.to_b200_linear(d, dev)

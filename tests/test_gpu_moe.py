@@ -267,3 +267,21 @@ def test_experts_adapter_token_counts_and_dropped_slots(dev, T):
     idx_ref[0, 1] = idx2[0, 0] ^ 1          # any other expert, weight zero
     ref2 = O.experts_forward(cases.to_oracle_moe(blk).experts, x, idx_ref, w2)
     assert cases.rel_l2(ge(x.to(dev), idx2.to(dev), w2.to(dev)).cpu(), ref2) <= REL_BLOCK
+
+
+# ---- other model families' block shapes ---------------------------------------------------------------
+@pytest.mark.parametrize("N", [1, 5, 40])
+def test_many_experts_top8_renormalised(dev, N):
+    """Qwen3-MoE style routing: 128 experts, top-8, renormalised weights, no shared expert."""
+    blk = cases.make_moe(520 + N, 256, 128, 128, 8, I_shared=0, rank=16, experts_per_cluster=8, norm_topk_prob=True)
+    mb, y, logits, ref, ref_logits = _run(blk, N, dev, 1520 + N)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
+    assert cases.rel_l2(logits.float(), ref_logits.float()) <= REL
+
+
+@pytest.mark.parametrize("N", [1, 16])
+def test_two_of_eight_experts_renormalised(dev, N):
+    """Mixtral style routing: 8 experts, top-2 always renormalised, no shared expert, wide intermediate."""
+    blk = cases.make_moe(530 + N, 256, 896, 8, 2, I_shared=0, rank=16, experts_per_cluster=2, norm_topk_prob=True)
+    mb, y, logits, ref, ref_logits = _run(blk, N, dev, 1530 + N)
+    assert cases.rel_l2(y, ref) <= REL_BLOCK
