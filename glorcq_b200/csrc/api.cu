@@ -284,44 +284,59 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
     int sk = 1;
     const long want_iters = (long)kStreamCtasPerSm * num_sms();
     while (sk < 8 && (long)n_problems * cdiv(g.npairs * sk, kWarpsPerCta) < want_iters && units >= 2 * sk) sk *= 2;
-    g.sk = sk;
-    g.kb_per_split = cdiv(units, sk) * group_blocks;
-    g.ips = cdiv(g.npairs * sk, kWarpsPerCta);
-    g.stage_bytes = std::max(kStreamCB * 2 * block_bytes_of(fmt), 4096);
-    size_t off = kWarpsPerCta * kMaxStages * 8;
-    off = (off + 127) / 128 * 128;
-    g.off_xs = (int)off;
-    if (g.i8) {
-        const int p8 = fmt == GLQ_FMT_Q2 ? 2 : 1;
-        off += (size_t)g.nkb * p8 * (2 * rows) * 4 * 16;
-        g.off_ox = (int)off;
-        off += (size_t)g.nkb * rows * 8;
-    } else {
-        const int xs_u4 = (fmt == GLQ_FMT_Q4) ? 8 : 16;
-        off += (size_t)g.nkb * xs_u4 * g.ntc * 16;
-        g.off_ox = (int)off;
-        off += (size_t)g.nkb * g.ntc * 8;
-    }
-    off = (off + 15) / 16 * 16;
-    g.off_as = (int)off;
-    off += (size_t)(g.swiglu ? 2 : 1) * rows * std::max(rank, 16) * 2;
-    off = (off + 127) / 128 * 128;
-    g.off_ring = (int)off;
-    const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.nt * 32 * 16 : 0;
-    // two CTAs per SM when the staged activations leave room for it, else one
-    size_t cap = (size_t)(kStreamCtasPerSm == 1 ? 220 : 110) * 1024;
     int ctas_per_sm = kStreamCtasPerSm;
-    if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) {
-        cap = 220 * 1024;
-        ctas_per_sm = 1;
+    for (;; sk /= 2) {
+        g.sk = sk;
+        g.kb_per_split = cdiv(units, sk) * group_blocks;
+        g.ips = cdiv(g.npairs * sk, kWarpsPerCta);
+        g.stage_bytes = std::max(kStreamCB * 2 * block_bytes_of(fmt), 4096);
+        size_t off = kWarpsPerCta * kMaxStages * 8;
+        off = (off + 127) / 128 * 128;
+        g.off_xs = (int)off;
+        if (g.i8) {
+            const int p8 = fmt == GLQ_FMT_Q2 ? 2 : 1;
+            off += (size_t)g.nkb * p8 * (2 * rows) * 4 * 16;
+            g.off_ox = (int)off;
+            off += (size_t)g.nkb * rows * 8;
+        } else {
+            const int xs_u4 = (fmt == GLQ_FMT_Q4) ? 8 : 16;
+            off += (size_t)g.nkb * xs_u4 * g.ntc * 16;
+            g.off_ox = (int)off;
+            off += (size_t)g.nkb * g.ntc * 8;
+        }
+        off = (off + 15) / 16 * 16;
+        g.off_as = (int)off;
+        off += (size_t)(g.swiglu ? 2 : 1) * rows * std::max(rank, 16) * 2;
+        off = (off + 127) / 128 * 128;
+        g.off_ring = (int)off;
+        const size_t red = sk > 1 ? (size_t)2 * kWarpsPerCta * 2 * g.nt * 32 * 16 : 0;
+        // two CTAs per SM when the staged activations leave room for it, else one
+        size_t cap = (size_t)(kStreamCtasPerSm == 1 ? 220 : 110) * 1024;
+        ctas_per_sm = kStreamCtasPerSm;
+        if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) {
+            cap = 220 * 1024;
+            ctas_per_sm = 1;
+        }
+        if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) {
+            if (sk > 1) continue;
+            return false;
+        }
+        int stages = (int)((cap - off - red) / ((size_t)kWarpsPerCta * g.stage_bytes));
+        g.stages = std::min(stages, kMaxStages);
+        off += (size_t)kWarpsPerCta * g.stages * g.stage_bytes;
+        g.off_red = (int)off;
+        off += red;
+        g.smem = off;
+        // the k-split reduction buffer may be what pushes the CTA over half an SM's shared memory: fewer
+        // splits with two CTAs per SM stream better, as long as every SM still gets work
+        if (ctas_per_sm == 1 && sk > 1 && kStreamCtasPerSm == 2 &&
+            (size_t)g.off_ring + (size_t)kWarpsPerCta * 2 * g.stage_bytes <= (size_t)110 * 1024 &&
+            (long)n_problems * cdiv(g.npairs, kWarpsPerCta) >= num_sms()) {
+            sk = 2;      // -> one split: no reduction buffer
+            continue;
+        }
+        break;
     }
-    if (off + red + (size_t)kWarpsPerCta * 2 * g.stage_bytes > cap) return false;
-    int stages = (int)((cap - off - red) / ((size_t)kWarpsPerCta * g.stage_bytes));
-    g.stages = std::min(stages, kMaxStages);
-    off += (size_t)kWarpsPerCta * g.stages * g.stage_bytes;
-    g.off_red = (int)off;
-    off += red;
-    g.smem = off;
     const long iters = (long)n_problems * g.ips;
     g.grid = (int)std::min<long>(iters, (long)ctas_per_sm * num_sms());
     *out = g;
