@@ -138,6 +138,7 @@ static int plan_geometry(int fmt, int epilogue, int N, int K, int group_size, in
 // launch with programmatic stream serialization: the grid may be scheduled while the previous kernel of
 // the stream still runs; the kernels wait for it (griddepcontrol.wait) before they read its results
 static thread_local bool t_dependent_launch = false;
+static thread_local bool t_share_sm = false;
 template <typename Kern, typename Params>
 static int launch_dependent(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, const Params& p) {
     cudaLaunchConfig_t cfg{};
@@ -403,10 +404,14 @@ static int launch_stream(int fmt, SkinnyParams& p, const StreamGeom& g, int N, i
     sp.off_as = g.off_as;
     sp.off_ring = g.off_ring;
     sp.off_red = g.off_red;
+    StreamGeom gl = g;
+    // a concurrent stream runs grouped products too: two thirds of the CTA slots, so that its kernels find room
+    // (measured on the MoE block: the shared expert's branch beside the routed experts')
+    if (t_share_sm && gl.grid > 4 * num_sms() / 3) gl.grid = 4 * num_sms() / 3;
     switch (fmt) {
-        case GLQ_FMT_Q2: return launch_stream_fmt<GLQ_FMT_Q2>(sp, g, st);
-        case GLQ_FMT_Q4: return launch_stream_fmt<GLQ_FMT_Q4>(sp, g, st);
-        case GLQ_FMT_T2: return launch_stream_fmt<GLQ_FMT_T2>(sp, g, st);
+        case GLQ_FMT_Q2: return launch_stream_fmt<GLQ_FMT_Q2>(sp, gl, st);
+        case GLQ_FMT_Q4: return launch_stream_fmt<GLQ_FMT_Q4>(sp, gl, st);
+        case GLQ_FMT_T2: return launch_stream_fmt<GLQ_FMT_T2>(sp, gl, st);
     }
     return GLQ_ERR_ARG;
 }
@@ -594,6 +599,7 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
     if (a->rank < 0 || a->rank % 16 != 0) return GLQ_ERR_UNSUPPORTED;
     if (a->rank > 0 && (a->a0 || a->a1) && (a->lda % 8 != 0 || !aligned16(a->a0) || !aligned16(a->a1)))
         return GLQ_ERR_ALIGN;
+    t_share_sm = (a->flags & GLQ_MM_SHARE_SM) != 0;
     TcGeom tg;
     const bool use_tc = plan_tc(a, &tg);
     if (use_tc && !tg.hybrid) {

@@ -16,6 +16,10 @@ using namespace glq;
 namespace {
 
 inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+inline bool share_sm() {
+    static const bool v = std::getenv("GLQ_NO_SHARE_SM") == nullptr;
+    return v;
+}
 inline bool no_dependent_launch() {
     static const bool v = std::getenv("GLQ_NO_PDL") != nullptr;
     return v;
@@ -437,6 +441,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         // (chaining every launch this way, GLQ_MM_AFTER_KERNEL, measured no faster than plain launches
         // inside a graph: only the two x.U edges, whose consumers have real independent work, are used)
         if (!after_kernel[on_aux ? 1 : 0]) mm.flags &= ~GLQ_MM_A_FROM_PREVIOUS_LAUNCH;
+        if (on_aux && forked && share_sm()) mm.flags |= GLQ_MM_SHARE_SM;      // the routed products run beside it
         after_kernel[on_aux ? 1 : 0] = true;
         mm.workspace = ws + (on_aux ? L.mm2 : L.mm);
         mm.workspace_bytes = L.mm_bytes;

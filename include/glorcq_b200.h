@@ -192,6 +192,8 @@ typedef struct glq_mm_args {
  * (no event wait or foreign work in between): the launch may be programmatically dependent on it; the
  * kernel waits for that launch before its first load. */
 #define GLQ_MM_AFTER_KERNEL 2
+/* Another stream runs grouped products at the same time: use two thirds of the CTA slots, so that both find room. */
+#define GLQ_MM_SHARE_SM 4
 
 /* Scratch bytes / arrival counters a call with these args needs (both 0 when no CTA-level k split is
  * used).  The counters must be zero when a call starts and are zero again when it ends, so one
