@@ -662,14 +662,17 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         if ((rc = finish(m)) != GLQ_OK) return rc;
         if (forked) {
             on_aux = false;
-            if (cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_join), reinterpret_cast<cudaStream_t>(aux_stream)) !=
-                    cudaSuccess ||
-                cudaStreamWaitEvent(st, reinterpret_cast<cudaEvent_t>(ev_join), 0) != cudaSuccess)
+            if (cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_join), reinterpret_cast<cudaStream_t>(aux_stream)) != cudaSuccess)
                 return GLQ_ERR_CUDA;
         }
     }
     }   // phases before the combine
     if (phase == GLQ_MOE_PHASE_EXPERTS) return GLQ_OK;
+    // the shared expert's branch joins only here: with expert parallelism the caller's exchange of the entry
+    // buffer, issued between the two phases, overlaps the rest of that branch
+    if (aux_stream != nullptr && ev_fork != nullptr && ev_join != nullptr && shared &&
+        cudaStreamWaitEvent(st, reinterpret_cast<cudaEvent_t>(ev_join), 0) != cudaSuccess)
+        return GLQ_ERR_CUDA;
 
     // 8. combine
     const dim3 grid((d->H / 8 + 255) / 256, n);
