@@ -318,10 +318,11 @@ def run_ours(args, rank, world, local_rank):
     mine = rank if batch > 1 else 0
 
     def token(x):
+        # the decoder's RMS norm between blocks keeps every layer's input at unit scale; it runs inside the
+        # block's combine kernel (same arithmetic as torch's rms_norm on the block output)
+        eps = torch.finfo(torch.float16).eps
         for blk in blocks:
-            x, _ = blk(x)
-            # the decoder's RMS norm between blocks (library op): keeps every layer's input at unit scale
-            x = torch.nn.functional.rms_norm(x, (x.shape[-1],))
+            _, _, x = blk(x, next_norm=(None, eps))
         return x
 
     # warm-up outside capture (builds workspaces), then capture one token

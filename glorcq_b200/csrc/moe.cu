@@ -366,6 +366,93 @@ __global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __r
     *reinterpret_cast<uint4*>(out + (size_t)t * H + c0) = *reinterpret_cast<const uint4*>(o);
 }
 
+// Combine with the decoder's next steps folded in: out = residual + block output (when a residual is given),
+// and normed = rms_norm(out) * weight.  One CTA per token, 8 columns per thread and step, up to 4 steps
+// (H <= 8192); the sum of squares goes through shared memory.
+__global__ void __launch_bounds__(256) moe_combine_norm_kernel(const __half* __restrict__ yd, const int* __restrict__ tok_entries,
+                                                               int n_entries, const int* __restrict__ sel, int k, int H,
+                                                               int by_expert, const __half* __restrict__ ysh,
+                                                               const __half* __restrict__ logits, int ldl, int gate_col,
+                                                               const __half* __restrict__ residual,
+                                                               const __half* __restrict__ norm_w, float eps,
+                                                               __half* __restrict__ out, __half* __restrict__ normed) {
+    const int t = blockIdx.x;
+    int order[16];
+    for (int s = 0; s < k; ++s) order[s] = s;
+    if (by_expert) {
+        for (int i = 1; i < k; ++i) {
+            const int v = order[i];
+            const int ev = sel[t * k + v];
+            int j = i - 1;
+            while (j >= 0 && sel[t * k + order[j]] > ev) {
+                order[j + 1] = order[j];
+                --j;
+            }
+            order[j + 1] = v;
+        }
+    }
+    const float gate = (ysh && gate_col >= 0) ? sigmoid16(__half2float(logits[(size_t)t * ldl + gate_col])) : 1.f;
+    float val[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+        const int c0 = (step * 256 + threadIdx.x) * 8;
+        if (c0 >= H) continue;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int s = 0; s < k; ++s) {
+            const int entry = tok_entries[t * k + order[s]];
+            if (entry < 0 || entry >= n_entries) continue;
+            __align__(16) __half v[8];
+            *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(yd + (size_t)entry * H + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = round16(acc[i] + __half2float(v[i]));
+        }
+        if (ysh) {
+            __align__(16) __half v[8];
+            *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(ysh + (size_t)t * H + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = round16(acc[i] + round16(gate * __half2float(v[i])));
+        }
+        if (residual) {
+            __align__(16) __half v[8];
+            *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(residual + (size_t)t * H + c0);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = round16(__half2float(v[i]) + acc[i]);
+        }
+        __align__(16) __half o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[i] = __float2half_rn(acc[i]);
+            val[step][i] = acc[i];
+            ss += acc[i] * acc[i];
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * H + c0) = *reinterpret_cast<const uint4*>(o);
+    }
+    __shared__ float red[8];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float r = rsqrtf(tot / H + eps);
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+        const int c0 = (step * 256 + threadIdx.x) * 8;
+        if (c0 >= H) continue;
+        __align__(16) __half o[8], wv[8];
+        if (norm_w) *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(norm_w + c0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float nv = val[step][i] * r;
+            o[i] = __float2half_rn(norm_w ? __half2float(wv[i]) * nv : nv);
+        }
+        *reinterpret_cast<uint4*>(normed + (size_t)t * H + c0) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
 }  // namespace
 
 extern "C" size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens) {
@@ -675,6 +762,16 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         return GLQ_ERR_CUDA;
 
     // 8. combine
+    if (ep && ep->normed_out) {
+        if (d->H > 8192) return GLQ_ERR_UNSUPPORTED;
+        moe_combine_norm_kernel<<<n, 256, 0, st>>>(
+            reinterpret_cast<const __half*>(p_yd), p_tok, nk, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
+            shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, ldl, d->router_rows > d->E ? d->E : -1,
+            reinterpret_cast<const __half*>(ep->residual), reinterpret_cast<const __half*>(ep->norm_weight), ep->norm_eps,
+            reinterpret_cast<__half*>(out), reinterpret_cast<__half*>(ep->normed_out));
+        return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
+    }
+    if (ep && ep->residual) return GLQ_ERR_ARG;     // a residual needs the fused form (normed_out)
     const dim3 grid((d->H / 8 + 255) / 256, n);
     moe_combine_kernel<<<grid, 256, 0, st>>>(
         reinterpret_cast<const __half*>(p_yd), p_tok, nk, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,

@@ -234,13 +234,21 @@ class GLoRCQDecoder(nn.Module):
             cache_position = torch.arange(T, device=input_ids.device)
         cos, sin = self._tables(past_key_values.max_cache_len, input_ids.device)
         x = F.embedding(input_ids, self.embed_tokens)
-        for l in range(c.num_hidden_layers):
-            h = F.rms_norm(x, (c.hidden_size,), self.ln1[l], c.rms_norm_eps)
+        L = c.num_hidden_layers
+        h = F.rms_norm(x, (c.hidden_size,), self.ln1[0], c.rms_norm_eps) if L > 0 else x
+        for l in range(L):
             x = x + self.attn[l](h, cache_position, past_key_values, cos, sin)
             h = F.rms_norm(x, (c.hidden_size,), self.ln2[l], c.rms_norm_eps)
-            m = self.mlp[l](h)
-            x = x + (m[0] if isinstance(m, tuple) else m)
-        x = F.rms_norm(x, (c.hidden_size,), self.norm, c.rms_norm_eps)
+            nxt = self.ln1[l + 1] if l + 1 < L else self.norm          # the norm that follows this layer
+            mlp = self.mlp[l]
+            if isinstance(mlp, GraphCompatibleMoeBlock) and c.hidden_size <= 8192:
+                # residual add and the following norm run inside the block's combine kernel
+                x, _, h = mlp(h, residual=x, next_norm=(nxt, c.rms_norm_eps))
+            else:
+                m = mlp(h)
+                x = x + (m[0] if isinstance(m, tuple) else m)
+                h = F.rms_norm(x, (c.hidden_size,), nxt, c.rms_norm_eps)
+        x = h if L > 0 else F.rms_norm(x, (c.hidden_size,), self.norm, c.rms_norm_eps)
         logits = x @ self.lm_head.t()
         return (logits, past_key_values)
 

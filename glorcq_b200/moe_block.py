@@ -242,9 +242,13 @@ class GraphCompatibleMoeBlock(nn.Module):
         return self
 
     # ---- forward (inference/moe_block.py:381-436) -----------------------------------------------
-    def forward(self, hidden_states, top_k_index=None, top_k_weights=None):
+    def forward(self, hidden_states, top_k_index=None, top_k_weights=None, residual=None, next_norm=None):
         """(B, S, H) -> ((B, S, H), router logits).  With top_k_index / top_k_weights ((B*S, k)) the routing
-        is the caller's and no logits are returned (the fused-experts adapter)."""
+        is the caller's and no logits are returned (the fused-experts adapter).
+
+        ``next_norm = (weight or None, eps)`` folds the decoder's next steps into the combine kernel: the
+        first result becomes ``residual + block output`` (``residual`` (B, S, H), optional) and a third result
+        is its RMS norm times ``weight``: ((B, S, H), logits, (B, S, H))."""
         batch_size, sequence_length, hidden_dim = hidden_states.shape
         x = hidden_states.reshape(-1, hidden_dim)
         if x.dtype != torch.float16:
@@ -268,6 +272,16 @@ class GraphCompatibleMoeBlock(nn.Module):
                 raise RuntimeError(f"top_k_index / top_k_weights must have shape ({n}, {d.top_k})")
         sel = torch.empty(n, d.top_k, dtype=torch.int32, device=x.device)
         wts = torch.empty(n, d.top_k, dtype=torch.float16, device=x.device)
+        normed = res2 = nw = None
+        if next_norm is not None:
+            nw, eps = next_norm
+            normed = torch.empty(n, d.H, dtype=torch.float16, device=x.device)
+            if nw is not None:
+                nw = nw.to(device=x.device, dtype=torch.float16).contiguous()
+            if residual is not None:
+                res2 = residual.reshape(-1, hidden_dim).to(torch.float16).contiguous()
+        elif residual is not None:
+            raise RuntimeError("a residual is folded in only together with next_norm")
         if n > 0:
             L = _lib.lib()
             with torch.cuda.device(x.device):
@@ -293,10 +307,14 @@ class GraphCompatibleMoeBlock(nn.Module):
                 ep_rank, ep_world, group = self._ep
 
                 def call(ep):
+                    if (given or normed is not None) and ep is None:
+                        ep = MoeEp(0, 1, _lib.MOE_PHASE_ALL, 0, None, None, None)
                     if given:
-                        if ep is None:
-                            ep = MoeEp(0, 1, _lib.MOE_PHASE_ALL, 0, None, None, None)
                         ep.sel_in, ep.weight_in = sel_in.data_ptr(), wts_in.data_ptr()
+                    if normed is not None:
+                        ep.normed_out, ep.norm_eps = normed.data_ptr(), float(eps)
+                        ep.residual = None if res2 is None else res2.data_ptr()
+                        ep.norm_weight = None if nw is None else nw.data_ptr()
                     _lib.check(L.glq_moe_forward_ep(C.byref(d), x.data_ptr(), n, out.data_ptr(),
                                                     None if logits is None else logits.data_ptr(),
                                                     sel.data_ptr(), wts.data_ptr(), base,
@@ -317,4 +335,7 @@ class GraphCompatibleMoeBlock(nn.Module):
                     ep.phase = _lib.MOE_PHASE_COMBINE
                     call(ep)
         self.last_selected_experts, self.last_routing_weights = sel, wts
+        if normed is not None:
+            return (out.reshape(batch_size, sequence_length, hidden_dim), logits,
+                    normed.reshape(batch_size, sequence_length, hidden_dim))
         return out.reshape(batch_size, sequence_length, hidden_dim), logits

@@ -295,6 +295,12 @@ typedef struct glq_moe_ep {
      * indices (an index outside [0, E) drops the slot), weight_in (n_tokens, top_k) fp16; both NULL for
      * the block's own router.  Needs I_shared == 0 and router_logits == NULL; router_t is not read. */
     const int32_t* sel_in; const void* weight_in;
+    /* The decoder's steps after the block (the transformers layer adds the residual and the next layer norm
+     * follows; the reference leaves both to that host model), folded into the combine: when normed_out is set,
+     * out = residual + block output (residual (n_tokens, H) fp16 or NULL) and normed_out (n_tokens, H) fp16 =
+     * rms_norm(out, norm_eps) * norm_weight ((H,) fp16, NULL = ones).  H <= 8192. */
+    const void* residual; const void* norm_weight; void* normed_out;
+    float norm_eps; int32_t reserved2;
 } glq_moe_ep_t;
 int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n_tokens, void* out, void* router_logits,
                        int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,

@@ -146,6 +146,27 @@ def test_non_finite_hidden_state_keeps_indices_in_range(dev):
     assert tiled.debug_error() is None
 
 
+@pytest.mark.parametrize("N", [1, 5, 40])
+def test_combine_with_residual_and_next_norm(dev, N):
+    """The decoder's residual add and following RMS norm folded into the combine kernel give what the
+    separate tensor ops give on the block output."""
+    blk = cases.make_moe(840 + N, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    mb = cases.to_b200_moe(blk, dev)
+    x = cases.make_x(1840 + N, N, 256).reshape(1, N, 256).to(dev)
+    res = cases.make_x(2840 + N, N, 256).reshape(1, N, 256).to(dev)
+    w = (1 + 0.1 * cases.make_x(3840, 1, 256).reshape(256)).to(dev)
+    y, logits = mb(x)
+    out, logits2, normed = mb(x, residual=res, next_norm=(w, 1e-6))
+    assert torch.equal(logits, logits2)
+    ref_out = res + y
+    assert torch.equal(out, ref_out)
+    ref_norm = torch.nn.functional.rms_norm(ref_out, (256,), w, 1e-6)
+    assert cases.rel_l2(normed.cpu(), ref_norm.cpu()) <= 1e-3
+    out3, _, normed3 = mb(x, next_norm=(None, 1e-3))
+    assert torch.equal(out3, y)
+    assert cases.rel_l2(normed3.cpu(), torch.nn.functional.rms_norm(y, (256,), None, 1e-3).cpu()) <= 1e-3
+
+
 # ---- expert parallelism ---------------------------------------------------------------------------
 @pytest.mark.parametrize("N,world", [(1, 2), (3, 2), (9, 2), (9, 4), (33, 3)])
 def test_expert_parallel_emulated_on_one_gpu(dev, N, world):
