@@ -83,6 +83,7 @@ _SIGS = {
     "glq_pack_f16": (C.c_int, [vp, C.c_long, C.c_long, C.c_int, C.c_int, vp, vp]),
     "glq_dequant_tiled": (C.c_int, [C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
     "glq_debug_error": (C.c_int, [vp, C.c_int]),
+    "glq_add_rmsnorm": (C.c_int, [vp, vp, vp, C.c_float, C.c_int, C.c_int, vp, vp, vp]),
     "glq_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "glq_attn_decode": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
                                   C.c_float, vp, C.c_size_t, vp, C.c_size_t, vp]),

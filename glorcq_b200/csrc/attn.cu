@@ -169,7 +169,61 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
     }
 }
 
+// x_out = x + delta (fp16), h_out = rms_norm(x_out) * w: the residual add and the layer norm that follow the
+// attention output projection in a decoder layer, one CTA per row (H <= 8192, a multiple of 8).
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ delta,
+                                                          const __half* __restrict__ w, float eps, int H,
+                                                          __half* __restrict__ x_out, __half* __restrict__ h_out) {
+    const size_t row = (size_t)blockIdx.x * H;
+    float val[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+        const int c0 = (step * 256 + threadIdx.x) * 8;
+        if (c0 >= H) continue;
+        __align__(16) __half a[8], b[8], o[8];
+        *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(x + row + c0);
+        *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(delta + row + c0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[i] = __float2half_rn(__half2float(a[i]) + __half2float(b[i]));
+            val[step][i] = __half2float(o[i]);
+            ss += val[step][i] * val[step][i];
+        }
+        *reinterpret_cast<uint4*>(x_out + row + c0) = *reinterpret_cast<const uint4*>(o);
+    }
+    __shared__ float red[8];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float r = rsqrtf(tot / H + eps);
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+        const int c0 = (step * 256 + threadIdx.x) * 8;
+        if (c0 >= H) continue;
+        __align__(16) __half o[8], wv[8];
+        if (w) *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w + c0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __float2half_rn(w ? __half2float(wv[i]) * (val[step][i] * r) : val[step][i] * r);
+        *reinterpret_cast<uint4*>(h_out + row + c0) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
 }  // namespace
+
+extern "C" int glq_add_rmsnorm(const void* x, const void* delta, const void* weight, float eps, int rows, int H, void* x_out,
+                               void* h_out, void* stream) {
+    if (!x || !delta || !x_out || !h_out || rows < 0 || H <= 0) return GLQ_ERR_ARG;
+    if (H % 8 != 0 || H > 8192) return GLQ_ERR_UNSUPPORTED;
+    if (rows == 0) return GLQ_OK;
+    add_rmsnorm_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(delta), reinterpret_cast<const __half*>(weight), eps,
+        H, reinterpret_cast<__half*>(x_out), reinterpret_cast<__half*>(h_out));
+    return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
+}
 
 // position splits per head: enough CTAs to fill the device for long caches
 static int attn_splits(int B, int n_heads, int max_len) {

@@ -64,6 +64,21 @@ def _rotate_half(x):
     return torch.cat([-x[..., h:], x[..., :h]], dim=-1)
 
 
+def _add_rmsnorm(x, delta, weight, eps):
+    """(x + delta, rms_norm(x + delta) * weight) in one launch for fp16 rows of up to 8192 columns."""
+    H = x.shape[-1]
+    if not (x.is_cuda and x.dtype == torch.float16 and delta.dtype == torch.float16 and H % 8 == 0 and H <= 8192):
+        y = x + delta
+        return y, F.rms_norm(y, (H,), weight, eps)
+    x, delta = x.contiguous(), delta.contiguous()
+    x_out, h_out = torch.empty_like(x), torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().glq_add_rmsnorm(x.data_ptr(), delta.data_ptr(), weight.data_ptr(), float(eps),
+                                              x.numel() // H, H, x_out.data_ptr(), h_out.data_ptr(),
+                                              tiled._stream_ptr(x.device)), "add_rmsnorm")
+    return x_out, h_out
+
+
 class _Attention(nn.Module):
     def __init__(self, cfg, layer_idx, mods: Dict[str, GLoRCQLinear], dense, prefix, device):
         super().__init__()
@@ -237,8 +252,7 @@ class GLoRCQDecoder(nn.Module):
         L = c.num_hidden_layers
         h = F.rms_norm(x, (c.hidden_size,), self.ln1[0], c.rms_norm_eps) if L > 0 else x
         for l in range(L):
-            x = x + self.attn[l](h, cache_position, past_key_values, cos, sin)
-            h = F.rms_norm(x, (c.hidden_size,), self.ln2[l], c.rms_norm_eps)
+            x, h = _add_rmsnorm(x, self.attn[l](h, cache_position, past_key_values, cos, sin), self.ln2[l], c.rms_norm_eps)
             nxt = self.ln1[l + 1] if l + 1 < L else self.norm          # the norm that follows this layer
             mlp = self.mlp[l]
             if isinstance(mlp, GraphCompatibleMoeBlock) and c.hidden_size <= 8192:

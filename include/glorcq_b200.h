@@ -327,6 +327,12 @@ int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const v
                     int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps, void* workspace,
                     size_t workspace_bytes, int32_t* counters, size_t n_counters, void* stream);
 
+/* x_out = x + delta and h_out = rms_norm(x_out, eps) * weight on (rows, H) fp16 rows (weight (H,) fp16 or NULL):
+ * the residual add and layer norm between the attention output projection and the MoE block of a decoder layer
+ * (host-model glue, as glq_attn_decode).  H a multiple of 8, at most 8192. */
+int glq_add_rmsnorm(const void* x, const void* delta, const void* weight, float eps, int rows, int H, void* x_out,
+                    void* h_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
