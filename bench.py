@@ -308,6 +308,22 @@ def run_ours(args, rank, world, local_rank):
                                        ep_world=world if ep else 1, **CFG) for l in range(layers)]
     _stage(rank, "blocks built")
     H = CFG["H"]
+    # the exchange: this library's kernel over peer-mapped memory (peer stores + flags), or NCCL's all-reduce
+    # when asked for or when the symmetric allocation is not to be had on every rank
+    peer = None
+    if ep and args.exchange == "peer":
+        from glorcq_b200 import parallel
+        ok = torch.ones(1, device=dev)
+        try:
+            peer = parallel.PeerExchange.get(None, dev, 16 * CFG["top_k"], H)
+        except Exception as exc:       # noqa: BLE001 - any failure here means "use NCCL"
+            _stage(rank, f"peer exchange unavailable: {exc!r}")
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) == 0:
+            peer = None
+        for blk in blocks:
+            blk.peer_exchange_max_tokens = 16 if peer is not None else 0
     # weak scaling: one token stream per rank, so a step decodes `batch` = N tokens; every rank holds all
     # N hidden states (the replicated router and shared expert see them all) and its share of the experts
     batch = world if ep and not args.strong else 1
@@ -333,6 +349,17 @@ def run_ours(args, rank, world, local_rank):
             token(static_x)
     torch.cuda.current_stream().wait_stream(s)
     torch.cuda.synchronize()
+    if peer is not None:
+        bad = torch.tensor([float(peer.error() != 0)], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if float(bad) != 0:            # a wait ran out during warm-up: do not time that
+            _stage(rank, "peer exchange: a wait ran out in warm-up, using NCCL")
+            peer = None
+            for blk in blocks:
+                blk.peer_exchange_max_tokens = 0
+            with torch.no_grad():
+                token(static_x)
+            torch.cuda.synchronize()
     _stage(rank, "eager warm-up done")
     if args.no_graph:
         class _Eager:
@@ -418,7 +445,8 @@ def run_ours(args, rank, world, local_rank):
         cfg = workload_config(layers)
         cfg.update({"parallelism": "single GPU" if world == 1 else
                     (f"expert parallel ep{world}: expert e on rank e % {world}, router and shared expert replicated, "
-                     f"NCCL all-reduce of the per-entry outputs once per block; {batch} token stream(s) per step"
+                     + ("exchange kernel over peer memory (peer stores + flags)" if peer is not None else
+                        "NCCL all-reduce of the per-entry outputs") + f" once per block; {batch} token stream(s) per step"
                      if ep else f"replicas x{world}"),
                     "batch": batch,
                     "algorithmic_bytes_per_token": bytes_tok,
@@ -429,10 +457,13 @@ def run_ours(args, rank, world, local_rank):
                 "config": cfg,
                 "e2e": {"value": streams * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
                         "d2h_bytes_per_step": H * 2},
-                "gpu_launches": args.steps * layers * 10,
+                "gpu_launches": args.steps * layers * (11 if peer is not None else 10),
                 "roofline": roof, "roofline_gemm": roof_gemm,
                 "cpu_baseline": cpu,
                 "clocks": clocks, "kernel_self_check": err}
+        if ep:
+            line["exchange"] = {"kind": "peer" if peer is not None else "nccl",
+                                "waits_run_out": None if peer is None else int(peer.error() != 0)}
         print(json.dumps(line), flush=True)
     if world > 1:
         # all ranks leave together (rank 0 was busy with the roofline and CPU legs); a teardown that does
@@ -465,6 +496,8 @@ def main():
     ap.add_argument("--rows", type=int, default=2048)
     ap.add_argument("--problems", type=int, default=240)
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: the per-block exchange, this library's peer-memory kernel or NCCL's all-reduce")
     ap.add_argument("--strong", action="store_true",
                     help="with --gpus N > 1: one token stream for all ranks (strong scaling) instead of one per rank")
     ap.add_argument("--replicas", action="store_true",

@@ -53,14 +53,20 @@ class MoeDesc(C.Structure):
                 ("rht_in", vp), ("rht_mid", vp), ("sh_rht_mid", vp)]
 
 
+class EpPeers(C.Structure):
+    """glq_ep_peers_t"""
+    _fields_ = [("entry_bufs", vp), ("flags", vp), ("epoch", vp), ("error", vp), ("half_elems", C.c_size_t)]
+
+
 class MoeEp(C.Structure):
     """glq_moe_ep_t"""
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phase", C.c_int32), ("reserved", C.c_int32),
                 ("entry_out", vp), ("sel_in", vp), ("weight_in", vp),
-                ("residual", vp), ("norm_weight", vp), ("normed_out", vp), ("norm_eps", C.c_float), ("reserved2", C.c_int32)]
+                ("residual", vp), ("norm_weight", vp), ("normed_out", vp), ("norm_eps", C.c_float), ("reserved2", C.c_int32),
+                ("peers", C.POINTER(EpPeers))]
 
 
-MOE_PHASE_ALL, MOE_PHASE_EXPERTS, MOE_PHASE_COMBINE = 0, 1, 2
+MOE_PHASE_ALL, MOE_PHASE_EXPERTS, MOE_PHASE_COMBINE, MOE_PHASE_EXCHANGE = 0, 1, 2, 3
 
 _SIGS = {
     "glq_version": (C.c_int, []),

@@ -317,14 +317,74 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
     }
 }
 
+// ---- exchange over peer memory ---------------------------------------------------------------------------
+// One CTA.  Step e = *epoch + 1 uses half (e & 1) of every rank's exchange buffer.  The rows of this rank's
+// slots (the plan's active list holds only its own experts) go from the local staging buffer to the same
+// rows of every rank's buffer, this rank's included, as 16-byte stores; after a system-wide fence the step
+// number is published in word [rank] of every rank's flags, and the CTA waits until its own flag words
+// all show step e.  The wait is bounded by the global timer; when it runs out *error is set and the
+// kernel returns (the step's result is then incomplete, the context stays usable).
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__global__ void __launch_bounds__(1024) moe_exchange_kernel(const __half* __restrict__ staged, const int* __restrict__ n_active,
+                                                            const int* __restrict__ slot_count,
+                                                            const int* __restrict__ slot_offset, int n_entries, int H,
+                                                            int rank, int world, void* const* __restrict__ bufs,
+                                                            int* const* __restrict__ flags, int* epoch, int* error,
+                                                            size_t half_elems, unsigned long long limit_ns) {
+    __shared__ int s_step;
+    if (threadIdx.x == 0) s_step = *epoch + 1;
+    __syncthreads();
+    const int step = s_step;
+    const size_t half = (size_t)(step & 1) * half_elems;
+    const int nact = min(*n_active, n_entries);
+    const int vec_per_row = H / 8;
+    for (int s = 0; s < nact; ++s) {
+        const int off = slot_offset[s], cnt = slot_count[s];
+        if (off < 0 || cnt <= 0 || off + cnt > n_entries) continue;
+        const int nvec = cnt * vec_per_row;
+        const uint4* src = reinterpret_cast<const uint4*>(staged + (size_t)off * H);
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            const uint4 v = src[i];
+            for (int p = 0; p < world; ++p)
+                reinterpret_cast<uint4*>(reinterpret_cast<__half*>(bufs[p]) + half + (size_t)off * H)[i] = v;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+        int* theirs = flags[threadIdx.x] + rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(step) : "memory");
+        const int* mine = flags[rank] + threadIdx.x;
+        const unsigned long long t0 = global_ns();
+        for (;;) {
+            int seen;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (seen - step >= 0) break;
+            if (global_ns() - t0 > limit_ns) {
+                atomicExch(error, step);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *epoch = step;
+}
+
 // ---- combine ------------------------------------------------------------------------------------------
 // out[t] = sum over the token's experts of (already weighted, fp16) down outputs, accumulated in fp16
 // in slot order or in expert order, + sigmoid(shared gate) * shared expert output.  8 columns/thread.
 __global__ void moe_combine_kernel(const __half* __restrict__ yd, const int* __restrict__ tok_entries, int n_entries,
                                    const int* __restrict__ sel, int k, int H, int by_expert,
                                    const __half* __restrict__ ysh, const __half* __restrict__ logits, int ldl,
-                                   int gate_col, __half* __restrict__ out) {
+                                   int gate_col, __half* __restrict__ out, const int* __restrict__ epoch,
+                                   size_t half_elems) {
     asm volatile("griddepcontrol.wait;" ::: "memory");              // no-op for a plain launch
+    if (epoch) yd += (size_t)(*epoch & 1) * half_elems;            // the half the last exchange filled
     const int t = blockIdx.y;
     const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c0 >= H) return;
@@ -375,8 +435,10 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const __half* __r
                                                                const __half* __restrict__ logits, int ldl, int gate_col,
                                                                const __half* __restrict__ residual,
                                                                const __half* __restrict__ norm_w, float eps,
-                                                               __half* __restrict__ out, __half* __restrict__ normed) {
+                                                               __half* __restrict__ out, __half* __restrict__ normed,
+                                                               const int* __restrict__ epoch, size_t half_elems) {
     const int t = blockIdx.x;
+    if (epoch) yd += (size_t)(*epoch & 1) * half_elems;
     int order[16];
     for (int s = 0; s < k; ++s) order[s] = s;
     if (by_expert) {
@@ -478,8 +540,16 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
                                   void* ev_join, const glq_moe_ep_t* ep) {
     if (!d || !x || !out || n < 0) return GLQ_ERR_ARG;
     const int ep_rank = ep ? ep->rank : 0, ep_world = ep ? ep->world : 1, phase = ep ? ep->phase : GLQ_MOE_PHASE_ALL;
-    if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world || phase < GLQ_MOE_PHASE_ALL || phase > GLQ_MOE_PHASE_COMBINE)
+    if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world || phase < GLQ_MOE_PHASE_ALL || phase > GLQ_MOE_PHASE_EXCHANGE)
         return GLQ_ERR_ARG;
+    const glq_ep_peers_t* px = ep ? ep->peers : nullptr;
+    if (phase == GLQ_MOE_PHASE_EXCHANGE &&
+        (!px || !px->entry_bufs || !px->flags || !px->epoch || !px->error || ep_world > 1024 ||
+         px->half_elems < (size_t)n * d->top_k * d->H))
+        return GLQ_ERR_ARG;
+    if (phase == GLQ_MOE_PHASE_EXPERTS && px) return GLQ_ERR_ARG;     // the staging buffer is not exchanged
+    const int* px_epoch = (phase == GLQ_MOE_PHASE_COMBINE && px) ? px->epoch : nullptr;
+    const size_t px_half = px ? px->half_elems : 0;
     if (ep_world > 1 && (phase == GLQ_MOE_PHASE_ALL || !ep->entry_out)) return GLQ_ERR_ARG;   // the exchange is the caller's
     if (n == 0) return GLQ_OK;
     if (d->top_k < 1 || d->top_k > 16 || d->E < d->top_k || d->E > 256 || d->H % 8 != 0 || d->I % 8 != 0)
@@ -515,6 +585,12 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     auto p_tok = reinterpret_cast<int*>(ws + L.tok_entries);
     const int ldl = d->dense0_rows;
 
+    if (phase == GLQ_MOE_PHASE_EXCHANGE) {
+        moe_exchange_kernel<<<1, 1024, 0, st>>>(reinterpret_cast<const __half*>(p_yd), p_nact, p_cnt, p_off, nk, d->H,
+                                                ep_rank, ep_world, px->entry_bufs, px->flags, px->epoch, px->error,
+                                                px->half_elems, 1000000000ull);
+        return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
+    }
     if (phase != GLQ_MOE_PHASE_COMBINE) {
     glq_mm_args_t m;
     // the shared expert's chain runs on aux_stream (forked after the first dense product, joined before
@@ -768,7 +844,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
             reinterpret_cast<const __half*>(p_yd), p_tok, nk, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
             shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, ldl, d->router_rows > d->E ? d->E : -1,
             reinterpret_cast<const __half*>(ep->residual), reinterpret_cast<const __half*>(ep->norm_weight), ep->norm_eps,
-            reinterpret_cast<__half*>(out), reinterpret_cast<__half*>(ep->normed_out));
+            reinterpret_cast<__half*>(out), reinterpret_cast<__half*>(ep->normed_out), px_epoch, px_half);
         return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
     }
     if (ep && ep->residual) return GLQ_ERR_ARG;     // a residual needs the fused form (normed_out)
@@ -776,7 +852,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     moe_combine_kernel<<<grid, 256, 0, st>>>(
         reinterpret_cast<const __half*>(p_yd), p_tok, nk, p_sel, k, d->H, n > d->slot_order_max_tokens ? 1 : 0,
         shared ? reinterpret_cast<const __half*>(ws + L.ysh) : nullptr, p_logits, ldl,
-        d->router_rows > d->E ? d->E : -1, reinterpret_cast<__half*>(out));
+        d->router_rows > d->E ? d->E : -1, reinterpret_cast<__half*>(out), px_epoch, px_half);
     if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
     return GLQ_OK;
 }

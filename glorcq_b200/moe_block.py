@@ -85,6 +85,8 @@ class GraphCompatibleMoeBlock(nn.Module):
         self.last_routing_weights = None
         self._ep = (0, 1, None)          # (rank, world, process group)
         self._exchange = parallel.exchange_entries
+        self.peer_exchange_max_tokens = 0   # > 0: steps of up to this many tokens exchange through peer memory
+        self._peers = None
 
     def set_expert_parallel(self, rank: int, world: int, group=None):
         """Shard the routed experts: this rank keeps experts e with e % world == rank (the other
@@ -331,9 +333,20 @@ class GraphCompatibleMoeBlock(nn.Module):
                     entries = self._ws[ekey]
                     ep = MoeEp(ep_rank, ep_world, _lib.MOE_PHASE_EXPERTS, 0, entries.data_ptr(), None, None)
                     call(ep)
-                    self._exchange(entries, group)
-                    ep.phase = _lib.MOE_PHASE_COMBINE
-                    call(ep)
+                    if 0 < n <= self.peer_exchange_max_tokens:
+                        # this library's exchange kernel: peer stores into every rank's buffer, then flags
+                        if self._peers is None:
+                            self._peers = parallel.PeerExchange.get(
+                                group, x.device, self.peer_exchange_max_tokens * d.top_k, d.H)
+                        px = self._peers
+                        ep.phase, ep.peers = _lib.MOE_PHASE_EXCHANGE, C.pointer(px.peers)
+                        call(ep)
+                        ep.phase, ep.entry_out = _lib.MOE_PHASE_COMBINE, px.local_ptr
+                        call(ep)
+                    else:
+                        self._exchange(entries, group)
+                        ep.phase = _lib.MOE_PHASE_COMBINE
+                        call(ep)
         self.last_selected_experts, self.last_routing_weights = sel, wts
         if normed is not None:
             return (out.reshape(batch_size, sequence_length, hidden_dim), logits,

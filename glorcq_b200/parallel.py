@@ -33,3 +33,60 @@ def exchange_entries(entry_out: torch.Tensor, group: Optional["dist.ProcessGroup
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(entry_out, op=dist.ReduceOp.SUM, group=group)
     return entry_out
+
+
+class PeerExchange:
+    """The exchange as this library's own kernel over peer-mapped memory (phase EXCHANGE of
+    glq_moe_forward_ep) instead of an all-reduce.
+
+    Every rank allocates the same buffer in symmetric memory: two halves of ``max_entries * H`` fp16
+    (alternate steps use alternate halves) followed by one int32 flag word per rank; the rendezvous gives
+    every rank the others' addresses, which are kept on the device as the pointer tables the kernel
+    reads.  One instance serves every block of a model with the same hidden size (the blocks run one
+    after another on one stream), so it is cached per (group, device, H).  NVLink multicast binding is
+    not needed (plain peer stores) and is switched off for the allocation.
+    """
+
+    _cache: dict = {}
+
+    def __init__(self, group, device: torch.device, max_entries: int, H: int):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.max_entries, self.H = int(max_entries), int(H)
+        self.half_elems = self.max_entries * self.H
+        flag_bytes = (4 * self.world + 255) // 256 * 256
+        with torch.cuda.device(device):
+            self._buf = symm.empty(4 * self.half_elems + flag_bytes, dtype=torch.uint8, device=device)
+            self._buf.zero_()
+            self._hdl = symm.rendezvous(self._buf, group)
+            torch.cuda.synchronize(device)
+        dist.barrier(group)          # every rank's flags are zero before any peer writes them
+        ptrs = [int(self._hdl.buffer_ptrs[r]) for r in range(self.world)]
+        if ptrs[self.rank] != self._buf.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned a foreign address for the local buffer")
+        self._bufs = torch.tensor(ptrs, dtype=torch.int64, device=device)
+        self._flags = torch.tensor([p + 4 * self.half_elems for p in ptrs], dtype=torch.int64, device=device)
+        self._state = torch.zeros(2, dtype=torch.int32, device=device)      # step counter, error word
+        self.peers = _lib.EpPeers(self._bufs.data_ptr(), self._flags.data_ptr(), self._state.data_ptr(),
+                                  self._state.data_ptr() + 4, self.half_elems)
+        self.local_ptr = ptrs[self.rank]
+
+    @classmethod
+    def get(cls, group, device: torch.device, max_entries: int, H: int) -> "PeerExchange":
+        key = (id(group), str(device), int(H))
+        px = cls._cache.get(key)
+        if px is None or px.max_entries < max_entries:
+            px = cls(group, device, max(int(max_entries), 64), H)
+            cls._cache[key] = px
+        return px
+
+    def error(self) -> int:
+        """Step number of the first wait that ran out (0: none).  Synchronises."""
+        return int(self._state[1].item())

@@ -286,7 +286,22 @@ int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n_tokens, void* 
  * bit-identical results for every world size.  The exchange itself is the caller's:
  *   phase EXPERTS  -> all-reduce(entry_out) on `stream` -> phase COMBINE.
  * ep == NULL, or world == 1 with phase ALL, is glq_moe_forward. */
-enum { GLQ_MOE_PHASE_ALL = 0, GLQ_MOE_PHASE_EXPERTS = 1, GLQ_MOE_PHASE_COMBINE = 2 };
+enum { GLQ_MOE_PHASE_ALL = 0, GLQ_MOE_PHASE_EXPERTS = 1, GLQ_MOE_PHASE_COMBINE = 2, GLQ_MOE_PHASE_EXCHANGE = 3 };
+/* The exchange as one kernel of this library over peer-mapped memory (NVLink / NVSwitch), instead of the
+ * caller's all-reduce:  phase EXPERTS (entry_out = a rank-local staging buffer) -> phase EXCHANGE -> phase
+ * COMBINE.  Phase EXCHANGE stores the rows of this rank's experts into every rank's exchange buffer
+ * (plain peer stores, 16 B each), publishes the step number in every rank's flag words and waits, for at
+ * most a second, until every rank has published the same step; a wait that runs out sets *error and the
+ * kernel returns.  The buffers have two halves used by alternate steps, so that a rank one step ahead
+ * never writes rows another rank still reads; phase COMBINE reads the half of the last exchanged step.
+ * entry_bufs and flags are device arrays of `world` pointers valid on this device (each rank's buffer of
+ * 2*half_elems fp16 and its `world` int32 flag words, zeroed once before the first step); epoch and
+ * error are this rank's own device words, zeroed once.  All ranks must run the same sequence of steps. */
+typedef struct glq_ep_peers {
+    void* const* entry_bufs; int32_t* const* flags;
+    int32_t* epoch; int32_t* error;
+    size_t half_elems;
+} glq_ep_peers_t;
 typedef struct glq_moe_ep {
     int32_t rank, world, phase, reserved;
     void* entry_out; /* NULL: use the workspace (world == 1 only) */
@@ -301,6 +316,7 @@ typedef struct glq_moe_ep {
      * rms_norm(out, norm_eps) * norm_weight ((H,) fp16, NULL = ones).  H <= 8192. */
     const void* residual; const void* norm_weight; void* normed_out;
     float norm_eps; int32_t reserved2;
+    const glq_ep_peers_t* peers; /* phases EXCHANGE and COMBINE: the peer-memory exchange; NULL otherwise */
 } glq_moe_ep_t;
 int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n_tokens, void* out, void* router_logits,
                        int32_t* sel_out, void* weight_out, void* workspace, size_t workspace_bytes, int32_t* counters,

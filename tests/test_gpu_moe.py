@@ -201,6 +201,70 @@ def test_expert_parallel_emulated_on_one_gpu(dev, N, world):
     assert tiled.debug_error() is None
 
 
+class _OneDevicePeers:
+    """The pointer tables of the peer-memory exchange for `world` ranks whose buffers all live on one device."""
+
+    def __init__(self, world, entries, H, dev, flag_value):
+        from glorcq_b200 import _lib
+        self._lib, self.entries, self.half = _lib, entries, entries * H
+        self.bufs = [torch.zeros(2 * self.half, dtype=torch.float16, device=dev) for _ in range(world)]
+        self.flags = [torch.full((world,), flag_value, dtype=torch.int32, device=dev) for _ in range(world)]
+        self.tb = torch.tensor([b.data_ptr() for b in self.bufs], dtype=torch.int64, device=dev)
+        self.tf = torch.tensor([f.data_ptr() for f in self.flags], dtype=torch.int64, device=dev)
+
+    def view(self, rank):
+        import types
+        state = torch.zeros(2, dtype=torch.int32, device=self.tb.device)
+        return types.SimpleNamespace(
+            peers=self._lib.EpPeers(self.tb.data_ptr(), self.tf.data_ptr(), state.data_ptr(), state.data_ptr() + 4,
+                                    self.half),
+            local_ptr=self.bufs[rank].data_ptr(), max_entries=self.entries, state=state, keep=self)
+
+
+@pytest.mark.parametrize("N,world", [(1, 2), (5, 2), (8, 4), (16, 3)])
+def test_peer_memory_exchange_emulated_on_one_gpu(dev, N, world):
+    """Phase EXCHANGE with every rank's buffer on one device, the ranks run in turn.  The flag words start
+    above the step number so that no rank waits for one that has not run yet; rank 0 runs once more at the
+    end (again as step 1) and must then see every rank's rows: bit-identical to the single-device block."""
+    blk = cases.make_moe(960 + N, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    x = cases.make_x(1960 + N, N, 256).reshape(1, N, 256).to(dev)
+    single, _ = cases.to_b200_moe(blk, dev)(x)
+    tables = _OneDevicePeers(world, N * 2, 256, dev, 1 << 20)
+    y = None
+    for rank in list(range(world)) + [0]:
+        mb = cases.to_b200_moe(blk, dev).set_expert_parallel(rank, world)
+        mb.peer_exchange_max_tokens = N
+        mb._peers = tables.view(rank)
+        y, _ = mb(x)
+        assert mb._peers.state.tolist() == [1, 0]          # one step taken, no wait ran out
+    assert torch.equal(y, single)
+    # every rank's buffer holds the same rows in the half of step 1
+    for b in tables.bufs[1:]:
+        assert torch.equal(b, tables.bufs[0])
+    assert not tables.bufs[0][:tables.half].any()           # the other half is untouched
+
+
+def test_peer_memory_exchange_wait_runs_out(dev):
+    """A flag that nothing sets: the exchange kernel gives up after its limit (one second), records the step
+    in the error word and returns; the context stays usable."""
+    import time
+    blk = cases.make_moe(970, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    x = cases.make_x(1970, 2, 256).reshape(1, 2, 256).to(dev)
+    tables = _OneDevicePeers(2, 4, 256, dev, 0)             # rank 1 never publishes
+    mb = cases.to_b200_moe(blk, dev).set_expert_parallel(0, 2)
+    mb.peer_exchange_max_tokens = 2
+    mb._peers = tables.view(0)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    y, _ = mb(x)
+    torch.cuda.synchronize()
+    assert 0.9 < time.time() - t0 < 5.0
+    assert mb._peers.state.tolist() == [1, 1]               # step 1 taken; the wait of step 1 ran out
+    assert tables.flags[1].tolist() == [1, 0] and tables.flags[0].tolist() == [1, 0]
+    single, _ = cases.to_b200_moe(blk, dev)(x)              # the device still works
+    assert torch.isfinite(single.float()).all() and torch.isfinite(y.float()).all()
+
+
 def _nccl_worker(rank, world, port, q):
     import os
     import torch.distributed as dist
@@ -218,14 +282,22 @@ def _nccl_worker(rank, world, port, q):
             y, _ = cases.to_b200_moe(blk, d).set_expert_parallel(rank, world)(x)
             torch.cuda.synchronize()
             res.append(bool(torch.equal(y, single)))
+            # the same through this library's exchange kernel over peer memory, several steps in a row
+            mb = cases.to_b200_moe(blk, d).set_expert_parallel(rank, world)
+            mb.peer_exchange_max_tokens = 16
+            for _ in range(3):
+                y, _ = mb(x)
+            torch.cuda.synchronize()
+            res.append(bool(torch.equal(y, single)) and mb._peers.error() == 0)
         q.put((rank, res))
     finally:
         dist.destroy_process_group()
 
 
-def test_expert_parallel_two_gpus_nccl(dev):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_nccl(dev, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import socket
     import torch.multiprocessing as mp
     with socket.socket() as s:
@@ -233,7 +305,7 @@ def test_expert_parallel_two_gpus_nccl(dev):
         port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_nccl_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=170) for _ in procs]
