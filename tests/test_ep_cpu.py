@@ -92,3 +92,44 @@ def test_two_rank_exchange_is_exact():
         assert ok_out, f"rank {rank}: combined output differs from the oracle block"
         rows += nrows
     assert rows == 12   # every entry was produced by exactly one rank
+
+
+def test_peer_exchange_protocol_never_overwrites_rows_being_read():
+    """The protocol of the peer-memory exchange (two buffer halves used by alternate steps, one flag word per
+    rank holding the last published step, no second barrier), run as a model under random interleavings of
+    the ranks: a rank's combine must always read the rows of its own step from every rank, i.e. no rank that
+    is ahead may have overwritten them."""
+    import random
+
+    for world in (2, 3, 4):
+        rng = random.Random(100 + world)
+        for _ in range(60):
+            steps = 6
+            # buf[r][half][src] = step whose rows rank `src` last stored into that half of rank r's buffer
+            buf = [[[0] * world for _ in range(2)] for _ in range(world)]
+            flags = [[0] * world for _ in range(world)]     # flags[r][src]: last step src published to r
+            pc = [("store", 1)] * world                      # per rank: (stage, step)
+            done = 0
+            while done < world:
+                r = rng.randrange(world)
+                stage, step = pc[r]
+                if stage == "end":
+                    continue
+                if stage == "store":
+                    for p in range(world):
+                        buf[p][step & 1][r] = step
+                    pc[r] = ("publish", step)
+                elif stage == "publish":
+                    for p in range(world):
+                        flags[p][r] = step
+                    pc[r] = ("wait", step)
+                elif stage == "wait":
+                    if all(f >= step for f in flags[r]):
+                        pc[r] = ("combine", step)
+                elif stage == "combine":
+                    assert buf[r][step & 1] == [step] * world, (world, r, step, buf[r])
+                    if step == steps:
+                        pc[r] = ("end", step)
+                        done += 1
+                    else:
+                        pc[r] = ("store", step + 1)
