@@ -63,6 +63,25 @@ def test_host_side_argument_checks(libpath):
     assert L.glq_gptq_dequant_matmul(None, None, None, None, None, None, 0, 8, 64, 128, 1, 0, None) == 0
     assert L.glq_pack_gptq(None, None, None, 2, 16, 128, 128, None, 0, 1, None) == -1
     assert L.glq_grouped_matmul(None, None) == -1
+    # expert-parallel phases: the peer-memory exchange needs its pointer tables, the other phases must not get them
+    import ctypes as C
+    d = _lib.MoeDesc()
+    d.top_k, d.H, d.E = 2, 64, 4
+    dummy = C.create_string_buffer(64)
+    ptr = C.cast(dummy, C.c_void_p).value
+
+    def ep_call(ep):
+        return L.glq_moe_forward_ep(C.byref(d), ptr, 1, ptr, None, None, None, None, 0, None, 0, None, None, None, None,
+                                    C.byref(ep))
+    ep = _lib.MoeEp(0, 2, _lib.MOE_PHASE_EXCHANGE, 0, ptr, None, None)
+    assert ep_call(ep) == -1                                   # no peers
+    peers = _lib.EpPeers(ptr, ptr, ptr, ptr, 0)
+    ep.peers = C.pointer(peers)
+    assert ep_call(ep) == -1                                   # buffers too small for the step (half_elems 0)
+    ep.phase = _lib.MOE_PHASE_EXPERTS
+    assert ep_call(ep) == -1                                   # the staging buffer is not exchanged
+    assert ep_call(_lib.MoeEp(2, 2, _lib.MOE_PHASE_EXPERTS, 0, ptr, None, None)) == -1   # rank outside the world
+    assert ep_call(_lib.MoeEp(0, 2, _lib.MOE_PHASE_ALL, 0, ptr, None, None)) == -1      # world > 1 needs phases
 
 
 def test_no_fallback_without_gpu():
