@@ -60,13 +60,14 @@ class EpPeers(C.Structure):
 
 class MoeEp(C.Structure):
     """glq_moe_ep_t"""
-    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phase", C.c_int32), ("reserved", C.c_int32),
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("phase", C.c_int32), ("flags", C.c_int32),
                 ("entry_out", vp), ("sel_in", vp), ("weight_in", vp),
                 ("residual", vp), ("norm_weight", vp), ("normed_out", vp), ("norm_eps", C.c_float), ("reserved2", C.c_int32),
                 ("peers", C.POINTER(EpPeers))]
 
 
 MOE_PHASE_ALL, MOE_PHASE_EXPERTS, MOE_PHASE_COMBINE, MOE_PHASE_EXCHANGE = 0, 1, 2, 3
+MOE_EP_NO_ZERO_FILL = 1
 
 _SIGS = {
     "glq_version": (C.c_int, []),

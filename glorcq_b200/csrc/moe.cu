@@ -675,7 +675,9 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
         after_kernel[0] = true;
     }
     // rows of remote experts' entries stay zero, so that summing the ranks' buffers is exact
-    if (ep_world > 1 && cudaMemsetAsync(p_yd, 0, (size_t)nk * d->H * 2, st) != cudaSuccess) return GLQ_ERR_CUDA;
+    if (ep_world > 1 && !(ep->flags & GLQ_MOE_EP_NO_ZERO_FILL) &&
+        cudaMemsetAsync(p_yd, 0, (size_t)nk * d->H * 2, st) != cudaSuccess)
+        return GLQ_ERR_CUDA;
 
     auto routed = [&](glq_mm_args_t& mm) {
         mm.slot_index = p_active;

@@ -331,9 +331,11 @@ class GraphCompatibleMoeBlock(nn.Module):
                     if ekey not in self._ws:
                         self._ws[ekey] = torch.empty(n * d.top_k, d.H, dtype=torch.float16, device=x.device)
                     entries = self._ws[ekey]
-                    ep = MoeEp(ep_rank, ep_world, _lib.MOE_PHASE_EXPERTS, 0, entries.data_ptr(), None, None)
+                    by_peers = 0 < n <= self.peer_exchange_max_tokens
+                    ep = MoeEp(ep_rank, ep_world, _lib.MOE_PHASE_EXPERTS, _lib.MOE_EP_NO_ZERO_FILL if by_peers else 0,
+                               entries.data_ptr(), None, None)
                     call(ep)
-                    if 0 < n <= self.peer_exchange_max_tokens:
+                    if by_peers:
                         # this library's exchange kernel: peer stores into every rank's buffer, then flags
                         if self._peers is None:
                             self._peers = parallel.PeerExchange.get(

@@ -302,8 +302,11 @@ typedef struct glq_ep_peers {
     int32_t* epoch; int32_t* error;
     size_t half_elems;
 } glq_ep_peers_t;
+/* flags of glq_moe_ep_t: phase EXPERTS leaves the rows of other ranks' entries unwritten instead of zeroing
+ * them (the peer-memory exchange copies only this rank's rows; an all-reduce needs the zeros) */
+#define GLQ_MOE_EP_NO_ZERO_FILL 1
 typedef struct glq_moe_ep {
-    int32_t rank, world, phase, reserved;
+    int32_t rank, world, phase, flags; /* GLQ_MOE_EP_* */
     void* entry_out; /* NULL: use the workspace (world == 1 only) */
     /* Routing decided by the caller instead of the block's router (the fused-experts adapter
      * GLoRCQExperts.forward, inference/quantized_linear.py:395-428): sel_in (n_tokens, top_k) int32 expert
