@@ -55,7 +55,8 @@ class MoeDesc(C.Structure):
 
 class EpPeers(C.Structure):
     """glq_ep_peers_t"""
-    _fields_ = [("entry_bufs", vp), ("flags", vp), ("epoch", vp), ("error", vp), ("half_elems", C.c_size_t)]
+    _fields_ = [("entry_bufs", vp), ("flags", vp), ("epoch", vp), ("error", vp), ("half_elems", C.c_size_t),
+                ("wait_limit_ns", C.c_uint64)]
 
 
 class MoeEp(C.Structure):
@@ -75,6 +76,7 @@ _SIGS = {
     "glq_last_cuda_error": (C.c_int, []),
     "glq_turbo_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
     "glq_static_scratch_bytes": (C.c_size_t, []),
+    "glq_static_scratch_needed": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "glq_turbo_dequant_matmul_static": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
     "glq_turbo_dequant_grouped_gemv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
     "glq_gptq_dequant_matmul": (C.c_int, [vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -26,6 +26,7 @@ static thread_local int g_last_cuda_error = 0;
     } while (0)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline bool aligned_to(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 static inline int pow2ceil(int v) {
     int p = 1;
@@ -80,15 +81,17 @@ struct Geometry {
     size_t smem, n_counters, scratch_bytes;
 };
 
+// SM count of the current device (cached per device: the planned splits follow the GPU the call runs on)
 static int num_sms() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) !=
-                                                      cudaSuccess || sms <= 0)
-            sms = 148;
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        sms[dev] = v;
     }
-    return sms;
+    return sms[dev];
 }
 
 static int plan_geometry(int fmt, int epilogue, int N, int K, int group_size, int n_problems, int max_rows,
@@ -801,11 +804,13 @@ static int turbo_rowmajor(const void* x, const uint8_t* packed, const float* nor
                           int n_problems, int rows, int N, int K, int slot_rows, void* stream) {
     if (!x || !packed || !norms || !centroids || !y) return GLQ_ERR_ARG;
     if (K <= 0 || K % 4 != 0) return GLQ_ERR_UNSUPPORTED;
+    if (!aligned_to(x, 2) || !aligned_to(y, 2) || !aligned_to(norms, 4) || !aligned_to(centroids, 4)) return GLQ_ERR_ALIGN;
     Geometry g;
     int rc = plan_geometry(GLQ_FMT_T2, GLQ_EPI_LINEAR, N, K, 0, n_problems, rows, false, &g);
     if (rc != GLQ_OK) return rc;
     SkinnyParams p{};
     p.w.codes = packed;
+    p.w.reserved = aligned_to(packed, 8) ? 1 : 0;   // 8-byte loads of the codes only from an 8-byte aligned base
     p.w.norms = norms;
     p.w.centroids = centroids;
     p.w.N = N;
@@ -847,6 +852,8 @@ extern "C" int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const vo
     if (B == 0 || N == 0) return GLQ_OK;
     if (!x || !q || !scales || !y || (!sym && !zeros)) return GLQ_ERR_ARG;
     if (groupsize <= 0 || n_groups <= 0 || (long)n_groups * groupsize < K) return GLQ_ERR_ARG;
+    if (!aligned_to(x, 4) || !aligned_to(y, 4) || !aligned_to(lora_out, 4) || !aligned_to(scales, 2) || !aligned_to(zeros, 2))
+        return GLQ_ERR_ALIGN;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)K * sizeof(float);
     for (int b0 = 0; b0 < B; b0 += 4) {
@@ -876,12 +883,20 @@ static __device__ __align__(256) unsigned char g_static_scratch[GLQ_STATIC_COUNT
 
 extern "C" size_t glq_static_scratch_bytes(void) { return GLQ_STATIC_SCRATCH_BYTES; }
 
+extern "C" size_t glq_static_scratch_needed(int B, int N, int K) {
+    Geometry g;
+    if (B <= 0 || N <= 0 || K <= 0 || K % 4 != 0) return 0;
+    if (plan_geometry(GLQ_FMT_T2, GLQ_EPI_LINEAR, N, K, 0, 1, B, true, &g) != GLQ_OK) return 0;
+    return g.scratch_bytes;
+}
+
 extern "C" int glq_turbo_dequant_matmul_static(const void* x_rot, const uint8_t* packed, const float* norms,
                                                const float* centroids, void* y, int B, int N, int K, void* stream) {
     if (B < 0 || N < 0) return GLQ_ERR_ARG;
     if (B == 0 || N == 0) return GLQ_OK;
     if (!x_rot || !packed || !norms || !centroids || !y) return GLQ_ERR_ARG;
     if (K <= 0 || K % 4 != 0) return GLQ_ERR_UNSUPPORTED;
+    if (!aligned_to(x_rot, 2) || !aligned_to(y, 2) || !aligned_to(norms, 4) || !aligned_to(centroids, 4)) return GLQ_ERR_ALIGN;
     // The array's name is only a host-side handle: its device address is looked up once per device,
     // with that device current, and it is that address the kernel gets.
     static unsigned char* dev_ptr[64] = {nullptr};
@@ -904,6 +919,7 @@ extern "C" int glq_turbo_dequant_matmul_static(const void* x_rot, const uint8_t*
     if (g.n_counters > 0) GLQ_CUDA(cudaMemsetAsync(dev_ptr[dev], 0, g.n_counters * sizeof(int), st));
     SkinnyParams p{};
     p.w.codes = packed;
+    p.w.reserved = aligned_to(packed, 8) ? 1 : 0;
     p.w.norms = norms;
     p.w.centroids = centroids;
     p.w.N = N;

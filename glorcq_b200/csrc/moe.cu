@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(1024) moe_exchange_kernel(const __half* __rest
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
             if (seen - step >= 0) break;
             if (global_ns() - t0 > limit_ns) {
-                atomicExch(error, step);
+                atomicCAS(error, 0, step);      // the first wait that ran out stays on record
                 break;
             }
             __nanosleep(100);
@@ -588,7 +588,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if (phase == GLQ_MOE_PHASE_EXCHANGE) {
         moe_exchange_kernel<<<1, 1024, 0, st>>>(reinterpret_cast<const __half*>(p_yd), p_nact, p_cnt, p_off, nk, d->H,
                                                 ep_rank, ep_world, px->entry_bufs, px->flags, px->epoch, px->error,
-                                                px->half_elems, 1000000000ull);
+                                                px->half_elems, px->wait_limit_ns ? px->wait_limit_ns : 1000000000ull);
         return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
     }
     if (phase != GLQ_MOE_PHASE_COMBINE) {

@@ -300,7 +300,7 @@ __device__ __forceinline__ void load_codes(const glq_weight_t& W, int rt, int pa
             const uint8_t* ptr = base + (size_t)row * rowbytes + boff;
             if (!GLQ_OKAY(row >= 0 && kb >= 0 && kb < nkb, 20, (size_t)row * rowbytes + boff, (size_t)W.N * rowbytes)) {
                 r[h] = make_uint2(0, 0);
-            } else if ((rowbytes & 7) == 0 && boff + 8 <= rowbytes) {
+            } else if (W.reserved != 0 && (rowbytes & 7) == 0 && boff + 8 <= rowbytes) {   // reserved: base is 8-byte aligned
                 r[h] = __ldg(reinterpret_cast<const uint2*>(ptr));
             } else {
                 uint32_t lo = 0, hi = 0;

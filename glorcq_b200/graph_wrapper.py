@@ -17,6 +17,7 @@ import torch
 
 from .decoder import StaticKVCache as StaticCache
 from .moe_block import GraphCompatibleMoeBlock
+from .parallel import PeerExchange
 
 
 class GLoRCQGraphWrapper:
@@ -120,6 +121,7 @@ class GLoRCQGraphWrapper:
             output_ids = torch.cat([output_ids, next_token], dim=1)
         torch.cuda.synchronize()
         end = time.time()
+        PeerExchange.check_all()      # expert parallel: a wait for another rank that ran out invalidates the tokens
         self.last_prefill_seconds, self.last_decode_seconds = prefill_end - start, end - prefill_end
         return output_ids, end - start
 

@@ -49,6 +49,8 @@ class PeerExchange:
 
     _cache: dict = {}
 
+    wait_limit_seconds = 1.0      # longest wait of the exchange kernel for the other ranks' flags
+
     def __init__(self, group, device: torch.device, max_entries: int, H: int):
         import os
 
@@ -75,7 +77,8 @@ class PeerExchange:
         self._flags = torch.tensor([p + 4 * self.half_elems for p in ptrs], dtype=torch.int64, device=device)
         self._state = torch.zeros(2, dtype=torch.int32, device=device)      # step counter, error word
         self.peers = _lib.EpPeers(self._bufs.data_ptr(), self._flags.data_ptr(), self._state.data_ptr(),
-                                  self._state.data_ptr() + 4, self.half_elems)
+                                  self._state.data_ptr() + 4, self.half_elems,
+                                  int(float(os.environ.get("GLQ_EP_WAIT_SECONDS", self.wait_limit_seconds)) * 1e9))
         self.local_ptr = ptrs[self.rank]
 
     @classmethod
@@ -90,3 +93,17 @@ class PeerExchange:
     def error(self) -> int:
         """Step number of the first wait that ran out (0: none).  Synchronises."""
         return int(self._state[1].item())
+
+    def raise_on_error(self):
+        """To be called at the host's own synchronisation points (end of a generation, after a timed
+        region): a wait that ran out means a rank did not publish its rows in time, and every result from
+        that step on is incomplete."""
+        step = self.error()
+        if step:
+            raise RuntimeError(f"expert-parallel exchange: the wait for the other ranks ran out at step {step} "
+                               f"(limit {self.peers.wait_limit_ns / 1e9:g} s); results from that step on are incomplete")
+
+    @classmethod
+    def check_all(cls):
+        for px in list(cls._cache.values()):
+            px.raise_on_error()

@@ -101,6 +101,9 @@ int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const void* scales,
  *     cleared on the stream before each launch, but two calls that overlap on the GPU (different
  *     streams, or different host threads) race on it: serialise them. */
 size_t glq_static_scratch_bytes(void);
+/* bytes of the fixed array a call with these sizes would use: 0 when the planned launch does not split k
+ * (it then never touches the array), more than glq_static_scratch_bytes() when the call would be refused */
+size_t glq_static_scratch_needed(int B, int N, int K);
 int glq_turbo_dequant_matmul_static(const void* x_rot, const uint8_t* packed, const float* norms,
                                     const float* centroids, void* y, int B, int N, int K, void* stream);
 
@@ -301,6 +304,9 @@ typedef struct glq_ep_peers {
     void* const* entry_bufs; int32_t* const* flags;
     int32_t* epoch; int32_t* error;
     size_t half_elems;
+    uint64_t wait_limit_ns; /* longest wait for the other ranks' flags, in nanoseconds of the GPU's global timer; 0: one
+                               second.  *error keeps the step number of the FIRST wait that ran out (0: none); the
+                               host reads it at its own synchronisation points and must not use results of later steps */
 } glq_ep_peers_t;
 /* flags of glq_moe_ep_t: phase EXPERTS leaves the rows of other ranks' entries unwritten instead of zeroing
  * them (the peer-memory exchange copies only this rank's rows; an all-reduce needs the zeros) */

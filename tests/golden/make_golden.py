@@ -142,6 +142,8 @@ MOE_CASES = [
                                 norm_topk_prob=True), 20),
     ("moe_turbo_7", dict(seed=35, H=256, I=128, E=6, top_k=2, I_shared=256, rank=16, experts_per_cluster=2,
                          fmt="turbo"), 7),
+    # the Qwen1.5-MoE block at its own dimensions, 8 tokens
+    ("moe_qwen15_shape_8", dict(seed=36, H=2048, I=1408, E=60, top_k=4, I_shared=5632, rank=64, experts_per_cluster=4), 8),
 ]
 
 

@@ -127,6 +127,46 @@ def test_decoder_logits_prefill_and_decode(dev, cfg, cache_len):
     assert cases.rel_l2(step.cpu(), ref[:, T:]) <= REL_LOGITS
 
 
+QWEN15_SHAPE = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=16,
+                    vocab_size=151936, num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408,
+                    shared_expert_intermediate_size=5632, norm_topk_prob=False, rms_norm_eps=1e-6,
+                    rope_theta=1000000.0, max_position_embeddings=64)
+
+
+@pytest.mark.timeout(1200)
+def test_decoder_logits_at_qwen15_moe_dimensions(dev):
+    """Two layers of the Qwen1.5-MoE-A2.7B shape at its own dimensions (hidden 2048, 16 heads of 128, 60
+    experts top-4 x 1408 + shared expert 5632, vocabulary 151936; attention 4-bit, experts 2-bit, rank 64, 128
+    cross-layer U clusters): logits of a 6-token prefill and of one decode step against the oracle's causal
+    forward, rel-L2 <= 5e-3, and the same greedy token."""
+    from glorcq_b200 import model_builder as MB
+    from glorcq_b200 import synthetic
+    from glorcq_b200.decoder import GLoRCQDecoder, StaticKVCache
+    cfg = QWEN15_SHAPE
+    md, cr, dense = synthetic.make_checkpoint(cfg, seed=51, rank=64, attn_rank=64, n_clusters=128, u_format="fp16",
+                                              sv_format="fp16")
+    layers, _ = MB.build_layers(md["model_config"], md["layers"], cr, device=dev)
+    model = GLoRCQDecoder(cfg, layers, dense=dense, device=dev)
+    T = 6
+    ids = torch.randint(0, cfg["vocab_size"], (1, T + 1), generator=torch.Generator().manual_seed(13))
+    cache = StaticKVCache(model.config, 1, 32, dev)
+    with torch.no_grad():
+        lg = model(input_ids=ids[:, :T].to(dev), cache_position=torch.arange(T, device=dev), past_key_values=cache)[0].cpu()
+        step = model(input_ids=ids[:, T:].to(dev), cache_position=torch.tensor([T], device=dev), past_key_values=cache)[0].cpu()
+    del model, layers
+    torch.cuda.empty_cache()
+    ref = O.decoder_forward(cfg, O.checkpoint_layers(md, cr), dense, ids)
+    assert step.shape == (1, 1, cfg["vocab_size"])
+    assert cases.rel_l2(lg, ref[:, :T]) <= REL_LOGITS
+    assert cases.rel_l2(step, ref[:, T:]) <= REL_LOGITS
+    # greedy token: identical whenever the oracle's two best logits are further apart than the logits differ
+    top2 = ref[0, T].float().topk(2).values
+    if float(top2[0] - top2[1]) > 2 * float((step[0, 0].float() - ref[0, T].float()).abs().max()):
+        assert int(step[0, 0].argmax()) == int(ref[0, T].argmax())
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
 def test_graph_wrapper_generate_matches_eager(dev, tmp_path):
     from glorcq_b200 import synthetic
     from glorcq_b200.graph_wrapper import GLoRCQGraphWrapper, run_speed_benchmark

@@ -78,6 +78,48 @@ def test_linear_forward(dev, N, K, rank, fmt, bits, gs, sym, B):
         assert cases.rel_l2(y2, ref) <= REL
 
 
+def _hostile_rows(B, K, seed):
+    """Activation rows that attack the block fixed-point staging of the integer decode path (each 128-channel
+    block of a row is scaled by a power of two taken from its largest magnitude): one element 2^10 times the
+    rest of its block, a block of fp16 subnormals, a block of zeros, elements at +-60000 beside ordinary
+    values, a row of tiny values, and blocks whose sign pattern makes the plain sum cancel."""
+    x = cases.make_x(seed, B, K).float()
+    nb = K // 128
+    for b in range(B):
+        x[b, (b % nb) * 128 + 5] *= 1024.0                               # outlier 2^10 x its block
+        blk = (b + 1) % nb
+        x[b, blk * 128:(blk + 1) * 128] = x[b, blk * 128:(blk + 1) * 128] * 3e-7    # fp16 subnormals
+        blk = (b + 2) % nb
+        x[b, blk * 128:(blk + 1) * 128] = 0.0
+        blk = (b + 3) % nb
+        x[b, blk * 128 + 17] = 60000.0
+        x[b, blk * 128 + 90] = -60000.0
+        blk = (b + 4) % nb
+        half = x[b, blk * 128:blk * 128 + 64].clone()
+        x[b, blk * 128 + 64:(blk + 1) * 128] = -half                       # sum of the block cancels exactly
+    if B > 1:
+        x[B - 1] *= 1e-3
+    return x.to(torch.float16)
+
+
+@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("N,K,bits", [(1408, 2048, 2), (2048, 1408, 2), (2048, 2048, 4)])
+def test_integer_path_hostile_activations(dev, N, K, bits, B):
+    """Up to 8 rows of affine codes run on the integer path, which rounds every 128-channel block of x to
+    16-bit fixed point relative to the block maximum (exact within 2^-13 of it, absolute error <= 2^-16 of it
+    below); the reference multiplies the exact fp16 values.  Outliers, subnormals and near-overflow values
+    must still land within the layer bar, rel-L2 <= 1e-3, per row as well as over all rows."""
+    d = cases.make_linear(77 * B + N + bits, N, K, rank=64, bits=bits)
+    lin = cases.to_b200_linear(d, dev)
+    x = _hostile_rows(B, K, 4000 + B + N)
+    y = lin(x.to(dev)).cpu()
+    ref = O.linear_forward(cases.to_oracle_linear(d), x)
+    assert torch.isfinite(ref.float()).all() and torch.isfinite(y.float()).all()
+    assert cases.rel_l2(y, ref) <= REL
+    for b in range(B):
+        assert cases.rel_l2(y[b], ref[b]) <= REL, f"row {b}"
+
+
 @pytest.mark.parametrize("N,K,rank,B,int_zeros", [(1408, 2048, 64, 128, True), (2048, 1408, 64, 300, True),
                                                    (100, 392, 16, 200, True), (256, 256, 16, 64, False),
                                                    (24, 128, 0, 40, True), (5632, 2048, 64, 96, True)])

@@ -22,19 +22,30 @@ def _rel_l2(a, b):
     return float((a - b).norm() / (b.norm() + 1e-30))
 
 
-@pytest.mark.parametrize("B,N,K", [(1, 1408, 2048), (4, 2048, 1408), (1, 96, 256)])
-def test_static_scratch_variant_matches(B, N, K):
+def _operands(B, N, K, dev, seed):
+    g = torch.Generator().manual_seed(seed)
+    packed = torch.randint(0, 256, (N, K // 4), generator=g, dtype=torch.int32).to(torch.uint8)
+    norms = torch.randn(N, generator=g).abs() + 0.1
+    centroids = torch.randn(4, generator=g)
+    x = torch.randn(B, K, generator=g).half()
+    return [t.to(dev) for t in (x, packed, norms, centroids)], (x, packed, norms, centroids)
+
+
+@pytest.mark.parametrize("B,N,K,splits", [(1, 1408, 2048, True), (4, 2048, 1408, True), (1, 96, 256, False)])
+def test_static_scratch_variant_matches(B, N, K, splits):
+    """Against the existing entry point AND against the CPU oracle of the reference's kernel, twice in a
+    row.  The first two shapes plan a k split over CTAs, the only case that touches the fixed array; the
+    third plans none and must work without it."""
     assert torch.cuda.is_available()
     from glorcq_b200 import _build, _lib
+    from oracle import glorcq_oracle as O
     _build.build()
     L = _lib.lib()
     dev = torch.device("cuda:0")
-    g = torch.Generator().manual_seed(B * 7 + N + K)
-    packed = torch.randint(0, 256, (N, K // 4), generator=g, dtype=torch.int32).to(torch.uint8).to(dev)
-    norms = (torch.randn(N, generator=g).abs() + 0.1).to(dev)
-    centroids = torch.randn(4, generator=g).to(dev)
-    x = torch.randn(B, K, generator=g).half().to(dev)
+    (x, packed, norms, centroids), host = _operands(B, N, K, dev, B * 7 + N + K)
     st = torch.cuda.current_stream().cuda_stream
+    needed = L.glq_static_scratch_needed(B, N, K)
+    assert (needed > 0) == splits and needed <= L.glq_static_scratch_bytes()
 
     ref = torch.empty(B, N, dtype=torch.float16, device=dev)
     _lib.check(L.glq_turbo_dequant_matmul(x.data_ptr(), packed.data_ptr(), norms.data_ptr(), centroids.data_ptr(),
@@ -47,10 +58,43 @@ def test_static_scratch_variant_matches(B, N, K):
                    "turbo_dequant_matmul_static")
         torch.cuda.synchronize()
         outs.append(y)
+    oracle = O.turbo_matmul(*host)
     for y in outs:
         assert torch.isfinite(y.float()).all()
         assert _rel_l2(y, ref) <= REL
+        assert _rel_l2(y.cpu(), oracle) <= REL
     assert torch.equal(outs[0], outs[1])     # deterministic, and unaffected by the leftovers of the first call
+
+
+def test_static_scratch_reused_in_stream_order():
+    """Different shapes enqueued back to back on one non-default stream, with no synchronisation in
+    between: stream order alone must make the shared array safe to reuse (each call clears its counters on
+    the stream before its launch)."""
+    from glorcq_b200 import _build, _lib
+    _build.build()
+    L = _lib.lib()
+    dev = torch.device("cuda:0")
+    shapes = [(4, 2048, 1408), (1, 1408, 2048), (4, 2048, 1408), (2, 5632, 2048), (1, 96, 256)]
+    ops = [_operands(B, N, K, dev, 100 + i)[0] for i, (B, N, K) in enumerate(shapes)]
+    refs, outs = [], []
+    main = torch.cuda.current_stream().cuda_stream
+    for (B, N, K), (x, packed, norms, centroids) in zip(shapes, ops):
+        r = torch.empty(B, N, dtype=torch.float16, device=dev)
+        _lib.check(L.glq_turbo_dequant_matmul(x.data_ptr(), packed.data_ptr(), norms.data_ptr(), centroids.data_ptr(),
+                                              r.data_ptr(), B, N, K, main), "turbo_dequant_matmul")
+        refs.append(r)
+        outs.append(torch.full((B, N), float("nan"), dtype=torch.float16, device=dev))
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            for (B, N, K), (x, packed, norms, centroids), y in zip(shapes, ops, outs):
+                _lib.check(L.glq_turbo_dequant_matmul_static(x.data_ptr(), packed.data_ptr(), norms.data_ptr(),
+                                                             centroids.data_ptr(), y.data_ptr(), B, N, K,
+                                                             side.cuda_stream), "turbo_dequant_matmul_static")
+    side.synchronize()
+    for y, r in zip(outs, refs):
+        assert _rel_l2(y, r) <= REL
 
 
 def test_static_scratch_limit_is_enforced():
