@@ -1,30 +1,37 @@
 """Benchmark of the GLoRCQ real-quant decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config qwen15|mixtral|qwen3]
 
-Workload (one GPU): batch-1 decode through the MoE blocks of the Qwen1.5-MoE-A2.7B-shaped model --
-24 layers of {router, 60 experts top-4 (intermediate 1408), shared expert (5632)}, every projection
-2-bit g128 with a rank-64 low-rank correction whose input-side factor U is shared by clustered
-experts across layers -- on seeded synthetic weights.  One step = one token through all layers, the
-output of a block feeding the next, replayed from one CUDA graph.  The weights of the 24 layers
-(5.7 GB) are far larger than L2, and every token touches ~0.67 GB of them.
+Workload (default, one GPU): greedy batch-1 decode of the whole Qwen1.5-MoE-A2.7B-shaped decoder after a
+512-token prompt -- 24 layers of {4-bit g128 attention projections with a rank-64 correction, attention over
+a static key/value cache, router, 60 experts top-4 (intermediate 1408) + shared expert (5632), every expert
+projection 2-bit g128 with a rank-64 low-rank correction whose input-side factor U is shared by 128 clusters
+of experts across layers}, final norm and the fp16 output projection over a vocabulary of 151936 with the
+arg-max -- on seeded synthetic weights.  One step = one decoded token: GLoRCQGraphWrapper.replay (token id and
+position into the static buffers, one CUDA-graph replay), the next token taken on the device.  The weights
+(6.6 GB) are far larger than L2 and a token touches ~1.5 GB of them.
 
 One JSON line on stdout:
-  value     tokens/s with the hidden state resident in HBM (device-timed with CUDA events)
-  e2e       the same through the public API with pinned host buffers: h2d of the hidden state, graph
-            replay, d2h of the block output, every step
+  value     decoded tokens/s, device-timed with CUDA events: the median of R >= 25 windows of exactly K steps,
+            each window bracketed by a barrier + synchronize and starting at the position after the prompt
+  e2e       the same through the public API with the token id coming from pinned host memory and the next
+            token id read back to the host, every step
   roofline  the dominant kernel (the grouped dequant-GEMV) timed alone, live, on 240 distinct
             expert-projection problems (1408 x 2048, 2-bit g128, rank 64; 240 MB, larger than L2):
             algorithmic bytes / CUDA-event time against the measured HBM peak
-  cpu_baseline  the CPU restatement of the reference's own path (oracle/), timed on the host cores on
-            a bounded sample (one layer, one token, repeated)
-`--impl reference` times that CPU path as the main line (rank 0 only).
+  moe_only  the 24 MoE blocks alone (no attention, no output projection), chained through their fused
+            residual + norm, one CUDA graph per token
+  cpu_baseline  the CPU restatement of the reference's own path (oracle/), timed on the host cores on a
+            bounded sample (one layer's pieces and the output projection for one token, repeated)
+`--impl reference` times that CPU path as the main line (rank 0 only).  N > 1: the routed experts are sharded
+over the ranks (expert e on rank e % N), everything else is replicated, one token stream per rank.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -36,19 +43,52 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-CFG = dict(H=2048, I=1408, E=60, top_k=4, I_shared=5632, rank=64, experts_per_cluster=4)
 METRIC = "moe_decode_tok_s"
 UNIT = "tok/s"
 
 
-def measured_peak_gbs():
+def model_config(name):
+    from glorcq_b200 import synthetic
+    if name == "qwen15":
+        return dict(synthetic.QWEN15_MOE_A27B), "Qwen1.5-MoE-A2.7B", 512
+    if name == "mixtral":
+        return dict(synthetic.MIXTRAL_8X7B), "Mixtral-8x7B", 1024
+    if name == "qwen3":
+        return dict(synthetic.QWEN3_30B_A3B), "Qwen3-30B-A3B", 512
+    raise ValueError(name)
+
+
+def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured"
+            return json.load(open(path))
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return None
+
+
+def measured_peak_gbs():
+    p = _peaks()
+    return (float(p["hbm_gbs"]), "measured") if p and "hbm_gbs" in p else (6650.0, "fallback")
+
+
+def measured_peak_tflops():
+    p = _peaks()
+    return (float(p["bf16_tflops"]), "measured") if p and "bf16_tflops" in p else (1590.0, "fallback")
+
+
+def profiled_traffic(name):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu summary committed under profiles/
+    (a line `traffic_bytes_per_launch: <number>` in profiles/<name>); None when there is none."""
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        for ln in open(path):
+            if ln.strip().startswith("traffic_bytes_per_launch:"):
+                return float(ln.split(":", 1)[1].split()[0])
+    except OSError:
+        pass
+    return None
 
 
 # ---- clocks ---------------------------------------------------------------------------------------
@@ -63,7 +103,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -98,68 +138,115 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-# ---- CPU baseline (reference arm) -----------------------------------------------------------------
-def cpu_layer_seconds(sample_seconds=12.0, max_reps=200):
-    """One layer, one token, through the CPU oracle (the reference's PyTorch path restated); returns
-    (median seconds per layer-forward, threads, reps)."""
-    from oracle import glorcq_oracle as O
-    from tests import cases
-    torch.set_num_threads(os.cpu_count() or 1)
-    blk = cases.make_moe(2001, CFG["H"], CFG["I"], CFG["E"], CFG["top_k"], I_shared=CFG["I_shared"], rank=CFG["rank"],
-                         experts_per_cluster=CFG["experts_per_cluster"])
-    ob = cases.to_oracle_moe(blk)
-    x = cases.make_x(3001, 1, CFG["H"]).reshape(1, 1, CFG["H"])
-    with torch.no_grad():
-        for _ in range(2):
-            O.moe_forward(ob, x)
-        ts, t_start = [], time.perf_counter()
-        while len(ts) < max_reps and (time.perf_counter() - t_start < sample_seconds or len(ts) < 3):
-            t0 = time.perf_counter()
-            O.moe_forward(ob, x)
-            ts.append(time.perf_counter() - t0)
-    ts.sort()
-    return ts[len(ts) // 2], torch.get_num_threads(), len(ts)
+# ---- CPU baseline (reference arm): the oracle's pieces of one decode token --------------------------
+class CpuToken:
+    """One decode token of the decoder through the CPU oracle (the reference's PyTorch path restated), as a
+    bounded sample: ONE layer's pieces -- q/k/v/o projections (4-bit + rank-64 correction), attention of the new
+    token over `context` cached positions, the MoE block -- and the output projection, each for one token.
+    seconds per token = layers x layer + output projection."""
+
+    def __init__(self, cfg, context):
+        from oracle import glorcq_oracle as O
+        from tests import cases
+        self.O, self.cfg = O, cfg
+        torch.set_num_threads(os.cpu_count() or 1)
+        H = cfg["hidden_size"]
+        nh = cfg["num_attention_heads"]
+        nkv = cfg.get("num_key_value_heads") or nh
+        hd = cfg.get("head_dim") or H // nh
+        E = cfg.get("num_experts", cfg.get("num_local_experts", 0))
+        I = cfg.get("moe_intermediate_size", cfg.get("intermediate_size"))
+        self.nh, self.nkv, self.hd = nh, nkv, hd
+        blk = cases.make_moe(2001, H, I, E, cfg["num_experts_per_tok"], I_shared=cfg.get("shared_expert_intermediate_size", 0),
+                             rank=64, experts_per_cluster=4, norm_topk_prob=cfg.get("norm_topk_prob", "num_local_experts" in cfg))
+        self.moe = cases.to_oracle_moe(blk)
+        self.attn = [cases.to_oracle_linear(cases.make_linear(2100 + i, n, k, rank=64, bits=4))
+                     for i, (n, k) in enumerate([(nh * hd, H), (nkv * hd, H), (nkv * hd, H), (H, nh * hd)])]
+        g = torch.Generator().manual_seed(2200)
+        self.k_cache = torch.randn(1, nkv, context, hd, generator=g).half()
+        self.v_cache = torch.randn(1, nkv, context, hd, generator=g).half()
+        self.lm_head = (torch.randn(cfg["vocab_size"], H, generator=g) * 0.02).half()
+        self.x = cases.make_x(3001, 1, H).reshape(1, 1, H)
+
+    @torch.no_grad()
+    def layer(self):
+        O, x = self.O, self.x
+        q = O.linear_forward(self.attn[0], x).view(1, 1, self.nh, self.hd).transpose(1, 2)
+        k = O.linear_forward(self.attn[1], x).view(1, 1, self.nkv, self.hd).transpose(1, 2)
+        v = O.linear_forward(self.attn[2], x).view(1, 1, self.nkv, self.hd).transpose(1, 2)
+        kk = torch.cat([self.k_cache, k], 2).repeat_interleave(self.nh // self.nkv, dim=1)
+        vv = torch.cat([self.v_cache, v], 2).repeat_interleave(self.nh // self.nkv, dim=1)
+        s = (q.float() @ kk.float().transpose(-1, -2)) / self.hd ** 0.5
+        a = (torch.softmax(s, -1).half() @ vv).transpose(1, 2).reshape(1, 1, -1)
+        y = x + O.linear_forward(self.attn[3], a)
+        out, _ = O.moe_forward(self.moe, y)
+        return out
+
+    @torch.no_grad()
+    def head(self):
+        return self.x.reshape(1, -1) @ self.lm_head.T
+
+    def seconds(self, sample_seconds, max_reps):
+        def med(fn):
+            fn()
+            ts, t_start = [], time.perf_counter()
+            while len(ts) < max_reps and (time.perf_counter() - t_start < sample_seconds or len(ts) < 3):
+                t0 = time.perf_counter()
+                fn()
+                ts.append(time.perf_counter() - t0)
+            ts.sort()
+            return ts[len(ts) // 2], len(ts)
+        tl, nl = med(self.layer)
+        th, _ = med(self.head)
+        return self.cfg["num_hidden_layers"] * tl + th, torch.get_num_threads(), nl
+
+
+def workload_config(cfg, name, prompt, batch, layers):
+    E = cfg.get("num_experts", cfg.get("num_local_experts", 0))
+    return {"workload": f"{name}-shaped decoder, greedy decode after a {prompt}-token prompt, batch {batch} per token stream set: "
+                        f"{layers} layers (hidden {cfg['hidden_size']}, {cfg['num_attention_heads']} heads, attention projections "
+                        f"4-bit g128 + rank 64, {E} experts top-{cfg['num_experts_per_tok']} x "
+                        f"{cfg.get('moe_intermediate_size', cfg.get('intermediate_size'))}"
+                        + (f" + shared expert {cfg['shared_expert_intermediate_size']}" if cfg.get("shared_expert_intermediate_size") else "")
+                        + f", experts 2-bit g128 + rank-64 correction with 128 cross-layer shared-U clusters), fp16 output projection "
+                        f"over {cfg['vocab_size']} tokens with arg-max; CUDA-graph replay per token",
+            "layers": layers, "prompt": prompt,
+            "l2": "per-token weight reads (~1.5 GB, different experts every token) far exceed the 126 MB L2"}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    layers = args.layers
+    cfg, name, prompt = model_config(args.config)
+    prompt = args.prompt or prompt
+    cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
+    cpu = CpuToken(cfg, prompt)
+    cpu.seconds(2.0, 3)                               # warm-up sample
     per = []
-    sec, threads, reps = cpu_layer_seconds(sample_seconds=3.0, max_reps=5)      # warm-up sample
     for _ in range(max(1, args.steps)):
-        sec, threads, reps = cpu_layer_seconds(sample_seconds=8.0 / max(1, args.steps) + 1.0, max_reps=50)
+        sec, threads, _ = cpu.seconds(6.0 / max(1, args.steps) + 0.5, 20)
         per.append(sec)
     per.sort()
     sec = per[len(per) // 2]
-    value = 1.0 / (sec * layers)
-    sample = f"1 of {layers} layers, 1 token, median of repeated CPU forwards; tok/s = 1 / ({layers} x layer time)"
+    value = 1.0 / sec
+    sample = (f"one token: 1 of {cfg['num_hidden_layers']} layers (4 attention projections, attention over {prompt} cached "
+              f"positions, MoE block) and the output projection, median of repeated CPU forwards; "
+              f"tok/s = 1 / ({cfg['num_hidden_layers']} x layer + output projection)")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * layers * 1e3, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(layers),
+            "config": workload_config(cfg, name, prompt, args.batch, cfg["num_hidden_layers"]),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def workload_config(layers):
-    return {"workload": f"Qwen1.5-MoE-A2.7B-shaped MoE decode, one token stream per GPU: {layers} MoE blocks (hidden 2048, 60 experts "
-                        "top-4 x 1408, shared expert 5632), 2-bit g128 + rank-64 shared-U correction; attention "
-                        "and lm_head not included", "layers": layers, "batch": 1,
-            "l2": "weights (240 MB per layer) far exceed L2; each token reads other experts' weights of 24 distinct layers"}
-
-
 # ---- GPU arm ----------------------------------------------------------------------------------------
-def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
-    """The grouped dequant-GEMV alone: P distinct 1408x2048 2-bit g128 rank-64 problems, one row each."""
-    import ctypes as C
-    from glorcq_b200 import _lib
+def _c1_problems(dev, P, seed):
     from glorcq_b200.tiled import TiledWeight
     N, K, r = 1408, 2048, 64
-    L = _lib.lib()
     g = torch.Generator(device=dev)
-    g.manual_seed(7)
+    g.manual_seed(seed)
     keep, descs = [], []
     for _ in range(P):
         tw = TiledWeight.from_gptq(torch.randint(0, 4, (N, K), generator=g, device=dev, dtype=torch.int32),
@@ -169,6 +256,16 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
         keep.append(tw)
         descs.append(tw.desc_bytes())
     table = torch.frombuffer(bytearray(b"".join(descs)), dtype=torch.uint8).to(dev)
+    return keep, table, g
+
+
+def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
+    """The grouped dequant-GEMV alone: P distinct 1408x2048 2-bit g128 rank-64 problems, one row each."""
+    import ctypes as C
+    from glorcq_b200 import _lib
+    N, K, r = 1408, 2048, 64
+    L = _lib.lib()
+    keep, table, g = _c1_problems(dev, P, 7)
     x = torch.randn(P, K, generator=g, device=dev).half()
     a = (torch.randn(P, r, generator=g, device=dev) * 0.1).half()
     y = torch.empty(P, N, dtype=torch.float16, device=dev)
@@ -191,28 +288,12 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
     # per problem: codes + (scale, zero) pairs + SV + x + a + y  (U is read by the separate x.U kernel)
     per = N * K // 4 + N * (K // 128) * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
     achieved = P * per / sec / 1e9
-    # DRAM bytes of one launch of this case from the ncu capture summarised under profiles/
-    # (dram__bytes_read.sum + dram__bytes_write.sum = 239.47 MB + 4.13 MB at P = 240); scaled by P otherwise
-    traffic = 243.60e6 * P / 240.0
+    t240 = profiled_traffic("gemv_stream_kernel_q2_240x1408x2048.md")       # ncu capture of the P = 240 case
     return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
-            "traffic": traffic, "kernel": "stream_kernel<Q2,int8 path> (grouped dequant-GEMV)",
+            "traffic": None if t240 is None else t240 * P / 240.0,
+            "kernel": "stream_kernel<Q2,int8 path> (grouped dequant-GEMV)",
             "launch_us": sec * 1e6, "bytes_per_launch": P * per, "peak_kind": peak_kind,
             "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), 1 row each; {P * per / 1e6:.0f} MB > L2"}
-
-
-def _stage(rank, what):
-    if os.environ.get("GLQ_BENCH_VERBOSE"):
-        print(f"[bench rank {rank}] {what}", file=sys.stderr, flush=True)
-
-
-def measured_peak_tflops():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        try:
-            return float(json.load(open(path))["bf16_tflops"]), "measured"
-        except Exception:
-            pass
-    return 1590.0, "fallback"
 
 
 def gemm_roofline(dev, P=8, rows=2048, iters=20):
@@ -220,20 +301,9 @@ def gemm_roofline(dev, P=8, rows=2048, iters=20):
     `rows` activation rows each (a prefill-sized grouped launch), x.U given."""
     import ctypes as C
     from glorcq_b200 import _lib
-    from glorcq_b200.tiled import TiledWeight
     N, K, r = 1408, 2048, 64
     L = _lib.lib()
-    g = torch.Generator(device=dev)
-    g.manual_seed(11)
-    keep, descs = [], []
-    for _ in range(P):
-        tw = TiledWeight.from_gptq(torch.randint(0, 4, (N, K), generator=g, device=dev, dtype=torch.int32),
-                                   (torch.randn(N, K // 128, generator=g, device=dev) * 0.02).abs().half(),
-                                   torch.randint(0, 4, (N, K // 128), generator=g, device=dev).half(), 2, 128)
-        tw.put_sv(0, (torch.randn(N, r, generator=g, device=dev) * 0.01).half())
-        keep.append(tw)
-        descs.append(tw.desc_bytes())
-    table = torch.frombuffer(bytearray(b"".join(descs)), dtype=torch.uint8).to(dev)
+    keep, table, g = _c1_problems(dev, P, 11)
     x = torch.randn(P * rows, K, generator=g, device=dev).half()
     a = (torch.randn(P * rows, r, generator=g, device=dev) * 0.1).half()
     y = torch.empty(P * rows, N, dtype=torch.float16, device=dev)
@@ -259,89 +329,284 @@ def gemm_roofline(dev, P=8, rows=2048, iters=20):
     peak, kind = measured_peak_tflops()
     ach = flops / sec / 1e12
     return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-            "kernel": "tc_pack_b_kernel + tc_ts_kernel<Q2> (grouped dequant-GEMM, tcgen05, weights unpacked into TMEM)", "launch_us": sec * 1e6,
+            "kernel": "grouped dequant-GEMM on tcgen05 (weights unpacked into tensor memory)", "launch_us": sec * 1e6,
             "flops_per_launch": flops, "peak_kind": kind,
             "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), {rows} rows each"}
 
 
-def run_full_model(args):
-    """BASELINE config 3: the whole Qwen1.5-MoE-A2.7B-shaped decoder (attention 4-bit g128, experts 2-bit
-    rank 64 with 128 random cross-layer U clusters, fp16 lm_head), 512-token prefill then 256 greedy decode
-    steps replayed from one CUDA graph.  Printed as its own JSON line (not the driver's metric line)."""
-    from glorcq_b200 import _build, synthetic
-    from glorcq_b200.graph_wrapper import GLoRCQGraphWrapper
-    _build.build()
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
-    cfg = dict(synthetic.QWEN15_MOE_A27B)
-    cfg["num_hidden_layers"] = args.layers
-    model = synthetic.make_decoder(cfg, dev, seed=77)
-    w = GLoRCQGraphWrapper(model, max_batch_size=1, max_seq_len=1024)
-    ids = torch.randint(0, cfg["vocab_size"], (1, args.prompt), generator=torch.Generator().manual_seed(5)).to(dev)
-    w.capture_graph()
-    w.generate(ids, max_new_tokens=8)                   # warm-up of prefill and replay
-    out, seconds = w.generate(ids, max_new_tokens=args.new_tokens)
-    line = {"full_model": {"workload": f"Qwen1.5-MoE-A2.7B-shaped decoder, {args.layers} layers, prompt {args.prompt}, "
-                                       f"{args.new_tokens} greedy tokens, CUDA graph decode",
-                           "decode_tok_s": (args.new_tokens - 1) / w.last_decode_seconds,
-                           "prefill_tok_s": args.prompt / w.last_prefill_seconds,
-                           "prefill_s": w.last_prefill_seconds, "decode_s": w.last_decode_seconds, "total_s": seconds,
-                           "generated": int(out.shape[1] - ids.shape[1])}}
-    print(json.dumps(line), flush=True)
+def lm_head_roofline(dev, peak_gbs, V=151936, H=2048, iters=30):
+    """The output projection alone (fp16 V x H, one row, arg-max folded in)."""
+    from glorcq_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    W = (torch.randn(V, H, generator=g, device=dev) * 0.02).half()
+    x = torch.randn(1, H, generator=g, device=dev).half()
+    logits = torch.empty(1, V, dtype=torch.float16, device=dev)
+    best = torch.empty(1, dtype=torch.int64, device=dev)
+    ws = torch.empty(L.glq_lm_head_workspace_bytes(), dtype=torch.uint8, device=dev)
+    ctr = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        _lib.check(L.glq_lm_head(x.data_ptr(), H, W.data_ptr(), 1, V, H, logits.data_ptr(), V, best.data_ptr(),
+                                 ws.data_ptr(), ws.numel(), ctr.data_ptr(), st))
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / iters * 1e-3
+    nbytes = V * H * 2 + H * 2 + V * 2
+    return {"bound": "hbm", "achieved": nbytes / sec / 1e9, "peak": peak_gbs, "unit": "GB/s",
+            "frac": nbytes / sec / 1e9 / peak_gbs, "launch_us": sec * 1e6, "bytes_per_launch": nbytes,
+            "kernel": "lm_head_kernel (fp16 GEMV + arg-max)", "problems": f"{V} x {H} fp16, 1 row; {nbytes / 1e6:.0f} MB > L2"}
+
+
+def _stage(rank, what):
+    if os.environ.get("GLQ_BENCH_VERBOSE"):
+        print(f"[bench rank {rank}] {what}", file=sys.stderr, flush=True)
+
+
+def token_bytes(cfg, layers, context, rank_=64):
+    """Algorithmic bytes of one decoded token at batch 1: every layer's attention projections (4-bit g128 +
+    rank-64 factors), the key/value cache of `context` positions, the MoE block, and the output projection."""
+    from glorcq_b200 import synthetic
+    H = cfg["hidden_size"]
+    nh = cfg["num_attention_heads"]
+    nkv = cfg.get("num_key_value_heads") or nh
+    hd = cfg.get("head_dim") or H // nh
+
+    def lin4(N, K):
+        return N * K // 2 + 2 * N * ((K + 127) // 128) * 2 + K * rank_ * 2 + N * rank_ * 2 + K * 2 + N * 2
+    attn = lin4(nh * hd, H) + 2 * lin4(nkv * hd, H) + lin4(H, nh * hd) + 2 * nkv * hd * context * 2
+    E = cfg.get("num_experts", cfg.get("num_local_experts", 0))
+    I = cfg.get("moe_intermediate_size", cfg.get("intermediate_size"))
+    moe = synthetic.block_bytes_per_token(H=H, I=I, top_k=cfg["num_experts_per_tok"],
+                                          I_shared=cfg.get("shared_expert_intermediate_size", 0), rank=rank_, E=E)
+    return layers * (attn + moe) + cfg["vocab_size"] * H * 2, layers * moe
+
+
+def launches_per_token(model):
+    """Kernel launches of this library inside one captured decode step, counted from the model's structure:
+    per layer the attention side (x.U and product of the grouped q/k/v, attention, x.U and product of the output
+    projection, residual + norm) and the MoE block (its own count), plus the output projection."""
+    from glorcq_b200.moe_block import GraphCompatibleMoeBlock
+    n = 1
+    for att, mlp in zip(model.attn, model.mlp):
+        n += (2 if att._qkv is not None else 6) + 1 + 2 + 1
+        n += mlp.launches_per_call() if isinstance(mlp, GraphCompatibleMoeBlock) else 6
+    return n
 
 
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from glorcq_b200 import _build, synthetic, tiled
+    from glorcq_b200.graph_wrapper import GLoRCQGraphWrapper
+    from glorcq_b200.parallel import PeerExchange
     _build.build()
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    layers = args.layers
-    pools = {}
-    # N > 1: the experts of every block are sharded over the ranks (expert e on rank e % N); router and
-    # shared expert are replicated; one all-reduce of the per-entry outputs per block (--replicas: N
-    # independent copies of the whole model instead)
+    cfg, name, prompt = model_config(args.config)
+    prompt = args.prompt or prompt
+    layers = cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
     ep = world > 1 and not args.replicas
-    blocks = [synthetic.make_moe_block(1000 + l, dev, pools=pools, ep_rank=rank if ep else 0,
-                                       ep_world=world if ep else 1, **CFG) for l in range(layers)]
-    _stage(rank, "blocks built")
-    H = CFG["H"]
-    # the exchange: this library's kernel over peer-mapped memory (peer stores + flags), or NCCL's all-reduce
-    # when asked for or when the symmetric allocation is not to be had on every rank
-    peer = None
-    if ep and args.exchange == "peer":
-        from glorcq_b200 import parallel
+    # weak scaling: `args.batch` token streams per rank; every rank holds all of them (attention, router and
+    # shared expert are replicated) and its share of the routed experts
+    streams = args.batch * (world if ep and not args.strong else 1)
+    K, W = max(1, args.steps), max(3, args.warmup)
+    peer_ok = ep and args.exchange == "peer" and streams <= 16
+    if peer_ok:
         ok = torch.ones(1, device=dev)
         try:
-            peer = parallel.PeerExchange.get(None, dev, 16 * CFG["top_k"], H)
+            PeerExchange.get(None, dev, 16 * cfg["num_experts_per_tok"], cfg["hidden_size"])
         except Exception as exc:       # noqa: BLE001 - any failure here means "use NCCL"
             _stage(rank, f"peer exchange unavailable: {exc!r}")
             ok.zero_()
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if float(ok) == 0:
-            peer = None
-        for blk in blocks:
-            blk.peer_exchange_max_tokens = 16 if peer is not None else 0
-    # weak scaling: one token stream per rank, so a step decodes `batch` = N tokens; every rank holds all
-    # N hidden states (the replicated router and shared expert see them all) and its share of the experts
-    batch = world if ep and not args.strong else 1
+        peer_ok = float(ok) != 0
+    model = synthetic.make_decoder(cfg, dev, seed=77, ep_rank=rank if ep else 0, ep_world=world if ep else 1,
+                                   peer_exchange_max_tokens=16 if peer_ok else 0)
+    _stage(rank, "model built")
+    if world > 1:
+        dist.barrier()          # the first step is a collective: the ranks start it together
+    w = GLoRCQGraphWrapper(model, max_batch_size=streams, max_seq_len=prompt + K + W + 24)
+    ids = torch.randint(0, cfg["vocab_size"], (streams, prompt), generator=torch.Generator().manual_seed(5)).to(dev)
+    w.capture_graph()
+    out, _ = w.generate(ids, max_new_tokens=8)           # the prompt's keys and values, and a first replay
+    torch.cuda.synchronize()
+    first = out[:, prompt:prompt + 1].contiguous()       # the token decoded from the prompt
+    _stage(rank, "captured, prompt processed")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def next_token():
+        return w.static_next if w.static_next is not None else torch.argmax(w.static_logits[:, -1, :], dim=-1, keepdim=True)
+
+    def window(steps):
+        tok = first
+        for i in range(steps):
+            w.replay(tok, prompt + i)
+            tok = next_token()
+        return tok
+
+    window(W)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    # ---- device-resident timing: R windows of exactly K steps ----
+    R = max(25, int(math.ceil(0.6 / max(1e-4, K * 1.0e-3))))
+    R = min(R, 400)
+    times = []
+    for _ in range(R):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        window(K)
+        e1.record()
+        barrier()
+        times.append(e0.elapsed_time(e1))
+    _stage(rank, "device timing done")
+    # ---- end to end: token id from pinned host memory in, next token id back to the host, every step ----
+    mine = rank if streams > 1 and ep else 0
+    h_in = torch.empty(args.batch if ep else streams, 1, dtype=torch.int64).pin_memory()
+    h_out = torch.empty_like(h_in).pin_memory()
+    rows = slice(mine * args.batch, (mine + 1) * args.batch) if ep else slice(0, streams)
+    own = torch.empty(h_in.shape, dtype=torch.int64, device=dev)
+    all_ids = torch.empty(streams, 1, dtype=torch.int64, device=dev)
+
+    def e2e_window(steps):
+        h_in.copy_(first[rows].cpu())
+        for i in range(steps):
+            if ep and not args.strong:
+                own.copy_(h_in, non_blocking=True)
+                dist.all_gather_into_tensor(all_ids, own)
+                w.replay(all_ids, prompt + i)
+            else:
+                all_ids.copy_(h_in, non_blocking=True)
+                w.replay(all_ids, prompt + i)
+            h_out.copy_(next_token()[rows], non_blocking=True)
+            torch.cuda.synchronize()
+            h_in.copy_(h_out)
+    e2e_window(3)
+    e2e_times = []
+    for _ in range(max(5, R // 3)):
+        barrier()
+        t0 = time.perf_counter()
+        e2e_window(K)
+        barrier()
+        e2e_times.append((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop() if rank == 0 else None
+    PeerExchange.check_all()
+
+    t = torch.tensor([times, e2e_times + [0.0] * (len(times) - len(e2e_times))], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)       # every window: the slowest rank's time
+    ms = float(t[0].median())
+    e2e_ms = float(t[1][:len(e2e_times)].median())
+
+    # ---- expert parallel: layer 0's block against an unsharded copy on the same inputs ----
+    ep_check = None
+    if ep and rank == 0:
+        single = synthetic.make_decoder({**cfg, "num_hidden_layers": 1}, dev, seed=77).mlp[0]
+        hx = torch.randn(1, streams, cfg["hidden_size"], device=dev, dtype=torch.float16,
+                         generator=torch.Generator(device=dev).manual_seed(11))
+        ref_y = single(hx)[0]
+        del single
+    if ep:
+        hx = torch.randn(1, streams, cfg["hidden_size"], device=dev, dtype=torch.float16,
+                         generator=torch.Generator(device=dev).manual_seed(11))
+        barrier()
+        with torch.no_grad():
+            got = model.mlp[0](hx)[0]
+        torch.cuda.synchronize()
+        if rank == 0:
+            ep_check = {"layer0_block_bit_equal_to_unsharded": bool(torch.equal(got, ref_y)), "tokens": streams}
+
+    # ---- the MoE blocks alone ----
+    moe_only = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        moe_only = moe_blocks_alone(model, dev, cfg, layers)
+    err = tiled.debug_error()
+    if rank == 0:
+        peak, kind = measured_peak_gbs()
+        roof = gemv_roofline(dev, peak, kind)
+        extras = {}
+        if not args.no_extras:
+            extras["roofline_gemm"] = gemm_roofline(dev)
+            extras["roofline_lm_head"] = lm_head_roofline(dev, peak, cfg["vocab_size"], cfg["hidden_size"])
+        cpu = None
+        if world == 1:      # the CPU leg is timed at N = 1 only
+            sec_tok, threads, reps = CpuToken(cfg, prompt).seconds(8.0, 100)
+            cpu = {"value": 1.0 / sec_tok, "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"one token: 1 of {layers} layers (4 attention projections, attention over {prompt} cached positions, "
+                             f"MoE block) and the output projection through the CPU oracle, median of {reps} forwards; "
+                             f"tok/s = 1 / ({layers} x layer + output projection)"}
+        bytes_tok, bytes_moe = token_bytes(cfg, layers, prompt + K // 2)
+        value = streams * K / (ms * 1e-3)
+        conf = workload_config(cfg, name, prompt, args.batch, layers)
+        conf.update({"parallelism": "single GPU" if world == 1 else
+                     (f"expert parallel ep{world}: expert e on rank e % {world}; attention, router, shared expert and output "
+                      f"projection replicated; " + ("exchange kernel over peer memory (peer stores + flags)" if peer_ok else
+                                                    "NCCL all-reduce of the per-entry outputs") + f" once per block; {streams} token stream(s) per step"
+                      if ep else f"replicas x{world}"),
+                     "batch": streams, "windows": R, "window_ms_min_median_max": [min(times), ms, max(times)],
+                     "algorithmic_bytes_per_token": bytes_tok,
+                     "token_hbm_frac_of_peak": bytes_tok * K / (ms * 1e-3) / 1e9 / peak})
+        nl = launches_per_token(model)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
+                "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
+                "scaling": "strong" if ep and args.strong else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": conf,
+                "e2e": {"value": streams * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8 * h_in.numel(),
+                        "d2h_bytes_per_step": 8 * h_out.numel()},
+                "gpu_launches": K * nl, "launches_per_token": nl,
+                "roofline": roof, **extras, "moe_only": moe_only,
+                "cpu_baseline": cpu, "clocks": clocks, "kernel_self_check": err}
+        if ep:
+            line["exchange"] = {"kind": "peer" if peer_ok else "nccl", "waits_run_out": 0}
+            line["ep_check"] = ep_check
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        # all ranks leave together (rank 0 was busy with the roofline legs); a teardown that does not return
+        # must not keep the launcher waiting
+        dist.barrier()
+        del w
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        tm = threading.Timer(20.0, os._exit, (0,))
+        tm.daemon = True
+        tm.start()
+        dist.destroy_process_group()
+
+
+def moe_blocks_alone(model, dev, cfg, layers, steps=100):
+    """One token through the decoder's MoE blocks alone, each block's output feeding the next through the fused
+    residual-free RMS norm, replayed from one CUDA graph: the part of a token the quantized expert path owns."""
+    from glorcq_b200 import synthetic
+    from glorcq_b200.moe_block import GraphCompatibleMoeBlock
+    blocks = [m for m in model.mlp if isinstance(m, GraphCompatibleMoeBlock)]
+    if not blocks:
+        return None
+    H = cfg["hidden_size"]
     gx = torch.Generator(device=dev)
     gx.manual_seed(4242)
-    static_x = torch.randn(1, batch, H, device=dev, dtype=torch.float16, generator=gx)
-    x0 = static_x.clone()
-    mine = rank if batch > 1 else 0
+    static_x = torch.randn(1, 1, H, device=dev, dtype=torch.float16, generator=gx)
+    eps = torch.finfo(torch.float16).eps
 
     def token(x):
-        # the decoder's RMS norm between blocks keeps every layer's input at unit scale; it runs inside the
-        # block's combine kernel (same arithmetic as torch's rms_norm on the block output)
-        eps = torch.finfo(torch.float16).eps
         for blk in blocks:
             _, _, x = blk(x, next_norm=(None, eps))
         return x
-
-    # warm-up outside capture (builds workspaces), then capture one token
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s), torch.no_grad():
@@ -349,157 +614,55 @@ def run_ours(args, rank, world, local_rank):
             token(static_x)
     torch.cuda.current_stream().wait_stream(s)
     torch.cuda.synchronize()
-    if peer is not None:
-        bad = torch.tensor([float(peer.error() != 0)], device=dev)
-        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
-        if float(bad) != 0:            # a wait ran out during warm-up: do not time that
-            _stage(rank, "peer exchange: a wait ran out in warm-up, using NCCL")
-            peer = None
-            for blk in blocks:
-                blk.peer_exchange_max_tokens = 0
-            with torch.no_grad():
-                token(static_x)
-            torch.cuda.synchronize()
-    _stage(rank, "eager warm-up done")
-    if args.no_graph:
-        class _Eager:
-            def replay(self):
-                with torch.no_grad():
-                    static_y.copy_(token(static_x))
-        with torch.no_grad():
-            static_y = token(static_x).clone()
-        graph = _Eager()
-    else:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph), torch.no_grad():
-            static_y = token(static_x)
-    _stage(rank, "captured")
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident timing ----
-    for _ in range(max(3, args.warmup)):
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), torch.no_grad():
+        static_y = token(static_x)
+    for _ in range(5):
         static_x.copy_(static_y)
         graph.replay()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    barrier()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        static_x.copy_(static_y)     # next token's hidden state stays on the device
+    for _ in range(steps):
+        static_x.copy_(static_y)
         graph.replay()
     e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    _stage(rank, f"device timing done: {ms:.2f} ms")
-    # ---- end to end: pinned host in, host out, every step ----
-    # every rank owns one token stream: its hidden state comes from its pinned host buffer, the ranks
-    # exchange the rows (all-gather, N > 1), the graph runs, the rank's own output row goes back
-    hx = torch.empty(1, H, dtype=torch.float16).pin_memory()
-    hy = torch.empty(1, H, dtype=torch.float16).pin_memory()
-    hx.copy_(x0[0, mine:mine + 1].cpu())
-    own = torch.empty(1, H, dtype=torch.float16, device=dev)
-
-    def e2e_step():
-        if batch > 1:
-            own.copy_(hx, non_blocking=True)
-            dist.all_gather_into_tensor(static_x.view(batch, H), own)
-        else:
-            static_x.view(1, H).copy_(hx, non_blocking=True)
-        graph.replay()
-        hy.copy_(static_y.view(batch, H)[mine:mine + 1], non_blocking=True)
-        torch.cuda.synchronize()
-        hx.copy_(hy)
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    clocks = sampler.stop() if rank == 0 else None
-
-    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
-    err = tiled.debug_error()
-    if rank == 0:
-        peak, kind = measured_peak_gbs()
-        roof = gemv_roofline(dev, peak, kind)
-        roof_gemm = gemm_roofline(dev)
-        cpu = None
-        if world == 1:      # the CPU leg is timed at N=1 only
-            sec_layer, threads, reps = cpu_layer_seconds()
-            cpu = {"value": 1.0 / (sec_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
-                   "sample": f"1 of {layers} layers, 1 token, median of {reps} CPU forwards of the oracle"}
-        bytes_tok = synthetic.block_bytes_per_token(**{k: CFG[k] for k in ("H", "I", "top_k", "I_shared", "rank", "E")}) * layers
-        streams = batch if ep else world      # token streams decoded at once
-        value = streams * args.steps / (ms * 1e-3)
-        cfg = workload_config(layers)
-        cfg.update({"parallelism": "single GPU" if world == 1 else
-                    (f"expert parallel ep{world}: expert e on rank e % {world}, router and shared expert replicated, "
-                     + ("exchange kernel over peer memory (peer stores + flags)" if peer is not None else
-                        "NCCL all-reduce of the per-entry outputs") + f" once per block; {batch} token stream(s) per step"
-                     if ep else f"replicas x{world}"),
-                    "batch": batch,
-                    "algorithmic_bytes_per_token": bytes_tok,
-                    "token_hbm_frac_of_peak": bytes_tok * args.steps / (ms * 1e-3) / 1e9 / peak})
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "strong" if ep and batch == 1 else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": cfg,
-                "e2e": {"value": streams * args.steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": H * 2,
-                        "d2h_bytes_per_step": H * 2},
-                "gpu_launches": args.steps * layers * (11 if peer is not None else 10),
-                "roofline": roof, "roofline_gemm": roof_gemm,
-                "cpu_baseline": cpu,
-                "clocks": clocks, "kernel_self_check": err}
-        if ep:
-            line["exchange"] = {"kind": "peer" if peer is not None else "nccl",
-                                "waits_run_out": None if peer is None else int(peer.error() != 0)}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        # all ranks leave together (rank 0 was busy with the roofline and CPU legs); a teardown that does
-        # not return must not keep the launcher waiting
-        dist.barrier()
-        del graph
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        t = threading.Timer(20.0, os._exit, (0,))
-        t.daemon = True
-        t.start()
-        dist.destroy_process_group()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    E = cfg.get("num_experts", cfg.get("num_local_experts", 0))
+    I = cfg.get("moe_intermediate_size", cfg.get("intermediate_size"))
+    nbytes = len(blocks) * synthetic.block_bytes_per_token(H=H, I=I, top_k=cfg["num_experts_per_tok"],
+                                                           I_shared=cfg.get("shared_expert_intermediate_size", 0), rank=64, E=E)
+    peak, _ = measured_peak_gbs()
+    return {"value": 1e3 / ms, "unit": UNIT, "ms_per_token": ms, "us_per_block": ms * 1e3 / len(blocks), "blocks": len(blocks),
+            "launches_per_block": blocks[0].launches_per_call(), "algorithmic_bytes_per_token": nbytes,
+            "hbm_frac_of_peak": nbytes / (ms * 1e-3) / 1e9 / peak}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--config", default="qwen15", choices=["qwen15", "mixtral", "qwen3"],
+                    help="decoder shape: Qwen1.5-MoE-A2.7B (default), Mixtral-8x7B or Qwen3-30B-A3B")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
+    ap.add_argument("--batch", type=int, default=1, help="token streams per rank")
+    ap.add_argument("--prompt", type=int, default=0, help="prompt length (0: the configuration's)")
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the grouped dequant-GEMV roofline case (small enough for an ncu capture)")
-    ap.add_argument("--full-model", action="store_true",
-                    help="time the whole decoder (prefill + graph decode) instead of the MoE-block metric line")
-    ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--gemm-only", action="store_true",
                     help="time only the grouped tcgen05 dequant-GEMM roofline case (small enough for an ncu capture)")
+    ap.add_argument("--lm-head-only", action="store_true", help="time only the output projection kernel")
+    ap.add_argument("--moe-only", action="store_true", help="time only the MoE blocks of the model (moe_only of the line)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / lm_head roofline legs and moe_only")
     ap.add_argument("--rows", type=int, default=2048)
     ap.add_argument("--problems", type=int, default=240)
-    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the per-block exchange, this library's peer-memory kernel or NCCL's all-reduce")
     ap.add_argument("--strong", action="store_true",
-                    help="with --gpus N > 1: one token stream for all ranks (strong scaling) instead of one per rank")
+                    help="with --gpus N > 1: the same token streams for all ranks (strong scaling) instead of --batch per rank")
     ap.add_argument("--replicas", action="store_true",
                     help="with --gpus N > 1: N independent copies of the model instead of expert parallelism")
     args = ap.parse_args()
@@ -509,22 +672,25 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
-    if args.gemv_only:
-        from glorcq_b200 import _build
+    if args.gemv_only or args.gemm_only or args.lm_head_only or args.moe_only:
+        from glorcq_b200 import _build, synthetic
         _build.build()
+        dev = torch.device("cuda:0")
         peak, kind = measured_peak_gbs()
-        print(json.dumps({"roofline": gemv_roofline(torch.device("cuda:0"), peak, kind, P=args.problems,
-                                                     iters=max(1, args.steps))}), flush=True)
-        return
-    if args.full_model:
-        run_full_model(args)
-        return
-    if args.gemm_only:
-        from glorcq_b200 import _build
-        _build.build()
-        P = args.problems if args.problems != 240 else 8
-        print(json.dumps({"roofline_gemm": gemm_roofline(torch.device("cuda:0"), P=P, rows=args.rows,
-                                                          iters=max(1, args.steps))}), flush=True)
+        if args.gemv_only:
+            out = {"roofline": gemv_roofline(dev, peak, kind, P=args.problems, iters=max(1, args.steps))}
+        elif args.gemm_only:
+            P = args.problems if args.problems != 240 else 8
+            out = {"roofline_gemm": gemm_roofline(dev, P=P, rows=args.rows, iters=max(1, args.steps))}
+        elif args.lm_head_only:
+            out = {"roofline_lm_head": lm_head_roofline(dev, peak, iters=max(1, args.steps))}
+        else:
+            cfg, name, prompt = model_config(args.config)
+            cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
+            torch.cuda.set_device(dev)
+            model = synthetic.make_decoder(cfg, dev, seed=77)
+            out = {"moe_only": moe_blocks_alone(model, dev, cfg, cfg["num_hidden_layers"], steps=max(1, args.steps))}
+        print(json.dumps(out), flush=True)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libglorcq_b200.so")
-SOURCES = ["api.cu", "moe.cu", "attn.cu"]
+SOURCES = ["api.cu", "moe.cu", "attn.cu", "lm_head.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 

@@ -96,6 +96,8 @@ _SIGS = {
     "glq_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "glq_attn_decode": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
                                   C.c_float, vp, C.c_size_t, vp, C.c_size_t, vp]),
+    "glq_lm_head_workspace_bytes": (C.c_size_t, []),
+    "glq_lm_head": (C.c_int, [vp, C.c_int64, vp, C.c_int, C.c_int, C.c_int, vp, C.c_int64, vp, vp, C.c_size_t, vp, vp]),
     "glq_rht_forward": (C.c_int, [vp, C.c_int, C.c_int64, vp, C.c_int, C.c_int, C.c_float, vp, C.c_int, C.c_int64, vp]),
     "glq_mm_workspace_bytes": (C.c_size_t, [C.POINTER(MMArgs)]),
     "glq_mm_counters": (C.c_size_t, [C.POINTER(MMArgs)]),

@@ -10,9 +10,10 @@ shared expert) layouts.
 
 The quantized projections and the MoE block run on this package's kernels, and so does the attention
 of a decode step (``glq_attn_decode``: q/k norms, rotary embedding, cache write and attention over the
-live positions in one launch).  Layer norms, the prefill attention (``scaled_dot_product_attention``
-over the static cache with a position mask), embedding lookup and the fp16 ``lm_head`` product are plain
-library calls: small or dense-fp16 work outside the quantized path.
+live positions in one launch) and the fp16 ``lm_head`` product of up to 64 rows (``glq_lm_head``: a streaming
+kernel over the row-major vocabulary matrix with the greedy arg-max folded in).  The first layer norm, the
+embedding lookup, the prompt's attention (``scaled_dot_product_attention``, causal over the new keys) and the
+logits of a whole prompt are plain library calls.
 """
 
 from __future__ import annotations
@@ -101,7 +102,7 @@ class _Attention(nn.Module):
                 (all(u is not None for u in uts) or all(u is None for u in uts)):
             self._qkv = tiled.GroupedLinear(tl, uts if uts[0] is not None else None)
 
-    def forward(self, x, cache_position, cache: StaticKVCache, cos, sin):
+    def forward(self, x, cache_position, cache: StaticKVCache, cos, sin, kv_len=None):
         c = self.cfg
         B, T, _ = x.shape
         if T == 1 and cache_position.numel() == 1 and c.head_dim in (32, 64, 128, 256):
@@ -135,10 +136,16 @@ class _Attention(nn.Module):
         q = q * cs + _rotate_half(q) * sn
         k = k * cs + _rotate_half(k) * sn
         k_all, v_all = cache.update(self.layer_idx, k, v, cache_position)
-        # position mask over the whole static cache: key j is visible to query t when j <= position(t)
-        mask = torch.arange(cache.max_cache_len, device=x.device)[None, :] <= cache_position[:, None]
-        y = F.scaled_dot_product_attention(q, k_all, v_all, attn_mask=mask[None, None],
-                                           enable_gqa=c.num_key_value_heads != c.num_attention_heads)
+        gqa = c.num_key_value_heads != c.num_attention_heads
+        if kv_len is not None and kv_len == T:
+            # a prompt written at positions 0..T-1: causal attention over the new keys only
+            y = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=gqa)
+        else:
+            # position mask over the live part of the static cache: key j is visible to query t when j <= position(t)
+            n_live = cache.max_cache_len if kv_len is None else kv_len
+            mask = torch.arange(n_live, device=x.device)[None, :] <= cache_position[:, None]
+            y = F.scaled_dot_product_attention(q, k_all[:, :, :n_live], v_all[:, :, :n_live], attn_mask=mask[None, None],
+                                               enable_gqa=gqa)
         return self.o_proj(y.transpose(1, 2).reshape(B, T, c.num_attention_heads * c.head_dim))
 
 
@@ -183,7 +190,11 @@ class GLoRCQDecoder(nn.Module):
     lm_head.weight, attention biases and q/k norms); what is missing is zero, as the reference's loader
     leaves every parameter it does not replace (inference/model_builder.py:314-330, 431-447)."""
 
-    def __init__(self, hf_config: dict, layers, dense: Optional[dict] = None, device="cuda:0"):
+    def __init__(self, hf_config: dict, layers, dense: Optional[dict] = None, device="cuda:0", ep_rank=0, ep_world=1,
+                 ep_group=None, peer_exchange_max_tokens=0):
+        """With ``ep_world`` > 1 the routed experts of every block are sharded (expert e on rank e % ep_world;
+        ``layers`` then only needs this rank's experts); everything else is replicated, and the ranks exchange the
+        experts' outputs once per block (glorcq_b200.parallel)."""
         super().__init__()
         c = self.config = _config(hf_config)
         dense = dense or {}
@@ -214,8 +225,11 @@ class GLoRCQDecoder(nn.Module):
                 blk.num_experts, blk.top_k, blk.norm_topk_prob = c.num_experts, c.num_experts_per_tok, c.norm_topk_prob
                 blk.gate = nn.Linear(H, c.num_experts, bias=False, device=dev, dtype=torch.float16)
                 blk.gate.weight.data.copy_(dense_param(f"{pre}.{mp}.gate.weight", (c.num_experts, H)))
-                blk.experts = nn.ModuleList([_Expert(mods[f"{mp}.experts.{e}.{gn}"], mods[f"{mp}.experts.{e}.{un}"],
-                                                     mods[f"{mp}.experts.{e}.{dn}"]) for e in range(c.num_experts)])
+                blk.experts = [_Expert(mods[f"{mp}.experts.{e}.{gn}"], mods[f"{mp}.experts.{e}.{un}"],
+                                       mods[f"{mp}.experts.{e}.{dn}"]) if e % ep_world == ep_rank else None
+                               for e in range(c.num_experts)]
+                if ep_world == 1:
+                    blk.experts = nn.ModuleList(blk.experts)
                 if f"{mp}.shared_expert.gate_proj" in mods:
                     blk.shared_expert = _Expert(mods[f"{mp}.shared_expert.gate_proj"], mods[f"{mp}.shared_expert.up_proj"],
                                                 mods[f"{mp}.shared_expert.down_proj"])
@@ -224,12 +238,17 @@ class GLoRCQDecoder(nn.Module):
                 else:
                     blk.shared_expert, blk.shared_expert_gate = None, None
                 moe = GraphCompatibleMoeBlock(blk)
+                if ep_world > 1:
+                    moe.set_expert_parallel(ep_rank, ep_world, ep_group)
+                    moe.peer_exchange_max_tokens = peer_exchange_max_tokens
                 moe.prepare(dev, release_linear_tiles=True)
                 self.mlp.append(moe)
             else:
                 self.mlp.append(_DenseMLP(mods["mlp.gate_proj"], mods["mlp.up_proj"], mods["mlp.down_proj"]))
         self._rope = None
         self._own_cache = None
+        self._lm_ws = {}
+        self.last_argmax = None     # (B * kept positions,) int64 greedy tokens of the last forward, when the kernel ran
 
     def _tables(self, need, device):
         if self._rope is None or self._rope[0].shape[0] < need:
@@ -237,8 +256,38 @@ class GLoRCQDecoder(nn.Module):
             self._rope = _rope_tables(self.config.head_dim, n, self.config.rope_theta, device)
         return self._rope
 
+    def _lm_head(self, x):
+        """(rows, H) fp16 -> (rows, V) logits; up to 64 rows go through this package's streaming kernel (8 rows
+        per pass of the weights) with the greedy arg-max of every row folded in (kept in ``last_argmax``),
+        longer inputs (the logits of a whole prompt) through a dense library product."""
+        rows, H = x.shape
+        V = self.lm_head.shape[0]
+        if not (x.is_cuda and 0 < rows <= 64 and H % 32 == 0 and H <= 8192 and self.lm_head.is_contiguous()):
+            self.last_argmax = None
+            return x @ self.lm_head.t()
+        x = x.contiguous()
+        logits = torch.empty(rows, V, dtype=torch.float16, device=x.device)
+        best = torch.empty(rows, dtype=torch.int64, device=x.device)
+        L = _lib.lib()
+        with torch.cuda.device(x.device):
+            key = ("lm_head", x.device.index, tiled._stream_ptr(x.device))
+            if key not in self._lm_ws:
+                self._lm_ws[key] = (torch.empty(L.glq_lm_head_workspace_bytes() + 16, dtype=torch.uint8, device=x.device),
+                                    torch.zeros(1, dtype=torch.int32, device=x.device))
+            ws, ctr = self._lm_ws[key]
+            for r0 in range(0, rows, 8):
+                nb = min(8, rows - r0)
+                _lib.check(L.glq_lm_head(x[r0:].data_ptr(), x.stride(0), self.lm_head.data_ptr(), nb, V, H,
+                                         logits[r0:].data_ptr(), V, best[r0:].data_ptr(),
+                                         (ws.data_ptr() + 15) // 16 * 16, ws.numel() - 16, ctr.data_ptr(),
+                                         tiled._stream_ptr(x.device)), "lm_head")
+        self.last_argmax = best
+        return logits
+
     def forward(self, input_ids=None, cache_position=None, past_key_values=None, use_cache=True, return_dict=False,
-                **_unused):
+                logits_to_keep=0, **_unused):
+        """``logits_to_keep`` = k > 0 computes the logits of the last k positions only (the greedy loop needs
+        one); 0 keeps them all, as the transformers models do by default."""
         c = self.config
         B, T = input_ids.shape
         if past_key_values is None:
@@ -251,8 +300,12 @@ class GLoRCQDecoder(nn.Module):
         x = F.embedding(input_ids, self.embed_tokens)
         L = c.num_hidden_layers
         h = F.rms_norm(x, (c.hidden_size,), self.ln1[0], c.rms_norm_eps) if L > 0 else x
+        # a prompt (T > 1, eager only): its first position is read back once, so that attention sees the live
+        # part of the static cache instead of all of it
+        kv_len = (int(cache_position[0]) + T) if T > 1 else None
         for l in range(L):
-            x, h = _add_rmsnorm(x, self.attn[l](h, cache_position, past_key_values, cos, sin), self.ln2[l], c.rms_norm_eps)
+            x, h = _add_rmsnorm(x, self.attn[l](h, cache_position, past_key_values, cos, sin, kv_len), self.ln2[l],
+                                c.rms_norm_eps)
             nxt = self.ln1[l + 1] if l + 1 < L else self.norm          # the norm that follows this layer
             mlp = self.mlp[l]
             if isinstance(mlp, GraphCompatibleMoeBlock) and c.hidden_size <= 8192:
@@ -263,7 +316,10 @@ class GLoRCQDecoder(nn.Module):
                 x = x + (m[0] if isinstance(m, tuple) else m)
                 h = F.rms_norm(x, (c.hidden_size,), nxt, c.rms_norm_eps)
         x = h if L > 0 else F.rms_norm(x, (c.hidden_size,), self.norm, c.rms_norm_eps)
-        logits = x @ self.lm_head.t()
+        if logits_to_keep and logits_to_keep < T:
+            x = x[:, T - logits_to_keep:]
+        keep = x.shape[1]
+        logits = self._lm_head(x.reshape(B * keep, c.hidden_size)).view(B, keep, -1)
         return (logits, past_key_values)
 
     @torch.no_grad()

@@ -35,6 +35,10 @@ class GLoRCQGraphWrapper:
         self.static_input_ids = torch.zeros((max_batch_size, 1), dtype=torch.long, device=self.device)
         self.static_cache_position = torch.zeros((1,), dtype=torch.long, device=self.device)
         self.static_logits = None
+        self.static_next = None
+        # this package's decoder can skip the logits of all prompt positions but the last
+        import inspect
+        self._keep_last_only = "logits_to_keep" in inspect.signature(model.forward).parameters
         self.graph = None
         self.graph_stream = torch.cuda.Stream(device=self.device)
         self.last_prefill_seconds = None
@@ -76,6 +80,9 @@ class GLoRCQGraphWrapper:
         self.static_cache_position.fill_(0)
         with torch.cuda.graph(self.graph, stream=self.graph_stream), torch.no_grad():
             self.static_logits = self._step()[0]
+        # the model's output projection may leave the greedy token of the step beside the logits
+        best = getattr(self.model, "last_argmax", None)
+        self.static_next = best.view(self.max_batch_size, 1) if best is not None else None
 
     @torch.no_grad()
     def replay(self, input_ids, cache_position_val):
@@ -97,8 +104,9 @@ class GLoRCQGraphWrapper:
         output_ids = input_ids.clone()
         self._set_moe_graph_mode(False)
         self.static_cache.reset()
+        kw = {"logits_to_keep": 1} if self._keep_last_only else {}
         logits = self.model(input_ids=input_ids, cache_position=torch.arange(seq_len, device=self.device),
-                            past_key_values=self.static_cache, use_cache=True, return_dict=False)[0]
+                            past_key_values=self.static_cache, use_cache=True, return_dict=False, **kw)[0]
         next_token = torch.argmax(logits[:, -1, :], dim=-1, keepdim=True)
         output_ids = torch.cat([output_ids, next_token], dim=1)
         torch.cuda.synchronize()
@@ -117,7 +125,10 @@ class GLoRCQGraphWrapper:
             if pos >= self.max_seq_len:
                 break
             logits = self.replay(next_token, pos)
-            next_token = torch.argmax(logits[:, -1, :], dim=-1, keepdim=True)
+            if self.static_next is not None:
+                next_token = self.static_next.clone()         # arg-max taken inside the captured step
+            else:
+                next_token = torch.argmax(logits[:, -1, :], dim=-1, keepdim=True)
             output_ids = torch.cat([output_ids, next_token], dim=1)
         torch.cuda.synchronize()
         end = time.time()

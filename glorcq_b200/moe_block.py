@@ -243,6 +243,24 @@ class GraphCompatibleMoeBlock(nn.Module):
                 self.shared_expert.gate_proj._tiled = self.shared_expert.up_proj._tiled = None
         return self
 
+    def launches_per_call(self) -> int:
+        """Kernel launches of one forward of a few tokens (affine formats; what a captured decode step holds):
+        router product, routing plan, x.U of the routed gate and up clusters, fused gate|up, h.U, down, combine,
+        the shared expert's gate|up, h.U and down, and with expert parallelism the exchange kernel."""
+        d = self._desc
+        if d is None:
+            return 0
+        n = 2 + (4 if d.rank > 0 else 2) + 1
+        if self.gate is None:
+            n -= 1
+        if d.I_shared > 0:
+            n += 3 if d.sh_ut_down else 2
+        if d.fmt == FMT_T2:
+            n += sum(1 for r in (d.rot_in or d.rht_in, d.rot_mid or d.rht_mid, d.I_shared > 0 and (d.sh_rot_mid or d.sh_rht_mid)) if r)
+        if self._ep[1] > 1 and self.peer_exchange_max_tokens > 0:
+            n += 1
+        return n
+
     # ---- forward (inference/moe_block.py:381-436) -----------------------------------------------
     def forward(self, hidden_states, top_k_index=None, top_k_weights=None, residual=None, next_norm=None):
         """(B, S, H) -> ((B, S, H), router logits).  With top_k_index / top_k_weights ((B*S, k)) the routing

@@ -212,11 +212,14 @@ def write_checkpoint(path, hf_config: dict, **kw):
 
 
 def make_decoder(hf_config: dict, device, seed=0, qbit=2, attn_bits=4, rank=64, attn_rank=64, groupsize=128,
-                 n_clusters=128):
+                 n_clusters=128, ep_rank=0, ep_world=1, ep_group=None, peer_exchange_max_tokens=0):
     """A whole random decoder of the given shape built directly on the device (no files: the int32 code
     tensors of the on-disk format would be 4 bytes per weight).  Same distributions and cluster rule as
     make_checkpoint: every (layer, expert, projection) draws its U cluster from `n_clusters`; attention
-    projections are `attn_bits` codes with their own clusters; the shared expert has no low-rank term."""
+    projections are `attn_bits` codes with their own clusters; the shared expert has no low-rank term.
+    Every module draws from its own seeded generator, so with ep_world > 1 (expert e of every layer on rank
+    e % ep_world, the others not materialised) all ranks hold identical replicated tensors and identical
+    copies of the experts they share with an unsharded build."""
     from .decoder import GLoRCQDecoder
     c = hf_config
     H, L = c["hidden_size"], c["num_hidden_layers"]
@@ -231,28 +234,39 @@ def make_decoder(hf_config: dict, device, seed=0, qbit=2, attn_bits=4, rank=64, 
     wt_of = dict(zip(names, ("gate_proj", "up_proj", "down_proj")))
     shapes = {"q_proj": (nh * hd, H), "k_proj": (nkv * hd, H), "v_proj": (nkv * hd, H), "o_proj": (H, nh * hd),
               "gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}
-    gen = torch.Generator(device=device)
-    gen.manual_seed(seed)
+    wtypes = list(shapes)
     pools = {}
 
-    def U(wtype, r):
+    def generator(*key):
+        g = torch.Generator(device=device)
+        g.manual_seed((seed * 1000003 + sum((i + 1) * 7919 ** (n + 1) * int(k) for n, (i, k) in enumerate(enumerate(key))))
+                      % (2 ** 62))
+        return g
+
+    def U(wtype, r, gen):
         gid = int(torch.randint(0, n_clusters, (1,), generator=gen, device=device))
-        if (wtype, gid) not in pools:
-            pools[(wtype, gid)] = (torch.randn(shapes[wtype][1], r, generator=gen, device=device) * 0.01).half()
+        if (wtype, gid) not in pools:     # the pool is shared by every layer: seeded by the cluster alone
+            pools[(wtype, gid)] = (torch.randn(shapes[wtype][1], r, generator=generator(9, wtypes.index(wtype), gid),
+                                               device=device) * 0.01).half()
         return pools[(wtype, gid)]
 
     layers, dense = {}, {}
     for l in range(L):
         mods = {}
-        for w in ("q_proj", "k_proj", "v_proj", "o_proj"):
-            mods[f"self_attn.{w}"] = _linear(gen, *shapes[w], attn_rank, U(w, attn_rank), device, bits=attn_bits,
+        for wi, w in enumerate(("q_proj", "k_proj", "v_proj", "o_proj")):
+            gen = generator(1, l, wi)
+            mods[f"self_attn.{w}"] = _linear(gen, *shapes[w], attn_rank, U(w, attn_rank, gen), device, bits=attn_bits,
                                              groupsize=groupsize)
         if E:
             for e in range(E):
-                for nm in names:
+                if e % ep_world != ep_rank:
+                    continue
+                for ni, nm in enumerate(names):
                     w = wt_of[nm]
-                    mods[f"{mp}.experts.{e}.{nm}"] = _linear(gen, *shapes[w], rank, U(w, rank), device, bits=qbit,
+                    gen = generator(2, l, e, ni)
+                    mods[f"{mp}.experts.{e}.{nm}"] = _linear(gen, *shapes[w], rank, U(w, rank, gen), device, bits=qbit,
                                                              groupsize=groupsize)
+            gen = generator(3, l)
             if Ish:
                 mods[f"{mp}.shared_expert.gate_proj"] = _linear(gen, Ish, H, 0, None, device, bits=qbit, groupsize=groupsize)
                 mods[f"{mp}.shared_expert.up_proj"] = _linear(gen, Ish, H, 0, None, device, bits=qbit, groupsize=groupsize)
@@ -260,18 +274,28 @@ def make_decoder(hf_config: dict, device, seed=0, qbit=2, attn_bits=4, rank=64, 
                 dense[f"model.layers.{l}.{mp}.shared_expert_gate.weight"] = (torch.randn(1, H, generator=gen, device=device) * 0.02).half()
             dense[f"model.layers.{l}.{mp}.gate.weight"] = (torch.randn(E, H, generator=gen, device=device) * 0.02).half()
         else:
-            for nm in ("gate_proj", "up_proj", "down_proj"):
-                mods[f"mlp.{nm}"] = _linear(gen, *shapes[nm], rank, U(nm, rank), device, bits=qbit, groupsize=groupsize)
+            for ni, nm in enumerate(("gate_proj", "up_proj", "down_proj")):
+                gen = generator(4, l, ni)
+                mods[f"mlp.{nm}"] = _linear(gen, *shapes[nm], rank, U(nm, rank, gen), device, bits=qbit, groupsize=groupsize)
         layers[l] = mods
         dense[f"model.layers.{l}.input_layernorm.weight"] = torch.ones(H, device=device).half()
         dense[f"model.layers.{l}.post_attention_layernorm.weight"] = torch.ones(H, device=device).half()
+    gen = generator(5)
     dense["model.embed_tokens.weight"] = (torch.randn(c["vocab_size"], H, generator=gen, device=device) * 0.02).half()
     dense["lm_head.weight"] = (torch.randn(c["vocab_size"], H, generator=gen, device=device) * 0.02).half()
     dense["model.norm.weight"] = torch.ones(H, device=device).half()
-    return GLoRCQDecoder(hf_config, layers, dense=dense, device=device)
+    return GLoRCQDecoder(hf_config, layers, dense=dense, device=device, ep_rank=ep_rank, ep_world=ep_world,
+                         ep_group=ep_group, peer_exchange_max_tokens=peer_exchange_max_tokens)
 
 
 QWEN15_MOE_A27B = dict(hidden_size=2048, num_hidden_layers=24, num_attention_heads=16, num_key_value_heads=16,
                        vocab_size=151936, num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408,
                        shared_expert_intermediate_size=5632, norm_topk_prob=False, rms_norm_eps=1e-6,
                        rope_theta=1000000.0, max_position_embeddings=8192)
+
+MIXTRAL_8X7B = dict(hidden_size=4096, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                    vocab_size=32000, num_local_experts=8, num_experts_per_tok=2, intermediate_size=14336,
+                    rms_norm_eps=1e-5, rope_theta=1000000.0, max_position_embeddings=8192)
+QWEN3_30B_A3B = dict(hidden_size=2048, num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                     vocab_size=151936, num_experts=128, num_experts_per_tok=8, moe_intermediate_size=768,
+                     norm_topk_prob=True, rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=8192)

@@ -358,6 +358,17 @@ int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const v
 int glq_add_rmsnorm(const void* x, const void* delta, const void* weight, float eps, int rows, int H, void* x_out,
                     void* h_out, void* stream);
 
+/* Output projection of the decoder with the greedy arg-max folded in: logits (B, V) fp16 = x (B, H) . W^T for
+ * a dense fp16 W (V, H) in the checkpoint's row-major layout (the `lm_head` of the transformers model the
+ * reference wraps; its decode loop takes the arg-max of the last position after every replay,
+ * inference/graph_wrapper.py:186-208).  B <= 8 rows, H a multiple of 32 (<= 8192), x and W 16-byte aligned.
+ * logits may be NULL (arg-max only) and argmax_out ((B,) int64: lowest index of the largest fp16-rounded
+ * logit per row) may be NULL (logits only).  With argmax_out: workspace of glq_lm_head_workspace_bytes()
+ * (contents irrelevant) and one int32 counter that is zero before the first call and left zero. */
+size_t glq_lm_head_workspace_bytes(void);
+int glq_lm_head(const void* x, int64_t ldx, const void* W, int B, int V, int H, void* logits, int64_t ldl,
+                int64_t* argmax_out, void* workspace, size_t workspace_bytes, int32_t* counter, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

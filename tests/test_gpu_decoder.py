@@ -127,6 +127,40 @@ def test_decoder_logits_prefill_and_decode(dev, cfg, cache_len):
     assert cases.rel_l2(step.cpu(), ref[:, T:]) <= REL_LOGITS
 
 
+@pytest.mark.parametrize("B,V,H", [(1, 151936, 2048), (8, 151936, 2048), (3, 1000, 64), (5, 32000, 4096), (1, 17, 32)])
+def test_lm_head_logits_and_argmax(dev, B, V, H):
+    """glq_lm_head through the C ABI against the fp32 product of the same fp16 operands: logits within one
+    fp16 rounding (rel-L2 <= 1e-3), arg-max = lowest index of the largest fp16-rounded logit, twice in a row
+    (the arrival counter must be left zero)."""
+    from glorcq_b200 import _lib
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(B + V + H)
+    W = (torch.randn(V, H, generator=g) * 0.02).half().to(dev)
+    x = torch.randn(B, H, generator=g).half().to(dev)
+    ref = (x.float() @ W.float().t())
+    ws = torch.empty(L.glq_lm_head_workspace_bytes(), dtype=torch.uint8, device=dev)
+    ctr = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        logits = torch.full((B, V), float("nan"), dtype=torch.float16, device=dev)
+        best = torch.full((B,), -1, dtype=torch.int64, device=dev)
+        _lib.check(L.glq_lm_head(x.data_ptr(), H, W.data_ptr(), B, V, H, logits.data_ptr(), V, best.data_ptr(),
+                                 ws.data_ptr(), ws.numel(), ctr.data_ptr(), st), "lm_head")
+        torch.cuda.synchronize()
+        assert int(ctr) == 0
+        assert cases.rel_l2(logits.cpu(), ref.cpu()) <= 1e-3
+        assert torch.equal(best, torch.argmax(logits, dim=-1))
+    # arg-max only, and logits only
+    best2 = torch.full((B,), -1, dtype=torch.int64, device=dev)
+    _lib.check(L.glq_lm_head(x.data_ptr(), H, W.data_ptr(), B, V, H, None, 0, best2.data_ptr(), ws.data_ptr(), ws.numel(),
+                             ctr.data_ptr(), st), "lm_head")
+    assert torch.equal(best2, best)
+    logits2 = torch.empty_like(logits)
+    _lib.check(L.glq_lm_head(x.data_ptr(), H, W.data_ptr(), B, V, H, logits2.data_ptr(), V, None, None, 0, None, st), "lm_head")
+    assert torch.equal(logits2, logits)
+    assert L.glq_lm_head(x.data_ptr(), H, W.data_ptr(), 9, V, H, logits2.data_ptr(), V, None, None, 0, None, st) == -3
+
+
 QWEN15_SHAPE = dict(hidden_size=2048, num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=16,
                     vocab_size=151936, num_experts=60, num_experts_per_tok=4, moe_intermediate_size=1408,
                     shared_expert_intermediate_size=5632, norm_topk_prob=False, rms_norm_eps=1e-6,
