@@ -50,7 +50,8 @@ class MoeDesc(C.Structure):
                 ("sh_gate_up", Weight), ("sh_down", Weight),
                 ("sh_ut_gate", vp), ("sh_ut_up", vp), ("sh_ut_down", vp),
                 ("rot_in", vp), ("rot_mid", vp), ("sh_rot_mid", vp),
-                ("rht_in", vp), ("rht_mid", vp), ("sh_rht_mid", vp)]
+                ("rht_in", vp), ("rht_mid", vp), ("sh_rht_mid", vp),
+                ("router_rm", vp), ("ut_rm_gate_up", vp), ("ut_rm_down", vp), ("sh_ut_rm_down", vp)]
 
 
 class EpPeers(C.Structure):
@@ -106,6 +107,8 @@ _SIGS = {
     "glq_linear_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.POINTER(Weight), C.c_int]),
     "glq_linear_forward": (C.c_int, [C.c_int, C.c_int, C.POINTER(Weight), vp, vp, C.c_int64, vp, vp, C.c_int64,
                                      C.c_int, vp, C.c_size_t, vp, C.c_size_t, vp]),
+    "glq_moe_fused_trace": (C.c_int, [vp, C.c_int]),
+    "glq_moe_uses_fused_kernel": (C.c_int, [C.POINTER(MoeDesc), C.c_int]),
     "glq_moe_workspace_bytes": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
     "glq_moe_counters": (C.c_size_t, [C.POINTER(MoeDesc), C.c_int]),
     "glq_moe_forward": (C.c_int, [C.POINTER(MoeDesc), vp, C.c_int, vp, vp, vp, vp, vp, C.c_size_t, vp, C.c_size_t, vp,

@@ -1048,6 +1048,8 @@ extern "C" int glq_rht_forward(const void* x, int x_is_f32, int64_t ldx, const f
     return launch_rht<__half, float>(x, ldx, signs, rows, d, n, scale, y, ldy, st);
 }
 
+int glq_moe_error_words(unsigned long long* out4, int clear);   // moe.cu: the error word of that translation unit
+
 extern "C" int glq_debug_error(unsigned long long* out4, int clear) {
     if (!out4) return GLQ_ERR_ARG;
     GLQ_CUDA(cudaMemcpyFromSymbol(out4, g_glq_err, 4 * sizeof(unsigned long long)));
@@ -1055,5 +1057,10 @@ extern "C" int glq_debug_error(unsigned long long* out4, int clear) {
         unsigned long long z[4] = {0, 0, 0, 0};
         GLQ_CUDA(cudaMemcpyToSymbol(g_glq_err, z, sizeof(z)));
     }
+    unsigned long long m[4] = {0, 0, 0, 0};
+    const int rc = glq_moe_error_words(m, clear);
+    if (rc != GLQ_OK) return rc;
+    if (out4[0] == 0 && m[0] != 0)
+        for (int i = 0; i < 4; ++i) out4[i] = m[i];
     return GLQ_OK;
 }

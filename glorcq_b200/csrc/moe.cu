@@ -10,8 +10,19 @@
 #include <cstring>
 
 #include "glq_common.cuh"
+#include "moe_fused.cuh"
 
 using namespace glq;
+
+// error word of this translation unit (the fused kernel's timed-out waits), merged by glq_debug_error
+int glq_moe_error_words(unsigned long long* out4, int clear) {
+    if (cudaMemcpyFromSymbol(out4, g_glq_err, 4 * sizeof(unsigned long long)) != cudaSuccess) return GLQ_ERR_CUDA;
+    if (clear) {
+        unsigned long long z[4] = {0, 0, 0, 0};
+        if (cudaMemcpyToSymbol(g_glq_err, z, sizeof(z)) != cudaSuccess) return GLQ_ERR_CUDA;
+    }
+    return GLQ_OK;
+}
 
 namespace {
 
@@ -324,11 +335,6 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
 // number is published in word [rank] of every rank's flags, and the CTA waits until its own flag words
 // all show step e.  The wait is bounded by the global timer; when it runs out *error is set and the
 // kernel returns (the step's result is then incomplete, the context stays usable).
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __global__ void __launch_bounds__(1024) moe_exchange_kernel(const __half* __restrict__ staged, const int* __restrict__ n_active,
                                                             const int* __restrict__ slot_count,
                                                             const int* __restrict__ slot_offset, int n_entries, int H,
@@ -515,6 +521,190 @@ __global__ void __launch_bounds__(256) moe_combine_norm_kernel(const __half* __r
     }
 }
 
+// ---- the fused decode kernel: eligibility, geometry, launch ---------------------------------------------------
+inline bool fused_disabled() {
+    static const bool v = std::getenv("GLQ_NO_FUSED_MOE") != nullptr;
+    return v;
+}
+inline int fused_sms() {
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        sms[dev] = v;
+    }
+    return sms[dev];
+}
+inline int cdiv_i(int a, int b) { return (a + b - 1) / b; }
+
+// true when the block with n tokens runs as the one persistent kernel; fills the launch parameters that do not
+// depend on the call's buffers
+bool plan_fused(const glq_moe_desc_t* d, int n, FusedParams* out, size_t* smem_bytes) {
+    if (fused_disabled() || n < 1 || n > kFRows) return false;
+    if (d->fmt != GLQ_FMT_Q2 && d->fmt != GLQ_FMT_Q4) return false;
+    if (!d->router_rm || !d->router_t) return false;
+    if (d->rank < 0 || d->rank % 16 != 0 || (d->rank > 0 && (!d->ut_rm_gate_up || !d->ut_rm_down))) return false;
+    if (d->top_k > 16 || n * d->top_k > kFMaxEntries || d->E > 256) return false;
+    if (d->H % 8 != 0 || d->I % 8 != 0 || d->I_shared % 8 != 0) return false;
+    const int KB = d->fmt == GLQ_FMT_Q2 ? 128 : 64;
+    if (d->group_size <= 0 || d->group_size % KB != 0) return false;
+    const int gb = d->group_size / KB;
+    const bool shared = d->I_shared > 0 && d->sh_gate_up.codes != nullptr;
+    const int R = d->rank;
+    int sh_rank = 0;
+    if (shared) {
+        if (!d->sh_down.codes) return false;
+        sh_rank = d->sh_gate_up.sv ? d->sh_gate_up.rank : 0;
+        if (sh_rank > 0) {
+            // the shared expert's x.U must come out of the router product, and its h.U needs the row-major U^T
+            if (sh_rank != R || d->sh_a_row <= 0 || d->dense0_rows < d->sh_a_row + 2 * R || !d->sh_ut_rm_down ||
+                !d->sh_down.sv || d->sh_down.rank != R || d->dense0_rows % 8 != 0)
+                return false;
+        } else if (d->sh_down.sv && d->sh_down.rank > 0) {
+            return false;
+        }
+    }
+    FusedParams P{};
+    const int sms = fused_sms();
+    P.n = n;
+    P.H = d->H;
+    P.I = d->I;
+    P.Is = shared ? d->I_shared : 0;
+    P.E = d->E;
+    P.k = d->top_k;
+    P.R = R;
+    P.renorm = d->norm_topk_prob;
+    P.ldl = d->dense0_rows;
+    P.dense_rows = d->dense0_rows;
+    P.sh_a_row = d->sh_a_row;
+    // CTAs of the shared expert's chain: in proportion to its bytes, between an eighth and a half of the SMs
+    const int est = n * d->top_k;
+    int gs = 0;
+    if (shared) {
+        const double fs = (double)d->I_shared / ((double)d->I_shared + (double)est * d->I);
+        // (the shared chain has slack -- nothing in it waits for the routing -- so it gets half its share)
+        static const char* gse = std::getenv("GLQ_FUSED_GSHARE");
+        gs = (int)((gse ? std::atof(gse) : 0.5) * fs * sms + 0.5);
+        gs = std::max(sms / 8, std::min(sms / 2, gs));
+        gs = std::max(gs, kFRows);
+    }
+    if (sms - gs < kFRows) return false;        // the combine needs one CTA per token
+    P.g_shared = gs;
+    int max_nkb = 0;
+    int base[2] = {0, 0};      // rotation of the iteration -> CTA map, per subset
+    auto set_phase = [&](int idx, bool live, int N, int K, int swiglu, int rank, int problems) {
+        FusedPhase& ph = P.ph[idx];
+        const int sub = (idx & 1) ? 1 : 0, sub_G = sub ? sms - gs : std::max(gs, 1);
+        ph.live = live ? 1 : 0;
+        ph.N = N;
+        ph.K = K;
+        ph.swiglu = swiglu;
+        ph.rank = rank;
+        ph.ns = rank > 0 ? cdiv_i(rank, 64) : 0;
+        ph.nkb = cdiv_i(std::max(K, 1), KB);
+        const int units = cdiv_i(ph.nkb, gb);
+        const int ntiles = cdiv_i(std::max(N, 1), kRowTile);
+        ph.npairs = swiglu ? ntiles : cdiv_i(ntiles, 2);
+        // k splits per pair (1, 2 or 4 adjacent warps): the fewest rounds of iterations over the subset's CTAs, then
+        // the shortest items (every round ends in an epilogue with its own chain of waits)
+        int sk = 1;
+        long best = -1;
+        static const char* ske = std::getenv("GLQ_FUSED_SK");
+        const int sk_lo = ske ? std::atoi(ske) : 1;
+        for (int c = sk_lo; c <= 4; c *= 2) {
+            if (c > sk_lo && units < c) break;
+            const long rounds = cdiv_i(problems * cdiv_i(ph.npairs, kFSW / c), sub_G);
+            const long cost = rounds * 1000 + cdiv_i(units, c);
+            if (best < 0 || cost < best) best = cost, sk = c;
+        }
+        ph.sk = sk;
+        ph.sk_log2 = sk == 1 ? 0 : (sk == 2 ? 1 : 2);
+        ph.kb_per_split = cdiv_i(units, sk) * gb;
+        ph.ppi = kFSW / sk;
+        ph.ipp = cdiv_i(ph.npairs, ph.ppi);
+        ph.cta_base = base[sub] % sub_G;
+        if (live) {
+            base[sub] += problems * ph.ipp;
+            max_nkb = std::max(max_nkb, ph.nkb);
+        }
+    };
+    set_phase(0, shared, d->I_shared, d->H, 1, sh_rank, 1);
+    set_phase(1, true, d->I, d->H, 1, R, est);
+    set_phase(2, shared, d->H, d->I_shared, 0, sh_rank, 1);
+    set_phase(3, true, d->H, d->I, 0, R, est);
+    P.ph[0].w = d->sh_gate_up;
+    P.ph[2].w = d->sh_down;
+    P.ph[1].table = d->gate_up;
+    P.ph[3].table = d->down;
+    // shared memory
+    const int pieces = d->fmt == GLQ_FMT_Q2 ? 2 : 1;
+    size_t off = (size_t)kFW * kFMaxStages * 8;
+    off = (off + 127) / 128 * 128;
+    P.off_act = (int)off;
+    off += (size_t)max_nkb * pieces * 512;
+    P.off_ox = (int)off;
+    off += (size_t)max_nkb * kFRows * 8;
+    off = (off + 15) / 16 * 16;
+    P.off_red = (int)off;
+    off += (size_t)2 * kFSW * 2 * 32 * sizeof(float2);     // k-split sums (two parities)
+    P.off_prob = (int)off;
+    off += (size_t)kFRows * (256 + 16) * sizeof(float);    // the routing's probabilities
+    off = (off + 15) / 16 * 16;
+    P.off_plan = (int)off;
+    off += sizeof(FusedPlan);
+    off = (off + 15) / 16 * 16;
+    P.off_tab = (int)off;
+    off += (size_t)d->E * sizeof(ExpertPtrs);
+    off = (off + 127) / 128 * 128;
+    P.off_ring = (int)off;
+    P.stage_bytes = std::max(kStreamCB * 2 * block_bytes_of(d->fmt), 4096);
+    const size_t cap = 227 * 1024;
+    if (off + (size_t)kFSW * P.stage_bytes > cap) return false;
+    P.stages = (int)std::min<size_t>((cap - off) / ((size_t)kFSW * P.stage_bytes), 3);
+    *smem_bytes = off + (size_t)kFSW * P.stages * P.stage_bytes;
+    // dense warps sharing one row of the shared down projection's U^T: segments of at most 2048 channels
+    P.s6_segs = 1;
+    while (P.s6_segs < kFW - kFSW && P.Is / P.s6_segs > 2048 && P.Is % (16 * P.s6_segs) == 0) P.s6_segs *= 2;
+    static const bool tr = std::getenv("GLQ_FUSED_TRACE") != nullptr;
+    P.trace = tr ? 1 : 0;
+    static const char* wl = std::getenv("GLQ_FUSED_WAIT_US");
+    P.wait_ns = wl ? (unsigned long long)std::atoll(wl) * 1000ull : 4000000ull;
+    *out = P;
+    return true;
+}
+
+template <int FMT>
+int launch_fused_t(const FusedParams& P, size_t smem, cudaStream_t st) {
+    auto kern = moe_fused_kernel<FMT>;
+    static size_t configured[64] = {0};
+    static int resident[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return GLQ_ERR_CUDA;
+    if (dev < 0 || dev >= 64) return GLQ_ERR_UNSUPPORTED;
+    if (configured[dev] < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return GLQ_ERR_CUDA;
+        int nb = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, kFT, smem) != cudaSuccess) return GLQ_ERR_CUDA;
+        resident[dev] = nb;
+        configured[dev] = smem;
+    }
+    if (resident[dev] < 1) return GLQ_ERR_UNSUPPORTED;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(fused_sms());
+    cfg.blockDim = dim3(kFT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeCooperative;      // all CTAs resident at once: they wait on one another
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, P) != cudaSuccess) return GLQ_ERR_CUDA;
+    return GLQ_OK;
+}
+
 }  // namespace
 
 extern "C" size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens) {
@@ -523,7 +713,23 @@ extern "C" size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens)
 }
 extern "C" size_t glq_moe_counters(const glq_moe_desc_t* d, int n_tokens) {
     if (!d || n_tokens <= 0) return 0;
-    return 2 * moe_layout(d, n_tokens).mm_counters;
+    // the matmul launches' arrival counters (two concurrent branches), or the fused kernel's
+    return std::max<size_t>(2 * moe_layout(d, n_tokens).mm_counters, (size_t)FL_COUNT);
+}
+
+// Diagnostic: with GLQ_FUSED_TRACE set in the environment, thread 0 of every CTA of the persistent kernel records
+// the GPU's global timer (ns) after each step; this copies the stamps of the last launch, [CTA][16], to the host.
+extern "C" int glq_moe_fused_trace(unsigned long long* out, int n_words) {
+    if (!out || n_words <= 0 || n_words > 256 * kFTraceSlots + 256) return GLQ_ERR_ARG;
+    return cudaMemcpyFromSymbol(out, g_fused_trace, (size_t)n_words * sizeof(unsigned long long)) == cudaSuccess
+               ? GLQ_OK : GLQ_ERR_CUDA;
+}
+
+extern "C" int glq_moe_uses_fused_kernel(const glq_moe_desc_t* d, int n_tokens) {
+    if (!d) return 0;
+    FusedParams fp;
+    size_t smem = 0;
+    return plan_fused(d, n_tokens, &fp, &smem) ? 1 : 0;
 }
 
 extern "C" int glq_moe_forward(const glq_moe_desc_t* d, const void* x, int n, void* out, void* router_logits,
@@ -591,7 +797,61 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
                                                 px->half_elems, px->wait_limit_ns ? px->wait_limit_ns : 1000000000ull);
         return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
     }
-    if (phase != GLQ_MOE_PHASE_COMBINE) {
+    FusedParams fp;
+    size_t fused_smem = 0;
+    const bool fused = !given && plan_fused(d, n, &fp, &fused_smem) && counters != nullptr && n_counters >= (size_t)FL_COUNT;
+    if (phase != GLQ_MOE_PHASE_COMBINE && fused) {
+        // rows of remote experts' entries stay zero, so that summing the ranks' buffers is exact
+        if (ep_world > 1 && !(ep->flags & GLQ_MOE_EP_NO_ZERO_FILL) &&
+            cudaMemsetAsync(p_yd, 0, (size_t)nk * d->H * 2, st) != cudaSuccess)
+            return GLQ_ERR_CUDA;
+        fp.ep_rank = ep_rank;
+        fp.ep_world = ep_world;
+        fp.x = reinterpret_cast<const __half*>(x);
+        fp.router_rm = reinterpret_cast<const __half*>(d->router_rm);
+        fp.ut_rm_gate_up = d->ut_rm_gate_up;
+        fp.ut_rm_down = d->ut_rm_down;
+        fp.sh_ut_rm_down = reinterpret_cast<const __half*>(d->sh_ut_rm_down);
+        fp.logits = p_logits;
+        fp.sel = p_sel;
+        fp.wts = p_wts;
+        fp.active = p_active;
+        fp.n_active = p_nact;
+        fp.slot_count = p_cnt;
+        fp.slot_offset = p_off;
+        fp.entry_row = p_erow;
+        fp.entry_scale = p_escale;
+        fp.tok_entries = p_tok;
+        fp.a_gate = reinterpret_cast<__half*>(ws + L.a_gu);
+        fp.a_up = fp.a_gate + (size_t)nk * std::max(R, 16);
+        fp.h = reinterpret_cast<__half*>(ws + L.h);
+        fp.b = reinterpret_cast<__half*>(ws + L.b);
+        fp.yd = reinterpret_cast<__half*>(p_yd);
+        fp.hs = shared ? reinterpret_cast<__half*>(ws + L.hs) : nullptr;
+        fp.bs = shared ? reinterpret_cast<__half*>(ws + L.bs) : nullptr;
+        fp.ysh = shared ? reinterpret_cast<__half*>(ws + L.ysh) : nullptr;
+        fp.logits_out = reinterpret_cast<__half*>(router_logits);
+        fp.sel_out = sel_out;
+        fp.wts_out = reinterpret_cast<__half*>(weight_out);
+        fp.flags = counters;
+        // one device, whole block: the combine runs inside the same launch
+        if (phase == GLQ_MOE_PHASE_ALL && ep_world == 1 && d->H <= 8192 && !(ep && ep->residual && !ep->normed_out)) {
+            fp.combine = 1;
+            fp.by_expert = n > d->slot_order_max_tokens ? 1 : 0;
+            fp.gate_col = d->router_rows > d->E ? d->E : -1;
+            fp.out = reinterpret_cast<__half*>(out);
+            if (ep && ep->normed_out) {
+                fp.normed = reinterpret_cast<__half*>(ep->normed_out);
+                fp.residual = reinterpret_cast<const __half*>(ep->residual);
+                fp.norm_w = reinterpret_cast<const __half*>(ep->norm_weight);
+                fp.norm_eps = ep->norm_eps;
+            }
+        }
+        const int rc = d->fmt == GLQ_FMT_Q2 ? launch_fused_t<GLQ_FMT_Q2>(fp, fused_smem, st)
+                                            : launch_fused_t<GLQ_FMT_Q4>(fp, fused_smem, st);
+        if (rc != GLQ_OK) return rc;
+        if (fp.combine) return GLQ_OK;
+    } else if (phase != GLQ_MOE_PHASE_COMBINE) {
     glq_mm_args_t m;
     // the shared expert's chain runs on aux_stream (forked after the first dense product, joined before
     // the combine) when the caller provides a stream and two events; it has its own scratch and counters
@@ -835,7 +1095,7 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if (phase == GLQ_MOE_PHASE_EXPERTS) return GLQ_OK;
     // the shared expert's branch joins only here: with expert parallelism the caller's exchange of the entry
     // buffer, issued between the two phases, overlaps the rest of that branch
-    if (aux_stream != nullptr && ev_fork != nullptr && ev_join != nullptr && shared &&
+    if (!fused && aux_stream != nullptr && ev_fork != nullptr && ev_join != nullptr && shared &&
         cudaStreamWaitEvent(st, reinterpret_cast<cudaEvent_t>(ev_join), 0) != cudaSuccess)
         return GLQ_ERR_CUDA;
 

@@ -22,7 +22,8 @@ namespace glq {
 // and the access is skipped, so a wrong index cannot fault the GPU.  Always on for the codebook
 // format (whose unchecked build faulted for a reason that reading the code did not show, while the
 // checked build is clean); on for every format when compiled with -DGLQ_CHECKED.
-__device__ unsigned long long g_glq_err[4] = {0, 0, 0, 0};
+// (one copy per translation unit; glq_debug_error reads them all)
+static __device__ unsigned long long g_glq_err[4] = {0, 0, 0, 0};
 __device__ __forceinline__ bool glq_ok(bool cond, unsigned long long code, unsigned long long idx,
                                        unsigned long long lim) {
     if (!cond) {

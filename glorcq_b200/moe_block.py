@@ -119,6 +119,7 @@ class GraphCompatibleMoeBlock(nn.Module):
         fmt, gs = g0._tiled.fmt, g0._tiled.group_size
         rank = g0._tiled.rank
         gate_up, down, utg, utu, utd = ([Weight() for _ in range(E)] for _ in range(5))
+        rm_gu, rm_d = [0] * (2 * E), [0] * E     # row-major U^T of the persistent decode kernel
         for e, (g, u, dn) in lins.items():
             f = _fuse_tiles(g._tiled, u._tiled)
             if (f.fmt, f.group_size, f.rank, f.N, f.K) != (fmt, gs, rank, I, H) or \
@@ -132,6 +133,9 @@ class GraphCompatibleMoeBlock(nn.Module):
                     ut = tiled.tiled_ut(lin.U)
                     self._keep.append(ut)
                     lst[e] = Weight(ut.codes.data_ptr(), None, None, None, None, None, ut.N, ut.K, 0, 0)
+                rms = [tiled.rowmajor_ut(lin.U) for lin in (g, u, dn)]
+                self._keep += rms
+                rm_gu[e], rm_gu[E + e], rm_d[e] = (t.data_ptr() for t in rms)
         d = MoeDesc()
         d.H, d.I, d.E, d.top_k = H, I, E, self.top_k
         d.rank, d.fmt, d.group_size = rank, fmt, gs
@@ -173,9 +177,15 @@ class GraphCompatibleMoeBlock(nn.Module):
                 rows.append(torch.zeros(pad, H, dtype=torch.float16, device=device))
             d.sh_a_row = router_rows + pad
             rows += [sg.U.t().to(torch.float16), su.U.t().to(torch.float16)]
-        router = TiledWeight.from_dense(torch.cat(rows, 0).contiguous())
-        self._keep.append(router)
+        router_rm = torch.cat(rows, 0).contiguous()
+        router = TiledWeight.from_dense(router_rm)
+        self._keep += [router, router_rm]
         d.router_t, d.dense0_rows = router.codes.data_ptr(), router.N
+        d.router_rm = router_rm.data_ptr()
+        if rank > 0:
+            ptrs = [torch.tensor(rm_gu, dtype=torch.int64, device=device), torch.tensor(rm_d, dtype=torch.int64, device=device)]
+            self._keep += ptrs
+            d.ut_rm_gate_up, d.ut_rm_down = ptrs[0].data_ptr(), ptrs[1].data_ptr()
         tabs = [_table(gate_up, device), _table(down, device)]
         d.gate_up, d.down = tabs[0].data_ptr(), tabs[1].data_ptr()
         if rank > 0:
@@ -201,6 +211,9 @@ class GraphCompatibleMoeBlock(nn.Module):
                 uts = [tiled.tiled_ut(lin.U) for lin in (sg, su, sd)]
                 self._keep += uts
                 d.sh_ut_gate, d.sh_ut_up, d.sh_ut_down = (u.codes.data_ptr() for u in uts)
+                sd_rm = tiled.rowmajor_ut(sd.U)
+                self._keep.append(sd_rm)
+                d.sh_ut_rm_down = sd_rm.data_ptr()
             if fmt == FMT_T2:
                 d.sh_rot_mid, d.sh_rht_mid = self._rotation(sd, device)
         self._desc = d
@@ -250,6 +263,10 @@ class GraphCompatibleMoeBlock(nn.Module):
         d = self._desc
         if d is None:
             return 0
+        if self.gate is not None and _lib.lib().glq_moe_uses_fused_kernel(C.byref(d), 1):
+            if self._ep[1] == 1:
+                return 1                                                   # the persistent kernel, combine included
+            return 2 + (1 if self.peer_exchange_max_tokens > 0 else 0)    # persistent kernel, (exchange,) combine
         n = 2 + (4 if d.rank > 0 else 2) + 1
         if self.gate is None:
             n -= 1

@@ -208,8 +208,24 @@ def tiled_ut(U: torch.Tensor) -> TiledWeight:
     return tw
 
 
+_UT_RM_POOL: Dict[Tuple[int, int, int, int], torch.Tensor] = {}
+
+
+def rowmajor_ut(U: torch.Tensor) -> torch.Tensor:
+    """U^T of a shared (K, r) factor as a plain row-major (r, K) fp16 tensor, one copy per distinct storage:
+    the operand of the persistent decode kernel's dense row tasks (one warp per row of U^T)."""
+    key = (U.device.index or 0, U.data_ptr(), U.shape[0], U.shape[1])
+    t = _UT_RM_POOL.get(key)
+    if t is None:
+        t = U.to(torch.float16).t().contiguous()
+        t._keep = U
+        _UT_RM_POOL[key] = t
+    return t
+
+
 def clear_pool():
     _UT_POOL.clear()
+    _UT_RM_POOL.clear()
 
 
 # ---- workspaces ------------------------------------------------------------------------------

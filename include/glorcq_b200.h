@@ -265,8 +265,24 @@ typedef struct glq_moe_desc {
     /* the same three rotations as randomized Hadamard transforms: (dim,) fp32 sign vectors, or NULL; a sign
      * vector takes precedence over the dense matrix of the same position (scale 1/sqrt(dim)) */
     const float* rht_in; const float* rht_mid; const float* sh_rht_mid;
+    /* Optional plain row-major fp16 copies of the dense operands.  With them (and 2/4-bit integer codes, up to 4
+     * tokens, the block's own router) the whole block up to the per-entry down outputs runs as ONE persistent
+     * cooperative kernel instead of nine launches; all NULL: the launches above.  router_rm: the rows of router_t
+     * (dense0_rows x H).  ut_rm_gate_up / ut_rm_down: device arrays of 2E / E pointers to U^T (rank x H / rank x I)
+     * in the order of ut_gate_up / ut_down.  sh_ut_rm_down: U^T (rank x I_shared) of the shared down projection
+     * (needed only when the shared expert has a low-rank term). */
+    const void* router_rm;
+    const void* const* ut_rm_gate_up;
+    const void* const* ut_rm_down;
+    const void* sh_ut_rm_down;
 } glq_moe_desc_t;
 
+/* 1 when a call with this descriptor and token count (and the block's own router) runs the persistent kernel */
+int glq_moe_uses_fused_kernel(const glq_moe_desc_t* d, int n_tokens);
+/* Diagnostic: with GLQ_FUSED_TRACE set in the environment, thread 0 of every CTA of the persistent kernel stamps
+ * the GPU's global timer (ns) after each of its steps; this copies the stamps of the last launch ([CTA][16]
+ * words, followed by the final values of the kernel's arrival counters; n_words <= 4352) to the host.  Synchronise first. */
+int glq_moe_fused_trace(unsigned long long* out, int n_words);
 size_t glq_moe_workspace_bytes(const glq_moe_desc_t* d, int n_tokens);
 size_t glq_moe_counters(const glq_moe_desc_t* d, int n_tokens);
 /* x (n_tokens, H) fp16 -> out (n_tokens, H) fp16; router_logits (n_tokens, E) fp16 may be NULL.
