@@ -367,6 +367,57 @@ def lm_head_roofline(dev, peak_gbs, V=151936, H=2048, iters=30):
             "kernel": "lm_head_kernel (fp16 GEMV + arg-max)", "problems": f"{V} x {H} fp16, 1 row; {nbytes / 1e6:.0f} MB > L2"}
 
 
+def dropins_vs_reference(dev, P=240):
+    """The drop-in GEMV entry points beside the reference's own CUDA kernels built for this GPU (oracle/_ref, when
+    present): P distinct C1-shaped problems (one row each; the weights of all of them exceed L2), each arm
+    captured as one CUDA graph of P calls and replayed; microseconds per call."""
+    from oracle import build_ref
+    import glorcq_b200.kernels as GK
+    rt, rg = build_ref.load_module("ref_turbo_matmul_cuda"), build_ref.load_module("ref_gptq_matmul_cuda")
+    if rt is None or rg is None:
+        return {"unavailable": "oracle/_ref holds no build of the reference's kernels (python oracle/build_ref.py)"}
+    N, K = 1408, 2048
+    g = torch.Generator(device=dev)
+    g.manual_seed(21)
+    packed = torch.randint(0, 256, (P, N, K // 4), generator=g, device=dev, dtype=torch.int32).to(torch.uint8)
+    norms = torch.rand(P, N, generator=g, device=dev) + 0.1
+    cent = torch.sort(torch.randn(4, generator=g, device=dev))[0] * 0.05
+    q8 = torch.randint(0, 4, (P, N, K), generator=g, device=dev, dtype=torch.int32).to(torch.int8)
+    sc = (torch.randn(P, N, K // 128, generator=g, device=dev) * 0.02).abs().half()
+    zr = torch.randint(0, 4, (P, N, K // 128), generator=g, device=dev).half()
+    xh = torch.randn(1, K, generator=g, device=dev).half()
+    xf = xh.float()
+    empty = torch.empty(0, device=dev)
+
+    def timed(fn):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for i in range(3):
+                fn(i)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(P):
+                fn(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (5 * P) * 1e3
+    out = {"problems": f"{P} x (1408x2048), 1 row, distinct weights > L2, CUDA graph of {P} calls",
+           "turbo_gemv_us": {"ours": timed(lambda i: GK.turbo_dequant_matmul(xh, packed[i], norms[i], cent)),
+                             "reference": timed(lambda i: rt.turbo_dequant_matmul(xh, packed[i], norms[i], cent))},
+           "gptq_gemv_us": {"ours": timed(lambda i: GK.gptq_dequant_matmul(xf, q8[i], sc[i], zr[i], 128, False, empty)),
+                            "reference": timed(lambda i: rg.gptq_dequant_matmul(xf, q8[i], sc[i], zr[i], 128, False, empty))}}
+    return out
+
+
 def _stage(rank, what):
     if os.environ.get("GLQ_BENCH_VERBOSE"):
         print(f"[bench rank {rank}] {what}", file=sys.stderr, flush=True)
@@ -544,6 +595,10 @@ def run_ours(args, rank, world, local_rank):
         if not args.no_extras:
             extras["roofline_gemm"] = gemm_roofline(dev)
             extras["roofline_lm_head"] = lm_head_roofline(dev, peak, cfg["vocab_size"], cfg["hidden_size"])
+            try:
+                extras["dropins_vs_reference_kernels"] = dropins_vs_reference(dev)
+            except Exception as exc:      # noqa: BLE001 - a side leg must not take the line down
+                extras["dropins_vs_reference_kernels"] = {"unavailable": repr(exc)[:200]}
         cpu = None
         if world == 1:      # the CPU leg is timed at N = 1 only
             sec_tok, threads, reps = CpuToken(cfg, prompt).seconds(8.0, 100)

@@ -663,6 +663,9 @@ bool plan_fused(const glq_moe_desc_t* d, int n, FusedParams* out, size_t* smem_b
     const size_t cap = 227 * 1024;
     if (off + (size_t)kFSW * P.stage_bytes > cap) return false;
     P.stages = (int)std::min<size_t>((cap - off) / ((size_t)kFSW * P.stage_bytes), 3);
+    // long reductions (an intermediate size in the ten thousands) leave room for one stage only: without a second
+    // one nothing overlaps the copies, and the separate launches with their deeper rings stream better
+    if (P.stages < 2) return false;
     *smem_bytes = off + (size_t)kFSW * P.stages * P.stage_bytes;
     // dense warps sharing one row of the shared down projection's U^T: segments of at most 2048 channels
     P.s6_segs = 1;

@@ -117,6 +117,7 @@ struct ExpertPtrs {
 
 struct FusedPlan {
     int n_valid, n_slots, dead, pad;
+    unsigned sel_mask[8];    // experts chosen by any token (E <= 256)
     int sel[kFMaxEntries];
     __half wts[kFMaxEntries];
     int entry_tok[kFMaxEntries];
@@ -439,92 +440,80 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
             }
         }
         // ---------------- S3: routing plan (every CTA for itself) ----------------
+        // Every dense warp polls the router's counter for itself (no barrier before the routing); warp dw routes
+        // token dw alone; one barrier; then one thread per (token, slot) places its entry and, for the first
+        // entry of an expert, the slot.
+        for (int i = dt; i < kFMaxEntries * kFRows; i += kDT) (&plan.slot_tok_entry[0][0])[i] = -1;
+        if (dt == 0) plan.n_slots = 0;
+        if (dt < 8) plan.sel_mask[dt] = 0u;
         dense_barrier();
-        if (dt == 0 && !flag_wait(flags + FL_R, p.dense_rows, p.wait_ns, 201)) plan.dead = 1;
-        dense_barrier();
-        dead = dead || plan.dead != 0;
+        {
+            int ok = 1;
+            if (lane == 0) ok = flag_wait(flags + FL_R, p.dense_rows, p.wait_ns, 201) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) dead = true, plan.dead = 1;
+        }
         trace(2);
         {
             const int k = p.k, nk = n * k, E = p.E;
             constexpr int kProbLd = 256 + 16;
-            // (a) probabilities of token dw by warp dw
-            if (dw < n) softmax_token(p.logits + (size_t)dw * p.ldl, E, lane, prob + dw * kProbLd);
-            dense_barrier();
-            // (b) rank of every (token, expert): the number of experts that beat it; rank < k is selected as slot `rank`
-            for (int q = dt; q < n * E; q += kDT) {
-                const int tok = q / E, e = q - tok * E;
-                const float* pr = prob + tok * kProbLd;
-                const float pe = pr[e];
-                int rank = 0;
+            if (dw < n) {
+                // probabilities, then ranks: an expert's rank is the number of experts that beat it (ties to the lower
+                // index); rank < k is selected as slot `rank`; the weights are the selected probabilities, optionally
+                // divided by their sum taken in selection order (the arithmetic of moe_plan_kernel)
+                float* pr = prob + dw * kProbLd;
+                softmax_token(p.logits + (size_t)dw * p.ldl, E, lane, pr);
+                __syncwarp();
+                for (int e = lane; e < E; e += 32) {
+                    const float pe = pr[e];
+                    int rank = 0;
 #pragma unroll 4
-                for (int j = 0; j < E; ++j) {
-                    const float pj = pr[j];
-                    rank += (pj > pe || (pj == pe && j < e)) ? 1 : 0;
+                    for (int j = 0; j < E; ++j) {
+                        const float pj = pr[j];
+                        rank += (pj > pe || (pj == pe && j < e)) ? 1 : 0;
+                    }
+                    if (rank < k) {
+                        plan.sel[dw * k + rank] = e;
+                        pr[256 + rank] = pe;
+                        atomicOr(&plan.sel_mask[e >> 5], 1u << (e & 31));
+                    }
                 }
-                if (rank < k) {
-                    plan.sel[tok * k + rank] = e;
-                    prob[tok * kProbLd + 256 + rank] = pe;
+                __syncwarp();
+                if (lane < k) {
+                    float wsum = 0.f;
+                    for (int s = 0; s < k; ++s) wsum += pr[256 + s];
+                    const float pe = pr[256 + lane];
+                    plan.wts[dw * k + lane] = __float2half_rn(p.renorm ? pe / wsum : pe);
                 }
             }
             dense_barrier();
-            // (c) weights: the selected probabilities, optionally divided by their sum taken in selection order
-            if (dt < nk) {
-                const int tok = dt / k;
-                const float* tp = prob + tok * kProbLd + 256;
-                float wsum = 0.f;
-                for (int s = 0; s < k; ++s) wsum += tp[s];
-                const float pe = tp[dt - tok * k];
-                plan.wts[dt] = __float2half_rn(p.renorm ? pe / wsum : pe);
-            }
-            dense_barrier();
-            // entries grouped by expert (ascending), in token order within an expert: every rank numbers them alike
+            // entries grouped by expert (ascending), in token order within an expert: every rank numbers them alike;
+            // slots: the experts of this rank among them, in the same order
             if (dt < nk) {
                 const int e = plan.sel[dt];
-                const bool ok = e >= 0 && e < E;
-                int pos = 0, nv = 0;
+                int pos = 0, cnt = 0, slot = 0, first = 1;
                 for (int j = 0; j < nk; ++j) {
                     const int ej = plan.sel[j];
-                    if (ej < 0 || ej >= E) continue;
-                    ++nv;
-                    if (ej < e || (ej == e && j < dt)) ++pos;
+                    pos += (ej < e || (ej == e && j < dt)) ? 1 : 0;
+                    cnt += ej == e ? 1 : 0;
+                    first &= !(ej == e && j < dt);
                 }
-                if (ok) {
-                    plan.entry_tok[pos] = dt / k;
-                    plan.entry_e[pos] = e;
-                    plan.entry_w[pos] = plan.wts[dt];
-                    plan.tok_entry[dt] = pos;
-                } else {
-                    plan.tok_entry[dt] = -1;
-                }
-                if (dt == 0) plan.n_valid = nv;
-            }
-            dense_barrier();
-            // slots: runs of one expert among the entries, those of this rank's experts only; one thread per entry
-            {
-                const int nv = plan.n_valid;
-                if (dt < nv) {
-                    const int e = plan.entry_e[dt];
-                    const bool head = dt == 0 || plan.entry_e[dt - 1] != e;
-                    const bool local = e % p.ep_world == p.ep_rank;
-                    int before = 0, total = 0;
-                    for (int q = 0; q < nv; ++q) {
-                        const int eq = plan.entry_e[q];
-                        const bool hq = (q == 0 || plan.entry_e[q - 1] != eq) && (eq % p.ep_world == p.ep_rank);
-                        total += hq ? 1 : 0;
-                        before += (hq && q < dt) ? 1 : 0;
+                // this rank's chosen experts below e
+                for (int e2 = p.ep_rank; e2 < e; e2 += p.ep_world) slot += (plan.sel_mask[e2 >> 5] >> (e2 & 31)) & 1u;
+                plan.entry_tok[pos] = dt / k;
+                plan.entry_e[pos] = e;
+                plan.entry_w[pos] = plan.wts[dt];
+                plan.tok_entry[dt] = pos;
+                if (e % p.ep_world == p.ep_rank) {
+                    plan.slot_tok_entry[slot][dt / k] = pos;
+                    if (first) {
+                        plan.slot_e[slot] = e;
+                        plan.slot_off[slot] = pos;
+                        plan.slot_cnt[slot] = cnt;
+                        atomicAdd(&plan.n_slots, 1);
                     }
-                    if (head && local) {
-                        int c = 1;
-                        while (dt + c < nv && plan.entry_e[dt + c] == e) ++c;
-                        plan.slot_e[before] = e;
-                        plan.slot_off[before] = dt;
-                        plan.slot_cnt[before] = c;
-#pragma unroll
-                        for (int tt = 0; tt < kFRows; ++tt) plan.slot_tok_entry[before][tt] = -1;
-                        for (int i = 0; i < c; ++i) plan.slot_tok_entry[before][plan.entry_tok[dt + i]] = dt + i;
-                    }
-                    if (dt == 0) plan.n_slots = total;
                 }
+                if (dt == 0) plan.n_valid = nk;
             }
         }
         // the plan is published to this CTA's stream warps (the routed CTAs' wait for it before their products, the

@@ -220,7 +220,7 @@ class GLoRCQDecoder(nn.Module):
             self.ln2.append(dense_param(f"{pre}.post_attention_layernorm.weight", (H,)))
             self.attn.append(_Attention(c, l, mods, dense, pre, dev))
             mp, (gn, un, dn) = c.moe_prefix, c.expert_names
-            if f"{mp}.experts.0.{gn}" in mods:
+            if any(k.startswith(f"{mp}.experts.") for k in mods):     # (with expert parallelism: this rank's experts only)
                 blk = SimpleNamespace()
                 blk.num_experts, blk.top_k, blk.norm_topk_prob = c.num_experts, c.num_experts_per_tok, c.norm_topk_prob
                 blk.gate = nn.Linear(H, c.num_experts, bias=False, device=dev, dtype=torch.float16)

@@ -29,6 +29,28 @@ def _empty_lora(device):
     return _empty_tensor_cache[key]
 
 
+_int8_cache: dict = {}
+
+
+def _int8_codes(qweight_int):
+    """int8 copy of an (N, K) code tensor, made once per tensor (the reference converts on every call,
+    inference/kernels/__init__.py:305-309).  The cache holds a weak reference to the source: an entry dies with it,
+    and a tensor whose storage or version changed is converted again."""
+    import weakref
+    if qweight_int.dtype == torch.int8:
+        return qweight_int
+    key = id(qweight_int)
+    hit = _int8_cache.get(key)
+    if hit is not None:
+        ref, ptr, ver, q8 = hit
+        if ref() is qweight_int and ptr == qweight_int.data_ptr() and ver == qweight_int._version:
+            return q8
+    q8 = qweight_int.to(torch.int8)
+    _int8_cache[key] = (weakref.ref(qweight_int, lambda _r, k=key: _int8_cache.pop(k, None)), qweight_int.data_ptr(),
+                        qweight_int._version, q8)
+    return q8
+
+
 def _available() -> bool:
     try:
         _lib.lib()
@@ -175,6 +197,30 @@ except Exception as e:  # pragma: no cover - registration is optional
     _turbo_dequant_matmul_op = turbo_dequant_matmul
     _gptq_dequant_matmul_op = gptq_dequant_matmul
 
+# The reference registers its ops as ``glorcq::turbo_dequant_matmul`` / ``glorcq::gptq_dequant_matmul``
+# (inference/kernels/__init__.py:69, 88); code that calls ``torch.ops.glorcq.*`` binds to this package the same
+# way, unless the reference package itself has been imported in this process and owns the names.
+try:
+    @torch.library.custom_op("glorcq::turbo_dequant_matmul", mutates_args=())
+    def _ref_name_turbo(x_rot: torch.Tensor, packed_indices: torch.Tensor, norms: torch.Tensor,
+                        centroids: torch.Tensor) -> torch.Tensor:
+        return turbo_dequant_matmul(x_rot, packed_indices, norms, centroids)
+
+    @_ref_name_turbo.register_fake
+    def _ref_name_turbo_fake(x_rot, packed_indices, norms, centroids):
+        return torch.empty(x_rot.shape[0], packed_indices.shape[0], dtype=torch.float16, device=x_rot.device)
+
+    @torch.library.custom_op("glorcq::gptq_dequant_matmul", mutates_args=())
+    def _ref_name_gptq(x: torch.Tensor, qweight_i8: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
+                       groupsize: int, sym: bool, lora_out: torch.Tensor) -> torch.Tensor:
+        return gptq_dequant_matmul(x, qweight_i8, scales, zeros, groupsize, sym, lora_out)
+
+    @_ref_name_gptq.register_fake
+    def _ref_name_gptq_fake(x, qweight_i8, scales, zeros, groupsize, sym, lora_out):
+        return torch.empty(x.shape[0], qweight_i8.shape[0], dtype=torch.float32, device=x.device)
+except Exception as e:  # pragma: no cover - the names are taken when the reference package is loaded too
+    logger.debug("glorcq:: op names not registered: %s", e)
+
 
 # ---------------------------------------------------------------------------------------------
 # Public API: codebook format
@@ -212,7 +258,7 @@ def turbo_dequant_grouped_gemv_fused(x_grouped, packed_cat, norms_cat, centroids
 def gptq_dequant_matmul_fused(x, qweight_int, scales, zeros, groupsize, sym=False, lora_USV=None):
     """int32 -> int8 codes if needed, optional Python-level low-rank term, fused dequant + matmul.
     Returns (B,N) fp16 (inference/kernels/__init__.py:284-346)."""
-    qweight_i8 = qweight_int if qweight_int.dtype == torch.int8 else qweight_int.to(torch.int8)
+    qweight_i8 = _int8_codes(qweight_int)
     lora_out = _empty_lora(x.device)
     if lora_USV is not None:
         U, S, V = lora_USV

@@ -25,6 +25,8 @@ import os
 import sys
 from typing import Dict, Optional, Tuple
 
+import logging
+
 import torch
 
 from .quantized_linear import GLoRCQLinear
@@ -254,9 +256,15 @@ def build_layers(model_config, layers_data, cross_layer_info, device="cuda", rot
                 if rotation_cache is None:
                     raise RuntimeError("codebook-format layers need a RotationCache")
                 ql.load_turbo(packed, rotation_cache, device=device)
+            elif "weight_quant" in packed:
+                # pre-dequantised weights: kept dense (inference/model_builder.py:386-415 loads them the same way)
+                out_f, in_f = packed["weight_quant"].shape
+                ql = GLoRCQLinear(in_f, out_f)
+                ql.load_dense(packed["weight_quant"], device=device, quant_type=packed.get("quant_method", "dense"))
             else:
-                raise RuntimeError(f"layer {layer_idx} module {module_name}: pre-dequantised weights "
-                                   f"({sorted(packed)}) have no packed form to run from")
+                # unknown record: the reference leaves the original (zero-initialised) layer in place
+                logger.warning("layer %s module %s: unknown record %s, skipped", layer_idx, module_name, sorted(packed))
+                continue
             _load_lora_for_module(ql, layer_idx, module_name, lookup, u_cache, per_expert_V, uv_bits, device,
                                   sv_bits=sv_bits)
             if biases and (layer_idx, module_name) in biases:

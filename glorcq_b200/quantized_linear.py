@@ -64,6 +64,8 @@ class GLoRCQLinear(nn.Module):
 
         # device layout of the kernels
         self._tiled = None           # TiledWeight
+        self._dense = None           # TiledWeight of pre-dequantised fp16 weights (load_dense)
+        self._sv_dense = None        # TiledWeight of SV for the dense route
         self._ut = None              # TiledWeight of U^T (shared through tiled.tiled_ut)
 
     # ---- loaders (inference/quantized_linear.py:195-269) ---------------------------------
@@ -106,6 +108,29 @@ class GLoRCQLinear(nn.Module):
         self._tiled = TiledWeight.from_turbo(self.packed_indices, self.norms, centroids.to(device))
         self._sync_tiled()
 
+    def load_dense(self, weight, device="cuda", quant_type="dense"):
+        """Pre-dequantised fp16 weights (``weight_quant`` records of a checkpoint,
+        inference/model_builder.py:386-415): kept dense, run through the dense fp16 kernels."""
+        self.quant_type = quant_type
+        W = weight.to(device=device, dtype=torch.float16).contiguous()
+        self._turbo_dequant_W = W
+        self._dense = TiledWeight.from_dense(W)
+        self._tiled = None
+        self._sync_tiled()
+
+    def load_turbo_predequant(self, compressed_data, turbo_quantizer, device="cuda"):
+        """Legacy route of the reference (inference/quantized_linear.py:229-247): the codebook weights are
+        dequantised once by the quantizer that produced them (a third-party object with a
+        ``dequantize(MSEQuantized(indices, norms, bits))`` method) and cached as dense fp16; forward is then
+        x . W^T on the unrotated input."""
+        from collections import namedtuple
+        self.turbo_bits = compressed_data["bits"]
+        self.turbo_dim = compressed_data["dim"]
+        MSEQuantized = namedtuple("MSEQuantized", ["indices", "norms", "bits"])
+        q = MSEQuantized(indices=compressed_data["packed_indices"].to(device), norms=compressed_data["norms"].to(device),
+                         bits=compressed_data["bits"])
+        self.load_dense(turbo_quantizer.dequantize(q), device=device, quant_type="turbo")
+
     def load_lora(self, U, S, V, device="cuda"):
         """Old format: pre-fuse S into V (inference/quantized_linear.py:249-259)."""
         if U is not None:
@@ -130,6 +155,10 @@ class GLoRCQLinear(nn.Module):
 
     def _sync_tiled(self):
         if self._tiled is None:
+            if self._dense is not None:
+                ok = self.U is not None and self.SV is not None
+                self._ut = tiled.tiled_ut(self.U) if ok else None
+                self._sv_dense = TiledWeight.from_dense(self.SV.contiguous()) if ok else None
             return
         if self.SV is not None:
             self._tiled.put_sv(0, self.SV)
@@ -154,8 +183,19 @@ class GLoRCQLinear(nn.Module):
         Pi = self._rotation_cache.get_pi(self.turbo_dim, self.turbo_bits, self.turbo_seed)
         return (x.float() @ Pi.float().T).half()
 
+    def _forward_dense(self, x, a):
+        y = tiled.dense_matmul(self._dense, x)
+        if self.SV is not None:
+            if a is None:
+                a = tiled.dense_matmul(self._ut, x)
+            y = y + tiled.dense_matmul(self._sv_dense, a.contiguous())
+        if self.bias_param is not None:
+            y = y + self.bias_param
+        return y
+
     def forward(self, x, precomputed_xU=None, precomputed_x_rot=None):
         orig_shape = x.shape
+        in_dtype = x.dtype
         if x.dim() != 2:
             x = x.reshape(-1, self.in_features)
         if x.dtype != torch.float16:
@@ -165,7 +205,9 @@ class GLoRCQLinear(nn.Module):
         if precomputed_xU is not None and self.SV is not None:
             a = precomputed_xU.reshape(-1, self.SV.shape[1]).to(torch.float16)
 
-        if self.quant_type == "gptq":
+        if self._tiled is None and self._dense is not None:
+            y = self._forward_dense(x, a)
+        elif self.quant_type == "gptq":
             if self._tiled is not None:
                 y = tiled.linear_forward(self._tiled, x, ut=self._ut, a=a)
             else:
@@ -195,7 +237,8 @@ class GLoRCQLinear(nn.Module):
 
         if len(orig_shape) != 2:
             y = y.reshape(*orig_shape[:-1], self.out_features)
-        return y
+        # the kernels compute in fp16; other floating-point inputs get their own dtype back
+        return y if in_dtype == torch.float16 or not in_dtype.is_floating_point else y.to(in_dtype)
 
     def extra_repr(self):
         s = f"in_features={self.in_features}, out_features={self.out_features}, quant_type={self.quant_type}"

@@ -99,6 +99,25 @@ def test_build_layers_matches_oracle(dev, fmt):
     assert cases.rel_l2(ql(x.to(dev)).cpu(), O.linear_forward(oq, x)) <= 1e-3
 
 
+def test_build_layers_dense_and_unknown_records(dev):
+    """A ``weight_quant`` record (pre-dequantised weights) loads as a dense layer with its low-rank factors, an
+    unknown record is skipped, as the reference's loader does (inference/model_builder.py:380-415)."""
+    from glorcq_b200 import model_builder as MB
+    from glorcq_b200 import synthetic
+    md, cr, _ = synthetic.make_checkpoint(CFG, seed=23, rank=16, attn_rank=32, n_clusters=3, u_format="fp16", sv_format="fp16")
+    rec = md["layers"][0]["self_attn.o_proj"]
+    W = O.gptq_tile_fp16(rec["qweight_int"], rec["scales"], rec["zeros"], rec["groupsize"])
+    md["layers"][0]["self_attn.o_proj"] = {"weight_quant": W, "quant_method": "rtn"}
+    md["layers"][0]["mlp.experts.0.up_proj"] = {"something_else": torch.zeros(1)}
+    layers, _ = MB.build_layers(md["model_config"], md["layers"], cr, device=dev)
+    assert "mlp.experts.0.up_proj" not in layers[0]
+    ql = layers[0]["self_attn.o_proj"]
+    assert ql.quant_type == "rtn" and ql.SV is not None
+    x = cases.make_x(6, 3, 256)
+    oq = O.checkpoint_layers({"model_config": md["model_config"], "layers": {0: {"self_attn.o_proj": rec}}}, cr)[0]["self_attn.o_proj"]
+    assert cases.rel_l2(ql(x.to(dev)).cpu(), O.linear_forward(oq, x)) <= 1e-3
+
+
 @pytest.mark.parametrize("cache_len", [32, 320])     # 320: the decode attention splits the positions over CTAs
 @pytest.mark.parametrize("cfg", [CFG, MIXTRAL, QWEN3], ids=["qwen2moe", "mixtral", "qwen3moe"])
 def test_decoder_logits_prefill_and_decode(dev, cfg, cache_len):

@@ -259,3 +259,51 @@ def test_gptq_i8_dropin(dev, B, N, K, sym, lora):
         yh = GK.gptq_dequant_matmul_fused(x.half().to(dev), d["qweight_int"].to(dev), d["scales"].to(dev),
                                           d["zeros"].to(dev), 128, sym)
         assert yh.dtype == torch.float16
+
+
+# ---- routes around the packed formats ----------------------------------------------------------------
+def test_dense_weight_route_dtype_and_reference_op_names(dev):
+    """Pre-dequantised weights (a checkpoint's ``weight_quant`` records and the legacy load_turbo_predequant)
+    run dense through the fp16 kernels with the low-rank term; a bf16 / fp32 input gets its own dtype back;
+    the reference's custom-op names ``torch.ops.glorcq.*`` bind to this package's kernels."""
+    from glorcq_b200.quantized_linear import GLoRCQLinear
+    import glorcq_b200.kernels as GK
+    g = torch.Generator().manual_seed(77)
+    N, K, r = 96, 256, 16
+    W = (torch.randn(N, K, generator=g) * 0.05).half()
+    U = (torch.randn(K, r, generator=g) * 0.01).half()
+    SV = (torch.randn(N, r, generator=g) * 0.01).half()
+    x = cases.make_x(78, 5, K)
+    ref = (x.float() @ W.float().T + (x.float() @ U.float()) @ SV.float().T)
+    lin = GLoRCQLinear(K, N)
+    lin.load_dense(W, device=dev)
+    lin.load_sv(U.to(dev), SV, device=dev)
+    y = lin(x.to(dev))
+    assert y.dtype == torch.float16 and cases.rel_l2(y.cpu(), ref) <= REL
+    for dt in (torch.bfloat16, torch.float32):
+        assert lin(x.to(dev).to(dt)).dtype == dt
+    d = cases.make_linear(79, N, K, rank=r)
+    assert cases.to_b200_linear(d, dev)(x.to(dev).float()).dtype == torch.float32
+
+    class _Quantizer:                      # stands in for the third-party quantizer object
+        def dequantize(self, q):
+            assert q.bits == 2 and q.indices.shape == (N, K // 4)
+            return W.to(q.indices.device)
+    lin2 = GLoRCQLinear(K, N)
+    lin2.load_turbo_predequant({"packed_indices": torch.zeros(N, K // 4, dtype=torch.uint8), "norms": torch.ones(N),
+                                "bits": 2, "dim": K}, _Quantizer(), device=dev)
+    assert lin2.quant_type == "turbo" and cases.rel_l2(lin2(x.to(dev)).cpu(), x.float() @ W.float().T) <= REL
+
+    t = cases.make_linear(80, 72, 256, fmt="turbo", with_lora=False)
+    y1 = torch.ops.glorcq.turbo_dequant_matmul(x.to(dev), t["packed_indices"].to(dev), t["norms"].to(dev), t["centroids"].to(dev))
+    assert cases.rel_l2(y1.cpu(), O.turbo_matmul(x, t["packed_indices"], t["norms"], t["centroids"])) <= REL
+    q = cases.make_linear(81, 64, 256, fmt="gptq", with_lora=False, signed_codes=True)
+    q32 = q["qweight_int"].to(dev)
+    y2 = torch.ops.glorcq.gptq_dequant_matmul(x.float().to(dev), q32.to(torch.int8), q["scales"].to(dev), q["zeros"].to(dev), 128,
+                                              False, torch.empty(0, device=dev))
+    assert cases.rel_l2(y2.cpu(), O.gptq_matmul(x.float(), q["qweight_int"], q["scales"], q["zeros"], 128, False, None)) <= 1e-5
+    # the int8 copy of int32 codes is made once per tensor, and again after the tensor changed
+    a8 = GK._int8_codes(q32)
+    assert GK._int8_codes(q32) is a8
+    q32 += 0
+    assert GK._int8_codes(q32) is not a8
