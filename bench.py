@@ -511,6 +511,16 @@ def run_ours(args, rank, world, local_rank):
         return tok
 
     window(W)
+    if args.profile_window:
+        # for `ncu --profile-from-start off`: one window of K steps between cudaProfilerStart / Stop, nothing else
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        window(K)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        if rank == 0:
+            print(json.dumps({"profile_window": {"steps": K, "launches_per_token": launches_per_token(model)}}), flush=True)
+        return
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -711,6 +721,9 @@ def main():
                     help="time only the grouped tcgen05 dequant-GEMM roofline case (small enough for an ncu capture)")
     ap.add_argument("--lm-head-only", action="store_true", help="time only the output projection kernel")
     ap.add_argument("--moe-only", action="store_true", help="time only the MoE blocks of the model (moe_only of the line)")
+    ap.add_argument("--profile-window", action="store_true",
+                    help="run one window of --steps tokens between cudaProfilerStart and cudaProfilerStop and exit "
+                         "(for ncu --profile-from-start off)")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMM / lm_head roofline legs and moe_only")
     ap.add_argument("--rows", type=int, default=2048)
     ap.add_argument("--problems", type=int, default=240)

@@ -856,16 +856,38 @@ extern "C" int glq_gptq_dequant_matmul(const float* x, const int8_t* q, const vo
         return GLQ_ERR_ALIGN;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const size_t smem = (size_t)K * sizeof(float);
-    for (int b0 = 0; b0 < B; b0 += 4) {
-        const int nb = std::min(4, B - b0);
+    // activation rows per pass over the codes: up to 8, as many as the staged rows leave room for (one pass for a
+    // decode batch; a long prompt re-reads the int8 matrix once per 8 rows)
+    int per = 8;
+    while (per > 1 && smem * per > 200 * 1024) per /= 2;
+    if (smem > 200 * 1024) return GLQ_ERR_UNSUPPORTED;
+    static size_t configured[2][64] = {{0}, {0}};
+    int dev = 0;
+    GLQ_CUDA(cudaGetDevice(&dev));
+    for (int b0 = 0; b0 < B; b0 += per) {
+        const int nb = std::min(per, B - b0);
+        const int wide = nb > 4 ? 1 : 0;
         const dim3 grid(cdiv(N, kWarpsPerCta));
-        if (smem * nb > 48 * 1024) {
-            GLQ_CUDA(cudaFuncSetAttribute(gptq_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)(smem * 4)));
+        const size_t need = smem * nb;
+        if (need > 48 * 1024 && (dev < 0 || dev >= 64 || configured[wide][dev] < need)) {
+            if (wide)
+                GLQ_CUDA(cudaFuncSetAttribute(gptq_i8_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem * per)));
+            else
+                GLQ_CUDA(cudaFuncSetAttribute(gptq_i8_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)(smem * std::min(per, 4))));
+            if (dev >= 0 && dev < 64) configured[wide][dev] = wide ? smem * per : smem * std::min(per, 4);
         }
-        gptq_i8_kernel<<<grid, kThreads, smem * nb, st>>>(
-            x + (size_t)b0 * K, q, reinterpret_cast<const __half*>(scales), reinterpret_cast<const __half*>(zeros),
-            lora_out ? lora_out + (size_t)b0 * N : nullptr, y + (size_t)b0 * N, nb, N, K, groupsize, n_groups, sym);
+        const float* xb = x + (size_t)b0 * K;
+        const float* lb = lora_out ? lora_out + (size_t)b0 * N : nullptr;
+        float* yb = y + (size_t)b0 * N;
+        if (wide)
+            gptq_i8_kernel<8><<<grid, kThreads, need, st>>>(xb, q, reinterpret_cast<const __half*>(scales),
+                                                            reinterpret_cast<const __half*>(zeros), lb, yb, nb, N, K,
+                                                            groupsize, n_groups, sym);
+        else
+            gptq_i8_kernel<4><<<grid, kThreads, need, st>>>(xb, q, reinterpret_cast<const __half*>(scales),
+                                                            reinterpret_cast<const __half*>(zeros), lb, yb, nb, N, K,
+                                                            groupsize, n_groups, sym);
         GLQ_CUDA(cudaGetLastError());
     }
     return GLQ_OK;

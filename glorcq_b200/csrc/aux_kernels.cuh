@@ -167,9 +167,12 @@ __global__ void dequant_tiled_t2_kernel(const unsigned char* __restrict__ tiled,
 // ---------------------------------------------------------------------------------------------
 // Drop-in for the reference's int8-code GPTQ module (one byte per weight, arbitrary int8 codes,
 // fp32 activations and output): y[b,n] = sum_k (q - z) * s * x[b,k] (+ lora_out[b,n]).
-// One warp per output row, 16 codes per lane and step, activations in shared memory, NB <= 4 rows
-// of x per launch.
+// One warp per output row; a lane owns 16 consecutive codes of every 512-code step and requests up to
+// four steps' codes (64 bytes) before it consumes the first, so that a row's whole 2 KB .. 16 KB is in
+// flight at once; activations of NB <= 8 rows in shared memory (fp32); the group's scale and zero point
+// are looked up once per 16 codes (16 divides the group sizes in use; otherwise per code).
 // ---------------------------------------------------------------------------------------------
+template <int NB>
 __global__ void __launch_bounds__(kThreads) gptq_i8_kernel(const float* __restrict__ x, const int8_t* __restrict__ q,
                                                            const __half* __restrict__ scales,
                                                            const __half* __restrict__ zeros,
@@ -183,33 +186,52 @@ __global__ void __launch_bounds__(kThreads) gptq_i8_kernel(const float* __restri
     if (n >= N) return;
     const int8_t* qrow = q + (size_t)n * K;
     const bool vec = ((reinterpret_cast<uintptr_t>(qrow) & 15u) == 0) && (K % 16 == 0);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int k0 = lane * 16; k0 < K; k0 += 32 * 16) {
-        __align__(16) int8_t c[16];
-        if (vec) {
-            *reinterpret_cast<uint4*>(c) = __ldg(reinterpret_cast<const uint4*>(qrow + k0));
-        } else {
+    const bool group16 = groupsize % 16 == 0;
+    float acc[NB];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) c[j] = (k0 + j < K) ? qrow[k0 + j] : (int8_t)0;
+    for (int b = 0; b < NB; ++b) acc[b] = 0.f;
+    constexpr int kAhead = 4;
+    for (int k00 = lane * 16; k00 < K; k00 += kAhead * 32 * 16) {
+        __align__(16) int8_t c[kAhead][16];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            const int k0 = k00 + a * 32 * 16;
+            if (vec && k0 < K) {
+                *reinterpret_cast<uint4*>(c[a]) = __ldg(reinterpret_cast<const uint4*>(qrow + k0));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) c[a][j] = (k0 + j < K) ? qrow[k0 + j] : (int8_t)0;
+            }
         }
-        int gi = -1;
-        float sv = 0.f, zv = 0.f;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int k = k0 + j;
-            if (k < K) {
-                const int gk = k / groupsize;
-                if (gk != gi) {
-                    gi = gk;
-                    sv = __half2float(scales[(size_t)n * G + gi]);
-                    zv = sym ? 0.f : __half2float(zeros[(size_t)n * G + gi]);
+        for (int a = 0; a < kAhead; ++a) {
+            const int k0 = k00 + a * 32 * 16;
+            if (k0 >= K) break;
+            int gi = -1;
+            float sv = 0.f, zv = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int k = k0 + j;
+                if (k < K) {
+                    if (j == 0 || !group16) {
+                        const int gk = k / groupsize;
+                        if (gk != gi) {
+                            gi = gk;
+                            sv = __half2float(scales[(size_t)n * G + gi]);
+                            zv = sym ? 0.f : __half2float(zeros[(size_t)n * G + gi]);
+                        }
+                    }
+                    const float wv = ((float)c[a][j] - zv) * sv;
+#pragma unroll
+                    for (int b = 0; b < NB; ++b)
+                        if (b < nb) acc[b] = fmaf(wv, xsm[b * K + k], acc[b]);
                 }
-                const float wv = ((float)c[j] - zv) * sv;
-                for (int b = 0; b < nb; ++b) acc[b] = fmaf(wv, xsm[b * K + k], acc[b]);
             }
         }
     }
-    for (int b = 0; b < nb; ++b) {
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        if (b >= nb) break;
         const float v = warp_sum(acc[b]);
         if (lane == 0) y[(size_t)b * N + n] = v + (lora_out ? lora_out[(size_t)b * N + n] : 0.f);
     }

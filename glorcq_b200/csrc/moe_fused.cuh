@@ -134,7 +134,7 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
     return v;
 }
 // Bounded wait for an arrival counter, by one thread.  Returns false when the wait ran out.
-__device__ __forceinline__ bool flag_wait(const int* f, int target, unsigned long long limit_ns, int code) {
+__device__ __noinline__ bool flag_wait(const int* f, int target, unsigned long long limit_ns, int code) {
     if (ld_acquire(f) >= target) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
@@ -407,6 +407,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
             const __half* xr[kFRows];
 #pragma unroll
             for (int i = 0; i < kFRows; ++i) xr[i] = i < n ? p.x + (size_t)i * p.H : nullptr;
+#pragma unroll 1
             for (int task = cta + G * dw; task < p.dense_rows; task += G * kDW) {
                 float out[kFRows];
                 dense_row_dots(p.router_rm + (size_t)task * p.H, 0, p.H, xr[0], xr[1], xr[2], xr[3], lane, out);
@@ -527,6 +528,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
         // ---------------- S4: x.U of the routed gate / up clusters (all CTAs) ----------------
         if (p.R > 0) {
             const int tasks = n_slots * 2 * p.R;
+#pragma unroll 1
             for (int task = cta + G * dw; task < tasks; task += G * kDW) {
                 const int slot = task / (2 * p.R), rem = task - slot * 2 * p.R;
                 const int proj = rem / p.R, row = rem - proj * p.R;
@@ -576,6 +578,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
                 const int rows_per_cta = kDW / s6_segs;
                 bool waited = false;
                 float* rbuf = prob;      // idle after the plan
+#pragma unroll 1
                 for (int base = sub_cta * rows_per_cta; base < p.R; base += sub_G * rows_per_cta) {
                     if (!waited) warp_wait(flags + FL_HS, p.ph[0].npairs, 202), waited = true;
                     const int task = base + dw / s6_segs, seg = dw % s6_segs;
@@ -606,12 +609,14 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
             // ---------------- S8: h.U of the routed down clusters ----------------
             const int tasks = n_slots * p.R;
             // the U^T rows towards L2 while gate|up still runs
+#pragma unroll 1
             for (int task = sub_cta + sub_G * dw; task < tasks; task += sub_G * kDW) {
                 const int slot = task / p.R, row = task - slot * p.R;
                 const char* rowp = reinterpret_cast<const char*>(tab[plan.slot_e[slot]].ut_down + (size_t)row * p.I);
                 for (int off = lane * 128; off < p.I * 2; off += 32 * 128) prefetch_l2(rowp + off);
             }
             int waited_slot = -1;
+#pragma unroll 1
             for (int task = sub_cta + sub_G * dw; task < tasks; task += sub_G * kDW) {
                 const int slot = task / p.R, row = task - slot * p.R;
                 if (slot != waited_slot) warp_wait(flags + FL_H + slot, p.ph[1].npairs, 204), waited_slot = slot;
@@ -751,6 +756,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
         fetch_fill();       // shared chain: the gate|up codes of this warp, on their way before anything else
         trace(6);
         int red_par = 0, n_slots = 0;
+#pragma unroll 1
         for (int pi = 0; pi < 2; ++pi) {
             const int ph = pi ? ph_b : ph_a;
             const FusedPhase& P = p.ph[ph];
@@ -792,6 +798,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
             const int total = nslots_of(ph) * P.ipp;
             const int sk = P.sk;
             int staged_slot = -1;
+#pragma unroll 1
             for (int it = first_iter(ph); it < total; it += sub_G) {
                 Item im;
                 make_item(im, ph, it);
@@ -808,6 +815,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
                 }
                 float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};   // [tile in pair][weight row g / g+8], activation row t
                 if (im.valid) {
+#pragma unroll 1
                     for (int c = 0; c < im.ncode; ++c) {
                         const uint32_t st = ring_wait();
                         const int kb0 = im.kb_lo + c * kStreamCB;
@@ -882,6 +890,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
                 float lo[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 const int nsv = im.nch - im.ncode;
                 if (nsv > 0) warp_wait(a_flag_base + (per_slot_a ? im.slot : 0), a_target, 210 + ph);
+#pragma unroll 1
                 for (int c = 0; c < nsv; ++c) {
                     const uint32_t st = ring_wait();
                     const int cc0 = c * 64 + 16 * t;
@@ -981,16 +990,14 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
                 }
             const float gate = (p.ysh && p.gate_col >= 0)
                                    ? sigmoid16(__half2float(__ldcg(p.logits + (size_t)tok * p.ldl + p.gate_col))) : 1.f;
-            constexpr int kSteps = 3;      // 3 x 384 threads x 8 columns >= 8192
-            float val[kSteps][8];
+            // 384 threads x 8 columns per step
             float ss = 0.f;
-#pragma unroll
-            for (int step = 0; step < kSteps; ++step) {
-                const int c0 = (step * kST + tid) * 8;
-                if (c0 >= H) continue;
+#pragma unroll 1
+            for (int c0 = tid * 8; c0 < H; c0 += kST * 8) {
                 float acc[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 1
                 for (int s = 0; s < k; ++s) {
                     const int entry = plan.tok_entry[tok * k + order[s]];
                     if (entry < 0) continue;     // dropped slot
@@ -1014,8 +1021,7 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
                 __align__(16) __half o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    o[i] = __float2half_rn(acc[i]);
-                    val[step][i] = acc[i];
+                    o[i] = __float2half_rn(acc[i]);       // exact: the sums above are already rounded to fp16
                     ss += acc[i] * acc[i];
                 }
                 *reinterpret_cast<uint4*>(p.out + (size_t)tok * H + c0) = *reinterpret_cast<const uint4*>(o);
@@ -1030,15 +1036,15 @@ __global__ void __launch_bounds__(kFT, 1) moe_fused_kernel(const FusedParams p) 
 #pragma unroll
                 for (int i = 0; i < kFSW; ++i) tot += rs[i];
                 const float r = rsqrtf(tot / H + p.norm_eps);
-#pragma unroll
-                for (int step = 0; step < kSteps; ++step) {
-                    const int c0 = (step * kST + tid) * 8;
-                    if (c0 >= H) continue;
-                    __align__(16) __half o[8], wv[8];
+#pragma unroll 1
+                for (int c0 = tid * 8; c0 < H; c0 += kST * 8) {
+                    // this thread's own outputs of the loop above (fp16, exactly the summed values)
+                    __align__(16) __half v[8], o[8], wv[8];
+                    *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(p.out + (size_t)tok * H + c0);
                     if (p.norm_w) *reinterpret_cast<uint4*>(wv) = __ldg(reinterpret_cast<const uint4*>(p.norm_w + c0));
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const float nv = val[step][i] * r;
+                        const float nv = __half2float(v[i]) * r;
                         o[i] = __float2half_rn(p.norm_w ? __half2float(wv[i]) * nv : nv);
                     }
                     *reinterpret_cast<uint4*>(p.normed + (size_t)tok * H + c0) = *reinterpret_cast<const uint4*>(o);

@@ -65,7 +65,8 @@ class GLoRCQGraphWrapper:
         torch.cuda.synchronize()
         gc.collect()
         torch.cuda.empty_cache()
-        s = torch.cuda.Stream(device=self.device)
+        # (warm-up on the stream the capture will use: per-stream workspaces are then found, not made, while capturing)
+        s = self.graph_stream
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s), torch.no_grad():
             for _ in range(3):

@@ -21,15 +21,16 @@ by (layer index, module name), and ``load_glorcq_model`` assembles them into thi
 from __future__ import annotations
 
 import json
+import logging
 import os
 import sys
 from typing import Dict, Optional, Tuple
 
-import logging
-
 import torch
 
 from .quantized_linear import GLoRCQLinear
+
+logger = logging.getLogger(__name__)
 
 WTYPES = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "w1", "w2", "w3")
 _MIXTRAL = {"w1": "gate_proj", "w2": "down_proj", "w3": "up_proj"}

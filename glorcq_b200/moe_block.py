@@ -322,7 +322,10 @@ class GraphCompatibleMoeBlock(nn.Module):
         if n > 0:
             L = _lib.lib()
             with torch.cuda.device(x.device):
-                key = (n, tiled._stream_ptr(x.device))
+                # one workspace per token count: a block's calls run one after another (it is not re-entrant across
+                # streams), and a workspace made by the warm-up call must be the one a later capture finds -- an
+                # allocation inside a capture would put its zero fill into the graph, once per replay
+                key = n
                 if key not in self._ws:
                     nbytes = L.glq_moe_workspace_bytes(C.byref(d), n)
                     nctr = L.glq_moe_counters(C.byref(d), n)

@@ -239,6 +239,13 @@ def workspace(device, nbytes: int, ncounters: int = 0):
     when the array is (re)allocated."""
     key = (torch.device(device).index or 0, _stream_ptr(device))
     ws, ctr = _WS.get(key, (None, None))
+    if (ws is None or ctr is None) and torch.cuda.is_current_stream_capturing():
+        # no allocation (and no zero fill) inside a capture: the workspace of the warm-up calls on this device serves
+        # the captured calls too (they run in stream order after them)
+        for (dev_idx, _), (ows, octr) in _WS.items():
+            if dev_idx == key[0] and ows.numel() >= nbytes and octr.numel() >= ncounters:
+                ws, ctr = ows, octr
+                break
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
     if ctr is None or ctr.numel() < ncounters:

@@ -1,8 +1,9 @@
 """The three drop-in entry points against the reference's OWN CUDA kernels, when those have been built for this
 GPU (oracle/build_ref.py compiles the reference's two extension sources, unchanged, for sm_100 into
 oracle/_ref/; without that folder these tests are skipped and the CPU oracle remains the only checker).
-Bars: the reference's kernel-test bound max|err| < 0.01 (inference/kernels/test_kernels.py:105) and
-rel-L2 <= 1e-3 between the two GPU implementations (both fp16 out, fp32 accumulation)."""
+Bars between the two GPU implementations (both accumulate in fp32): rel-L2 <= 1e-3, and no element further apart
+than two fp16 roundings at the largest output magnitude (the reference's own kernel tests use the absolute bound
+max|err| < 0.01 on outputs of order one, inference/kernels/test_kernels.py:105; these cases reach tens)."""
 
 import pytest
 import torch
@@ -37,6 +38,12 @@ def ref_gptq():
     return m
 
 
+def _close_fp16(ours, ref):
+    bound = max(0.01, 2.0 * float(ref.float().abs().max()) * 2.0 ** -10)
+    assert float((ours.float() - ref.float()).abs().max()) <= bound
+    assert cases.rel_l2(ours.cpu(), ref.cpu()) <= 1e-3
+
+
 @pytest.mark.parametrize("B,N,K", [(1, 1408, 2048), (4, 2048, 1408), (16, 512, 2048), (5, 5632, 2048), (0, 64, 64)])
 def test_turbo_matmul_against_reference_kernel(dev, ref_turbo, B, N, K):
     import glorcq_b200.kernels as GK
@@ -48,8 +55,7 @@ def test_turbo_matmul_against_reference_kernel(dev, ref_turbo, B, N, K):
     torch.cuda.synchronize()
     assert ours.shape == ref.shape and ours.dtype == ref.dtype == torch.float16
     if B:
-        assert float((ours.float() - ref.float()).abs().max()) < 0.01
-        assert cases.rel_l2(ours.cpu(), ref.cpu()) <= 1e-3
+        _close_fp16(ours, ref)
 
 
 @pytest.mark.parametrize("E,n_out,K", [(3, 16, 128), (60, 2048, 1408)])
@@ -61,8 +67,7 @@ def test_turbo_grouped_gemv_against_reference_kernel(dev, ref_turbo, E, n_out, K
     ours = GK.turbo_dequant_grouped_gemv(x, *ops, n_out)
     ref = ref_turbo.turbo_dequant_grouped_gemv(x, *ops, n_out)
     torch.cuda.synchronize()
-    assert float((ours.float() - ref.float()).abs().max()) < 0.01
-    assert cases.rel_l2(ours.cpu(), ref.cpu()) <= 1e-3
+    _close_fp16(ours, ref)
 
 
 @pytest.mark.parametrize("B,N,K,sym,lora", [(1, 1408, 2048, False, False), (8, 2048, 1408, False, True), (3, 100, 392, True, False)])
