@@ -11,6 +11,7 @@
 #include "skinny_mm.cuh"
 #include "stream_mm.cuh"
 #include "tc_mm.cuh"
+#include "tc_ps.cuh"
 
 using namespace glq;
 
@@ -471,7 +472,7 @@ static bool plan_tc(const glq_mm_args_t* a, TcGeom* out) {
     if (tiles > 65535) return false;
     g.tiles_max = (int)tiles;
     g.tile_bytes = (long long)g.nkb * g.tn * 256 + (long long)g.ns * g.na * g.tn * 128;
-    g.xp_bytes = (size_t)g.tiles_max * (size_t)g.tile_bytes;
+    g.xp_bytes = (size_t)g.tiles_max * (size_t)g.tile_bytes + 256;   // + the work-item counter of the persistent kernel
     // device-side row counts with few rows per problem on average: the streaming kernels take the
     // problems with up to 32 rows (one launch for <= 8 rows on the integer path, one for 9..32), this
     // kernel only the larger ones
@@ -515,6 +516,30 @@ static int launch_tc_ts_t(const TcParams& p, int N, cudaStream_t st) {
     return GLQ_OK;
 }
 
+// persistent form of the tensor-memory variant: one CTA per SM over all (token tile, feature tile) items
+static bool ps_disabled() {
+    static const bool v = std::getenv("GLQ_NO_TC_PERSISTENT") != nullptr;
+    return v;
+}
+template <int TN, bool SW>
+static int launch_tc_ps_t(const TcParams& p, cudaStream_t st) {
+    using C = TcPsCfg<TN, SW>;
+    static bool configured[64] = {};
+    int dev = 0;
+    GLQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        GLQ_CUDA(cudaFuncSetAttribute(tc_ps_kernel<TN, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    tc_pack_b_kernel<TN><<<dim3(p.tiles_max, p.nkb + p.ns), 256, 0, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    const long work = (long)p.n_ft * p.tiles_max;
+    const int grid = (int)std::min<long>(work, num_sms());
+    tc_ps_kernel<TN, SW><<<grid, kTcThreads, C::SMEM, st>>>(p);
+    GLQ_CUDA(cudaGetLastError());
+    return GLQ_OK;
+}
+
 static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st, int min_rows = 0) {
     if (!a->workspace || a->workspace_bytes < g.xp_bytes) return GLQ_ERR_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(a->workspace) & 127u) != 0) return GLQ_ERR_ALIGN;
@@ -550,8 +575,19 @@ static int launch_tc(const glq_mm_args_t* a, const TcGeom& g, cudaStream_t st, i
     p.min_rows = min_rows;
     const bool sw = a->epilogue == GLQ_EPI_SWIGLU;
     const bool big = g.tn == 128;
+    p.N = a->N;
+    p.n_ft = cdiv(a->N, kTcFeat);
+    p.y_vec = ((reinterpret_cast<uintptr_t>(a->y) & 15u) == 0 && a->ldy % 8 == 0 && a->N % 8 == 0) ? 1 : 0;
+    p.x_vec16 = ((reinterpret_cast<uintptr_t>(a->x) & 15u) == 0 && a->ldx % 8 == 0) ? 1 : 0;
+    p.tile_ctr = nullptr;
     if (a->fmt == GLQ_FMT_Q2 && !ts_disabled()) {
         p.ts = 1;
+        if (!ps_disabled()) {
+            p.tile_ctr = reinterpret_cast<int*>(p.xp + (g.xp_bytes - 256));
+            if (g.tn == 256) return launch_tc_ps_t<256, false>(p, st);
+            if (big) return sw ? launch_tc_ps_t<128, true>(p, st) : launch_tc_ps_t<128, false>(p, st);
+            return sw ? launch_tc_ps_t<64, true>(p, st) : launch_tc_ps_t<64, false>(p, st);
+        }
         if (g.tn == 256) return launch_tc_ts_t<256, false>(p, a->N, st);
         if (big) return sw ? launch_tc_ts_t<128, true>(p, a->N, st) : launch_tc_ts_t<128, false>(p, a->N, st);
         return sw ? launch_tc_ts_t<64, true>(p, a->N, st) : launch_tc_ts_t<64, false>(p, a->N, st);

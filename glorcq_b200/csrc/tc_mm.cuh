@@ -52,6 +52,10 @@ struct TcParams {
     int fmt;                  // GLQ_FMT_*: fixes the channel order inside a group of 16
     int min_rows;             // only problems with more rows than this are this launch's
     int ts;                   // 1: K positions of a stage in the order of the tensor-memory variant
+    int N, n_ft;              // output features of every problem; 128-feature tiles (persistent kernel)
+    int y_vec;                // y rows allow 16-byte bulk stores
+    int x_vec16;              // x rows allow 16-byte loads
+    int* tile_ctr;            // work-item counter of the persistent kernel (in the workspace, zeroed by the pre-pass)
 };
 
 // ---- token tile -> (problem slot, local tile) -----------------------------------------------------
@@ -108,11 +112,37 @@ __host__ __device__ __forceinline__ int tc_ts_channel_of(int P) {
 // position c ^ (r & 7) (the 128-byte swizzle).  grid = (tiles_max, nkb + ns), 256 threads.
 template <int TN>
 __global__ void __launch_bounds__(256) tc_pack_b_kernel(const TcParams p) {
+    if (p.tile_ctr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *p.tile_ctr = 0;
     int slot, lt, cnt, e0;
     if (!tc_find_tile<TN>(p, blockIdx.x, slot, lt, cnt, e0)) return;
     unsigned char* tile = p.xp + (size_t)blockIdx.x * p.tile_bytes;
     const int st = blockIdx.y;
-    if (st < p.nkb) {
+    if (st < p.nkb && p.ts && p.x_vec16 && st * 128 + 128 <= p.K) {
+        // tensor-memory order, whole stage inside K: a thread takes 16 consecutive channels (two 16-byte
+        // loads) of one row, channels 32*t + 16*w + (0..15), and writes the four 8-byte pieces
+        // {c, c+8, c+1, c+9}, c = 2n, that k step n of atom w holds for lane t
+        unsigned char* sdst = tile + (size_t)st * TN * 256;
+#pragma unroll 2
+        for (int idx = threadIdx.x; idx < TN * 8; idx += 256) {
+            const int r = idx >> 3, q8 = idx & 7, t = q8 >> 1, w = q8 & 1;
+            const int rr = lt * TN + r;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            if (rr < cnt) {
+                const long long row = p.entry_row ? __ldg(p.entry_row + e0 + rr) : (long long)(e0 + rr);
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + row * p.ldx + st * 128 + 32 * t + 16 * w);
+                lo = __ldg(src);
+                hi = __ldg(src + 1);
+            }
+            const uint32_t a[4] = {lo.x, lo.y, lo.z, lo.w}, b[4] = {hi.x, hi.y, hi.z, hi.w};
+            unsigned char* rdst = sdst + (size_t)w * (TN * 128) + (size_t)r * 128 + (t & 1) * 8;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const int c = (2 * n + (t >> 1)) ^ (r & 7);
+                *reinterpret_cast<uint2*>(rdst + c * 16) =
+                    make_uint2(__byte_perm(a[n], b[n], 0x5410), __byte_perm(a[n], b[n], 0x7632));
+            }
+        }
+    } else if (st < p.nkb) {
         uint4* dst = reinterpret_cast<uint4*>(tile + (size_t)st * TN * 256);
         for (int ci = threadIdx.x; ci < TN * 16; ci += 256) {
             const int atom = ci / (TN * 8), r = (ci >> 3) % TN, cpos = ci & 7;
@@ -259,20 +289,19 @@ template <int TN, bool SW> struct TcCfg {
     static constexpr size_t SMEM = (size_t)S * STAGE + 1024;
 };
 
-// (1024 + code) or (64 + code) pairs -> fp16(fp16(q - z) * s).  Integer zero points (what the
-// quantizer writes) fold into one exact subtraction of offset + z; any other zero point takes
-// (offset + code - offset) - z, the fp16 rounding of fp16(code) - z.
+// (1024 + code) or (64 + code) pairs -> fp16(fp16(q - z) * s).  When offset + z is exact in fp16 (what
+// integer zero points, the quantizer's output, always are) one subtraction of it from offset + code
+// rounds once, to fp16(q - z), as the two-step form does; any other zero point takes
+// (offset + code - offset) - z.
 struct TcAffine {
     __half2 s2, z2, zc, koff;
     bool integral;
     __device__ __forceinline__ TcAffine(uint32_t sz, float off) {
         s2 = __half2half2(__ushort_as_half((unsigned short)(sz & 0xffffu)));
-        const __half zh = __ushort_as_half((unsigned short)(sz >> 16));
-        const float zf = __half2float(zh);
+        z2 = __half2half2(__ushort_as_half((unsigned short)(sz >> 16)));
         koff = __float2half2_rn(off);
-        integral = zf == rintf(zf) && zf >= -1024.f && zf <= 900.f;
-        z2 = __half2half2(zh);
         zc = __hadd2(z2, koff);
+        integral = __hbeq2(__hsub2(zc, koff), z2);      // offset + z kept every bit of z
     }
     __device__ __forceinline__ uint32_t exact(uint32_t h) const {
         const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&h), zc), s2);
