@@ -136,6 +136,25 @@ def test_many_rows_tensor_core_path(dev, N, K, rank, B, int_zeros):
     assert tiled.debug_error() is None
 
 
+@pytest.mark.parametrize("N,K,rank,B,int_zeros", [(5632, 2048, 64, 1300, True), (2816, 1024, 16, 2100, False)])
+def test_many_rows_more_items_than_sms(dev, N, K, rank, B, int_zeros):
+    """Prefill-sized calls whose (token tile, feature tile) items outnumber the SMs: every CTA of the persistent
+    tcgen05 kernel takes several items, so the rings run across item boundaries, the accumulator is handed back
+    and forth and the results of one item are written while the next one is multiplied.  Last token tile ragged."""
+    d = cases.make_linear(5 * N + K + B, N, K, rank=rank, int_zeros=int_zeros)
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(N + 7 * K + B, B, K)
+    y = lin(x.to(dev)).cpu()
+    ref = O.linear_forward(cases.to_oracle_linear(d), x)
+    assert cases.rel_l2(y, ref) <= REL
+    for b in (0, 255, 256, 1023, 1024, B - 1):
+        assert cases.rel_l2(y[b], ref[b]) <= REL, f"row {b}"
+    y2 = lin(x.to(dev)).cpu()
+    assert torch.equal(y, y2), "two calls in a row differ"
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
 @pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336)])
 @pytest.mark.parametrize("B", [1, 40])
 def test_mixtral_expert_projection_shapes(dev, N, K, B):
