@@ -242,16 +242,22 @@ def run_reference(args, rank):
 
 
 # ---- GPU arm ----------------------------------------------------------------------------------------
-def _c1_problems(dev, P, seed):
+def _c1_problems(dev, P, seed, fmt="q2"):
     from glorcq_b200.tiled import TiledWeight
     N, K, r = 1408, 2048, 64
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
     keep, descs = [], []
     for _ in range(P):
-        tw = TiledWeight.from_gptq(torch.randint(0, 4, (N, K), generator=g, device=dev, dtype=torch.int32),
-                                   (torch.randn(N, K // 128, generator=g, device=dev) * 0.02).abs().half(),
-                                   torch.randint(0, 4, (N, K // 128), generator=g, device=dev).half(), 2, 128)
+        if fmt == "t2":       # 2-bit codebook codes, per-row norms, the reference's Lloyd-Max codebook shape
+            tw = TiledWeight.from_turbo(torch.randint(0, 256, (N, K // 4), generator=g, device=dev, dtype=torch.uint8),
+                                        (torch.rand(N, generator=g, device=dev) + 0.5).float(),
+                                        torch.tensor([-1.51, -0.4528, 0.4528, 1.51], device=dev) / (K ** 0.5))
+        else:
+            bits = 4 if fmt == "q4" else 2
+            tw = TiledWeight.from_gptq(torch.randint(0, 1 << bits, (N, K), generator=g, device=dev, dtype=torch.int32),
+                                       (torch.randn(N, K // 128, generator=g, device=dev) * 0.02).abs().half(),
+                                       torch.randint(0, 1 << bits, (N, K // 128), generator=g, device=dev).half(), bits, 128)
         tw.put_sv(0, (torch.randn(N, r, generator=g, device=dev) * 0.01).half())
         keep.append(tw)
         descs.append(tw.desc_bytes())
@@ -259,18 +265,20 @@ def _c1_problems(dev, P, seed):
     return keep, table, g
 
 
-def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
-    """The grouped dequant-GEMV alone: P distinct 1408x2048 2-bit g128 rank-64 problems, one row each."""
+def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50, fmt="q2"):
+    """The grouped dequant-GEMV alone: P distinct 1408x2048 rank-64 problems, one row each (2-bit g128 codes;
+    `fmt` "q4" / "t2": 4-bit g128 / 2-bit codebook codes)."""
     import ctypes as C
     from glorcq_b200 import _lib
     N, K, r = 1408, 2048, 64
     L = _lib.lib()
-    keep, table, g = _c1_problems(dev, P, 7)
+    keep, table, g = _c1_problems(dev, P, 7, fmt)
     x = torch.randn(P, K, generator=g, device=dev).half()
     a = (torch.randn(P, r, generator=g, device=dev) * 0.1).half()
     y = torch.empty(P, N, dtype=torch.float16, device=dev)
     m = _lib.MMArgs()
-    m.fmt, m.group_size, m.epilogue, m.n_problems, m.max_rows, m.rows_stride = _lib.FMT_Q2, 128, 0, P, 1, 1
+    lib_fmt = {"q2": _lib.FMT_Q2, "q4": _lib.FMT_Q4, "t2": _lib.FMT_T2}[fmt]
+    m.fmt, m.group_size, m.epilogue, m.n_problems, m.max_rows, m.rows_stride = lib_fmt, (0 if fmt == "t2" else 128), 0, P, 1, 1
     m.N, m.K, m.rank = N, K, r
     m.w_table = table.data_ptr()
     m.x, m.ldx, m.a0, m.lda, m.y, m.ldy = x.data_ptr(), K, a.data_ptr(), r, y.data_ptr(), N
@@ -286,14 +294,19 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50):
     torch.cuda.synchronize()
     sec = e0.elapsed_time(e1) / iters * 1e-3
     # per problem: codes + (scale, zero) pairs + SV + x + a + y  (U is read by the separate x.U kernel)
-    per = N * K // 4 + N * (K // 128) * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
+    if fmt == "t2":       # codes + row norms + SV + x + a + y
+        per = N * K // 4 + N * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
+    else:
+        per = N * K * (4 if fmt == "q4" else 2) // 8 + N * (K // 128) * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
     achieved = P * per / sec / 1e9
-    t240 = profiled_traffic("gemv_stream_kernel_q2_240x1408x2048.md")       # ncu capture of the P = 240 case
+    t240 = profiled_traffic("gemv_stream_kernel_q2_240x1408x2048.md") if fmt == "q2" else None   # ncu capture, P = 240
+    names = {"q2": ("stream_kernel<Q2,int8 path>", "2-bit g128"), "q4": ("stream_kernel<Q4,int8 path>", "4-bit g128"),
+             "t2": ("stream_kernel<T2,fp16 path>", "2-bit codebook")}[fmt]
     return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
             "traffic": None if t240 is None else t240 * P / 240.0,
-            "kernel": "stream_kernel<Q2,int8 path> (grouped dequant-GEMV)",
+            "kernel": f"{names[0]} (grouped dequant-GEMV)",
             "launch_us": sec * 1e6, "bytes_per_launch": P * per, "peak_kind": peak_kind,
-            "problems": f"{P} x (1408x2048, 2-bit g128, rank 64), 1 row each; {P * per / 1e6:.0f} MB > L2"}
+            "problems": f"{P} x (1408x2048, {names[1]}, rank 64), 1 row each; {P * per / 1e6:.0f} MB > L2"}
 
 
 def gemm_roofline(dev, P=8, rows=2048, iters=20):
@@ -715,6 +728,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--batch", type=int, default=1, help="token streams per rank")
     ap.add_argument("--prompt", type=int, default=0, help="prompt length (0: the configuration's)")
+    ap.add_argument("--gemv-fmt", choices=["q2", "q4", "t2"], default="q2",
+                    help="with --gemv-only: 2-bit g128 codes (default), 4-bit g128 codes or 2-bit codebook codes")
     ap.add_argument("--gemv-only", action="store_true",
                     help="time only the grouped dequant-GEMV roofline case (small enough for an ncu capture)")
     ap.add_argument("--gemm-only", action="store_true",
@@ -746,7 +761,7 @@ def main():
         dev = torch.device("cuda:0")
         peak, kind = measured_peak_gbs()
         if args.gemv_only:
-            out = {"roofline": gemv_roofline(dev, peak, kind, P=args.problems, iters=max(1, args.steps))}
+            out = {"roofline": gemv_roofline(dev, peak, kind, P=args.problems, iters=max(1, args.steps), fmt=args.gemv_fmt)}
         elif args.gemm_only:
             P = args.problems if args.problems != 240 else 8
             out = {"roofline_gemm": gemm_roofline(dev, P=P, rows=args.rows, iters=max(1, args.steps))}
