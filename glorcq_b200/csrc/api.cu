@@ -645,6 +645,36 @@ extern "C" int glq_grouped_matmul(const glq_mm_args_t* a, void* stream) {
         if (!a->w_table && !a->w.codes) return GLQ_ERR_ARG;
         return launch_tc(a, tg, reinterpret_cast<cudaStream_t>(stream));
     }
+    // 9..32 rows of the same problems, counts known on the host: the integer path stages at most 8 rows (4 when the
+    // staged activations of a long reduction leave no room for 8) and streams at a multiple of the fp16 path's rate,
+    // so it runs over chunks of rows; after the first chunk the weights come from L2 where they fit
+    if (!use_tc && !a->slot_count && !a->slot_offset && a->max_rows > 8 && a->max_rows <= 32 && !i8_disabled() &&
+        (a->fmt == GLQ_FMT_Q2 || a->fmt == GLQ_FMT_Q4)) {
+        int chunk = 0;
+        for (int c : {8, 4}) {
+            StreamGeom cg;
+            if (plan_stream(a->fmt, a->epilogue, a->N, a->K, a->rank, a->group_size, a->n_problems, c, &cg) && cg.i8) {
+                chunk = c;
+                break;
+            }
+        }
+        if (chunk) {
+            for (int r0 = 0; r0 < a->max_rows; r0 += chunk) {
+                glq_mm_args_t b = *a;
+                b.max_rows = std::min(chunk, a->max_rows - r0);
+                b.rows_stride = a->rows_stride > 0 ? a->rows_stride : a->max_rows;
+                if (a->entry_row) b.entry_row = a->entry_row + r0;
+                else b.x = static_cast<const char*>(a->x) + (size_t)r0 * a->ldx * 2;
+                if (a->entry_scale) b.entry_scale = static_cast<const char*>(a->entry_scale) + (size_t)r0 * 2;
+                if (a->a0) b.a0 = static_cast<const char*>(a->a0) + (size_t)r0 * a->lda * 2;
+                if (a->a1) b.a1 = static_cast<const char*>(a->a1) + (size_t)r0 * a->lda * 2;
+                b.y = static_cast<char*>(a->y) + (size_t)r0 * a->ldy * 2;
+                const int rc = glq_grouped_matmul(&b, stream);
+                if (rc != GLQ_OK) return rc;
+            }
+            return GLQ_OK;
+        }
+    }
     StreamGeom sg;
     // Row-count classes (device-side counts): slots with <= 8 rows go to the integer path, 9..16 to the
     // fp16 path with two activation tiles, and above that to the tcgen05 kernel when the call may have

@@ -61,6 +61,25 @@ def _table(descs: List[Weight], device) -> torch.Tensor:
     return torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
 
 
+_SHARED_WS_FROM = 256 << 20       # scratch sizes above this come from the per-device pool below
+_BIG_WS = {}
+
+
+def _shared_big_workspace(device, nbytes, ncounters):
+    """Scratch and arrival counters for prompt-sized calls, one pair per device (grown on demand, never shrunk).
+    The counters are zero before a call and every kernel leaves them zero."""
+    key = torch.device(device).index or 0
+    ws, ctr = _BIG_WS.get(key, (None, None))
+    if ws is None or ws.numel() < nbytes:
+        ws = None
+        _BIG_WS.pop(key, None)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    if ctr is None or ctr.numel() < ncounters:
+        ctr = torch.zeros(ncounters, dtype=torch.int32, device=device)
+    _BIG_WS[key] = (ws, ctr)
+    return ws, ctr
+
+
 class GraphCompatibleMoeBlock(nn.Module):
     """Drop-in replacement for Qwen2MoeSparseMoeBlock running on the fused kernels."""
 
@@ -329,9 +348,15 @@ class GraphCompatibleMoeBlock(nn.Module):
                 if key not in self._ws:
                     nbytes = L.glq_moe_workspace_bytes(C.byref(d), n)
                     nctr = L.glq_moe_counters(C.byref(d), n)
-                    self._ws[key] = (torch.empty(nbytes + 256, dtype=torch.uint8, device=x.device),
-                                     torch.zeros(max(nctr, 1), dtype=torch.int32, device=x.device))
-                ws, ctr = self._ws[key]
+                    if nbytes > _SHARED_WS_FROM and not torch.cuda.is_current_stream_capturing():
+                        # prompt-sized calls: one scratch per device for all blocks (they run one after another;
+                        # a private copy per block of a 32-layer model would not fit the device)
+                        ws, ctr = _shared_big_workspace(x.device, nbytes + 256, max(nctr, 1))
+                    else:
+                        self._ws[key] = (torch.empty(nbytes + 256, dtype=torch.uint8, device=x.device),
+                                         torch.zeros(max(nctr, 1), dtype=torch.int32, device=x.device))
+                if key in self._ws:
+                    ws, ctr = self._ws[key]
                 base = (ws.data_ptr() + 255) // 256 * 256
                 aux = fork = join = None
                 if self.parallel_shared_expert and d.I_shared > 0:
