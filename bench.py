@@ -667,6 +667,53 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def prefill_alone(dev, cfg, prompt, reps=5, profile=False):
+    """The prompt pass of the whole decoder alone (batch 1, eager, as `generate` runs it): every quantized product
+    goes through the tcgen05 dequant-GEMM, experts grouped by the device-side routing.  Tokens per second and the
+    rate of the quantized products' arithmetic (2 flops per weight of every projection a token passes through)."""
+    from glorcq_b200 import synthetic
+    from glorcq_b200.graph_wrapper import GLoRCQGraphWrapper
+    model = synthetic.make_decoder(cfg, dev, seed=77)
+    w = GLoRCQGraphWrapper(model, max_batch_size=1, max_seq_len=prompt + 32)
+    ids = torch.randint(0, cfg["vocab_size"], (1, prompt), generator=torch.Generator().manual_seed(5)).to(dev)
+    w._set_moe_graph_mode(False)
+    kw = {"logits_to_keep": 1} if w._keep_last_only else {}
+
+    def run():
+        w.static_cache.reset()
+        return w.model(input_ids=ids, cache_position=torch.arange(prompt, device=dev), past_key_values=w.static_cache,
+                       use_cache=True, return_dict=False, **kw)[0]
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    if profile:        # for `ncu --profile-from-start off`: one prompt pass between cudaProfilerStart / Stop
+        torch.cuda.profiler.start()
+        run()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = sorted(times)[len(times) // 2]
+    H, k = cfg["hidden_size"], cfg["num_experts_per_tok"]
+    I = cfg.get("moe_intermediate_size", cfg.get("intermediate_size"))
+    Is = cfg.get("shared_expert_intermediate_size", 0) or 0
+    nh = cfg["num_attention_heads"]
+    nkv, hd = cfg.get("num_key_value_heads") or nh, cfg.get("head_dim") or H // nh
+    per_tok = 2.0 * (H * hd * (2 * nh + 2 * nkv) + 3 * H * I * k + 3 * H * Is)
+    layers = cfg["num_hidden_layers"]
+    peak, kind = measured_peak_tflops()
+    tf = per_tok * layers * prompt / (ms * 1e-3) / 1e12
+    return {"prompt_tokens": prompt, "ms": ms, "tok_s": prompt / (ms * 1e-3), "quantized_products_tflops": tf,
+            "frac_of_bf16_peak": tf / peak, "peak_kind": kind, "layers": layers,
+            "note": "whole prompt pass incl. attention (library call), norms, routing and the output projection of the last token"}
+
+
 def moe_blocks_alone(model, dev, cfg, layers, steps=100):
     """One token through the decoder's MoE blocks alone, each block's output feeding the next through the fused
     residual-free RMS norm, replayed from one CUDA graph: the part of a token the quantized expert path owns."""
@@ -728,6 +775,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (0: all)")
     ap.add_argument("--batch", type=int, default=1, help="token streams per rank")
     ap.add_argument("--prompt", type=int, default=0, help="prompt length (0: the configuration's)")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="time the prompt pass of the whole decoder alone (--prompt tokens, default 4096; batch 1)")
     ap.add_argument("--gemv-fmt", choices=["q2", "q4", "t2"], default="q2",
                     help="with --gemv-only: 2-bit g128 codes (default), 4-bit g128 codes or 2-bit codebook codes")
     ap.add_argument("--gemv-only", action="store_true",
@@ -754,6 +803,16 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.prefill_only:
+        from glorcq_b200 import _build
+        _build.build()
+        dev = torch.device("cuda:0")
+        torch.cuda.set_device(dev)
+        cfg, name, prompt = model_config(args.config)
+        cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
+        print(json.dumps({"prefill": {"model": name, **prefill_alone(dev, cfg, args.prompt or 4096, reps=max(3, args.steps), profile=args.profile_window)}}),
+              flush=True)
         return
     if args.gemv_only or args.gemm_only or args.lm_head_only or args.moe_only:
         from glorcq_b200 import _build, synthetic

@@ -40,6 +40,7 @@ inline bool no_dependent_launch() {
 struct MoeLayout {
     size_t logits, sel, wts, active, n_active, slot_count, slot_offset, entry_row, entry_scale, tok_entries;
     size_t active2, n_active2, slot_count2, slot_offset2;   // gate and up x.U as one launch: 2E slots
+    size_t plan_blk;                                        // per-block expert counts of the many-token plan
     size_t a_gu, h, b, yd, a_sg, a_su, hs, bs, ysh, xr, hr, hsr, mm, mm2;
     size_t total, mm_bytes, mm_counters;
 };
@@ -99,6 +100,7 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
     L.n_active2 = take(4);
     L.slot_count2 = take(2 * PS * 4);
     L.slot_offset2 = take(2 * PS * 4);
+    L.plan_blk = take(((nk + 511) / 512) * (size_t)d->E * 4);
     L.a_gu = take(2 * nk * R * 2);
     L.h = take(nk * d->I * 2);
     L.b = take(nk * R * 2);
@@ -153,6 +155,131 @@ MoeLayout moe_layout(const glq_moe_desc_t* d, int n) {
 // the lower expert index), optional renormalisation, weights rounded to fp16.  Phase B, warp per
 // expert: entry counts, offsets and the expert's entry list in token order (ballot scans:
 // deterministic), and the compacted list of live experts.
+// Routing of one token by one warp: soft-max over the experts (lanes over experts, E <= 256), top-k by
+// repeated arg-max (first maximum wins), optional renormalisation, fp16 weights.
+__device__ __forceinline__ void route_token(int t, int lane, const __half* __restrict__ logits, int ldl, int E, int k, int renorm,
+                                            int* __restrict__ sel, __half* __restrict__ wts, __half* __restrict__ logits_out,
+                                            int* __restrict__ sel_out, __half* __restrict__ wts_out) {
+    const __half* row = logits + (size_t)t * ldl;
+    float lv[8], pv[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        lv[i] = e < E ? __half2float(row[e]) : -INFINITY;
+        mx = fmaxf(mx, lv[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        pv[i] = (lane + 32 * i) < E ? expf(lv[i] - mx) : 0.f;
+        sum += pv[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    // a probability that is not a number (non-finite hidden state) counts as zero: the top-k below then
+    // still selects k distinct experts and no index leaves the tables
+    for (int i = 0; i < 8; ++i) {
+        const float pr = pv[i] / sum;
+        pv[i] = (lane + 32 * i) < E ? (pr >= 0.f ? pr : 0.f) : -1.f;
+    }
+    float wk[16];
+    int ek[16];
+    float wsum = 0.f;
+    for (int s = 0; s < k; ++s) {
+        float best = -1.f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (pv[i] > best) {   // increasing i = increasing expert index: first maximum wins
+                best = pv[i];
+                be = lane + 32 * i;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ob > best || (ob == best && oe < be)) {
+                best = ob;
+                be = oe;
+            }
+        }
+        wk[s] = best;
+        ek[s] = be;
+        wsum += best;
+        if ((be & 31) == lane) pv[be >> 5] = -1.f;   // taken
+    }
+    if (lane == 0) {
+        for (int s = 0; s < k; ++s) {
+            const float wv = renorm ? wk[s] / wsum : wk[s];
+            const __half wh = __float2half_rn(wv);
+            sel[t * k + s] = ek[s];
+            wts[t * k + s] = wh;
+            if (sel_out) sel_out[t * k + s] = ek[s];
+            if (wts_out) wts_out[t * k + s] = wh;
+        }
+    }
+    if (logits_out)
+        for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = row[e];
+}
+
+// Warp 0 of a CTA: exclusive prefix of the per-expert counts in sm_cnt (entry offsets are global: every rank
+// numbers the entries alike) into sm_off, and the compacted lists of the live experts this rank holds.
+__device__ __forceinline__ void plan_lists(int lane, const int* sm_cnt, int* sm_off, int E, int nk, int chunk, int ep_rank,
+                                           int ep_world, int* __restrict__ active, int* __restrict__ n_active,
+                                           int* __restrict__ slot_count, int* __restrict__ slot_offset,
+                                           int* __restrict__ active2, int* __restrict__ n_active2,
+                                           int* __restrict__ slot_count2, int* __restrict__ slot_offset2) {
+    int base = 0, j = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int c = e < E ? sm_cnt[e] : 0;
+        int v = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int tv = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += tv;
+        }
+        const int off = base + v - c;
+        if (e < E) sm_off[e] = off;
+        const bool act = e < E && c > 0 && e % ep_world == ep_rank;
+        // slots of this expert: one, or ceil(c / chunk) of at most `chunk` consecutive entries each
+        const int ns = act ? (chunk > 0 ? (c + chunk - 1) / chunk : 1) : 0;
+        int sv = ns;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int tv = __shfl_up_sync(0xffffffffu, sv, o);
+            if (lane >= o) sv += tv;
+        }
+        for (int i = 0; i < ns; ++i) {
+            const int pos = j + sv - ns + i;
+            const int cc = chunk > 0 ? min(chunk, c - i * chunk) : c;
+            const int oo = off + (chunk > 0 ? i * chunk : 0);
+            active[pos] = e;
+            slot_count[pos] = cc;
+            slot_offset[pos] = oo;
+            // the same lists twice, for gate (table entry e, entries 0..nk) and up (entry E+e, entries nk..2nk)
+            active2[pos] = e;
+            slot_count2[pos] = cc;
+            slot_offset2[pos] = oo;
+        }
+        j += __shfl_sync(0xffffffffu, sv, 31);
+        base += __shfl_sync(0xffffffffu, v, 31);
+    }
+    __syncwarp();
+    for (int i = lane; i < j; i += 32) {
+        active2[j + i] = E + active[i];
+        slot_count2[j + i] = slot_count[i];
+        slot_offset2[j + i] = nk + slot_offset[i];
+    }
+    if (lane == 0) {
+        *n_active = j;
+        *n_active2 = 2 * j;
+    }
+}
+
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict__ logits, int ldl, int n, int E, int k,
                                                         int renorm, int* __restrict__ sel, __half* __restrict__ wts,
                                                         int* __restrict__ active, int* __restrict__ n_active,
@@ -179,71 +306,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
             if (e < 0 || e >= E) tok_entries[i] = -1;
         }
     }
-    for (int t = warp; t < n && !sel_in; t += nwarps) {
-        const __half* row = logits + (size_t)t * ldl;
-        float lv[8], pv[8];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = lane + 32 * i;
-            lv[i] = e < E ? __half2float(row[e]) : -INFINITY;
-            mx = fmaxf(mx, lv[i]);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            pv[i] = (lane + 32 * i) < E ? expf(lv[i] - mx) : 0.f;
-            sum += pv[i];
-        }
-        sum = warp_sum(sum);
-#pragma unroll
-        // a probability that is not a number (non-finite hidden state) counts as zero: the top-k below then
-        // still selects k distinct experts and no index leaves the tables
-        for (int i = 0; i < 8; ++i) {
-            const float pr = pv[i] / sum;
-            pv[i] = (lane + 32 * i) < E ? (pr >= 0.f ? pr : 0.f) : -1.f;
-        }
-        float wk[16];
-        int ek[16];
-        float wsum = 0.f;
-        for (int s = 0; s < k; ++s) {
-            float best = -1.f;
-            int be = 0x7fffffff;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                if (pv[i] > best) {   // increasing i = increasing expert index: first maximum wins
-                    best = pv[i];
-                    be = lane + 32 * i;
-                }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ob > best || (ob == best && oe < be)) {
-                    best = ob;
-                    be = oe;
-                }
-            }
-            wk[s] = best;
-            ek[s] = be;
-            wsum += best;
-            if ((be & 31) == lane) pv[be >> 5] = -1.f;   // taken
-        }
-        if (lane == 0) {
-            for (int s = 0; s < k; ++s) {
-                const float wv = renorm ? wk[s] / wsum : wk[s];
-                const __half wh = __float2half_rn(wv);
-                sel[t * k + s] = ek[s];
-                wts[t * k + s] = wh;
-                if (sel_out) sel_out[t * k + s] = ek[s];
-                if (wts_out) wts_out[t * k + s] = wh;
-            }
-        }
-        if (logits_out)
-            for (int e = lane; e < E; e += 32) logits_out[(size_t)t * E + e] = row[e];
-    }
+    for (int t = warp; t < n && !sel_in; t += nwarps)
+        route_token(t, lane, logits, ldl, E, k, renorm, sel, wts, logits_out, sel_out, wts_out);
     __syncthreads();
     const int nk = n * k;
     const unsigned lt = (1u << lane) - 1u;
@@ -259,54 +323,9 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
     __syncthreads();
     // Phase B2, warp 0: exclusive prefix of the counts (entry offsets are global: every rank numbers the
     // entries alike) and the compacted list of live experts this rank holds (e mod world == rank)
-    if (warp == 0) {
-        int base = 0, j = 0;
-        for (int e0 = 0; e0 < E; e0 += 32) {
-            const int e = e0 + lane;
-            const int c = e < E ? sm_cnt[e] : 0;
-            int v = c;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int tv = __shfl_up_sync(0xffffffffu, v, o);
-                if (lane >= o) v += tv;
-            }
-            const int off = base + v - c;
-            if (e < E) sm_off[e] = off;
-            const bool act = e < E && c > 0 && e % ep_world == ep_rank;
-            // slots of this expert: one, or ceil(c / chunk) of at most `chunk` consecutive entries each
-            const int ns = act ? (chunk > 0 ? (c + chunk - 1) / chunk : 1) : 0;
-            int sv = ns;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int tv = __shfl_up_sync(0xffffffffu, sv, o);
-                if (lane >= o) sv += tv;
-            }
-            for (int i = 0; i < ns; ++i) {
-                const int pos = j + sv - ns + i;
-                const int cc = chunk > 0 ? min(chunk, c - i * chunk) : c;
-                const int oo = off + (chunk > 0 ? i * chunk : 0);
-                active[pos] = e;
-                slot_count[pos] = cc;
-                slot_offset[pos] = oo;
-                // the same lists twice, for gate (table entry e, entries 0..nk) and up (entry E+e, entries nk..2nk)
-                active2[pos] = e;
-                slot_count2[pos] = cc;
-                slot_offset2[pos] = oo;
-            }
-            j += __shfl_sync(0xffffffffu, sv, 31);
-            base += __shfl_sync(0xffffffffu, v, 31);
-        }
-        __syncwarp();
-        for (int i = lane; i < j; i += 32) {
-            active2[j + i] = E + active[i];
-            slot_count2[j + i] = slot_count[i];
-            slot_offset2[j + i] = nk + slot_offset[i];
-        }
-        if (lane == 0) {
-            *n_active = j;
-            *n_active2 = 2 * j;
-        }
-    }
+    if (warp == 0)
+        plan_lists(lane, sm_cnt, sm_off, E, nk, chunk, ep_rank, ep_world, active, n_active, slot_count, slot_offset, active2,
+                   n_active2, slot_count2, slot_offset2);
     __syncthreads();
     // Phase B3: each expert's entries in token order, one warp per expert
     for (int e = warp; e < E; e += nwarps) {
@@ -325,6 +344,109 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __half* __restrict
             }
             pos += __popc(m);
         }
+    }
+}
+
+// ---- the same plan for many tokens, spread over the SMs -----------------------------------------------------
+// moe_plan_kernel is one CTA (the decode step wants one short launch); with thousands of tokens its scans over
+// all entries per expert take a millisecond.  Four small launches give the identical plan: (a) one warp per
+// token routes; (b) one warp per block of kPlanChunk consecutive entries counts its entries per expert;
+// (c) one CTA sums the counts, builds the lists (plan_lists) and turns the per-block counts into per-block
+// bases; (d) every block scatters its entries in entry order from its bases -- a stable counting sort, so each
+// expert's entries come out in token order exactly as in the one-CTA kernel.
+constexpr int kPlanChunk = 512;
+constexpr long long kPlanParallelFrom = 2048;   // entries (tokens x top-k) from which the plan runs as four launches
+
+__global__ void __launch_bounds__(256) moe_route_kernel(const __half* __restrict__ logits, int ldl, int n, int E, int k, int renorm,
+                                                        int* __restrict__ sel, __half* __restrict__ wts,
+                                                        int* __restrict__ tok_entries, __half* __restrict__ logits_out,
+                                                        int* __restrict__ sel_out, __half* __restrict__ wts_out,
+                                                        const int* __restrict__ sel_in, const __half* __restrict__ wts_in) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (sel_in) {   // routing decided by the caller: copy it; an index outside [0, E) marks a dropped slot
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n * k; i += gridDim.x * blockDim.x) {
+            const int e = sel_in[i];
+            sel[i] = e;
+            wts[i] = wts_in[i];
+            if (e < 0 || e >= E) tok_entries[i] = -1;
+        }
+        return;
+    }
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t < n) route_token(t, lane, logits, ldl, E, k, renorm, sel, wts, logits_out, sel_out, wts_out);
+}
+
+// one warp per block: blk[b][e] = entries of expert e among the block's kPlanChunk entries
+__global__ void __launch_bounds__(32) moe_plan_count_kernel(const int* __restrict__ sel, int nk, int E, int* __restrict__ blk) {
+    extern __shared__ int sm_c[];
+    const int lane = threadIdx.x, b = blockIdx.x;
+    for (int e = lane; e < E; e += 32) sm_c[e] = 0;
+    __syncwarp();
+    const int i_end = min(nk, (b + 1) * kPlanChunk);
+    for (int i0 = b * kPlanChunk; i0 < i_end; i0 += 32) {
+        const int i = i0 + lane;
+        const int e = i < i_end ? sel[i] : -1;
+        const bool valid = e >= 0 && e < E;
+        const unsigned m = __match_any_sync(0xffffffffu, valid ? e : E + lane);
+        if (valid && lane == __ffs(m) - 1) sm_c[e] += __popc(m);
+        __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) blk[(size_t)b * E + e] = sm_c[e];
+}
+
+__global__ void __launch_bounds__(1024) moe_plan_lists_kernel(int* __restrict__ blk, int nb, int nk, int E, int chunk, int ep_rank,
+                                                              int ep_world, int* __restrict__ active, int* __restrict__ n_active,
+                                                              int* __restrict__ slot_count, int* __restrict__ slot_offset,
+                                                              int* __restrict__ active2, int* __restrict__ n_active2,
+                                                              int* __restrict__ slot_count2, int* __restrict__ slot_offset2) {
+    extern __shared__ int sm_cnt[];  // [E] counts, then [E] offsets
+    int* sm_off = sm_cnt + E;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int b = 0; b < nb; ++b) c += blk[(size_t)b * E + e];
+        sm_cnt[e] = c;
+    }
+    __syncthreads();
+    if (warp == 0)
+        plan_lists(lane, sm_cnt, sm_off, E, nk, chunk, ep_rank, ep_world, active, n_active, slot_count, slot_offset, active2,
+                   n_active2, slot_count2, slot_offset2);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {   // counts -> first entry number of (block, expert)
+        int run = sm_off[e];
+        for (int b = 0; b < nb; ++b) {
+            const int c = blk[(size_t)b * E + e];
+            blk[(size_t)b * E + e] = run;
+            run += c;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(32) moe_plan_scatter_kernel(const int* __restrict__ sel, const __half* __restrict__ wts, int nk,
+                                                              int E, int k, const int* __restrict__ blk,
+                                                              int* __restrict__ entry_row, __half* __restrict__ entry_scale,
+                                                              int* __restrict__ tok_entries) {
+    extern __shared__ int sm_b[];
+    const int lane = threadIdx.x, b = blockIdx.x;
+    const unsigned lt = (1u << lane) - 1u;
+    for (int e = lane; e < E; e += 32) sm_b[e] = blk[(size_t)b * E + e];
+    __syncwarp();
+    const int i_end = min(nk, (b + 1) * kPlanChunk);
+    for (int i0 = b * kPlanChunk; i0 < i_end; i0 += 32) {
+        const int i = i0 + lane;
+        const int e = i < i_end ? sel[i] : -1;
+        const bool valid = e >= 0 && e < E;
+        const unsigned m = __match_any_sync(0xffffffffu, valid ? e : E + lane);
+        if (valid) {
+            const int q = sm_b[e] + __popc(m & lt);
+            entry_row[q] = i / k;
+            entry_row[nk + q] = i / k;
+            entry_scale[q] = wts[i];
+            tok_entries[i] = q;
+        }
+        __syncwarp();
+        if (valid && lane == __ffs(m) - 1) sm_b[e] += __popc(m);
+        __syncwarp();
     }
 }
 
@@ -916,7 +1038,24 @@ extern "C" int glq_moe_forward_ep(const glq_moe_desc_t* d, const void* x, int n,
     if (forked && cudaEventRecord(reinterpret_cast<cudaEvent_t>(ev_fork), st) != cudaSuccess) return GLQ_ERR_CUDA;
 
     // 2. routing plan
-    {
+    if ((long long)nk >= kPlanParallelFrom) {
+        // many tokens: routing, per-block counts, lists and scatter as four launches over the SMs
+        const int nb = (nk + kPlanChunk - 1) / kPlanChunk;
+        int* blk = reinterpret_cast<int*>(ws + L.plan_blk);
+        const int* s_in = given ? (const int*)ep->sel_in : (const int*)nullptr;
+        const __half* w_in = given ? reinterpret_cast<const __half*>(ep->weight_in) : (const __half*)nullptr;
+        moe_route_kernel<<<given ? std::min(1024, (nk + 255) / 256) : (n + 7) / 8, 256, 0, st>>>(
+            (const __half*)p_logits, ldl, n, (int)d->E, k, (int)d->norm_topk_prob, p_sel, p_wts, p_tok,
+            reinterpret_cast<__half*>(router_logits), (int*)sel_out, reinterpret_cast<__half*>(weight_out), s_in, w_in);
+        moe_plan_count_kernel<<<nb, 32, d->E * sizeof(int), st>>>(p_sel, nk, (int)d->E, blk);
+        moe_plan_lists_kernel<<<1, 1024, 2 * d->E * sizeof(int), st>>>(
+            blk, nb, nk, (int)d->E, chunk, ep_rank, ep_world, p_active, p_nact, p_cnt, p_off,
+            reinterpret_cast<int*>(ws + L.active2), reinterpret_cast<int*>(ws + L.n_active2),
+            reinterpret_cast<int*>(ws + L.slot_count2), reinterpret_cast<int*>(ws + L.slot_offset2));
+        moe_plan_scatter_kernel<<<nb, 32, d->E * sizeof(int), st>>>(p_sel, p_wts, nk, (int)d->E, k, blk, p_erow, p_escale, p_tok);
+        if (cudaGetLastError() != cudaSuccess) return GLQ_ERR_CUDA;
+        after_kernel[0] = true;
+    } else {
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(1024);
