@@ -97,14 +97,40 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
     // this CTA's share of the cached positions (the grid's z dimension splits them)
     const long long per = (pos + nsplit - 1) / nsplit;
     const long long t_lo = (long long)z * per, t_hi = t_lo + per < pos ? t_lo + per : pos;
-    for (long long t = t_lo + warp; t < t_hi; t += kAttnWarps) {
-        float kk[EPL], vv[EPL];
+    // the rows of up to kAhead positions are requested before the first of them is used: the loop is a chain of
+    // dependent updates, and one cache round trip per position would set its pace
+    constexpr int kAhead = 8;
+    for (long long t0 = t_lo + warp; t0 < t_hi; t0 += (long long)kAttnWarps * kAhead) {
+        __half kr[kAhead][EPL], vr[kAhead][EPL];
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-            kk[i] = __half2float(kc[(size_t)t * HD + lane * EPL + i]);
-            vv[i] = __half2float(vc[(size_t)t * HD + lane * EPL + i]);
+        for (int u = 0; u < kAhead; ++u) {
+            const long long t = t0 + (long long)u * kAttnWarps;
+            if (t < t_hi) {
+                if constexpr (EPL == 4) {
+                    *reinterpret_cast<uint2*>(kr[u]) = *reinterpret_cast<const uint2*>(kc + (size_t)t * HD + lane * EPL);
+                    *reinterpret_cast<uint2*>(vr[u]) = *reinterpret_cast<const uint2*>(vc + (size_t)t * HD + lane * EPL);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) {
+                        kr[u][i] = kc[(size_t)t * HD + lane * EPL + i];
+                        vr[u][i] = vc[(size_t)t * HD + lane * EPL + i];
+                    }
+                }
+            }
         }
-        visit(kk, vv);
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const long long t = t0 + (long long)u * kAttnWarps;
+            if (t < t_hi) {
+                float kk[EPL], vv[EPL];
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    kk[i] = __half2float(kr[u][i]);
+                    vv[i] = __half2float(vr[u][i]);
+                }
+                visit(kk, vv);
+            }
+        }
     }
     if (warp == 0 && z == 0) visit(kn, vn);
     // combine the warps
