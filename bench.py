@@ -481,27 +481,41 @@ def run_ours(args, rank, world, local_rank):
     prompt = args.prompt or prompt
     layers = cfg["num_hidden_layers"] = args.layers or cfg["num_hidden_layers"]
     ep = world > 1 and not args.replicas
-    # weak scaling: `args.batch` token streams per rank; every rank holds all of them (attention, router and
-    # shared expert are replicated) and its share of the routed experts
-    streams = args.batch * (world if ep and not args.strong else 1)
+    # expert-parallel degree D: ranks [g*D, (g+1)*D) share one copy of the routed experts (expert e on the group's rank
+    # e % D) and step the same D * batch token streams; world / D such groups run side by side on different streams.
+    # Default: at most 4, so that a step of one stream per rank (4 tokens) stays inside the persistent block kernel.
+    D = 1
+    if ep:
+        D = args.ep_degree or min(world, 4)
+        if world % D != 0:
+            raise SystemExit(f"--ep-degree {D} does not divide --gpus {world}")
+    G = world // D
+    gid, grank = rank // D, rank % D
+    grp = None
+    if ep and G > 1:
+        groups = [dist.new_group(list(range(g * D, (g + 1) * D))) for g in range(G)]   # every rank creates every group
+        grp = groups[gid]
+    # weak scaling: `args.batch` token streams per rank; every rank of a group holds all of the group's streams
+    # (attention, router and shared expert are replicated) and its share of the routed experts
+    streams = args.batch * (D if ep and not args.strong else 1)
     K, W = max(1, args.steps), max(3, args.warmup)
     peer_ok = ep and args.exchange == "peer" and streams <= 16
     if peer_ok:
         ok = torch.ones(1, device=dev)
         try:
-            PeerExchange.get(None, dev, 16 * cfg["num_experts_per_tok"], cfg["hidden_size"])
+            PeerExchange.get(grp, dev, 16 * cfg["num_experts_per_tok"], cfg["hidden_size"])
         except Exception as exc:       # noqa: BLE001 - any failure here means "use NCCL"
             _stage(rank, f"peer exchange unavailable: {exc!r}")
             ok.zero_()
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         peer_ok = float(ok) != 0
-    model = synthetic.make_decoder(cfg, dev, seed=77, ep_rank=rank if ep else 0, ep_world=world if ep else 1,
+    model = synthetic.make_decoder(cfg, dev, seed=77, ep_rank=grank if ep else 0, ep_world=D if ep else 1, ep_group=grp,
                                    peer_exchange_max_tokens=16 if peer_ok else 0)
     _stage(rank, "model built")
     if world > 1:
         dist.barrier()          # the first step is a collective: the ranks start it together
     w = GLoRCQGraphWrapper(model, max_batch_size=streams, max_seq_len=prompt + K + W + 24)
-    ids = torch.randint(0, cfg["vocab_size"], (streams, prompt), generator=torch.Generator().manual_seed(5)).to(dev)
+    ids = torch.randint(0, cfg["vocab_size"], (streams, prompt), generator=torch.Generator().manual_seed(5 + gid)).to(dev)
     w.capture_graph()
     out, _ = w.generate(ids, max_new_tokens=8)           # the prompt's keys and values, and a first replay
     torch.cuda.synchronize()
@@ -551,7 +565,7 @@ def run_ours(args, rank, world, local_rank):
         times.append(e0.elapsed_time(e1))
     _stage(rank, "device timing done")
     # ---- end to end: token id from pinned host memory in, next token id back to the host, every step ----
-    mine = rank if streams > 1 and ep else 0
+    mine = grank if streams > 1 and ep else 0
     h_in = torch.empty(args.batch if ep else streams, 1, dtype=torch.int64).pin_memory()
     h_out = torch.empty_like(h_in).pin_memory()
     rows = slice(mine * args.batch, (mine + 1) * args.batch) if ep else slice(0, streams)
@@ -563,7 +577,7 @@ def run_ours(args, rank, world, local_rank):
         for i in range(steps):
             if ep and not args.strong:
                 own.copy_(h_in, non_blocking=True)
-                dist.all_gather_into_tensor(all_ids, own)
+                dist.all_gather_into_tensor(all_ids, own, group=grp)
                 w.replay(all_ids, prompt + i)
             else:
                 all_ids.copy_(h_in, non_blocking=True)
@@ -630,14 +644,17 @@ def run_ours(args, rank, world, local_rank):
                              f"MoE block) and the output projection through the CPU oracle, median of {reps} forwards; "
                              f"tok/s = 1 / ({layers} x layer + output projection)"}
         bytes_tok, bytes_moe = token_bytes(cfg, layers, prompt + K // 2)
-        value = streams * K / (ms * 1e-3)
+        total_streams = streams * (G if ep else 1)
+        value = total_streams * K / (ms * 1e-3)
         conf = workload_config(cfg, name, prompt, args.batch, layers)
         conf.update({"parallelism": "single GPU" if world == 1 else
-                     (f"expert parallel ep{world}: expert e on rank e % {world}; attention, router, shared expert and output "
+                     (f"expert parallel ep{D}" + (f" x {G} groups of {D} GPUs (each group one copy of the routed experts)" if G > 1 else "")
+                      + f": expert e on rank e % {D}" + (" of its group" if G > 1 else "") + "; attention, router, shared expert and output "
                       f"projection replicated; " + ("exchange kernel over peer memory (peer stores + flags)" if peer_ok else
                                                     "NCCL all-reduce of the per-entry outputs") + f" once per block; {streams} token stream(s) per step"
+                      + (f" and group, {total_streams} in all" if G > 1 else "")
                       if ep else f"replicas x{world}"),
-                     "batch": streams, "windows": R, "window_ms_min_median_max": [min(times), ms, max(times)],
+                     "batch": total_streams, "windows": R, "window_ms_min_median_max": [min(times), ms, max(times)],
                      "algorithmic_bytes_per_token": bytes_tok,
                      "token_hbm_frac_of_peak": bytes_tok * K / (ms * 1e-3) / 1e9 / peak})
         nl = launches_per_token(model)
@@ -645,7 +662,7 @@ def run_ours(args, rank, world, local_rank):
                 "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
                 "scaling": "strong" if ep and args.strong else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": conf,
-                "e2e": {"value": streams * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8 * h_in.numel(),
+                "e2e": {"value": total_streams * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8 * h_in.numel(),
                         "d2h_bytes_per_step": 8 * h_out.numel()},
                 "gpu_launches": K * nl, "launches_per_token": nl,
                 "roofline": roof, **extras, "moe_only": moe_only,
@@ -795,6 +812,9 @@ def main():
                     help="N > 1: the per-block exchange, this library's peer-memory kernel or NCCL's all-reduce")
     ap.add_argument("--strong", action="store_true",
                     help="with --gpus N > 1: the same token streams for all ranks (strong scaling) instead of --batch per rank")
+    ap.add_argument("--ep-degree", type=int, default=0,
+                    help="with --gpus N > 1: GPUs that share one copy of the routed experts (N / degree groups run side by "
+                         "side); default min(N, 4)")
     ap.add_argument("--replicas", action="store_true",
                     help="with --gpus N > 1: N independent copies of the model instead of expert parallelism")
     args = ap.parse_args()
