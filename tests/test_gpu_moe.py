@@ -123,6 +123,24 @@ def test_prefill_block_many_rows(dev, N):
     assert tiled.debug_error() is None
 
 
+def test_many_token_plan_matches_one_cta_plan(dev):
+    """From 2048 entries (tokens x top-k) the routing plan runs as four launches over the SMs instead of one CTA.
+    1100 tokens (2200 entries) against the oracle, and the first 1000 rows bit-equal to a call with 1000 tokens
+    (2000 entries: the one-CTA plan) -- a token's output does not depend on the other tokens of the call."""
+    blk = cases.make_moe(911, 256, 128, 8, 2, I_shared=256, rank=16, experts_per_cluster=3)
+    mb = cases.to_b200_moe(blk, dev)
+    x = cases.make_x(912, 1100, 256).reshape(1, 1100, 256)
+    y, logits = mb(x.to(dev))
+    sel = mb.last_selected_experts.clone()
+    ref, ref_logits = O.moe_forward(cases.to_oracle_moe(blk), x)
+    assert cases.rel_l2(y.cpu().reshape(ref.shape), ref) <= REL_BLOCK
+    y2, _ = mb(x[:, :1000].contiguous().to(dev))
+    assert torch.equal(mb.last_selected_experts, sel[:1000])
+    assert torch.equal(y2.reshape(1000, -1), y.reshape(1100, -1)[:1000])
+    from glorcq_b200 import tiled
+    assert tiled.debug_error() is None
+
+
 def test_qwen_moe_shape_prefill(dev):
     blk = cases.make_moe(4242, 2048, 1408, 60, 4, I_shared=5632, rank=64, experts_per_cluster=4)
     mb, y, logits, ref, ref_logits = _run(blk, 128, dev, 4243)
