@@ -195,6 +195,54 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_kernel(
     }
 }
 
+// The prompt's form of the first half of attn_decode_kernel: per (token, head) one warp applies the optional RMS norm
+// and the rotary embedding at the token's position to q and k in place, and writes the new keys and values into the
+// static cache.  Same arithmetic (rope_norm) as the decode step.
+template <int EPL>
+__global__ void __launch_bounds__(kAttnWarps * 32) rope_prefill_kernel(
+    __half* __restrict__ q, __half* __restrict__ k, const __half* __restrict__ v, const __half* __restrict__ cos_t,
+    const __half* __restrict__ sin_t, const long long* __restrict__ positions, __half* __restrict__ k_cache,
+    __half* __restrict__ v_cache, int T, int n_heads, int n_kv, int max_len, const __half* __restrict__ q_norm_w,
+    const __half* __restrict__ k_norm_w, float eps) {
+    constexpr int HD = EPL * 32;
+    const int lane = threadIdx.x & 31, hw = blockIdx.y * kAttnWarps + (threadIdx.x >> 5);
+    if (hw >= n_heads + 2 * n_kv) return;
+    const int bt = blockIdx.x, b = bt / T, t = bt - b * T;
+    long long pos = positions[t];
+    if (pos < 0) pos = 0;
+    if (pos >= max_len) pos = max_len - 1;
+    const __half* cs = cos_t + (size_t)pos * HD;
+    const __half* sn = sin_t + (size_t)pos * HD;
+    float val[EPL];
+    if (hw < n_heads) {
+        __half* row = q + ((size_t)bt * n_heads + hw) * HD + lane * EPL;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) val[i] = __half2float(row[i]);
+        rope_norm<EPL>(val, q_norm_w, eps, HD, cs, sn, lane);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) row[i] = __float2half_rn(val[i]);
+    } else if (hw < n_heads + n_kv) {
+        const int kvh = hw - n_heads;
+        __half* row = k + ((size_t)bt * n_kv + kvh) * HD + lane * EPL;
+        __half* crow = k_cache + (((size_t)b * n_kv + kvh) * max_len + pos) * HD + lane * EPL;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) val[i] = __half2float(row[i]);
+        rope_norm<EPL>(val, k_norm_w, eps, HD, cs, sn, lane);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            const __half h = __float2half_rn(val[i]);
+            row[i] = h;
+            crow[i] = h;
+        }
+    } else {
+        const int kvh = hw - n_heads - n_kv;
+        const __half* row = v + ((size_t)bt * n_kv + kvh) * HD + lane * EPL;
+        __half* crow = v_cache + (((size_t)b * n_kv + kvh) * max_len + pos) * HD + lane * EPL;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) crow[i] = row[i];
+    }
+}
+
 // x_out = x + delta (fp16), h_out = rms_norm(x_out) * w: the residual add and the layer norm that follow the
 // attention output projection in a decoder layer, one CTA per row (H <= 8192, a multiple of 8).
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ delta,
@@ -296,5 +344,30 @@ extern "C" int glq_attn_decode(const void* q, const void* k_new, const void* v_n
         default: return GLQ_ERR_UNSUPPORTED;
     }
 #undef GLQ_ATTN
+    return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
+}
+
+extern "C" int glq_rope_prefill(void* q, void* k, const void* v, const void* cos_t, const void* sin_t, const int64_t* positions,
+                                void* k_cache, void* v_cache, int B, int T, int n_heads, int n_kv, int head_dim, int max_len,
+                                const void* q_norm_w, const void* k_norm_w, float eps, void* stream) {
+    if (!q || !k || !v || !cos_t || !sin_t || !positions || !k_cache || !v_cache) return GLQ_ERR_ARG;
+    if (B < 0 || T < 0 || n_heads <= 0 || n_kv <= 0 || max_len <= 0) return GLQ_ERR_ARG;
+    if (B == 0 || T == 0) return GLQ_OK;
+    const dim3 grid(B * T, (n_heads + 2 * n_kv + kAttnWarps - 1) / kAttnWarps);
+    auto st = reinterpret_cast<cudaStream_t>(stream);
+#define GLQ_ROPE_CASE(EPL)                                                                                                  \
+    rope_prefill_kernel<EPL><<<grid, kAttnWarps * 32, 0, st>>>(                                                             \
+        reinterpret_cast<__half*>(q), reinterpret_cast<__half*>(k), reinterpret_cast<const __half*>(v),                     \
+        reinterpret_cast<const __half*>(cos_t), reinterpret_cast<const __half*>(sin_t),                                     \
+        reinterpret_cast<const long long*>(positions), reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache), \
+        T, n_heads, n_kv, max_len, reinterpret_cast<const __half*>(q_norm_w), reinterpret_cast<const __half*>(k_norm_w), eps)
+    switch (head_dim) {
+        case 32: GLQ_ROPE_CASE(1); break;
+        case 64: GLQ_ROPE_CASE(2); break;
+        case 128: GLQ_ROPE_CASE(4); break;
+        case 256: GLQ_ROPE_CASE(8); break;
+        default: return GLQ_ERR_UNSUPPORTED;
+    }
+#undef GLQ_ROPE_CASE
     return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
 }

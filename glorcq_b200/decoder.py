@@ -125,9 +125,31 @@ class _Attention(nn.Module):
                     None if self.k_norm is None else self.k_norm.data_ptr(), float(c.rms_norm_eps),
                     ws.data_ptr(), ws.numel(), ctr.data_ptr(), ctr.numel(), tiled._stream_ptr(x.device)), "attn_decode")
             return self.o_proj(y.view(B, 1, -1))
-        q = self.q_proj(x).view(B, T, c.num_attention_heads, c.head_dim)
-        k = self.k_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
-        v = self.v_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
+        if self._qkv is not None and x.is_cuda:
+            # q, k and v of one shape: one grouped launch pair for the whole prompt too
+            q, k, v = self._qkv.forward(x.reshape(B * T, -1).contiguous())
+            q = q.view(B, T, c.num_attention_heads, c.head_dim)
+            k = k.view(B, T, c.num_key_value_heads, c.head_dim)
+            v = v.view(B, T, c.num_key_value_heads, c.head_dim)
+        else:
+            q = self.q_proj(x).view(B, T, c.num_attention_heads, c.head_dim)
+            k = self.k_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
+            v = self.v_proj(x).view(B, T, c.num_key_value_heads, c.head_dim)
+        if x.is_cuda and q.dtype == torch.float16 and c.head_dim in (32, 64, 128, 256) and cache_position.numel() == T:
+            # norms, rotary embedding and the cache write of the whole prompt in one launch
+            q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+            kc, vc = cache.k[self.layer_idx], cache.v[self.layer_idx]
+            with torch.cuda.device(x.device):
+                _lib.check(_lib.lib().glq_rope_prefill(
+                    q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                    cache_position.to(torch.int64).contiguous().data_ptr(), kc.data_ptr(), vc.data_ptr(), B, T,
+                    c.num_attention_heads, c.num_key_value_heads, c.head_dim, cache.max_cache_len,
+                    None if self.q_norm is None else self.q_norm.data_ptr(),
+                    None if self.k_norm is None else self.k_norm.data_ptr(), float(c.rms_norm_eps),
+                    tiled._stream_ptr(x.device)), "rope_prefill")
+            q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+            k_all, v_all = kc[:B], vc[:B]
+            return self._prompt_attention(q, k, v, k_all, v_all, cache, cache_position, kv_len, B, T)
         if self.q_norm is not None:
             q = F.rms_norm(q, (c.head_dim,), self.q_norm, c.rms_norm_eps)
             k = F.rms_norm(k, (c.head_dim,), self.k_norm, c.rms_norm_eps)
@@ -136,6 +158,10 @@ class _Attention(nn.Module):
         q = q * cs + _rotate_half(q) * sn
         k = k * cs + _rotate_half(k) * sn
         k_all, v_all = cache.update(self.layer_idx, k, v, cache_position)
+        return self._prompt_attention(q, k, v, k_all, v_all, cache, cache_position, kv_len, B, T)
+
+    def _prompt_attention(self, q, k, v, k_all, v_all, cache, cache_position, kv_len, B, T):
+        c = self.cfg
         gqa = c.num_key_value_heads != c.num_attention_heads
         if kv_len is not None and kv_len == T:
             # a prompt written at positions 0..T-1: causal attention over the new keys only
@@ -143,7 +169,7 @@ class _Attention(nn.Module):
         else:
             # position mask over the live part of the static cache: key j is visible to query t when j <= position(t)
             n_live = cache.max_cache_len if kv_len is None else kv_len
-            mask = torch.arange(n_live, device=x.device)[None, :] <= cache_position[:, None]
+            mask = torch.arange(n_live, device=q.device)[None, :] <= cache_position[:, None]
             y = F.scaled_dot_product_attention(q, k_all[:, :, :n_live], v_all[:, :, :n_live], attn_mask=mask[None, None],
                                                enable_gqa=gqa)
         return self.o_proj(y.transpose(1, 2).reshape(B, T, c.num_attention_heads * c.head_dim))

@@ -368,6 +368,14 @@ int glq_attn_decode(const void* q, const void* k_new, const void* v_new, const v
                     int head_dim, int max_len, const void* q_norm_w, const void* k_norm_w, float eps, void* workspace,
                     size_t workspace_bytes, int32_t* counters, size_t n_counters, void* stream);
 
+/* The prompt's form of the first half of glq_attn_decode: q (B, T, n_heads, head_dim) and k (B, T, n_kv, head_dim) get
+ * the optional per-head RMS norm and the rotary embedding of positions[t] in place; the new keys and v (B, T, n_kv,
+ * head_dim) are written into the static cache at positions[t] (host-model glue; the reference lets the transformers
+ * attention modules do this, inference/graph_wrapper.py:84-127).  head_dim 32, 64, 128 or 256. */
+int glq_rope_prefill(void* q, void* k, const void* v, const void* cos_t, const void* sin_t, const int64_t* positions,
+                     void* k_cache, void* v_cache, int B, int T, int n_heads, int n_kv, int head_dim, int max_len,
+                     const void* q_norm_w, const void* k_norm_w, float eps, void* stream);
+
 /* x_out = x + delta and h_out = rms_norm(x_out, eps) * weight on (rows, H) fp16 rows (weight (H,) fp16 or NULL):
  * the residual add and layer norm between the attention output projection and the MoE block of a decoder layer
  * (host-model glue, as glq_attn_decode).  H a multiple of 8, at most 8192. */
