@@ -146,6 +146,43 @@ def test_decoder_logits_prefill_and_decode(dev, cfg, cache_len):
     assert cases.rel_l2(step.cpu(), ref[:, T:]) <= REL_LOGITS
 
 
+@pytest.mark.parametrize("B,T,nh,nkv,hd,norms", [(1, 37, 4, 4, 128, False), (2, 19, 8, 2, 64, True), (1, 5, 2, 1, 32, True)])
+def test_rope_prefill_matches_tensor_ops(dev, B, T, nh, nkv, hd, norms):
+    """The prompt's norms + rotary embedding + cache write in one launch against the fp16 tensor operations it
+    replaces (same roundings: bit-equal), with positions that are not 0..T-1 and grouped-query head counts."""
+    import torch.nn.functional as F
+    from glorcq_b200 import _lib, tiled
+    from glorcq_b200.decoder import _rope_tables, _rotate_half
+    g = torch.Generator().manual_seed(B * 1000 + T)
+    max_len = 64
+    q = torch.randn(B, T, nh, hd, generator=g).half().to(dev)
+    k = torch.randn(B, T, nkv, hd, generator=g).half().to(dev)
+    v = torch.randn(B, T, nkv, hd, generator=g).half().to(dev)
+    qw = (torch.rand(hd, generator=g) + 0.5).half().to(dev) if norms else None
+    kw = (torch.rand(hd, generator=g) + 0.5).half().to(dev) if norms else None
+    pos = (torch.randperm(max_len, generator=g)[:T]).to(dev)
+    cos, sin = _rope_tables(hd, max_len, 10000.0, dev)
+    qr, kr = q, k
+    if norms:
+        qr, kr = F.rms_norm(q, (hd,), qw, 1e-6), F.rms_norm(k, (hd,), kw, 1e-6)
+    cs, sn = cos[pos][None, :, None], sin[pos][None, :, None]
+    qr = qr * cs + _rotate_half(qr) * sn
+    kr = kr * cs + _rotate_half(kr) * sn
+    kc = torch.zeros(B, nkv, max_len, hd, dtype=torch.float16, device=dev)
+    vc = torch.zeros_like(kc)
+    q2, k2 = q.clone(), k.clone()
+    _lib.check(_lib.lib().glq_rope_prefill(q2.data_ptr(), k2.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                           pos.data_ptr(), kc.data_ptr(), vc.data_ptr(), B, T, nh, nkv, hd, max_len,
+                                           None if qw is None else qw.data_ptr(), None if kw is None else kw.data_ptr(),
+                                           1e-6, tiled._stream_ptr(dev)), "rope_prefill")
+    torch.cuda.synchronize()
+    assert torch.equal(q2, qr) and torch.equal(k2, kr)
+    assert torch.equal(kc[:, :, pos], kr.transpose(1, 2)) and torch.equal(vc[:, :, pos], v.transpose(1, 2))
+    rest = torch.ones(max_len, dtype=torch.bool, device=dev)
+    rest[pos] = False
+    assert not kc[:, :, rest].any() and not vc[:, :, rest].any()
+
+
 @pytest.mark.parametrize("B,V,H", [(1, 151936, 2048), (8, 151936, 2048), (3, 1000, 64), (5, 32000, 4096), (1, 17, 32)])
 def test_lm_head_logits_and_argmax(dev, B, V, H):
     """glq_lm_head through the C ABI against the fp32 product of the same fp16 operands: logits within one
