@@ -101,6 +101,12 @@ class _Attention(nn.Module):
         if all(t is not None for t in tl) and len({(t.fmt, t.N, t.K, t.group_size, t.rank) for t in tl}) == 1 and \
                 (all(u is not None for u in uts) or all(u is None for u in uts)):
             self._qkv = tiled.GroupedLinear(tl, uts if uts[0] is not None else None)
+        # grouped-query attention: k and v still share a shape -- one launch pair for the two
+        self._kv = None
+        if self._qkv is None and all(t is not None for t in tl[1:]) and \
+                len({(t.fmt, t.N, t.K, t.group_size, t.rank) for t in tl[1:]}) == 1 and \
+                (all(u is not None for u in uts[1:]) or all(u is None for u in uts[1:])):
+            self._kv = tiled.GroupedLinear(tl[1:], uts[1:] if uts[1] is not None else None)
 
     def forward(self, x, cache_position, cache: StaticKVCache, cos, sin, kv_len=None):
         c = self.cfg
@@ -110,6 +116,9 @@ class _Attention(nn.Module):
             # one launch; the position stays on the device (graph replay)
             if self._qkv is not None:
                 q, k, v = self._qkv.forward(x.view(B, -1).contiguous())
+            elif self._kv is not None:
+                q = self.q_proj(x).view(B, -1)
+                k, v = self._kv.forward(x.view(B, -1).contiguous())
             else:
                 q, k, v = self.q_proj(x).view(B, -1), self.k_proj(x).view(B, -1), self.v_proj(x).view(B, -1)
             y = torch.empty_like(q)
@@ -129,6 +138,11 @@ class _Attention(nn.Module):
             # q, k and v of one shape: one grouped launch pair for the whole prompt too
             q, k, v = self._qkv.forward(x.reshape(B * T, -1).contiguous())
             q = q.view(B, T, c.num_attention_heads, c.head_dim)
+            k = k.view(B, T, c.num_key_value_heads, c.head_dim)
+            v = v.view(B, T, c.num_key_value_heads, c.head_dim)
+        elif self._kv is not None and x.is_cuda:
+            q = self.q_proj(x).view(B, T, c.num_attention_heads, c.head_dim)
+            k, v = self._kv.forward(x.reshape(B * T, -1).contiguous())
             k = k.view(B, T, c.num_key_value_heads, c.head_dim)
             v = v.view(B, T, c.num_key_value_heads, c.head_dim)
         else:
