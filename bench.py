@@ -301,7 +301,9 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50, fmt="q2"):
     achieved = P * per / sec / 1e9
     t240 = profiled_traffic("gemv_stream_kernel_q2_240x1408x2048.md") if fmt == "q2" else None   # ncu capture, P = 240
     names = {"q2": ("stream_kernel<Q2,int8 path>", "2-bit g128"), "q4": ("stream_kernel<Q4,int8 path>", "4-bit g128"),
-             "t2": ("stream_kernel<T2,fp16 path>", "2-bit codebook")}[fmt]
+             "t2": ("stream_kernel<T2,int8 path>", "2-bit codebook")}[fmt]
+    if os.environ.get("GLQ_NO_I8", "")[:1] == "1":      # the library's switch back to the fp16 path
+        names = (names[0].replace("int8 path", "fp16 path"), names[1])
     return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
             "traffic": None if t240 is None else t240 * P / 240.0,
             "kernel": f"{names[0]} (grouped dequant-GEMV)",

@@ -266,9 +266,8 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
         if (group_size <= 0 || group_size % kb != 0) return false;
         group_blocks = group_size / kb;
     }
-    const bool affine = fmt != GLQ_FMT_T2;
     int rows;
-    if (affine && max_rows <= 8 && !i8_disabled()) {
+    if (max_rows <= 8 && !i8_disabled()) {
         g.i8 = 1;
         g.nt = max_rows <= 4 ? 1 : 2;
         rows = 4 * g.nt;
@@ -299,7 +298,7 @@ static bool plan_stream(int fmt, int epilogue, int N, int K, int rank, int group
         off = (off + 127) / 128 * 128;
         g.off_xs = (int)off;
         if (g.i8) {
-            const int p8 = fmt == GLQ_FMT_Q2 ? 2 : 1;
+            const int p8 = fmt == GLQ_FMT_Q4 ? 1 : 2;
             off += (size_t)g.nkb * p8 * (2 * rows) * 4 * 16;
             g.off_ox = (int)off;
             off += (size_t)g.nkb * rows * 8;
@@ -366,11 +365,9 @@ static int launch_stream_one(const StreamParams& sp, const StreamGeom& g, cudaSt
 
 template <int FMT>
 static int launch_stream_fmt(const StreamParams& sp, const StreamGeom& g, cudaStream_t st) {
-    if constexpr (FMT != GLQ_FMT_T2) {
-        if (g.i8) {
-            if (g.nt == 1) return launch_stream_one<FMT, true, 1>(sp, g, st);
-            return launch_stream_one<FMT, true, 2>(sp, g, st);
-        }
+    if (g.i8) {
+        if (g.nt == 1) return launch_stream_one<FMT, true, 1>(sp, g, st);
+        return launch_stream_one<FMT, true, 2>(sp, g, st);
     }
     if (g.nt == 1) return launch_stream_one<FMT, false, 1>(sp, g, st);
     if (g.nt == 2) return launch_stream_one<FMT, false, 2>(sp, g, st);

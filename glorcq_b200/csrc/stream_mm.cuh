@@ -208,7 +208,7 @@ __device__ __forceinline__ void stage_x_i8(const SkinnyParams& p, uint4* xs, flo
         if (valid) {
             uint4 lo, hi;  // digit 0, digit 1
             int t, piece;
-            if constexpr (FMT == GLQ_FMT_Q2) {
+            if constexpr (FMT != GLQ_FMT_Q4) {
                 t = wi >> 1;
                 piece = wi & 1;
                 lo = make_uint4(pack4(d0, 0, 4, 8, 12), pack4(d0, 1, 5, 9, 13), pack4(d0, 2, 6, 10, 14),
@@ -293,7 +293,7 @@ __device__ __forceinline__ void tile_block_i8(const uint4 q, const uint4 (&bx)[N
                 imma16832(c[nt], a2, b2, a3, b3, x.z, x.w, c[nt][0], c[nt][1], c[nt][2], c[nt][3]);
             }
         }
-    } else {  // Q4: a word holds 8 codes = the A operand of one op
+    } else if constexpr (FMT == GLQ_FMT_Q4) {  // a word holds 8 codes = the A operand of one op
         const uint32_t m = 0x0F0F0F0Fu;
         const uint32_t a0 = q.x & m, a1 = (q.x >> 4) & m, a2 = q.y & m, a3 = (q.y >> 4) & m;
         const uint32_t b0 = q.z & m, b1 = (q.z >> 4) & m, b2 = q.w & m, b3 = (q.w >> 4) & m;
@@ -306,14 +306,60 @@ __device__ __forceinline__ void tile_block_i8(const uint4 q, const uint4 (&bx)[N
     }
 }
 
+// ---- integer path of the codebook format -----------------------------------------------------------
+// A 4-entry codebook is c(q) = c0 + d0*q + dh*(2*b1) + e*(b0 & b1) with q = b0 + 2*b1 the code,
+// d0 = c1 - c0, dh = (c2 - c0)/2 - d0, e = c3 - c2 - c1 + c0.  A symmetric codebook (-a, -b, b, a) has
+// e = 0: two integer products per k block, codes against digits (cq) and the high code bits against
+// digits (cb); the third (ce) is computed only for a codebook with e != 0 (warp-uniform).
+template <int NT>
+__device__ __forceinline__ void tile_block_t2_i8(const uint4 q, const uint4 (&bx)[NT][2], bool cross,
+                                                 int (&cq)[NT][4], int (&cb)[NT][4], int (&ce)[NT][4]) {
+    const uint32_t m = 0x03030303u, mh = 0x02020202u, m1 = 0x01010101u;
+    const uint32_t wa[2] = {q.x, q.y}, wb[2] = {q.z, q.w};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t a0 = wa[u] & m, a1 = (wa[u] >> 2) & m, a2 = (wa[u] >> 4) & m, a3 = (wa[u] >> 6) & m;
+        const uint32_t b0 = wb[u] & m, b1 = (wb[u] >> 2) & m, b2 = (wb[u] >> 4) & m, b3 = (wb[u] >> 6) & m;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint4 x = bx[nt][u];
+            if (u == 0) {
+                imma16832(cq[nt], a0, b0, a1, b1, x.x, x.y, 0, 0, 0, 0);
+                imma16832(cb[nt], a0 & mh, b0 & mh, a1 & mh, b1 & mh, x.x, x.y, 0, 0, 0, 0);
+            } else {
+                imma16832(cq[nt], a0, b0, a1, b1, x.x, x.y, cq[nt][0], cq[nt][1], cq[nt][2], cq[nt][3]);
+                imma16832(cb[nt], a0 & mh, b0 & mh, a1 & mh, b1 & mh, x.x, x.y, cb[nt][0], cb[nt][1], cb[nt][2],
+                          cb[nt][3]);
+            }
+            imma16832(cq[nt], a2, b2, a3, b3, x.z, x.w, cq[nt][0], cq[nt][1], cq[nt][2], cq[nt][3]);
+            imma16832(cb[nt], a2 & mh, b2 & mh, a3 & mh, b3 & mh, x.z, x.w, cb[nt][0], cb[nt][1], cb[nt][2],
+                      cb[nt][3]);
+        }
+        if (cross) {
+            const uint32_t e0 = a0 & (a0 >> 1) & m1, e1 = a1 & (a1 >> 1) & m1, e2 = a2 & (a2 >> 1) & m1,
+                           e3 = a3 & (a3 >> 1) & m1;
+            const uint32_t f0 = b0 & (b0 >> 1) & m1, f1 = b1 & (b1 >> 1) & m1, f2 = b2 & (b2 >> 1) & m1,
+                           f3 = b3 & (b3 >> 1) & m1;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint4 x = bx[nt][u];
+                if (u == 0)
+                    imma16832(ce[nt], e0, f0, e1, f1, x.x, x.y, 0, 0, 0, 0);
+                else
+                    imma16832(ce[nt], e0, f0, e1, f1, x.x, x.y, ce[nt][0], ce[nt][1], ce[nt][2], ce[nt][3]);
+                imma16832(ce[nt], e2, f2, e3, f3, x.z, x.w, ce[nt][0], ce[nt][1], ce[nt][2], ce[nt][3]);
+            }
+        }
+    }
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------
-// I8 = true : NT tiles of 4 activation rows (integer path, affine formats only)
+// I8 = true : NT tiles of 4 activation rows (integer path: affine formats and the 2-bit codebook)
 // I8 = false: NT tiles of 8 activation rows (fp16 path)
 template <int FMT, bool I8, int NT>
 __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(const StreamParams sp) {
     using F = Fmt<FMT>;
     static_assert(FMT != GLQ_FMT_F16, "dense weights use the fallback kernel");
-    static_assert(!I8 || FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4, "integer path needs integer codes");
     constexpr bool kAffine = (FMT == GLQ_FMT_Q2 || FMT == GLQ_FMT_Q4);
     constexpr int BB = block_bytes<FMT>();
     constexpr int kPieces = I8 ? F::UPK / 4 : F::XS / 4;  // uint4 fragments per k block, lane and column
@@ -467,6 +513,9 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
     while (f_live && f_inflight < S) fetch_one();
 
     uint32_t TL[2] = {0, 0}, TH[2] = {0, 0};  // codebook tables of the two tiles of a pair
+    // integer path of the codebook format: coefficients of the two tiles' codebooks (tile_block_t2_i8)
+    float cb_c0[2] = {0.f, 0.f}, cb_d0[2] = {0.f, 0.f}, cb_dh[2] = {0.f, 0.f}, cb_e[2] = {0.f, 0.f};
+    bool cb_cross = false;
     int staged_slot = -1, red_par = 0;
     bool dep_waited = false;
     constexpr int ncol_i8 = 2 * kRows;  // digit columns staged on the integer path
@@ -502,8 +551,28 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
             staged_slot = im.slot;
             if constexpr (FMT == GLQ_FMT_T2) {
                 // a fused gate|up weight carries two codebooks (4 floats each)
-                make_t2_tables(cs.centroids, TL[0], TH[0]);
-                make_t2_tables(cs.centroids + (swiglu ? 4 : 0), TL[1], TH[1]);
+                if constexpr (I8) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float* cbk = cs.centroids + ((j && swiglu) ? 4 : 0);
+                        const float c0 = __ldg(cbk), c1 = __ldg(cbk + 1), c2 = __ldg(cbk + 2), c3 = __ldg(cbk + 3);
+                        cb_c0[j] = c0;
+                        cb_d0[j] = c1 - c0;
+                        cb_dh[j] = 0.5f * (c2 - c0) - (c1 - c0);
+                        cb_e[j] = (c3 - c2) - (c1 - c0);
+                    }
+                    // a cross term below 2^-22 of the codebook's span (the residue of an iterative codebook
+                    // fit) is dropped: its share of an output is below 2^-16 of the output for K <= 2^16
+                    cb_cross = false;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float span = fabsf(cb_c0[j]) + fabsf(cb_c0[j] + cb_d0[j]) + fabsf(cb_dh[j]);
+                        if (fabsf(cb_e[j]) > span * 2.384185791015625e-7f) cb_cross = true;
+                    }
+                } else {
+                    make_t2_tables(cs.centroids, TL[0], TH[0]);
+                    make_t2_tables(cs.centroids + (swiglu ? 4 : 0), TL[1], TH[1]);
+                }
             }
         }
         if (!im.valid) continue;
@@ -545,19 +614,40 @@ __global__ void __launch_bounds__(kThreads, kStreamCtasPerSm) stream_kernel(cons
                     for (int j = 0; j < 2; ++j) {
                         const uint32_t blk = st + (uint32_t)((b * 2 + j) * BB);
                         const uint4 q = lds128(blk + lane * 16);
-                        const uint2 szv = lds64(blk + 512 + g * 8);
-                        int ci[NT][4];
-                        tile_block_i8<FMT, NT>(q, bx, ci);
-                        const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv.x);
-                        const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv.y);
-                        const float s0 = __low2float(sz0), z0 = __high2float(sz0);
-                        const float s1 = __low2float(sz1), z1 = __high2float(sz1);
+                        if constexpr (FMT == GLQ_FMT_T2) {
+                            int cq[NT][4], cb[NT][4], ce[NT][4];
+                            tile_block_t2_i8<NT>(q, bx, cb_cross, cq, cb, ce);
 #pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            const float f0 = (float)(ci[nt][0] + (ci[nt][1] << 8)) * o[nt].x;
-                            const float f1 = (float)(ci[nt][2] + (ci[nt][3] << 8)) * o[nt].x;
-                            acc[j][nt][0] = fmaf(s0, fmaf(-z0, o[nt].y, f0), acc[j][nt][0]);
-                            acc[j][nt][2] = fmaf(s1, fmaf(-z1, o[nt].y, f1), acc[j][nt][2]);
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const float kd = cb_d0[j] * o[nt].x, kh = cb_dh[j] * o[nt].x;
+                                const float base = cb_c0[j] * o[nt].y;
+                                float v0 = fmaf(kd, (float)(cq[nt][0] + (cq[nt][1] << 8)),
+                                                fmaf(kh, (float)(cb[nt][0] + (cb[nt][1] << 8)), base));
+                                float v1 = fmaf(kd, (float)(cq[nt][2] + (cq[nt][3] << 8)),
+                                                fmaf(kh, (float)(cb[nt][2] + (cb[nt][3] << 8)), base));
+                                if (cb_cross) {
+                                    const float ke = cb_e[j] * o[nt].x;
+                                    v0 = fmaf(ke, (float)(ce[nt][0] + (ce[nt][1] << 8)), v0);
+                                    v1 = fmaf(ke, (float)(ce[nt][2] + (ce[nt][3] << 8)), v1);
+                                }
+                                acc[j][nt][0] += v0;
+                                acc[j][nt][2] += v1;
+                            }
+                        } else {
+                            const uint2 szv = lds64(blk + 512 + g * 8);
+                            int ci[NT][4];
+                            tile_block_i8<FMT, NT>(q, bx, ci);
+                            const __half2 sz0 = *reinterpret_cast<const __half2*>(&szv.x);
+                            const __half2 sz1 = *reinterpret_cast<const __half2*>(&szv.y);
+                            const float s0 = __low2float(sz0), z0 = __high2float(sz0);
+                            const float s1 = __low2float(sz1), z1 = __high2float(sz1);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const float f0 = (float)(ci[nt][0] + (ci[nt][1] << 8)) * o[nt].x;
+                                const float f1 = (float)(ci[nt][2] + (ci[nt][3] << 8)) * o[nt].x;
+                                acc[j][nt][0] = fmaf(s0, fmaf(-z0, o[nt].y, f0), acc[j][nt][0]);
+                                acc[j][nt][2] = fmaf(s1, fmaf(-z1, o[nt].y, f1), acc[j][nt][2]);
+                            }
                         }
                     }
                 } else {

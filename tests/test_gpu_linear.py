@@ -196,6 +196,23 @@ def test_linear_turbo_with_rotation(dev):
     assert cases.rel_l2(lin(x.to(dev), precomputed_x_rot=xr.to(dev)).cpu(), ref) <= REL
 
 
+@pytest.mark.parametrize("B", [1, 3, 8, 13])
+@pytest.mark.parametrize("N,K,rank", [(1408, 2048, 64), (2048, 1408, 64), (52, 192, 16)])
+@pytest.mark.parametrize("residue", [0.0, 2e-7])
+def test_linear_turbo_symmetric_codebook(dev, N, K, rank, B, residue):
+    """A codebook (-a, -b, b, a), the shape a Lloyd-Max fit of a symmetric density gives (exactly, or up to the
+    residue of the fit's last iteration): up to 8 rows take the integer path with two integer products per
+    block; the sorted random codebooks of the other cases take its three-product form."""
+    d = cases.make_linear(900 + N + B, N, K, rank=rank, fmt="turbo")
+    c = torch.tensor([-1.51, -0.4528, 0.4528, 1.51], dtype=torch.float64) / K ** 0.5
+    c[3] += residue * c[3]
+    d["centroids"] = c.float()
+    lin = cases.to_b200_linear(d, dev)
+    x = cases.make_x(901 + B, B, K)
+    ref = O.linear_forward(cases.to_oracle_linear(d), x, x_rot_half=True)
+    assert cases.rel_l2(lin(x.to(dev)).cpu(), ref) <= REL
+
+
 def test_shared_u_is_tiled_once(dev):
     from glorcq_b200 import tiled
     blk = cases.make_moe(77, 256, 128, 4, 2, rank=16, experts_per_cluster=2)
