@@ -299,7 +299,8 @@ def gemv_roofline(dev, peak_gbs, peak_kind, P=240, iters=50, fmt="q2"):
     else:
         per = N * K * (4 if fmt == "q4" else 2) // 8 + N * (K // 128) * 4 + N * r * 2 + K * 2 + r * 2 + N * 2
     achieved = P * per / sec / 1e9
-    t240 = profiled_traffic("gemv_stream_kernel_q2_240x1408x2048.md") if fmt == "q2" else None   # ncu capture, P = 240
+    # ncu captures at P = 240 (none for the 4-bit launch)
+    t240 = profiled_traffic(f"gemv_stream_kernel_{fmt}_240x1408x2048.md") if fmt in ("q2", "t2") else None
     names = {"q2": ("stream_kernel<Q2,int8 path>", "2-bit g128"), "q4": ("stream_kernel<Q4,int8 path>", "4-bit g128"),
              "t2": ("stream_kernel<T2,int8 path>", "2-bit codebook")}[fmt]
     if os.environ.get("GLQ_NO_I8", "")[:1] == "1":      # the library's switch back to the fp16 path
