@@ -731,7 +731,8 @@ def prefill_alone(dev, cfg, prompt, reps=5, profile=False):
     tf = per_tok * layers * prompt / (ms * 1e-3) / 1e12
     return {"prompt_tokens": prompt, "ms": ms, "tok_s": prompt / (ms * 1e-3), "quantized_products_tflops": tf,
             "frac_of_bf16_peak": tf / peak, "peak_kind": kind, "layers": layers,
-            "note": "whole prompt pass incl. attention (library call), norms, routing and the output projection of the last token"}
+            "note": "whole prompt pass incl. attention (glq_attn_prefill below 2048 tokens, the library call from there), "
+                    "norms, routing and the output projection of the last token"}
 
 
 def moe_blocks_alone(model, dev, cfg, layers, steps=100):

@@ -97,6 +97,7 @@ _SIGS = {
     "glq_attn_decode_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "glq_rope_prefill": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
                          C.c_float, vp]),
+    "glq_attn_prefill": (C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "glq_attn_decode": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp,
                                   C.c_float, vp, C.c_size_t, vp, C.c_size_t, vp]),
     "glq_lm_head_workspace_bytes": (C.c_size_t, []),

@@ -243,6 +243,209 @@ __global__ void __launch_bounds__(kAttnWarps * 32) rope_prefill_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Causal attention of a prompt written at positions 0..T-1: y[t] = softmax(q[t] . k[0..t]^T / sqrt(hd)) v[0..t] per
+// (batch, head), keys and values of the head's group (grouped-query attention).  One CTA = 64 queries of one head
+// (four warps x 16 rows), key blocks of 64 up to the diagonal only; scores and the weighted values on the fp16
+// `mma.m16n8k16` op with fp32 accumulators, softmax in base 2 with a running row maximum and row sum in registers
+// (the probabilities are rounded to fp16 as the second product's operand), key / value blocks double-buffered in
+// shared memory by 16-byte asynchronous copies (rows past T arrive as zeros).  q (B, T, n_heads, HD),
+// k / v (B, T, n_kv, HD), y (B, T, n_heads, HD): the layout the projections write and the output projection reads.
+// (inference/graph_wrapper.py:84-127 leaves this to the transformers attention modules.)
+template <int HD>
+struct PrefillCfg {
+    static constexpr int BM = 64, BN = 64, LD = HD + 8;          // 16-byte pad per row: conflict-free fragment reads
+    static constexpr int STAGE = 2 * BN * LD;                    // halfs per stage: keys, then values
+    static constexpr size_t SMEM = (size_t)2 * STAGE * sizeof(__half);
+};
+
+__device__ __forceinline__ uint32_t pf_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool live) {
+    const int bytes = live ? 16 : 0;     // 0: the 16 bytes are filled with zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
+                                                           const __half* __restrict__ v, __half* __restrict__ y, int T,
+                                                           int n_heads, int n_kv) {
+    using C = PrefillCfg<HD>;
+    constexpr int LD = C::LD, KS = HD / 16, NT = HD / 8;
+    extern __shared__ __align__(16) unsigned char pf_smem[];
+    __half* sm = reinterpret_cast<__half*>(pf_smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;       // the longest rows first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / (n_heads / n_kv);
+    const int q0 = qb * C::BM + warp * 16;                      // first query row of this warp
+    const __half* kbase = k + ((size_t)b * T * n_kv + kvh) * HD;
+    const __half* vbase = v + ((size_t)b * T * n_kv + kvh) * HD;
+    const size_t kv_row = (size_t)n_kv * HD;
+
+    auto load_block = [&](int kb, int stage) {
+        __half* ks = sm + (size_t)stage * C::STAGE;
+        __half* vs = ks + C::BN * LD;
+        for (int idx = tid; idx < C::BN * (HD / 8); idx += 128) {
+            const int r = idx / (HD / 8), c = idx % (HD / 8);
+            const int key = kb * C::BN + r;
+            const bool live = key < T;
+            const size_t off = (size_t)(live ? key : 0) * kv_row + c * 8;
+            cp_async_16(pf_smem_addr(ks + r * LD + c * 8), kbase + off, live);
+            cp_async_16(pf_smem_addr(vs + r * LD + c * 8), vbase + off, live);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const int nkb = qb + 1;            // key blocks 0 .. qb (BM == BN)
+    load_block(0, 0);
+
+    // the warp's 16 query rows as the first operand's fragments: rows g and g + 8, channels 16*ks + 2t (+8)
+    uint32_t qf[KS][4];
+    {
+        const int r0 = q0 + g, r1 = q0 + g + 8;
+        const __half* p0 = q + (((size_t)b * T + min(r0, T - 1)) * n_heads + h) * HD;
+        const __half* p1 = q + (((size_t)b * T + min(r1, T - 1)) * n_heads + h) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = r0 < T ? *reinterpret_cast<const uint32_t*>(p0 + 16 * ks + 2 * t) : 0u;
+            qf[ks][1] = r1 < T ? *reinterpret_cast<const uint32_t*>(p1 + 16 * ks + 2 * t) : 0u;
+            qf[ks][2] = r0 < T ? *reinterpret_cast<const uint32_t*>(p0 + 16 * ks + 8 + 2 * t) : 0u;
+            qf[ks][3] = r1 < T ? *reinterpret_cast<const uint32_t*>(p1 + 16 * ks + 8 + 2 * t) : 0u;
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;     // rows g and g + 8: running maximum, this lane's share of the sum
+    const float sc = rsqrtf((float)HD) * 1.4426950408889634f;     // scores in base 2
+
+    for (int kb = 0; kb < nkb; ++kb) {
+        if (kb + 1 < nkb) {
+            load_block(kb + 1, (kb + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __half* ks_ = sm + (size_t)(kb & 1) * C::STAGE;
+        const __half* vs_ = ks_ + C::BN * LD;
+        // a warp whose rows all lie before this key block has nothing to add (only in the diagonal block, never)
+        float sacc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sacc[j][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            // keys as the second operand: 8x8 matrix loads, rows = keys (two 8-key tiles x two channel halves each)
+            const int krow = (lane & 7) + (lane >> 4) * 8, kcol = 16 * ks + ((lane >> 3) & 1) * 8;
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(pf_smem_addr(ks_ + (16 * jp + krow) * LD + kcol), b0, b1, b2, b3);
+                mma16816(sacc[2 * jp], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                mma16816(sacc[2 * jp + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+            }
+        }
+        // scale; the diagonal block hides keys after the query and keys past T
+        const bool diag = kb == nkb - 1;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float sv = sacc[j][e] * sc;
+                if (diag) {
+                    const int key = kb * C::BN + 8 * j + 2 * t + (e & 1);
+                    const int row = q0 + g + 8 * (e >> 1);
+                    if (key > row || key >= T) sv = -INFINITY;
+                }
+                sacc[j][e] = sv;
+                if (e < 2) mx0 = fmaxf(mx0, sv);
+                else mx1 = fmaxf(mx1, sv);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        // a row with nothing visible so far keeps a zero offset (its probabilities are all exp2(-inf) = 0)
+        const float f0 = n0 == -INFINITY ? 0.f : n0, f1 = n1 == -INFINITY ? 0.f : n1;
+        const float a0 = exp2f(m0 - f0), a1 = exp2f(m1 - f1);
+        m0 = n0;
+        m1 = n1;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sacc[j][0] = exp2f(sacc[j][0] - f0);
+            sacc[j][1] = exp2f(sacc[j][1] - f0);
+            sacc[j][2] = exp2f(sacc[j][2] - f1);
+            sacc[j][3] = exp2f(sacc[j][3] - f1);
+            s0 += sacc[j][0] + sacc[j][1];
+            s1 += sacc[j][2] + sacc[j][3];
+        }
+        l0 = l0 * a0 + s0;
+        l1 = l1 * a1 + s1;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            o[j][0] *= a0;
+            o[j][1] *= a0;
+            o[j][2] *= a1;
+            o[j][3] *= a1;
+        }
+        // weighted values: probabilities as the first operand (keys 16*kk .. +15), values through transposing
+        // 8x8 matrix loads (rows = keys, two 8-channel tiles per instruction)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t pa0 = pack_half2(sacc[2 * kk][0], sacc[2 * kk][1]);
+            const uint32_t pa1 = pack_half2(sacc[2 * kk][2], sacc[2 * kk][3]);
+            const uint32_t pa2 = pack_half2(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+            const uint32_t pa3 = pack_half2(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+            const int vrow = 16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+            for (int jp = 0; jp < NT / 2; ++jp) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(pf_smem_addr(vs_ + vrow * LD + 16 * jp + (lane >> 4) * 8), b0, b1, b2, b3);
+                mma16816(o[2 * jp], pa0, pa1, pa2, pa3, b0, b1);
+                mma16816(o[2 * jp + 1], pa0, pa1, pa2, pa3, b2, b3);
+            }
+        }
+        __syncthreads();          // the stage is overwritten by the copy issued in the next iteration
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    const int r0 = q0 + g, r1 = q0 + g + 8;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        if (r0 < T)
+            *reinterpret_cast<uint32_t*>(y + (((size_t)b * T + r0) * n_heads + h) * HD + 8 * j + 2 * t) =
+                pack_half2(o[j][0] * i0, o[j][1] * i0);
+        if (r1 < T)
+            *reinterpret_cast<uint32_t*>(y + (((size_t)b * T + r1) * n_heads + h) * HD + 8 * j + 2 * t) =
+                pack_half2(o[j][2] * i1, o[j][3] * i1);
+    }
+}
+
 // x_out = x + delta (fp16), h_out = rms_norm(x_out) * w: the residual add and the layer norm that follow the
 // attention output projection in a decoder layer, one CTA per row (H <= 8192, a multiple of 8).
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ delta,
@@ -369,5 +572,36 @@ extern "C" int glq_rope_prefill(void* q, void* k, const void* v, const void* cos
         default: return GLQ_ERR_UNSUPPORTED;
     }
 #undef GLQ_ROPE_CASE
+    return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
+}
+
+extern "C" int glq_attn_prefill(const void* q, const void* k, const void* v, void* y, int B, int T, int n_heads, int n_kv,
+                                int head_dim, void* stream) {
+    if (!q || !k || !v || !y) return GLQ_ERR_ARG;
+    if (B < 0 || T < 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return GLQ_ERR_ARG;
+    if (B == 0 || T == 0) return GLQ_OK;
+    if (head_dim != 64 && head_dim != 128) return GLQ_ERR_UNSUPPORTED;
+    if (B > 65535 || n_heads > 65535) return GLQ_ERR_UNSUPPORTED;
+    for (const void* ptr : {q, k, v, (const void*)y})
+        if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return GLQ_ERR_ALIGN;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const dim3 grid((T + 63) / 64, n_heads, B);
+#define GLQ_PREFILL(HD)                                                                                                  \
+    {                                                                                                                    \
+        static bool configured[64] = {};                                                                                 \
+        int dev = 0;                                                                                                     \
+        if (cudaGetDevice(&dev) != cudaSuccess) return GLQ_ERR_CUDA;                                                     \
+        if (dev < 0 || dev >= 64 || !configured[dev]) {                                                                  \
+            if (cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,               \
+                                     (int)PrefillCfg<HD>::SMEM) != cudaSuccess)                                          \
+                return GLQ_ERR_CUDA;                                                                                     \
+            if (dev >= 0 && dev < 64) configured[dev] = true;                                                            \
+        }                                                                                                                \
+        attn_prefill_kernel<HD><<<grid, 128, PrefillCfg<HD>::SMEM, st>>>(                                                \
+            reinterpret_cast<const __half*>(q), reinterpret_cast<const __half*>(k), reinterpret_cast<const __half*>(v),  \
+            reinterpret_cast<__half*>(y), T, n_heads, n_kv);                                                             \
+    }
+    if (head_dim == 64) GLQ_PREFILL(64) else GLQ_PREFILL(128)
+#undef GLQ_PREFILL
     return cudaGetLastError() == cudaSuccess ? GLQ_OK : GLQ_ERR_CUDA;
 }

@@ -11,9 +11,11 @@ shared expert) layouts.
 The quantized projections and the MoE block run on this package's kernels, and so does the attention
 of a decode step (``glq_attn_decode``: q/k norms, rotary embedding, cache write and attention over the
 live positions in one launch) and the fp16 ``lm_head`` product of up to 64 rows (``glq_lm_head``: a streaming
-kernel over the row-major vocabulary matrix with the greedy arg-max folded in).  The first layer norm, the
-embedding lookup, the prompt's attention (``scaled_dot_product_attention``, causal over the new keys) and the
-logits of a whole prompt are plain library calls.
+kernel over the row-major vocabulary matrix with the greedy arg-max folded in).  A prompt written at positions
+0..T-1 runs its norms, rotary embedding and cache write in ``glq_rope_prefill`` and its causal attention in
+``glq_attn_prefill`` (head sizes 64 and 128; prompts of 2048 tokens and more, where the library's kernel is
+measurably faster, and prompts appended to a filled cache go through ``scaled_dot_product_attention``).  The first
+layer norm, the embedding lookup and the logits of a whole prompt are plain library calls.
 """
 
 from __future__ import annotations
@@ -25,9 +27,17 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+import os
+
 from . import _lib, tiled
 from .moe_block import GraphCompatibleMoeBlock
 from .quantized_linear import GLoRCQLinear
+
+# Prompts of at least this many tokens hand their causal attention to the library call instead of
+# glq_attn_prefill (GLQ_PROMPT_ATTN_LIBRARY_FROM; 0 = always the library, a huge value = never).  Measured on the
+# 24-layer model, whole prompt pass with this kernel / with the library: 512 tokens 15.5 / 15.5 ms, 1024: 19.0 / 18.7,
+# 2048: 28.2 / 26.6, 4096: 50.4 / 43.6.
+_PROMPT_ATTN_LIBRARY_FROM = int(os.environ.get("GLQ_PROMPT_ATTN_LIBRARY_FROM", "2048"))
 
 
 class StaticKVCache:
@@ -161,6 +171,14 @@ class _Attention(nn.Module):
                     None if self.q_norm is None else self.q_norm.data_ptr(),
                     None if self.k_norm is None else self.k_norm.data_ptr(), float(c.rms_norm_eps),
                     tiled._stream_ptr(x.device)), "rope_prefill")
+            if kv_len is not None and kv_len == T and c.head_dim in (64, 128) and T < _PROMPT_ATTN_LIBRARY_FROM:
+                # a prompt written at positions 0..T-1: causal attention over the new keys, in the projections' layout
+                y = torch.empty_like(q)
+                with torch.cuda.device(x.device):
+                    _lib.check(_lib.lib().glq_attn_prefill(
+                        q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), B, T, c.num_attention_heads,
+                        c.num_key_value_heads, c.head_dim, tiled._stream_ptr(x.device)), "attn_prefill")
+                return self.o_proj(y.view(B, T, c.num_attention_heads * c.head_dim))
             q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
             k_all, v_all = kc[:B], vc[:B]
             return self._prompt_attention(q, k, v, k_all, v_all, cache, cache_position, kv_len, B, T)

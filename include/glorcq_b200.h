@@ -376,6 +376,14 @@ int glq_rope_prefill(void* q, void* k, const void* v, const void* cos_t, const v
                      void* k_cache, void* v_cache, int B, int T, int n_heads, int n_kv, int head_dim, int max_len,
                      const void* q_norm_w, const void* k_norm_w, float eps, void* stream);
 
+/* Causal attention of a prompt written at positions 0..T-1, after glq_rope_prefill: y[b, t, h] =
+ * softmax(q[b, t, h] . k[b, 0..t, h / group]^T / sqrt(head_dim)) v[b, 0..t, h / group], fp16 with fp32 accumulation;
+ * q and y (B, T, n_heads, head_dim), k and v (B, T, n_kv, head_dim), contiguous and 16-byte aligned; only the keys up
+ * to each query are read.  head_dim 64 or 128 (GLQ_ERR_UNSUPPORTED otherwise).  Host-model glue: the reference lets
+ * the transformers attention modules do this (inference/graph_wrapper.py:84-127). */
+int glq_attn_prefill(const void* q, const void* k, const void* v, void* y, int B, int T, int n_heads, int n_kv,
+                     int head_dim, void* stream);
+
 /* x_out = x + delta and h_out = rms_norm(x_out, eps) * weight on (rows, H) fp16 rows (weight (H,) fp16 or NULL):
  * the residual add and layer norm between the attention output projection and the MoE block of a decoder layer
  * (host-model glue, as glq_attn_decode).  H a multiple of 8, at most 8192. */

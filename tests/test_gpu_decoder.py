@@ -183,6 +183,34 @@ def test_rope_prefill_matches_tensor_ops(dev, B, T, nh, nkv, hd, norms):
     assert not kc[:, :, rest].any() and not vc[:, :, rest].any()
 
 
+@pytest.mark.parametrize("B,T,nh,nkv,hd", [(1, 1, 2, 2, 128), (2, 200, 4, 2, 128), (1, 64, 2, 2, 64), (1, 513, 16, 16, 128),
+                                          (3, 65, 8, 2, 64), (1, 1031, 4, 1, 128)])
+def test_attn_prefill_matches_fp32_attention(dev, B, T, nh, nkv, hd):
+    """The prompt's causal attention kernel (grouped-query head counts, lengths off the 64-row blocks) against
+    softmax(q k^T / sqrt(hd)) v in fp32 on the same fp16 operands; fp16 probabilities and outputs in the kernel:
+    rel-L2 <= 2e-3 and every element within 4e-3 of the row's largest magnitude."""
+    from glorcq_b200 import _lib, tiled
+    g = torch.Generator().manual_seed(T * 7 + nh)
+    q = torch.randn(B, T, nh, hd, generator=g).half().to(dev)
+    k = torch.randn(B, T, nkv, hd, generator=g).half().to(dev)
+    v = torch.randn(B, T, nkv, hd, generator=g).half().to(dev)
+    y = torch.full_like(q, float("nan"))
+    _lib.check(_lib.lib().glq_attn_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), B, T, nh, nkv, hd,
+                                           tiled._stream_ptr(dev)), "attn_prefill")
+    torch.cuda.synchronize()
+    qf = q.float().transpose(1, 2)                                              # (B, nh, T, hd)
+    kf = k.float().transpose(1, 2).repeat_interleave(nh // nkv, dim=1)
+    vf = v.float().transpose(1, 2).repeat_interleave(nh // nkv, dim=1)
+    s = qf @ kf.transpose(-1, -2) / hd ** 0.5
+    s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool, device=dev), 1), float("-inf"))
+    ref = (torch.softmax(s, -1) @ vf).transpose(1, 2)                           # (B, T, nh, hd)
+    assert torch.isfinite(y).all()
+    assert cases.rel_l2(y.cpu(), ref.cpu()) <= 2e-3
+    assert ((y.float() - ref).abs() <= 4e-3 * ref.abs().amax(-1, keepdim=True) + 1e-4).all()
+    assert _lib.lib().glq_attn_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), B, T, nh, nkv, 96,
+                                       tiled._stream_ptr(dev)) == -3       # GLQ_ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("B,V,H", [(1, 151936, 2048), (8, 151936, 2048), (3, 1000, 64), (5, 32000, 4096), (1, 17, 32)])
 def test_lm_head_logits_and_argmax(dev, B, V, H):
     """glq_lm_head through the C ABI against the fp32 product of the same fp16 operands: logits within one
