@@ -633,6 +633,7 @@ def run_ours(args, rank, world, local_rank):
         roof = gemv_roofline(dev, peak, kind)
         extras = {}
         if not args.no_extras:
+            extras["roofline_t2"] = gemv_roofline(dev, peak, kind, fmt="t2")     # the same launch on 2-bit codebook codes
             extras["roofline_gemm"] = gemm_roofline(dev)
             extras["roofline_lm_head"] = lm_head_roofline(dev, peak, cfg["vocab_size"], cfg["hidden_size"])
             try:
