@@ -274,23 +274,31 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"(addr));
 }
+// 2^x by the special-function unit alone (2 ulp; -inf -> 0; results below the normal range flush to zero)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
 template <int HD>
-__global__ void __launch_bounds__(128) attn_prefill_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
-                                                           const __half* __restrict__ v, __half* __restrict__ y, int T,
-                                                           int n_heads, int n_kv) {
+__global__ void __launch_bounds__(128, 3) attn_prefill_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
+                                                           const __half* __restrict__ v, __half* __restrict__ y, int B,
+                                                           int T, int n_heads, int n_kv) {
     using C = PrefillCfg<HD>;
     constexpr int LD = C::LD, KS = HD / 16, NT = HD / 8;
     extern __shared__ __align__(16) unsigned char pf_smem[];
     __half* sm = reinterpret_cast<__half*>(pf_smem);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int qb = (int)gridDim.x - 1 - (int)blockIdx.x;       // the longest rows first
-    const int h = blockIdx.y, b = blockIdx.z;
+    // launch order = work order: the query blocks with the most keys first, over all heads and batch rows
+    const int n_hb = n_heads * B;
+    const int qb = (int)(gridDim.x / n_hb) - 1 - (int)(blockIdx.x / n_hb);
+    const int h = (int)(blockIdx.x % n_hb) % n_heads, b = (int)(blockIdx.x % n_hb) / n_heads;
     const int kvh = h / (n_heads / n_kv);
     const int q0 = qb * C::BM + warp * 16;                      // first query row of this warp
     const __half* kbase = k + ((size_t)b * T * n_kv + kvh) * HD;
@@ -388,16 +396,16 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __half* __restr
         const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
         // a row with nothing visible so far keeps a zero offset (its probabilities are all exp2(-inf) = 0)
         const float f0 = n0 == -INFINITY ? 0.f : n0, f1 = n1 == -INFINITY ? 0.f : n1;
-        const float a0 = exp2f(m0 - f0), a1 = exp2f(m1 - f1);
+        const float a0 = ex2_approx(m0 - f0), a1 = ex2_approx(m1 - f1);
         m0 = n0;
         m1 = n1;
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            sacc[j][0] = exp2f(sacc[j][0] - f0);
-            sacc[j][1] = exp2f(sacc[j][1] - f0);
-            sacc[j][2] = exp2f(sacc[j][2] - f1);
-            sacc[j][3] = exp2f(sacc[j][3] - f1);
+            sacc[j][0] = ex2_approx(sacc[j][0] - f0);
+            sacc[j][1] = ex2_approx(sacc[j][1] - f0);
+            sacc[j][2] = ex2_approx(sacc[j][2] - f1);
+            sacc[j][3] = ex2_approx(sacc[j][3] - f1);
             s0 += sacc[j][0] + sacc[j][1];
             s1 += sacc[j][2] + sacc[j][3];
         }
@@ -581,11 +589,11 @@ extern "C" int glq_attn_prefill(const void* q, const void* k, const void* v, voi
     if (B < 0 || T < 0 || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0) return GLQ_ERR_ARG;
     if (B == 0 || T == 0) return GLQ_OK;
     if (head_dim != 64 && head_dim != 128) return GLQ_ERR_UNSUPPORTED;
-    if (B > 65535 || n_heads > 65535) return GLQ_ERR_UNSUPPORTED;
+    if ((long long)((T + 63) / 64) * n_heads * B > 0x7fffffffll) return GLQ_ERR_UNSUPPORTED;
     for (const void* ptr : {q, k, v, (const void*)y})
         if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return GLQ_ERR_ALIGN;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const dim3 grid((T + 63) / 64, n_heads, B);
+    const dim3 grid((unsigned)((T + 63) / 64 * n_heads * B));     // every (query block, head, batch row), most keys first
 #define GLQ_PREFILL(HD)                                                                                                  \
     {                                                                                                                    \
         static bool configured[64] = {};                                                                                 \
@@ -599,7 +607,7 @@ extern "C" int glq_attn_prefill(const void* q, const void* k, const void* v, voi
         }                                                                                                                \
         attn_prefill_kernel<HD><<<grid, 128, PrefillCfg<HD>::SMEM, st>>>(                                                \
             reinterpret_cast<const __half*>(q), reinterpret_cast<const __half*>(k), reinterpret_cast<const __half*>(v),  \
-            reinterpret_cast<__half*>(y), T, n_heads, n_kv);                                                             \
+            reinterpret_cast<__half*>(y), B, T, n_heads, n_kv);                                                              \
     }
     if (head_dim == 64) GLQ_PREFILL(64) else GLQ_PREFILL(128)
 #undef GLQ_PREFILL

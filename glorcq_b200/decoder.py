@@ -36,7 +36,7 @@ from .quantized_linear import GLoRCQLinear
 # Prompts of at least this many tokens hand their causal attention to the library call instead of
 # glq_attn_prefill (GLQ_PROMPT_ATTN_LIBRARY_FROM; 0 = always the library, a huge value = never).  Measured on the
 # 24-layer model, whole prompt pass with this kernel / with the library: 512 tokens 15.5 / 15.5 ms, 1024: 19.0 / 18.7,
-# 2048: 28.2 / 26.6, 4096: 50.4 / 43.6.
+# 2048: 28.0 / 26.6, 4096: 48.4 / 43.6.
 _PROMPT_ATTN_LIBRARY_FROM = int(os.environ.get("GLQ_PROMPT_ATTN_LIBRARY_FROM", "2048"))
 
 
